@@ -1,0 +1,69 @@
+"""The CPU oracle must reproduce the outputs of the reference's own CPU Pairformer.
+
+Fixtures: tests/golden/*.npz, written by tests/golden/make_golden.py from
+tt_bio.reference.PairformerModule / PairformerNoSeqModule (fp32, eval, use_kernels=False).
+"""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import pairformer_oracle as orc
+from tests.golden.make_golden import weight_checksum
+from tt_boltz_b200 import synthetic
+from tests.conftest import rel_l2
+
+CASES = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.npz")))
+
+
+def load_case(golden_dir, name):
+    g = np.load(os.path.join(golden_dir, name + ".npz"))
+    n, nb, with_s = int(g["n"]), int(g["blocks"]), bool(g["with_s"])
+    sd = synthetic.make_weights(nb, seed=1, std=float(g["std"]), affine_jitter=float(g["jitter"]), with_s=with_s)
+    assert abs(weight_checksum(sd) - float(g["weight_checksum"])) <= 1e-6 * float(g["weight_checksum"]), \
+        "regenerated weights differ from the ones the fixture was made with"
+    s, z = synthetic.make_inputs(n, seed=0, with_s=with_s)
+    return g, sd, s, z, torch.from_numpy(g["mask"]), torch.from_numpy(g["pair_mask"])
+
+
+def test_fixtures_present():
+    assert len(CASES) >= 5
+
+
+@pytest.mark.parametrize("name", CASES)
+def test_oracle_matches_reference_outputs(golden_dir, name):
+    g, sd, s, z, m, pm = load_case(golden_dir, name)
+    with torch.no_grad():
+        s_o, z_o = orc.pairformer_stack(None if s is None else s[0], z[0], m[0], pm[0], sd, int(g["blocks"]))
+    assert rel_l2(z_o, torch.from_numpy(g["z_out"])[0]) < 2e-6
+    if s is not None:
+        assert rel_l2(s_o, torch.from_numpy(g["s_out"])[0]) < 2e-6
+
+
+def test_oracle_sub_op_taps(golden_dir):
+    g, sd, s, z, m, pm = load_case(golden_dir, "layer_n16_taps")
+    taps = {}
+    with torch.no_grad():
+        orc.pairformer_layer(s[0], z[0], m[0], pm[0], sd, "layers.0.", taps=taps)
+    for k in ("tri_mul_out", "tri_mul_in", "tri_att_start", "tri_att_end", "transition_z"):
+        assert rel_l2(taps[k], torch.from_numpy(g["tap_" + k])[0]) < 2e-6, k
+
+
+def test_oracle_padding_isolated(golden_dir):
+    """Values stored at masked-out tokens must not leak into the valid region (exactly)."""
+    g, sd, s, z, m, pm = load_case(golden_dir, "stack2_n20_tailpad")
+    gen = torch.Generator().manual_seed(11)
+    z2, s2 = z.clone(), s.clone()
+    pad = (m[0] == 0)
+    z2[0, pad] = 50 * torch.randn(z2[0, pad].shape, generator=gen)
+    z2[0, :, pad] = 50 * torch.randn(z2[0, :, pad].shape, generator=gen)
+    s2[0, pad] = 50 * torch.randn(s2[0, pad].shape, generator=gen)
+    with torch.no_grad():
+        sa, za = orc.pairformer_stack(s[0], z[0], m[0], pm[0], sd, 2)
+        sb, zb = orc.pairformer_stack(s2[0], z2[0], m[0], pm[0], sd, 2)
+    v = ~pad
+    assert torch.equal(za[v][:, v], zb[v][:, v])
+    assert torch.equal(sa[v], sb[v])
+    assert torch.isfinite(zb).all() and torch.isfinite(sb).all()
