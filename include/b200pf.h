@@ -1,0 +1,194 @@
+/* b200pf — C ABI of the B200 (sm_100a) Pairformer trunk kernels.
+ *
+ * The reference project (moritztng/tt-boltz, "TT-Bio") is pure Python and has no FFI; the
+ * interface each entry point stands in for is therefore a Python call site of the reference's
+ * device backend (tt_bio/tenstorrent.py) or of its CPU modules (tt_bio/reference.py,
+ * tt_bio/boltz2.py).  Each declaration cites the call site it replaces.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer on the current CUDA device unless said otherwise;
+ *   - no entry point allocates, frees or synchronises the device (unless stated); work is
+ *     enqueued on `stream` (a cudaStream_t passed as void*; NULL = the legacy default stream);
+ *   - return value: 0 on success, a negative B200PF_ERR_* code otherwise;
+ *     b200pf_last_error() gives the message of the calling thread's last failure;
+ *   - pair tensors use the reference layout: z[i][j][c], c contiguous, B = 1 folded away;
+ *   - "planes" are channel-major bf16 matrices p[d][row][col] with a row pitch in elements
+ *     (multiple of 8) and a plane stride in elements;
+ *   - masks are uint8 (0 / 1), converted once by the host from the reference's float masks.
+ */
+#ifndef B200PF_H
+#define B200PF_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200PF_OK               0
+#define B200PF_ERR_INVALID     -1   /* bad argument (null pointer, size, alignment)          */
+#define B200PF_ERR_UNSUPPORTED -2   /* shape outside what the kernels are instantiated for   */
+#define B200PF_ERR_CUDA        -3   /* a CUDA runtime / driver call failed                   */
+#define B200PF_ERR_DEVICE      -4   /* a kernel reported a bounded wait that ran out         */
+
+typedef uint16_t b200pf_bf16;       /* raw bfloat16 bits */
+
+int         b200pf_version(void);
+const char* b200pf_last_error(void);
+/* Number of kernels this library has launched in the calling process (for benchmarks). */
+long long   b200pf_launch_count(void);
+/* Reads (and clears) the device status word kernels set when a bounded wait runs out.
+ * Synchronises `stream`.  0 = clean. */
+int         b200pf_device_status(void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * fp32 validation tier: un-fused SIMT kernels, arithmetic in fp32 throughout.
+ * Stand in for torch.nn.functional calls of the reference's CPU path.
+ * ---------------------------------------------------------------------------------------- */
+
+/* y[r][:] = LayerNorm(x[r][:]) * gamma + beta, eps 1e-5, biased variance.
+ * Replaces nn.LayerNorm as used at tt_bio/reference.py:456, 467, 331 and tt_bio/boltz2.py:1241. */
+int b200pf_f32_layernorm(const float* x, const float* gamma, const float* beta, float* y,
+                         long long rows, int c, void* stream);
+
+/* y[r][n] (+)= sum_k x[r][k] * w[n][k] (+ bias[n]); accumulate != 0 adds into y.
+ * Replaces nn.Linear (tt_bio/boltz2.py:638-731) on the CPU path. */
+int b200pf_f32_linear(const float* x, const float* w, const float* bias, float* y,
+                      long long rows, int k, int n_out, int accumulate, void* stream);
+
+/* Element-wise gates over [rows][c]; row_mask (may be NULL) has one byte per row.
+ *   mode 0: y = a * sigmoid(b) * mask      (tt_bio/reference.py:458-461)
+ *   mode 1: y = silu(a) * b                (tt_bio/boltz2.py:1244-1245)
+ *   mode 2: y += a * sigmoid(b)            (tt_bio/reference.py:470 plus the residual :878) */
+int b200pf_f32_gate(const float* a, const float* b, const uint8_t* row_mask, float* y,
+                    long long rows, int c, int mode, void* stream);
+
+/* t[i][j][c] = sum_k a[i][k][c] * b[j][k][c]   (incoming == 0, tt_bio/reference.py:467)
+ * t[i][j][c] = sum_k a[k][i][c] * b[k][j][c]   (incoming != 0, tt_bio/reference.py:556)
+ * a and b are [n][n][*] views with `in_pitch` floats between (row, col) positions; t is dense. */
+int b200pf_f32_trimul_contract(const float* a, const float* b, float* t, int n, int d,
+                               int in_pitch, int incoming, void* stream);
+
+/* Softmax attention with additive mask and bias, fp32 (tt_bio/boltz2.py:790-810 and :357-364).
+ *   logit[r][h][q][k] = scale * <Q[r][q][h], K[r][k][h]> (+) mask term (+) bias[h][q][k]
+ *   mask term = -inf_value * (1 - mask[r*mask_rs + k*mask_ks]);
+ *   order 0 adds the mask term first, then the bias (triangle attention);
+ *   order 1 adds the bias first, then the mask term (single-track attention).
+ * Q/K/V/O element (r, pos, h, e) lives at ptr[r*rs + pos*ps + h*hd + e]. */
+int b200pf_f32_attention(const float* q, const float* k, const float* v, float* o,
+                         const float* bias, long long bias_hs, long long bias_qs, long long bias_ks,
+                         const uint8_t* mask, long long mask_rs, long long mask_ks,
+                         int batch, int n_q, int n_k, int heads, int hd,
+                         long long rs, long long ps, float scale, float inf_value, int order,
+                         void* stream);
+
+/* dst[j][i][:] (+)= src[i][j][:] for an [n][n][c] tensor (tt_bio/reference.py:326-328, 362-363). */
+int b200pf_f32_transpose01(const float* src, float* dst, int n, int c, int accumulate, void* stream);
+
+/* out[h][r] = sum_c LayerNorm(z[r][:])[c] * w[h][c]  (heads <= 16), fp32, one pass over z.
+ * Replaces proj_z = LayerNorm -> Linear(c_z -> heads) -> 'b i j h -> b h i j'
+ * (tt_bio/boltz2.py:331-337; device form tt_bio/tenstorrent.py:755-769) and the triangle bias
+ * projection (tt_bio/reference.py:338-341).  `out_hs` = elements between heads. */
+int b200pf_ln_proj_heads(const float* z, const float* gamma, const float* beta, const float* w,
+                         float* out, long long out_hs, long long rows, int c, int heads, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * bf16 tier: fused kernels.  z stays fp32 in HBM (the residual stream); operands are bf16,
+ * accumulation fp32.  c_z = hidden = 128, 4 heads x 32 for triangle attention.
+ * `rows` is the number of z rows [i] held locally (== n on one GPU); `n` is the full token count.
+ * ---------------------------------------------------------------------------------------- */
+
+/* Weight packing for the fused kernels is done once by the host (tt_boltz_b200/weights.py):
+ * LayerNorm gains are folded into the bf16 weight rows, LayerNorm offsets become fp32 bias
+ * vectors (W beta), and rows are re-ordered so that values a thread combines (p with g, fc1 with
+ * fc2) land in the same thread.  The layouts are stated at each entry point. */
+
+/* Triangle-multiplication producer: LN_in -> [p_in | g_in] projection -> p*sigmoid(g) -> mask
+ * -> a/b written channel-major.  Replaces tt_bio/tenstorrent.py:410-452 (reference.py:456-464).
+ *   z: fp32 [rows][n][128];  mask: [rows][n];
+ *   w_pg: bf16 [512][128] in 8 chunks of 64 rows; chunk q = channels 32*(q%4)..+31 of operand a
+ *         (q < 4) or b (q >= 4): their 32 p_in rows then their 32 g_in rows;  bias_pg: fp32 [512].
+ *   incoming == 0: a[d][r][k] = u_a[r][k][d]  (plane rows = local z rows, cols = k)
+ *   incoming != 0: a[d][c][r] = u_a[r][c][d]  (plane rows = z columns, cols = local z rows)
+ *   value_mode 0 = bf16 planes (the only mode built so far; a_scales / b_scales unused). */
+int b200pf_trimul_producer(const float* z, const uint8_t* mask, const float* bias_pg,
+                           const b200pf_bf16* w_pg, void* a_planes, void* b_planes,
+                           void* a_scales, void* b_scales, long long plane_stride, int pitch,
+                           int rows, int n, int incoming, int value_mode, void* stream);
+
+/* Operand description for the contraction: element (seg, d, row, col) of an operand lives at
+ * ptr[seg*seg_stride + d*plane_stride + row*pitch + col]. */
+typedef struct b200pf_planes {
+    const void* ptr;
+    long long   plane_stride;   /* elements between channels d                              */
+    long long   seg_stride;     /* elements between segments (ignored when nseg == 1)       */
+    int         pitch;          /* elements between rows; multiple of 8                     */
+    int         rows;           /* rows per segment                                         */
+    int         cols;           /* valid columns (contraction index) per segment            */
+    int         nseg;           /* number of segments                                       */
+    int         seg_is_k;       /* 1: segments split the contraction index; 0: split rows   */
+} b200pf_planes;
+
+/* x[d][i][j] = sum_k A[d][i][k] * B[d][j][k] for d < channels: the N x N x N contraction of
+ * the triangle multiplication as a batched K-major GEMM (tcgen05 + TMEM, TMA-fed).
+ * Replaces the per-chunk ttnn.matmul at tt_bio/tenstorrent.py:453-460 (reference.py:467, 556).
+ * x is bf16 planes x[d][i][j] with pitch x_pitch.  variant 0 = tcgen05 bf16, 1 = SIMT bf16
+ * (debug cross-check of variant 0). */
+int b200pf_trimul_contract(const b200pf_planes* a, const b200pf_planes* b,
+                           const void* a_scales, const void* b_scales,
+                           b200pf_bf16* x, long long x_plane_stride, int x_pitch,
+                           int channels, int variant, void* stream);
+
+/* Triangle-multiplication epilogue: z += (LN_out(x) W_pout^T) * sigmoid(LN_in(z) W_gout^T).
+ * Replaces tt_bio/tenstorrent.py:463-502 plus the residual add :1007-1011.
+ * Reads z (pre-update) and writes z in place; x planes as written by the contraction.
+ *   w_pout / w_gout: bf16 [128][128] with the LN_out / LN_in gain folded in;  bias_*: fp32 [128]. */
+int b200pf_trimul_epilogue(float* z, const b200pf_bf16* x, long long x_plane_stride, int x_pitch,
+                           const b200pf_bf16* w_pout, const b200pf_bf16* w_gout,
+                           const float* bias_pout, const float* bias_gout,
+                           int rows, int n, void* stream);
+
+/* Triangle-attention producer: LN -> [q|k|v|g] projection and the 4-head triangle bias.
+ * Replaces tt_bio/tenstorrent.py:545-567, 603-614 (reference.py:331-341, 99-120).
+ *   w_qkvg: bf16 [528][128] = q rows (scaled by log2(e)/sqrt(32)), k, v, g rows, the 4 bias rows
+ *           (scaled by log2(e)), 12 zero rows;  bias_qkvg: fp32 [528].
+ * Outputs (bf16):
+ *   q,k,v: [line][head][pos][32] where (line,pos) = (i,j) for the starting node and (j,i) for
+ *          the ending node;
+ *   g:     sigmoid(gate) in z layout [i][j][128];
+ *   tri_bias: [head][q][k], row pitch bias_pitch, head stride bias_hs (elements);
+ *          starting: (q,k) = (i,j); ending: (q,k) = (j,i). */
+int b200pf_triatt_producer(const float* z, const b200pf_bf16* w_qkvg, const float* bias_qkvg,
+                           b200pf_bf16* q, b200pf_bf16* k, b200pf_bf16* v, b200pf_bf16* g,
+                           b200pf_bf16* tri_bias, long long bias_hs, int bias_pitch,
+                           int rows, int n, int ending, void* stream);
+
+/* Fused flash-style triangle attention: for each line and head, softmax(q k^T + mask + bias) v
+ * with online softmax in the log2 domain; logits never leave the SM.  Replaces the SDPA call at
+ * tt_bio/tenstorrent.py:569-572 (reference.py:343-360, boltz2.py:790-810).
+ *   mask byte for (line, key) = mask[line*mask_ls + key*mask_ks]; masked keys get -1e9.
+ *   o is written in z layout: element (line, pos, c) at o[line*o_line_stride + pos*o_pos_stride + c].
+ *   lines_per_cta: 1, 2 or 4 lines share one fetch of each bias tile (0 = default). */
+int b200pf_triatt_core(const b200pf_bf16* q, const b200pf_bf16* k, const b200pf_bf16* v,
+                       const b200pf_bf16* bias, long long bias_hs, int bias_pitch,
+                       const uint8_t* mask, long long mask_ls, long long mask_ks,
+                       b200pf_bf16* o, long long o_line_stride, long long o_pos_stride,
+                       int lines, int n, int lines_per_cta, void* stream);
+
+/* Triangle-attention epilogue: z += (o * g) W_o^T  (g already passed through the sigmoid).
+ * Replaces tt_bio/tenstorrent.py:580-591 and the residual :1013-1021 (reference.py:122-136). */
+int b200pf_triatt_epilogue(float* z, const b200pf_bf16* o, const b200pf_bf16* g,
+                           const b200pf_bf16* w_o, long long n_rows_flat, void* stream);
+
+/* Pair transition: z += W3( silu(W1 LN(z)) * (W2 LN(z)) ), hidden 512 kept on chip.
+ * Replaces tt_bio/tenstorrent.py:869-946 and the residual :1023-1025 (boltz2.py:1241-1246).
+ *   w12: bf16 [1024][128], 32 groups of 32 rows = 16 fc1 rows then the 16 fc2 rows of the same
+ *        hidden channels;  bias12: fp32 [1024];  w3: bf16 [8][128][64] (fc3 columns per step). */
+int b200pf_transition_z(float* z, const b200pf_bf16* w12, const float* bias12,
+                        const b200pf_bf16* w3, long long n_rows_flat, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200PF_H */

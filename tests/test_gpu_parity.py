@@ -1,0 +1,262 @@
+"""GPU parity tests: the CUDA path (through the C ABI) against the CPU oracle and the golden
+fixtures made from the reference's own CPU modules.
+
+Tolerances (rel-L2 = ||x - ref|| / ||ref||):
+  fp32 tier  : <= 1e-4 on z and s per layer
+  bf16 tier  : <= 2e-2 (sub-operation updates and stacked layers)
+Mask handling: values stored at masked-out tokens must not change the valid region at all.
+"""
+import ctypes as C
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import pairformer_oracle as orc
+from tests.conftest import rel_l2
+from tt_boltz_b200 import B200PairformerLayer, B200PairformerModule, B200PairformerNoSeqModule, synthetic
+
+pytestmark = pytest.mark.gpu
+GOLDEN = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.npz")))
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    return torch.device("cuda:0")
+
+
+def strip(sd, i=0):
+    pre = f"layers.{i}."
+    return {k[len(pre):]: v for k, v in sd.items() if k.startswith(pre)}
+
+
+def run_module(sd, blocks, s, z, m, pm, dev, precision, with_s=True, **attrs):
+    if with_s:
+        mod = B200PairformerModule(384, 128, blocks, v2=True, precision=precision)
+    else:
+        mod = B200PairformerNoSeqModule(128, blocks, precision=precision)
+    mod.load_state_dict(sd, strict=True)
+    for layer in mod.layers:
+        for k, v in attrs.items():
+            setattr(layer, k, v)
+    if with_s:
+        so, zo = mod(s.to(dev), z.to(dev), m.to(dev), pm.to(dev))
+        return so.cpu(), zo.cpu()
+    return None, mod(z.to(dev), pm.to(dev)).cpu()
+
+
+# ---------------------------------------------------------------------------------------------
+# golden fixtures (outputs of the reference's CPU modules)
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("precision,tol", [("fp32", 1e-4), ("bf16", 2e-2)])
+@pytest.mark.parametrize("name", GOLDEN)
+def test_golden_fixture(golden_dir, dev, name, precision, tol):
+    g = np.load(os.path.join(golden_dir, name + ".npz"))
+    n, nb, with_s = int(g["n"]), int(g["blocks"]), bool(g["with_s"])
+    sd = synthetic.make_weights(nb, seed=1, std=float(g["std"]), affine_jitter=float(g["jitter"]), with_s=with_s)
+    s, z = synthetic.make_inputs(n, seed=0, with_s=with_s)
+    m, pm = torch.from_numpy(g["mask"]), torch.from_numpy(g["pair_mask"])
+    so, zo = run_module(sd, nb, s, z, m, pm, dev, precision, with_s)
+    valid = m[0].bool()
+    zr = torch.from_numpy(g["z_out"])
+    assert torch.isfinite(zo).all()
+    assert rel_l2(zo[0][valid][:, valid], zr[0][valid][:, valid]) < tol
+    if with_s:
+        sr = torch.from_numpy(g["s_out"])
+        assert rel_l2(so[0][valid], sr[0][valid]) < tol
+
+
+# ---------------------------------------------------------------------------------------------
+# configuration 1 of the benchmark: one layer, fp32, N = 128, all-ones masks, N(0, 0.02) weights
+# ---------------------------------------------------------------------------------------------
+def test_cfg1_layer_fp32_n128(dev):
+    n = 128
+    sd = synthetic.make_weights(1, seed=1)
+    s, z = synthetic.make_inputs(n, seed=0)
+    m, pm = synthetic.tail_padding_mask(n, 0)
+    so, zo = run_module(sd, 1, s, z, m, pm, dev, "fp32")
+    sr, zr = orc.pairformer_stack(s[0], z[0], m[0], pm[0], sd, 1)
+    assert rel_l2(zo[0], zr) < 1e-4
+    assert rel_l2(so[0], sr) < 1e-4
+    # the bf16 tier on the same input
+    so, zo = run_module(sd, 1, s, z, m, pm, dev, "bf16")
+    assert rel_l2(zo[0], zr) < 2e-2 and rel_l2(so[0], sr) < 2e-2
+
+
+# ---------------------------------------------------------------------------------------------
+# sub-operations, bf16 tier, ragged sizes and general 2-D masks (update compared on its own)
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("n", [37, 100, 128, 200])
+def test_sub_operations_bf16(dev, n):
+    from tt_boltz_b200 import ops, weights
+    sd = strip(synthetic.make_weights(1, seed=5, std=0.05, affine_jitter=0.3))
+    _, z = synthetic.make_inputs(n, seed=4, with_s=False)
+    g = torch.Generator().manual_seed(9)
+    tm = torch.ones(n)
+    tm[n - max(1, n // 10):] = 0
+    pm = (torch.rand(n, n, generator=g) > 0.15).float() * tm[:, None] * tm[None, :]
+    pm_u8 = (pm != 0).to(torch.uint8).to(dev)
+    ws = ops.Workspace(n, dev)
+    v = tm.bool()
+    cases = [
+        ("tri_mul_out", lambda zz: ops.tri_mul_bf16(zz, pm_u8, weights.pack_trimul(sd, "tri_mul_out.", dev), ws, False),
+         lambda zc: orc.tri_mul(zc, sd, "tri_mul_out", pm, False)),
+        ("tri_mul_in", lambda zz: ops.tri_mul_bf16(zz, pm_u8, weights.pack_trimul(sd, "tri_mul_in.", dev), ws, True),
+         lambda zc: orc.tri_mul(zc, sd, "tri_mul_in", pm, True)),
+        ("tri_att_start", lambda zz: ops.tri_att_bf16(zz, pm_u8, weights.pack_triatt(sd, "tri_att_start.", dev), ws, False),
+         lambda zc: orc.tri_att(zc, sd, "tri_att_start", pm, False)),
+        ("tri_att_end", lambda zz: ops.tri_att_bf16(zz, pm_u8, weights.pack_triatt(sd, "tri_att_end.", dev), ws, True),
+         lambda zc: orc.tri_att(zc, sd, "tri_att_end", pm, True)),
+        ("transition_z", lambda zz: ops.transition_z_bf16(zz, weights.pack_transition_z(sd, "transition_z.", dev)),
+         lambda zc: orc.transition(zc, sd, "transition_z")),
+    ]
+    for name, run, ref in cases:
+        zd = z[0].to(dev).clone()
+        run(zd)
+        torch.cuda.synchronize()
+        upd = (zd.cpu() - z[0])
+        want = ref(z[0])
+        assert torch.isfinite(upd).all(), name
+        assert rel_l2(upd[v][:, v], want[v][:, v]) < 2e-2, name
+
+
+def test_contraction_tcgen05_matches_simt_and_einsum(dev):
+    from tt_boltz_b200._lib import Planes, call, ptr, stream
+    from tt_boltz_b200 import _lib
+    for n in (24, 100, 128, 264, 512):
+        pitch = (n + 7) // 8 * 8
+        ps = n * pitch
+        g = torch.Generator().manual_seed(n)
+        a = torch.randn(128, n, pitch, generator=g).bfloat16()
+        b = torch.randn(128, n, pitch, generator=g).bfloat16()
+        ad, bd = a.to(dev), b.to(dev)
+        outs = []
+        for variant in (0, 1):
+            x = torch.zeros(128, n, pitch, dtype=torch.bfloat16, device=dev)
+            pa = Planes(ptr(ad), ps, 0, pitch, n, n, 1, 0)
+            pb = Planes(ptr(bd), ps, 0, pitch, n, n, 1, 0)
+            call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), None, None, ptr(x), ps, pitch, 128, variant, stream())
+            assert _lib.device_status() == 0
+            outs.append(x[:, :, :n].float().cpu())
+        ref = torch.einsum("dik,djk->dij", a[:, :, :n].float(), b[:, :, :n].float())
+        assert rel_l2(outs[0], ref) < 4e-3, n       # bf16 rounding of the stored result
+        assert rel_l2(outs[1], ref) < 4e-3, n
+        assert rel_l2(outs[0], outs[1]) < 1e-3, n
+
+
+# ---------------------------------------------------------------------------------------------
+# masks: what is stored at masked-out tokens must not reach the valid region (bit-exact)
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("precision", ["fp32", "bf16"])
+def test_padding_is_isolated_exactly(dev, precision):
+    n, npad = 72, 9
+    sd = synthetic.make_weights(1, seed=1, std=0.05, affine_jitter=0.2)
+    s, z = synthetic.make_inputs(n, seed=0)
+    m, pm = synthetic.tail_padding_mask(n, npad)
+    g = torch.Generator().manual_seed(11)
+    z2, s2 = z.clone(), s.clone()
+    z2[0, n - npad:] = 30 * torch.randn(npad, n, 128, generator=g)
+    z2[0, :, n - npad:] = 30 * torch.randn(n, npad, 128, generator=g)
+    s2[0, n - npad:] = 30 * torch.randn(npad, 384, generator=g)
+    sa, za = run_module(sd, 1, s, z, m, pm, dev, precision)
+    sb, zb = run_module(sd, 1, s2, z2, m, pm, dev, precision)
+    v = n - npad
+    assert torch.equal(za[0, :v, :v], zb[0, :v, :v])
+    assert torch.equal(sa[0, :v], sb[0, :v])
+    assert torch.isfinite(zb).all() and torch.isfinite(sb).all()
+
+
+def test_fully_masked_line_matches_reference(dev):
+    """A line whose keys are all masked attends uniformly (finite), as the reference does."""
+    n = 40
+    sd = synthetic.make_weights(1, seed=3, std=0.05, with_s=False)
+    _, z = synthetic.make_inputs(n, seed=2, with_s=False)
+    pm = torch.ones(1, n, n)
+    pm[0, 5, :] = 0
+    pm[0, :, 7] = 0
+    for precision, tol in (("fp32", 1e-4), ("bf16", 2e-2)):
+        _, zo = run_module(sd, 1, None, z, None, pm, dev, precision, with_s=False)
+        zr = orc.pairformer_stack(None, z[0], None, pm[0], sd, 1)[1]
+        assert rel_l2(zo[0], zr) < tol, precision
+
+
+# ---------------------------------------------------------------------------------------------
+# benchmark configurations 2 and 3 at full size (bf16 tier)
+# ---------------------------------------------------------------------------------------------
+def test_cfg2_trimul_out_in_n512(dev):
+    from tt_boltz_b200 import ops, weights
+    n = 512
+    sd = strip(synthetic.make_weights(1, seed=1, bf16_round=True, with_s=False))
+    _, z = synthetic.make_inputs(n, seed=0, with_s=False, bf16_round=True)
+    m, pm = synthetic.tail_padding_mask(n, 51)
+    pm_u8 = (pm[0] != 0).to(torch.uint8).to(dev)
+    ws = ops.Workspace(n, dev)
+    zd = z[0].to(dev).clone()
+    ops.tri_mul_bf16(zd, pm_u8, weights.pack_trimul(sd, "tri_mul_out.", dev), ws, False)
+    ops.tri_mul_bf16(zd, pm_u8, weights.pack_trimul(sd, "tri_mul_in.", dev), ws, True)
+    z1 = z[0] + orc.tri_mul(z[0], sd, "tri_mul_out", pm[0], False)
+    z2 = z1 + orc.tri_mul(z1, sd, "tri_mul_in", pm[0], True)
+    v = n - 51
+    got = zd.cpu()
+    assert rel_l2(got[:v, :v], z2[:v, :v]) < 2e-2
+    assert rel_l2((got - z[0])[:v, :v], (z2 - z[0])[:v, :v]) < 2e-2      # the update itself
+    # masked operands contribute exactly zero: re-run with garbage in the padded tokens
+    z_g = z[0].clone()
+    z_g[v:] = 100.0
+    z_g[:, v:] = -100.0
+    zd2 = z_g.to(dev).clone()
+    ops.tri_mul_bf16(zd2, pm_u8, weights.pack_trimul(sd, "tri_mul_out.", dev), ws, False)
+    ops.tri_mul_bf16(zd2, pm_u8, weights.pack_trimul(sd, "tri_mul_in.", dev), ws, True)
+    assert torch.equal(zd2.cpu()[:v, :v], got[:v, :v])
+
+
+def test_cfg3_triatt_start_end_n768(dev):
+    from tt_boltz_b200 import ops, weights
+    n = 768
+    sd = strip(synthetic.make_weights(1, seed=1, bf16_round=True, with_s=False))
+    _, z = synthetic.make_inputs(n, seed=0, with_s=False, bf16_round=True)
+    for keep in (True, False):
+        m, pm, _ = synthetic.chain_block_mask(n, 3, n_pad=32, seed=2, keep_inter_chain=keep)
+        pm_u8 = (pm[0] != 0).to(torch.uint8).to(dev)
+        ws = ops.Workspace(n, dev)
+        zd = z[0].to(dev).clone()
+        ops.tri_att_bf16(zd, pm_u8, weights.pack_triatt(sd, "tri_att_start.", dev), ws, False)
+        ops.tri_att_bf16(zd, pm_u8, weights.pack_triatt(sd, "tri_att_end.", dev), ws, True)
+        z1 = z[0] + orc.tri_att(z[0], sd, "tri_att_start", pm[0], False)
+        z2 = z1 + orc.tri_att(z1, sd, "tri_att_end", pm[0], True)
+        v = n - 32
+        got = zd.cpu()
+        assert torch.isfinite(got).all()
+        assert rel_l2(got[:v, :v], z2[:v, :v]) < 2e-2
+        assert rel_l2((got - z[0])[:v, :v], (z2 - z[0])[:v, :v]) < 2e-2
+
+
+# ---------------------------------------------------------------------------------------------
+# depth: error growth over a stack stays inside the bf16 tier
+# ---------------------------------------------------------------------------------------------
+def test_stack_depth_bf16(dev):
+    n, nb = 64, 16
+    sd = synthetic.make_weights(nb, seed=1)
+    s, z = synthetic.make_inputs(n, seed=0)
+    m, pm = synthetic.tail_padding_mask(n, 0)
+    so, zo = run_module(sd, nb, s, z, m, pm, dev, "bf16")
+    sr, zr = orc.pairformer_stack(s[0], z[0], m[0], pm[0], sd, nb)
+    assert rel_l2(zo[0], zr) < 2e-2
+    assert rel_l2(so[0], sr) < 2e-2
+
+
+def test_layer_forward_signature(dev):
+    """PairformerLayer.forward(s, z, mask, pair_mask, chunk_size_tri_attn, use_kernels) returns new tensors."""
+    n = 32
+    sd = strip(synthetic.make_weights(1, seed=1))
+    layer = B200PairformerLayer(384, 128, v2=True, precision="bf16")
+    layer.load_state_dict(sd, strict=True)
+    s, z = synthetic.make_inputs(n, seed=0)
+    m, pm = synthetic.tail_padding_mask(n, 2)
+    zd = z.to(dev)
+    so, zo = layer(s.to(dev), zd, m.to(dev), pm.to(dev), 128, False)
+    assert zo.shape == z.shape and so.shape == s.shape and zo.data_ptr() != zd.data_ptr()
+    assert torch.equal(zd.cpu(), z)            # the caller's tensor is untouched

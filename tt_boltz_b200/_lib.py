@@ -1,0 +1,104 @@
+"""ctypes binding of libb200pf.so (the C ABI declared in include/b200pf.h).
+
+There is no fallback: if the shared library is missing and cannot be built, importing the
+binding raises.  Every call checks the status code and raises ``RuntimeError`` with the
+library's own message.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional
+
+import torch
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libb200pf.so")
+
+_vp, _i, _ll, _f = C.c_void_p, C.c_int, C.c_longlong, C.c_float
+
+
+class Planes(C.Structure):
+    """Mirror of ``b200pf_planes``."""
+    _fields_ = [("ptr", _vp), ("plane_stride", _ll), ("seg_stride", _ll), ("pitch", _i), ("rows", _i),
+                ("cols", _i), ("nseg", _i), ("seg_is_k", _i)]
+
+
+# name -> argtypes (all return int unless listed in _RESTYPES)
+SIGNATURES = {
+    "b200pf_version": [],
+    "b200pf_last_error": [],
+    "b200pf_launch_count": [],
+    "b200pf_device_status": [_vp],
+    "b200pf_f32_layernorm": [_vp, _vp, _vp, _vp, _ll, _i, _vp],
+    "b200pf_f32_linear": [_vp, _vp, _vp, _vp, _ll, _i, _i, _i, _vp],
+    "b200pf_f32_gate": [_vp, _vp, _vp, _vp, _ll, _i, _i, _vp],
+    "b200pf_f32_trimul_contract": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "b200pf_f32_attention": [_vp, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _i, _i, _i, _i, _i,
+                             _ll, _ll, _f, _f, _i, _vp],
+    "b200pf_f32_transpose01": [_vp, _vp, _i, _i, _i, _vp],
+    "b200pf_ln_proj_heads": [_vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _vp],
+    "b200pf_trimul_producer": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _vp],
+    "b200pf_trimul_contract": [C.POINTER(Planes), C.POINTER(Planes), _vp, _vp, _vp, _ll, _i, _i, _i, _vp],
+    "b200pf_trimul_epilogue": [_vp, _vp, _ll, _i, _vp, _vp, _vp, _vp, _i, _i, _vp],
+    "b200pf_triatt_producer": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _vp],
+    "b200pf_triatt_core": [_vp, _vp, _vp, _vp, _ll, _i, _vp, _ll, _ll, _vp, _ll, _ll, _i, _i, _i, _vp],
+    "b200pf_triatt_epilogue": [_vp, _vp, _vp, _vp, _ll, _vp],
+    "b200pf_transition_z": [_vp, _vp, _vp, _vp, _ll, _vp],
+}
+_RESTYPES = {"b200pf_last_error": C.c_char_p, "b200pf_launch_count": _ll}
+
+_lib: Optional[C.CDLL] = None
+
+
+def load(build_if_missing: bool = True) -> C.CDLL:
+    """Load (building first if needed) the shared library and declare every entry point."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        if not build_if_missing:
+            raise RuntimeError(f"{LIB_PATH} is missing; run `python -m tt_boltz_b200.build`")
+        from . import build as _build
+        _build.build()
+    lib = C.CDLL(LIB_PATH)
+    for name, args in SIGNATURES.items():
+        fn = getattr(lib, name)          # AttributeError here = the .so does not export the symbol
+        fn.argtypes = args
+        fn.restype = _RESTYPES.get(name, _i)
+    _lib = lib
+    return lib
+
+
+def last_error() -> str:
+    return load().b200pf_last_error().decode(errors="replace")
+
+
+def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    """Device address of a contiguous CUDA tensor (None -> NULL)."""
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise RuntimeError("b200pf kernels take CUDA tensors only (there is no CPU path)")
+    if not t.is_contiguous():
+        raise RuntimeError("b200pf kernels take contiguous tensors")
+    return t.data_ptr()
+
+
+def stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def call(name: str, *args) -> None:
+    rc = getattr(load(), name)(*args)
+    if rc != 0:
+        raise RuntimeError(f"{name} failed with status {rc}: {last_error()}")
+
+
+def launch_count() -> int:
+    return int(load().b200pf_launch_count())
+
+
+def device_status() -> int:
+    """Synchronise the current stream and return the device status word (0 = clean)."""
+    return int(load().b200pf_device_status(stream()))

@@ -1,0 +1,325 @@
+// Triangle-multiplication contraction: x[d][i][j] = sum_k A[d][i][k] * B[d][j][k].
+//
+// One batched K-major GEMM over the 128 channels.  Persistent, warp-specialised kernel:
+//   warp 0   : TMA producer (one lane) - 128x64 bf16 boxes, 128-byte swizzle, 4-stage ring
+//   warp 1   : TMEM owner + MMA issuer (one lane) - tcgen05.mma 128x256x16, fp32 accumulators
+//   warps 2-5: epilogue - tcgen05.ld the finished 128x256 accumulator, round to bf16, store
+// Two accumulators (2 x 256 TMEM columns) let the epilogue of tile t overlap the MMAs of t+1.
+// Ragged sizes need no padding: TMA zero-fills out-of-range rows / columns, stores are guarded.
+#include "sm100.cuh"
+
+namespace b200pf {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+
+struct GemmShape {
+    int m_rows;          // rows of A (output rows)
+    int n_rows;          // rows of B over all row segments (output columns)
+    int k_total;         // contraction length over all k segments
+    int a_kseg_cols;     // columns per k segment of A (== k_total when unsegmented)
+    int b_kseg_cols;
+    int b_rowseg_rows;   // rows per row segment of B (== n_rows when unsegmented)
+    int channels;
+    int x_pitch;
+    long long x_plane_stride;
+};
+
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+trimul_contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                          __nv_bfloat16* __restrict__ x, GemmShape s, unsigned int* status) {
+    using namespace sm100;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    uint64_t* full = bars;                    // [STAGES]
+    uint64_t* empty = bars + STAGES;          // [STAGES]
+    uint64_t* acc_full = bars + 2 * STAGES;   // [2]
+    uint64_t* acc_empty = acc_full + 2;       // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int mt = (s.m_rows + BM - 1) / BM, nt = (s.n_rows + BN - 1) / BN;
+    const int kb_total = (s.k_total + BK - 1) / BK;
+    const long long tiles = (long long)s.channels * mt * nt;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- TMA producer ----------------
+        tma_prefetch_desc(&map_a);
+        tma_prefetch_desc(&map_b);
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+            int d = (int)(t / (mt * nt));
+            int rem = (int)(t % (mt * nt));
+            int m0 = (rem / nt) * BM, n0 = (rem % nt) * BN;
+            for (int kb = 0; kb < kb_total; ++kb) {
+                ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag);
+                if (!ok) break;
+                uint8_t* sa = smem + stage * STAGE_BYTES;
+                uint8_t* sb = sa + A_BYTES;
+                mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
+                int k0 = kb * BK;
+                tma_load_4d(sa, &map_a, &full[stage], k0 % s.a_kseg_cols, m0, d, k0 / s.a_kseg_cols);
+                int kseg_b = k0 / s.b_kseg_cols, kin_b = k0 % s.b_kseg_cols;
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    int j = n0 + half * 128;
+                    int rseg = j / s.b_rowseg_rows, rin = j % s.b_rowseg_rows;
+                    tma_load_4d(sb + half * (128 * BK * 2), &map_b, &full[stage], kin_b, rin, d, rseg + kseg_b);
+                }
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+        if (!ok) {   // give copies in flight time to land before the CTA's shared memory goes away
+            atomicOr(status, DEV_STATUS_MBAR_TIMEOUT);
+            uint64_t t0 = global_timer_ns();
+            while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer ----------------
+        constexpr uint32_t idesc = make_idesc_bf16(BM, BN);
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        long long it = 0;
+        for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
+            uint32_t ab = (uint32_t)(it & 1), aphase = (uint32_t)((it >> 1) & 1);
+            ok = mbar_wait(&acc_empty[ab], aphase ^ 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t tmem_d = tmem_base + ab * BN;
+            for (int kb = 0; kb < kb_total; ++kb) {
+                ok = mbar_wait(&full[stage], phase, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+                uint32_t sb = sa + A_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < BK / 16; ++kk) {
+                    uint64_t da = make_desc_k_sw128(sa + kk * 32);
+                    uint64_t db = make_desc_k_sw128(sb + kk * 32);
+                    umma_bf16(tmem_d, da, db, idesc, (kb | kk) ? 1u : 0u);
+                }
+                umma_commit(&empty[stage]);
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+            if (ok) umma_commit(&acc_full[ab]);
+        }
+        if (!ok) atomicOr(status, DEV_STATUS_MBAR_TIMEOUT);
+    } else if (warp >= 2) {
+        // ---------------- epilogue ----------------
+        const int quarter = warp & 3;                 // TMEM lanes this warp may touch: 32*quarter ..
+        bool ok = true;
+        long long it = 0;
+        for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
+            uint32_t ab = (uint32_t)(it & 1), aphase = (uint32_t)((it >> 1) & 1);
+            int d = (int)(t / (mt * nt));
+            int rem = (int)(t % (mt * nt));
+            int m0 = (rem / nt) * BM, n0 = (rem % nt) * BN;
+            ok = mbar_wait(&acc_full[ab], aphase, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            int row = m0 + quarter * 32 + lane;
+            __nv_bfloat16* xrow = x + (long long)d * s.x_plane_stride + (long long)row * s.x_pitch;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                int col = n0 + c * 32;
+                if (col >= s.x_pitch) break;          // warp-uniform
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + ab * BN + c * 32, r);
+                tmem_ld_wait();
+                if (row < s.m_rows) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        if (col + v * 8 + 8 <= s.x_pitch) {
+                            uint4 o;
+                            o.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+                            o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+                            o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+                            o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+                            *reinterpret_cast<uint4*>(xrow + col + v * 8) = o;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[ab]);
+        }
+        if (!ok && lane == 0) atomicOr(status, DEV_STATUS_MBAR_TIMEOUT);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+// ---- legacy SIMT cross-check (same operand description, no tensor cores) ---------------------
+struct PlaneView {
+    const __nv_bfloat16* ptr;
+    long long plane_stride, seg_stride;
+    int pitch, rows, cols, nseg, seg_is_k;
+};
+__device__ __forceinline__ float plane_at(const PlaneView& p, int d, int row, int k) {
+    int seg = 0;
+    if (p.nseg > 1) {
+        if (p.seg_is_k) { seg = k / p.cols; k -= seg * p.cols; }
+        else { seg = row / p.rows; row -= seg * p.rows; }
+    }
+    return __bfloat162float(p.ptr[seg * p.seg_stride + d * p.plane_stride + (long long)row * p.pitch + k]);
+}
+__global__ void __launch_bounds__(256)
+trimul_contract_simt_kernel(PlaneView a, PlaneView b, __nv_bfloat16* __restrict__ x, GemmShape s) {
+    __shared__ float as[16][64 + 1], bs[16][64 + 1];
+    int d = blockIdx.z, i0 = blockIdx.y * 64, j0 = blockIdx.x * 64;
+    int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < s.k_total; k0 += 16) {
+        for (int e = threadIdx.x; e < 64 * 16; e += 256) {
+            int r = e >> 4, kk = e & 15;
+            as[kk][r] = (i0 + r < s.m_rows && k0 + kk < s.k_total) ? plane_at(a, d, i0 + r, k0 + kk) : 0.f;
+            bs[kk][r] = (j0 + r < s.n_rows && k0 + kk < s.k_total) ? plane_at(b, d, j0 + r, k0 + kk) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < 16; ++kk)
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int v = 0; v < 4; ++v) acc[u][v] = fmaf(as[kk][ty * 4 + u], bs[kk][tx * 4 + v], acc[u][v]);
+        __syncthreads();
+    }
+    for (int u = 0; u < 4; ++u)
+        for (int v = 0; v < 4; ++v) {
+            int i = i0 + ty * 4 + u, j = j0 + tx * 4 + v;
+            if (i < s.m_rows && j < s.n_rows)
+                x[d * s.x_plane_stride + (long long)i * s.x_pitch + j] = __float2bfloat16(acc[u][v]);
+        }
+}
+
+// ---- host: tensor maps -----------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+static int make_plane_map(CUtensorMap* map, const b200pf_planes* p, int channels, const char* what) {
+    EncodeTiledFn fn = encode_fn();
+    B200PF_REQUIRE(fn != nullptr, B200PF_ERR_CUDA, "cuTensorMapEncodeTiled not available from the driver");
+    long long seg_stride = p->nseg > 1 ? p->seg_stride : p->plane_stride * channels;
+    cuuint64_t dims[4] = {(cuuint64_t)p->cols, (cuuint64_t)p->rows, (cuuint64_t)channels, (cuuint64_t)p->nseg};
+    cuuint64_t strides[3] = {(cuuint64_t)p->pitch * 2, (cuuint64_t)p->plane_stride * 2, (cuuint64_t)seg_stride * 2};
+    cuuint32_t box[4] = {(cuuint32_t)BK, 128u, 1u, 1u};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(p->ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    B200PF_REQUIRE(r == CUDA_SUCCESS, B200PF_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)r);
+    return B200PF_OK;
+}
+
+static int check_planes(const b200pf_planes* p, const char* what) {
+    B200PF_REQUIRE(p && p->ptr, B200PF_ERR_INVALID, "trimul_contract: %s is null", what);
+    B200PF_REQUIRE(aligned16(p->ptr), B200PF_ERR_INVALID, "trimul_contract: %s not 16-byte aligned", what);
+    B200PF_REQUIRE(p->rows > 0 && p->cols > 0 && p->nseg >= 1, B200PF_ERR_INVALID, "trimul_contract: %s has empty extent", what);
+    B200PF_REQUIRE(p->pitch >= p->cols && p->pitch % 8 == 0, B200PF_ERR_INVALID,
+                   "trimul_contract: %s pitch %d must be >= cols %d and a multiple of 8", what, p->pitch, p->cols);
+    B200PF_REQUIRE(p->plane_stride % 8 == 0 && p->plane_stride >= (long long)p->pitch * p->rows, B200PF_ERR_INVALID,
+                   "trimul_contract: %s plane stride too small or not a multiple of 8", what);
+    if (p->nseg > 1) {
+        B200PF_REQUIRE(p->seg_stride % 8 == 0 && p->seg_stride > 0, B200PF_ERR_INVALID, "trimul_contract: %s bad segment stride", what);
+        if (p->seg_is_k)
+            B200PF_REQUIRE(p->cols % BK == 0, B200PF_ERR_UNSUPPORTED,
+                           "trimul_contract: %s k segments must be multiples of %d columns", what, BK);
+        else
+            B200PF_REQUIRE(p->rows % 128 == 0, B200PF_ERR_UNSUPPORTED,
+                           "trimul_contract: %s row segments must be multiples of 128 rows", what);
+    }
+    return B200PF_OK;
+}
+
+}  // namespace b200pf
+
+using namespace b200pf;
+
+extern "C" int b200pf_trimul_contract(const b200pf_planes* a, const b200pf_planes* b,
+                                      const void* a_scales, const void* b_scales,
+                                      b200pf_bf16* x, long long x_plane_stride, int x_pitch,
+                                      int channels, int variant, void* stream) {
+    (void)a_scales; (void)b_scales;
+    int rc;
+    if ((rc = check_planes(a, "A")) != B200PF_OK) return rc;
+    if ((rc = check_planes(b, "B")) != B200PF_OK) return rc;
+    B200PF_REQUIRE(x && aligned16(x) && channels > 0, B200PF_ERR_INVALID, "trimul_contract: bad output");
+    B200PF_REQUIRE(!(a->nseg > 1 && !a->seg_is_k), B200PF_ERR_UNSUPPORTED, "trimul_contract: A cannot be row-segmented");
+    GemmShape s;
+    s.m_rows = a->rows;
+    s.n_rows = (b->nseg > 1 && !b->seg_is_k) ? b->rows * b->nseg : b->rows;
+    int ka = (a->nseg > 1) ? a->cols * a->nseg : a->cols;
+    int kb = (b->nseg > 1 && b->seg_is_k) ? b->cols * b->nseg : b->cols;
+    B200PF_REQUIRE(ka == kb, B200PF_ERR_INVALID, "trimul_contract: contraction lengths differ (%d vs %d)", ka, kb);
+    s.k_total = ka;
+    s.a_kseg_cols = a->nseg > 1 ? a->cols : (ka + BK);          // never reached by k0 when unsegmented
+    s.b_kseg_cols = (b->nseg > 1 && b->seg_is_k) ? b->cols : (kb + BK);
+    s.b_rowseg_rows = (b->nseg > 1 && !b->seg_is_k) ? b->rows : (s.n_rows + BN);
+    s.channels = channels;
+    s.x_pitch = x_pitch;
+    s.x_plane_stride = x_plane_stride;
+    B200PF_REQUIRE(x_pitch % 8 == 0 && x_pitch >= s.n_rows && x_plane_stride >= (long long)x_pitch * s.m_rows,
+                   B200PF_ERR_INVALID, "trimul_contract: bad x pitch / plane stride");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (variant == 1) {
+        PlaneView va{(const __nv_bfloat16*)a->ptr, a->plane_stride, a->seg_stride, a->pitch, a->rows, a->cols, a->nseg, a->seg_is_k};
+        PlaneView vb{(const __nv_bfloat16*)b->ptr, b->plane_stride, b->seg_stride, b->pitch, b->rows, b->cols, b->nseg, b->seg_is_k};
+        dim3 grid((s.n_rows + 63) / 64, (s.m_rows + 63) / 64, channels);
+        trimul_contract_simt_kernel<<<grid, 256, 0, st>>>(va, vb, (__nv_bfloat16*)x, s);
+        B200PF_LAUNCH_CHECK();
+        return B200PF_OK;
+    }
+    B200PF_REQUIRE(variant == 0, B200PF_ERR_UNSUPPORTED, "trimul_contract: variant %d is not built", variant);
+    unsigned int* status = device_status_word();
+    B200PF_REQUIRE(status, B200PF_ERR_CUDA, "trimul_contract: no device status word");
+    CUtensorMap map_a, map_b;
+    if ((rc = make_plane_map(&map_a, a, channels, "A")) != B200PF_OK) return rc;
+    if ((rc = make_plane_map(&map_b, b, channels, "B")) != B200PF_OK) return rc;
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    B200PF_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        B200PF_CUDA(cudaFuncSetAttribute(trimul_contract_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM));
+        attr_set[dev] = true;
+    }
+    int sms = 0;
+    B200PF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    long long tiles = (long long)channels * ((s.m_rows + BM - 1) / BM) * ((s.n_rows + BN - 1) / BN);
+    unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+    trimul_contract_tc_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(map_a, map_b, (__nv_bfloat16*)x, s, status);
+    B200PF_LAUNCH_CHECK();
+    return B200PF_OK;
+}

@@ -1,0 +1,194 @@
+"""Host orchestration of the Pairformer sub-operations on one GPU.
+
+Each function enqueues b200pf kernels (through the C ABI) on torch's current stream and updates
+the fp32 residual tensor in place.  Tensors here are B = 1 folded away: z [N, N, 128] fp32,
+s [N, 384] fp32, masks uint8.  Nothing in this file computes on the CPU or with torch math.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Dict, Optional
+
+import torch
+
+from . import _lib
+from ._lib import Planes, call, ptr, stream
+
+C_Z = 128
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+class Workspace:
+    """bf16 scratch for one token count: five [N*pitch*128] buffers shared by the sub-operations
+    (triangle multiplication uses three as a / b / x planes, triangle attention five as
+    q / k / v / g / o), plus the triangle-bias tile source [4][N][pitch]."""
+
+    def __init__(self, n: int, device) -> None:
+        self.n = n
+        self.pitch = _round_up(n, 8)
+        self.plane_stride = n * self.pitch
+        elems = C_Z * self.plane_stride
+        self.buf = [torch.empty(elems, dtype=torch.bfloat16, device=device) for _ in range(5)]
+        self.tri_bias = torch.empty(4 * n * self.pitch, dtype=torch.bfloat16, device=device)
+
+
+# ------------------------------------------------------------------------------------------------
+# bf16 tier (fused kernels)
+# ------------------------------------------------------------------------------------------------
+def tri_mul_bf16(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Tensor], ws: Workspace,
+                 incoming: bool, contract_variant: int = 0) -> None:
+    n = z.shape[0]
+    a, b, x = ws.buf[0], ws.buf[1], ws.buf[2]
+    st = stream()
+    call("b200pf_trimul_producer", ptr(z), ptr(mask_u8), ptr(w["bias_pg"]), ptr(w["w_pg"]), ptr(a), ptr(b),
+         None, None, ws.plane_stride, ws.pitch, n, n, int(incoming), 0, st)
+    pa = Planes(ptr(a), ws.plane_stride, 0, ws.pitch, n, n, 1, 0)
+    pb = Planes(ptr(b), ws.plane_stride, 0, ws.pitch, n, n, 1, 0)
+    call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), None, None, ptr(x), ws.plane_stride, ws.pitch,
+         C_Z, contract_variant, st)
+    call("b200pf_trimul_epilogue", ptr(z), ptr(x), ws.plane_stride, ws.pitch, ptr(w["w_pout"]), ptr(w["w_gout"]),
+         ptr(w["bias_pout"]), ptr(w["bias_gout"]), n, n, st)
+
+
+def tri_att_bf16(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Tensor], ws: Workspace,
+                 ending: bool, lines_per_cta: int = 0) -> None:
+    n = z.shape[0]
+    q, k, v, g, o = ws.buf
+    st = stream()
+    bias_hs = n * ws.pitch
+    call("b200pf_triatt_producer", ptr(z), ptr(w["w_qkvg"]), ptr(w["bias_qkvg"]), ptr(q), ptr(k), ptr(v), ptr(g),
+         ptr(ws.tri_bias), bias_hs, ws.pitch, n, n, int(ending), st)
+    if ending:      # line = column j: mask(line, key) = M[key][line]; o element (line, pos) -> z position [pos][line]
+        mask_ls, mask_ks, o_ls, o_ps = 1, n, C_Z, n * C_Z
+    else:
+        mask_ls, mask_ks, o_ls, o_ps = n, 1, n * C_Z, C_Z
+    call("b200pf_triatt_core", ptr(q), ptr(k), ptr(v), ptr(ws.tri_bias), bias_hs, ws.pitch, ptr(mask_u8),
+         mask_ls, mask_ks, ptr(o), o_ls, o_ps, n, n, lines_per_cta, st)
+    call("b200pf_triatt_epilogue", ptr(z), ptr(o), ptr(g), ptr(w["w_o"]), n * n, st)
+
+
+def transition_z_bf16(z: torch.Tensor, w: Dict[str, torch.Tensor]) -> None:
+    n = z.shape[0]
+    call("b200pf_transition_z", ptr(z), ptr(w["w12"]), ptr(w["bias12"]), ptr(w["w3"]), n * n, stream())
+
+
+# ------------------------------------------------------------------------------------------------
+# fp32 tier (un-fused SIMT kernels) - also the single-track path of every tier
+# ------------------------------------------------------------------------------------------------
+def _empty(rows: int, c: int, like: torch.Tensor) -> torch.Tensor:
+    return torch.empty(rows, c, dtype=torch.float32, device=like.device)
+
+
+def f32_layernorm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor) -> torch.Tensor:
+    rows, c = x.numel() // x.shape[-1], x.shape[-1]
+    y = _empty(rows, c, x)
+    call("b200pf_f32_layernorm", ptr(x), ptr(gamma), ptr(beta), ptr(y), rows, c, stream())
+    return y
+
+
+def f32_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+               out: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
+    k = w.shape[1]
+    rows = x.numel() // k
+    if out is None:
+        out = _empty(rows, w.shape[0], x)
+    call("b200pf_f32_linear", ptr(x), ptr(w), ptr(bias), ptr(out), rows, k, w.shape[0], int(accumulate), stream())
+    return out
+
+
+def f32_gate(a: torch.Tensor, b: torch.Tensor, mode: int, row_mask: Optional[torch.Tensor] = None,
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    c = a.shape[-1]
+    rows = a.numel() // c
+    if out is None:
+        out = _empty(rows, c, a)
+    call("b200pf_f32_gate", ptr(a), ptr(b), ptr(row_mask), ptr(out), rows, c, mode, stream())
+    return out
+
+
+def tri_mul_f32(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Tensor], incoming: bool) -> None:
+    n = z.shape[0]
+    x = f32_layernorm(z, w["norm_in.weight"], w["norm_in.bias"])
+    u = f32_gate(f32_linear(x, w["p_in.weight"]), f32_linear(x, w["g_in.weight"]), 0, mask_u8)     # [N*N, 2D]
+    d = u.shape[1] // 2
+    t = _empty(n * n, d, z)
+    call("b200pf_f32_trimul_contract", ptr(u), u.data_ptr() + 4 * d, ptr(t), n, d, 2 * d, int(incoming), stream())
+    tn = f32_layernorm(t, w["norm_out.weight"], w["norm_out.bias"])
+    f32_gate(f32_linear(tn, w["p_out.weight"]), f32_linear(x, w["g_out.weight"]), 2, out=z)
+
+
+def _attention_f32(q, k, v, bias, bias_strides, mask_u8, mask_strides, batch, n_q, n_k, heads, hd, rs, ps,
+                   scale, inf_value, order) -> torch.Tensor:
+    o = torch.empty_like(q)
+    call("b200pf_f32_attention", ptr(q), ptr(k), ptr(v), ptr(o), ptr(bias), *bias_strides, ptr(mask_u8),
+         *mask_strides, batch, n_q, n_k, heads, hd, rs, ps, scale, inf_value, order, stream())
+    return o
+
+
+def tri_att_f32(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Tensor], ending: bool) -> None:
+    n = z.shape[0]
+    st = stream()
+    if ending:      # the reference transposes z and the mask, runs the starting-node path, transposes back
+        src = torch.empty_like(z)
+        call("b200pf_f32_transpose01", ptr(z), ptr(src), n, C_Z, 0, st)
+        mask_ls, mask_ks = 1, n
+    else:
+        src = z
+        mask_ls, mask_ks = n, 1
+    heads = w["linear.weight"].shape[0]
+    hd = w["mha.linear_q.weight"].shape[0] // heads
+    x = f32_layernorm(src, w["layer_norm.weight"], w["layer_norm.bias"])
+    bias = torch.empty(heads, n * n, dtype=torch.float32, device=z.device)
+    call("b200pf_ln_proj_heads", ptr(src), ptr(w["layer_norm.weight"]), ptr(w["layer_norm.bias"]),
+         ptr(w["linear.weight"]), ptr(bias), n * n, n * n, C_Z, heads, st)
+    q = f32_linear(x, w["mha.linear_q.weight"])
+    k = f32_linear(x, w["mha.linear_k.weight"])
+    v = f32_linear(x, w["mha.linear_v.weight"])
+    g = f32_linear(x, w["mha.linear_g.weight"])
+    o = _attention_f32(q, k, v, bias, (n * n, n, 1), mask_u8, (mask_ls, mask_ks), n, n, n, heads, hd,
+                       n * heads * hd, heads * hd, 1.0 / math.sqrt(hd), 1e9, 0)
+    og = f32_gate(o, g, 0)
+    if ending:
+        upd = f32_linear(og, w["mha.linear_o.weight"])
+        call("b200pf_f32_transpose01", ptr(upd), ptr(z), n, C_Z, 1, st)
+    else:
+        f32_linear(og, w["mha.linear_o.weight"], out=z, accumulate=True)
+
+
+def transition_f32(x_res: torch.Tensor, w: Dict[str, torch.Tensor]) -> None:
+    x = f32_layernorm(x_res, w["norm.weight"], w["norm.bias"])
+    h = f32_gate(f32_linear(x, w["fc1.weight"]), f32_linear(x, w["fc2.weight"]), 1)
+    f32_linear(h, w["fc3.weight"], out=x_res, accumulate=True)
+
+
+def pair_bias_heads(z: torch.Tensor, w: Dict[str, torch.Tensor]) -> torch.Tensor:
+    """bias[h][i*N + j] of the single-track attention: one fp32 pass over z."""
+    n = z.shape[0]
+    heads = w["proj_z.1.weight"].shape[0]
+    bias = torch.empty(heads, n * n, dtype=torch.float32, device=z.device)
+    call("b200pf_ln_proj_heads", ptr(z), ptr(w["proj_z.0.weight"]), ptr(w["proj_z.0.bias"]),
+         ptr(w["proj_z.1.weight"]), ptr(bias), n * n, n * n, C_Z, heads, stream())
+    return bias
+
+
+def single_track(s: torch.Tensor, z: torch.Tensor, tok_mask_u8: torch.Tensor, w_norm: Dict[str, torch.Tensor],
+                 w_att: Dict[str, torch.Tensor], w_trans: Dict[str, torch.Tensor], num_heads: int,
+                 bias: Optional[torch.Tensor] = None) -> None:
+    """s += AttentionPairBias(LN(s), z); s += Transition(s) in fp32 (tt_bio/reference.py:906-912)."""
+    n, cs = s.shape
+    hd = cs // num_heads
+    sn = f32_layernorm(s, w_norm["weight"], w_norm["bias"])
+    q = f32_linear(sn, w_att["proj_q.weight"], w_att["proj_q.bias"])
+    k = f32_linear(sn, w_att["proj_k.weight"])
+    v = f32_linear(sn, w_att["proj_v.weight"])
+    g = f32_linear(sn, w_att["proj_g.weight"])
+    if bias is None:
+        bias = pair_bias_heads(z, w_att)
+    o = _attention_f32(q, k, v, bias, (n * n, n, 1), tok_mask_u8, (0, 1), 1, n, n, num_heads, hd, 0, cs,
+                       1.0 / math.sqrt(hd), 1e6, 1)
+    f32_linear(f32_gate(o, g, 0), w_att["proj_o.weight"], out=s, accumulate=True)
+    transition_f32(s, w_trans)

@@ -1,0 +1,189 @@
+"""Drop-in Pairformer modules backed by the b200pf CUDA kernels.
+
+Call surface mirrors the reference:
+  * ``B200PairformerModule(token_s, token_z, num_blocks, num_heads=16, dropout=0.25,
+    pairwise_head_width=32, pairwise_num_heads=4, post_layer_norm=False,
+    activation_checkpointing=False, v2=False, **kw).forward(s, z, mask, pair_mask,
+    use_kernels=False) -> (s, z)``            (tt_bio/reference.py:921-1003)
+  * ``B200PairformerNoSeqModule(token_z, num_blocks, ...).forward(z, pair_mask,
+    use_kernels=False) -> z``                 (tt_bio/reference.py:1096-1139)
+  * ``B200PairformerLayer.forward(s, z, mask, pair_mask, chunk_size_tri_attn=None,
+    use_kernels=False, ...)``                 (tt_bio/reference.py:865-914)
+Parameters carry the reference's state-dict key names, so ``load_state_dict`` of a reference
+checkpoint slice works unchanged (tt_bio/tenstorrent.py:2179-2180 does the same for its backend).
+
+Inference only (eval-mode semantics: dropout masks are 1).  Inputs must be CUDA tensors; there
+is no CPU path.  ``precision``: "bf16" (fused tensor-core kernels, fp32 residual stream) or
+"fp32" (un-fused fp32 kernels, the validation tier).
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+from torch import nn
+
+from . import ops, weights
+from .synthetic import layer_param_shapes
+
+
+def _register_tree(root: nn.Module, name: str, shape) -> None:
+    parts = name.split(".")
+    mod = root
+    for p in parts[:-1]:
+        if p not in mod._modules:
+            mod.add_module(p, nn.Module())
+        mod = mod._modules[p]
+    mod.register_parameter(parts[-1], nn.Parameter(torch.zeros(shape), requires_grad=False))
+
+
+def _mask_u8(m: Optional[torch.Tensor], shape, device) -> torch.Tensor:
+    if m is None:
+        return torch.ones(shape, dtype=torch.uint8, device=device)
+    return (m.reshape(shape) != 0).to(device=device, dtype=torch.uint8).contiguous()
+
+
+class B200PairformerLayer(nn.Module):
+    """One Pairformer block (with or without the single track)."""
+
+    def __init__(self, token_s: int = 384, token_z: int = 128, num_heads: int = 16, dropout: float = 0.25,
+                 pairwise_head_width: int = 32, pairwise_num_heads: int = 4, post_layer_norm: bool = False,
+                 v2: bool = False, precision: str = "bf16", with_s: bool = True) -> None:
+        super().__init__()
+        if post_layer_norm:
+            raise NotImplementedError("post_layer_norm=True is not used by Boltz-2 and is not built")
+        if precision not in ("bf16", "fp32"):
+            raise ValueError("precision must be 'bf16' or 'fp32'")
+        self.token_s, self.token_z, self.num_heads = token_s, token_z, num_heads
+        self.dropout, self.with_s, self.precision = dropout, with_s, precision
+        self.contract_variant = 0      # 0 = tcgen05, 1 = SIMT cross-check
+        self.lines_per_cta = 0
+        for name, shape in layer_param_shapes(token_s, token_z, num_heads, pairwise_num_heads,
+                                              pairwise_head_width, with_s):
+            _register_tree(self, name, shape)
+        self._packed: Optional[Dict[str, Dict[str, torch.Tensor]]] = None
+        self.register_load_state_dict_post_hook(lambda module, incompatible: module.reset_static_cache())
+
+    # same name as the reference backend's cache reset (tt_bio/tenstorrent.py:2185-2191)
+    def reset_static_cache(self) -> None:
+        self._packed = None
+
+    def _pack(self, device) -> Dict[str, Dict[str, torch.Tensor]]:
+        if self._packed is not None and self._packed["_device"] == device:
+            return self._packed
+        sd = {k: v for k, v in self.state_dict().items()}
+        pk: Dict[str, Dict[str, torch.Tensor]] = {"_device": device}
+        for name in ("tri_mul_out", "tri_mul_in"):
+            pk[name] = (weights.pack_trimul(sd, name + ".", device) if self.precision == "bf16"
+                        else weights.to_device_f32(sd, name + ".", device))
+        for name in ("tri_att_start", "tri_att_end"):
+            pk[name] = (weights.pack_triatt(sd, name + ".", device) if self.precision == "bf16"
+                        else weights.to_device_f32(sd, name + ".", device))
+        pk["transition_z"] = (weights.pack_transition_z(sd, "transition_z.", device) if self.precision == "bf16"
+                              else weights.to_device_f32(sd, "transition_z.", device))
+        if self.with_s:
+            pk["pre_norm_s"] = weights.to_device_f32(sd, "pre_norm_s.", device)
+            pk["attention"] = weights.to_device_f32(sd, "attention.", device)
+            pk["transition_s"] = weights.to_device_f32(sd, "transition_s.", device)
+        self._packed = pk
+        return pk
+
+    def forward_inplace(self, s: Optional[torch.Tensor], z: torch.Tensor, tok_mask_u8: Optional[torch.Tensor],
+                        pair_mask_u8: torch.Tensor, ws: Optional[ops.Workspace]) -> None:
+        """Update fp32 working copies z [N,N,128] and s [N,c_s] in place."""
+        pk = self._pack(z.device)
+        if self.precision == "bf16":
+            ops.tri_mul_bf16(z, pair_mask_u8, pk["tri_mul_out"], ws, False, self.contract_variant)
+            ops.tri_mul_bf16(z, pair_mask_u8, pk["tri_mul_in"], ws, True, self.contract_variant)
+            ops.tri_att_bf16(z, pair_mask_u8, pk["tri_att_start"], ws, False, self.lines_per_cta)
+            ops.tri_att_bf16(z, pair_mask_u8, pk["tri_att_end"], ws, True, self.lines_per_cta)
+            ops.transition_z_bf16(z, pk["transition_z"])
+        else:
+            ops.tri_mul_f32(z, pair_mask_u8, pk["tri_mul_out"], False)
+            ops.tri_mul_f32(z, pair_mask_u8, pk["tri_mul_in"], True)
+            ops.tri_att_f32(z, pair_mask_u8, pk["tri_att_start"], False)
+            ops.tri_att_f32(z, pair_mask_u8, pk["tri_att_end"], True)
+            ops.transition_f32(z, pk["transition_z"])
+        if self.with_s and s is not None:
+            ops.single_track(s, z, tok_mask_u8, pk["pre_norm_s"], pk["attention"], pk["transition_s"], self.num_heads)
+
+    def forward(self, s: Optional[torch.Tensor], z: torch.Tensor, mask: Optional[torch.Tensor] = None,
+                pair_mask: Optional[torch.Tensor] = None, chunk_size_tri_attn: Optional[int] = None,
+                use_kernels: bool = False, use_cuequiv_mul: bool = False, use_cuequiv_attn: bool = False
+                ) -> Tuple[Optional[torch.Tensor], torch.Tensor]:
+        return _run_layers([self], s, z, mask, pair_mask)
+
+
+def _run_layers(layers, s, z, mask, pair_mask, ws_cache: Optional[dict] = None):
+    if not z.is_cuda:
+        raise RuntimeError("B200 Pairformer: inputs must be CUDA tensors (there is no CPU path)")
+    if z.dim() != 4 or z.shape[0] != 1 or z.shape[1] != z.shape[2]:
+        raise RuntimeError(f"B200 Pairformer: z must be [1, N, N, C], got {tuple(z.shape)}")
+    n = z.shape[1]
+    with torch.cuda.device(z.device), torch.no_grad():
+        zw = z[0].to(torch.float32).clone(memory_format=torch.contiguous_format)
+        sw = None if s is None else s[0].to(torch.float32).clone(memory_format=torch.contiguous_format)
+        pm = _mask_u8(pair_mask, (n, n), z.device)
+        tm = _mask_u8(mask, (n,), z.device) if s is not None else None
+        ws = None
+        if any(l.precision == "bf16" for l in layers):
+            key = (n, z.device)
+            if ws_cache is not None and key in ws_cache:
+                ws = ws_cache[key]
+            else:
+                ws = ops.Workspace(n, z.device)
+                if ws_cache is not None:
+                    ws_cache.clear()
+                    ws_cache[key] = ws
+        for layer in layers:
+            layer.forward_inplace(sw, zw, tm, pm, ws)
+    z_out = zw.unsqueeze(0).to(z.dtype)
+    s_out = None if sw is None else sw.unsqueeze(0).to(s.dtype)
+    return s_out, z_out
+
+
+class B200PairformerModule(nn.Module):
+    """Stack of Pairformer blocks with the reference's constructor and forward signature."""
+
+    def __init__(self, token_s: int, token_z: int, num_blocks: int, num_heads: int = 16, dropout: float = 0.25,
+                 pairwise_head_width: int = 32, pairwise_num_heads: int = 4, post_layer_norm: bool = False,
+                 activation_checkpointing: bool = False, v2: bool = False, precision: str = "bf16", **kwargs) -> None:
+        super().__init__()
+        self.token_z, self.num_blocks, self.num_heads = token_z, num_blocks, num_heads
+        self.layers = nn.ModuleList([
+            B200PairformerLayer(token_s, token_z, num_heads, dropout, pairwise_head_width, pairwise_num_heads,
+                                post_layer_norm, v2, precision, with_s=True) for _ in range(num_blocks)])
+        self._ws_cache: dict = {}
+
+    def reset_static_cache(self) -> None:
+        self._ws_cache.clear()
+        for layer in self.layers:
+            layer.reset_static_cache()
+
+    def forward(self, s: torch.Tensor, z: torch.Tensor, mask: Optional[torch.Tensor] = None,
+                pair_mask: Optional[torch.Tensor] = None, use_kernels: bool = False
+                ) -> Tuple[torch.Tensor, torch.Tensor]:
+        return _run_layers(list(self.layers), s, z, mask, pair_mask, self._ws_cache)
+
+
+class B200PairformerNoSeqModule(nn.Module):
+    """Pair-only stack (templates, affinity, MSA pair stack): forward(z, pair_mask) -> z."""
+
+    def __init__(self, token_z: int, num_blocks: int, dropout: float = 0.25, pairwise_head_width: int = 32,
+                 pairwise_num_heads: int = 4, post_layer_norm: bool = False, activation_checkpointing: bool = False,
+                 precision: str = "bf16", **kwargs) -> None:
+        super().__init__()
+        self.token_z, self.num_blocks = token_z, num_blocks
+        self.layers = nn.ModuleList([
+            B200PairformerLayer(384, token_z, 16, dropout, pairwise_head_width, pairwise_num_heads,
+                                post_layer_norm, False, precision, with_s=False) for _ in range(num_blocks)])
+        self._ws_cache: dict = {}
+
+    def reset_static_cache(self) -> None:
+        self._ws_cache.clear()
+        for layer in self.layers:
+            layer.reset_static_cache()
+
+    def forward(self, z: torch.Tensor, pair_mask: Optional[torch.Tensor] = None, use_kernels: bool = False
+                ) -> torch.Tensor:
+        return _run_layers(list(self.layers), None, z, None, pair_mask, self._ws_cache)[1]

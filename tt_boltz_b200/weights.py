@@ -1,0 +1,78 @@
+"""Host-side weight packing for the b200pf kernels.
+
+Input: the reference's flat state dict for one layer (keys as in tt_bio/reference.py:825-863).
+Output: device tensors in the layouts include/b200pf.h documents.  LayerNorm gains are folded
+into the weight rows and LayerNorm offsets into fp32 bias vectors, so that the kernels only
+compute (x - mean) * rstd; rows are re-ordered so that values one thread combines sit together.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict
+
+import torch
+
+LOG2E = 1.4426950408889634
+C_Z = 128
+TRI_HEADS, TRI_HEAD_DIM = 4, 32
+
+
+def _fold(w: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor):
+    """(W * gamma) as the new weight and W @ beta as the bias: LN(x) W^T = xhat (W*gamma)^T + W beta."""
+    return w * gamma[None, :], w @ beta
+
+
+def pack_trimul(sd: Dict[str, torch.Tensor], pre: str, device) -> Dict[str, torch.Tensor]:
+    f = {k: sd[pre + k].detach().float().cpu() for k in
+         ("norm_in.weight", "norm_in.bias", "p_in.weight", "g_in.weight", "norm_out.weight", "norm_out.bias",
+          "p_out.weight", "g_out.weight")}
+    d = f["p_in.weight"].shape[0] // 2
+    if d != C_Z or f["p_in.weight"].shape[1] != C_Z:
+        raise RuntimeError("the fused triangle-multiplication kernels are built for c_z = hidden = 128")
+    rows = []
+    for q in range(8):
+        ch0 = (q // 4) * d + (q % 4) * 32
+        rows += [f["p_in.weight"][ch0:ch0 + 32], f["g_in.weight"][ch0:ch0 + 32]]
+    w_pg, bias_pg = _fold(torch.cat(rows, 0), f["norm_in.weight"], f["norm_in.bias"])
+    w_pout, bias_pout = _fold(f["p_out.weight"], f["norm_out.weight"], f["norm_out.bias"])
+    w_gout, bias_gout = _fold(f["g_out.weight"], f["norm_in.weight"], f["norm_in.bias"])
+    bf = lambda t: t.to(device=device, dtype=torch.bfloat16).contiguous()
+    fp = lambda t: t.to(device=device, dtype=torch.float32).contiguous()
+    return {"w_pg": bf(w_pg), "bias_pg": fp(bias_pg), "w_pout": bf(w_pout), "bias_pout": fp(bias_pout),
+            "w_gout": bf(w_gout), "bias_gout": fp(bias_gout)}
+
+
+def pack_triatt(sd: Dict[str, torch.Tensor], pre: str, device) -> Dict[str, torch.Tensor]:
+    f = {k: sd[pre + k].detach().float().cpu() for k in
+         ("layer_norm.weight", "layer_norm.bias", "linear.weight", "mha.linear_q.weight", "mha.linear_k.weight",
+          "mha.linear_v.weight", "mha.linear_g.weight", "mha.linear_o.weight")}
+    if f["linear.weight"].shape != (TRI_HEADS, C_Z) or f["mha.linear_q.weight"].shape != (TRI_HEADS * TRI_HEAD_DIM, C_Z):
+        raise RuntimeError("the fused triangle-attention kernels are built for c_z = 128 and 4 heads x 32")
+    rows = torch.cat([f["mha.linear_q.weight"] * (LOG2E / math.sqrt(TRI_HEAD_DIM)), f["mha.linear_k.weight"],
+                      f["mha.linear_v.weight"], f["mha.linear_g.weight"], f["linear.weight"] * LOG2E,
+                      torch.zeros(12, C_Z)], 0)
+    w, b = _fold(rows, f["layer_norm.weight"], f["layer_norm.bias"])
+    return {"w_qkvg": w.to(device=device, dtype=torch.bfloat16).contiguous(),
+            "bias_qkvg": b.to(device=device, dtype=torch.float32).contiguous(),
+            "w_o": f["mha.linear_o.weight"].to(device=device, dtype=torch.bfloat16).contiguous()}
+
+
+def pack_transition_z(sd: Dict[str, torch.Tensor], pre: str, device) -> Dict[str, torch.Tensor]:
+    f = {k: sd[pre + k].detach().float().cpu() for k in ("norm.weight", "norm.bias", "fc1.weight", "fc2.weight", "fc3.weight")}
+    hidden = f["fc1.weight"].shape[0]
+    if hidden != 4 * C_Z or f["fc1.weight"].shape[1] != C_Z:
+        raise RuntimeError("the fused transition kernel is built for 128 -> 512 -> 128")
+    rows = []
+    for grp in range(hidden // 16):
+        rows += [f["fc1.weight"][grp * 16:(grp + 1) * 16], f["fc2.weight"][grp * 16:(grp + 1) * 16]]
+    w12, bias12 = _fold(torch.cat(rows, 0), f["norm.weight"], f["norm.bias"])
+    w3 = torch.stack([f["fc3.weight"][:, st * 64:(st + 1) * 64] for st in range(hidden // 64)], 0)   # [8][128][64]
+    return {"w12": w12.to(device=device, dtype=torch.bfloat16).contiguous(),
+            "bias12": bias12.to(device=device, dtype=torch.float32).contiguous(),
+            "w3": w3.to(device=device, dtype=torch.bfloat16).contiguous()}
+
+
+def to_device_f32(sd: Dict[str, torch.Tensor], pre: str, device) -> Dict[str, torch.Tensor]:
+    """fp32 device copies of every tensor under ``pre`` (keys relative to ``pre``)."""
+    return {k[len(pre):]: v.detach().to(device=device, dtype=torch.float32).contiguous()
+            for k, v in sd.items() if k.startswith(pre)}
