@@ -1,0 +1,305 @@
+"""Benchmark of the Boltz-2 Pairformer trunk hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (the configuration the headline metric is quoted on): a 64-block Pairformer trunk at
+N = 1024 tokens, bf16 tier, s [1,1024,384], z [1,1024,1024,128] ~ N(0,1), all-ones masks,
+weights N(0,0.02); one *step* is one pass of the 64 blocks.  Metric: milliseconds per block
+(lower is better); TFLOP/s uses the algorithmic 2.8307 TFLOP of one block.
+One JSON line is printed by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+C = 128
+
+
+def block_flops(n: int) -> float:
+    """Algorithmic FLOPs of one block: projections, contraction, attention, transitions, single track."""
+    tri_mul = 2 * n ** 3 * C + n * n * (8 * C * C + 2 * C * C + 2 * C * C)
+    tri_att = 4 * n ** 3 * C + n * n * (8 * C * C + 2 * C * 4 + 2 * C * C)
+    trans_z = 6 * n * n * C * 4 * C
+    cs = 384
+    s_track = n * (8 * cs * cs + 2 * cs * cs) + 4 * n * n * cs + 2 * n * n * C * 16 + 6 * n * cs * 4 * cs
+    return 2 * tri_mul + 2 * tri_att + trans_z + s_track
+
+
+def kernel_work(n: int):
+    """Per-launch algorithmic FLOPs and HBM bytes of each fused kernel (E = n*n*128 elements)."""
+    e = n * n * C
+    return {
+        "b200pf_trimul_producer": (2 * n * n * C * 512, 8 * e),
+        "b200pf_trimul_contract": (2 * n ** 3 * C, 6 * e),
+        "b200pf_trimul_epilogue": (2 * n * n * C * 256, 10 * e),
+        "b200pf_triatt_producer": (2 * n * n * C * 516, 12 * e),
+        "b200pf_triatt_core": (4 * n ** 3 * C, 8 * e + 2 * 4 * n * n),
+        "b200pf_triatt_epilogue": (2 * n * n * C * C, 12 * e),
+        "b200pf_transition_z": (6 * n * n * C * 4 * C, 8 * e),
+        "b200pf_ln_proj_heads": (2 * n * n * C * 16, 4 * e + 4 * 16 * n * n),
+    }
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "tflops_burst": p["bf16_tflops"], "tflops_sustained": p["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops_burst": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int) -> None:
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_block_seconds(n: int, rows: int, repeats: int, threads: int):
+    """Row-sampled fp32 oracle timing of one block on the host cores (see oracle/sampled.py)."""
+    from oracle import sampled
+    from tt_boltz_b200 import synthetic
+    torch.set_num_threads(threads)
+    torch.set_float32_matmul_precision("highest")
+    sd = synthetic.make_weights(1, seed=1)
+    s, z = synthetic.make_inputs(n, seed=0)
+    m, pm = synthetic.tail_padding_mask(n, 0)
+    times = []
+    for r in range(repeats + 1):            # first repeat is a warm-up
+        t = sampled.sampled_block_seconds(s[0], z[0], m[0], pm[0], sd, "layers.0.", rows, seed=r)
+        if r:
+            times.append(t["total"])
+    return statistics.median(times)
+
+
+def run_reference(args, rank: int) -> None:
+    """Reference arm: the reference's CPU algorithm (oracle restatement) on the host cores."""
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    n = args.n
+    from oracle import sampled
+    from tt_boltz_b200 import synthetic
+    torch.set_num_threads(threads)
+    sd = synthetic.make_weights(1, seed=1)
+    s, z = synthetic.make_inputs(n, seed=0)
+    m, pm = synthetic.tail_padding_mask(n, 0)
+    per_block = []
+    for it in range(args.warmup + args.steps):
+        t = sampled.sampled_block_seconds(s[0], z[0], m[0], pm[0], sd, "layers.0.", args.cpu_rows, seed=it)["total"]
+        if it >= args.warmup:
+            per_block.append(t)
+    ms = 1e3 * sum(per_block) / len(per_block)
+    sample = (f"{args.cpu_rows} of {n} rows of every sub-operation of one block, fp32 oracle (port of "
+              f"tt_bio/reference.py), scaled by {n}/{args.cpu_rows}; single track timed in full")
+    line = {"impl": "reference", "metric": "pairformer_ms_per_block", "value": ms, "unit": "ms", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms * args.blocks, "higher_is_better": False,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "tflops": block_flops(n) / (ms * 1e-3) / 1e12,
+            "config": {"workload": f"Pairformer trunk, {args.blocks} blocks, N={n}, c_z=128, c_s=384", "tokens": n,
+                       "blocks": args.blocks},
+            "cpu_baseline": {"value": ms, "unit": "ms", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": ms, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--n", type=int, default=1024, help="tokens")
+    ap.add_argument("--blocks", type=int, default=64)
+    ap.add_argument("--cpu-rows", type=int, default=64, help="rows sampled by the CPU baseline")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the b200pf kernels have no CPU path")
+
+    import torch.distributed as dist
+    from tt_boltz_b200 import B200PairformerModule, _lib, synthetic
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    n, nb = args.n, args.blocks
+    sd = synthetic.make_weights(nb, seed=1)
+    s_cpu, z_cpu = synthetic.make_inputs(n, seed=0)
+    m_cpu, pm_cpu = synthetic.tail_padding_mask(n, 0)
+    if world > 1:
+        from tt_boltz_b200.sharded import ShardedPairformerModule
+        mod = ShardedPairformerModule(384, 128, nb, v2=True, precision="bf16")
+    else:
+        mod = B200PairformerModule(384, 128, nb, v2=True, precision="bf16")
+    mod.load_state_dict(sd, strict=True)
+    del sd
+    s_pin, z_pin = s_cpu.pin_memory(), z_cpu.pin_memory()
+    m_pin, pm_pin = m_cpu.pin_memory(), pm_cpu.pin_memory()
+    s_d, z_d, m_d, pm_d = (t.to(dev) for t in (s_pin, z_pin, m_pin, pm_pin))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    step_dev = lambda: mod(s_d, z_d, m_d, pm_d)
+    for _ in range(args.warmup):
+        step_dev()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = _lib.launch_count()
+    total_ms = timed(step_dev, args.steps)
+    launches = _lib.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    ms_step = total_ms / args.steps
+    ms_block = ms_step / nb
+
+    # ---- end to end through the module API with host buffers ----
+    e2e = None
+    if not args.no_e2e:
+        s_out = torch.empty_like(s_pin).pin_memory()
+        z_out = torch.empty_like(z_pin).pin_memory()
+
+        def step_e2e():
+            so, zo = mod(s_pin.to(dev, non_blocking=True), z_pin.to(dev, non_blocking=True),
+                         m_pin.to(dev, non_blocking=True), pm_pin.to(dev, non_blocking=True))
+            s_out.copy_(so, non_blocking=True)
+            z_out.copy_(zo, non_blocking=True)
+
+        step_e2e()
+        e2e_ms = timed(step_e2e, args.steps) / args.steps
+        h2d = sum(t.numel() * t.element_size() for t in (s_pin, z_pin, m_pin, pm_pin))
+        d2h = sum(t.numel() * t.element_size() for t in (s_out, z_out))
+        e2e = {"value": e2e_ms / nb, "unit": "ms", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h}
+
+    # ---- per-kernel pass (one extra, untimed-for-the-metric step with CUDA events per launch) ----
+    peaks = measured_peaks()
+    kernels, roofline = {}, None
+    if world == 1:
+        _lib.timer = _lib.KernelTimer()
+        step_dev()
+        summ = _lib.timer.summary()
+        _lib.timer = None
+        work = kernel_work(n)
+        tot = sum(v[0] for v in summ.values())
+        for name, (ms, cnt) in sorted(summ.items(), key=lambda kv: -kv[1][0]):
+            ent = {"launches": cnt, "ms_per_launch": ms / cnt, "share": ms / tot}
+            if name in work:
+                fl, by = work[name]
+                sec = ms / cnt * 1e-3
+                ent.update({"tflops": fl / sec / 1e12, "gbs": by / sec / 1e9,
+                            "frac_tensor": fl / sec / 1e12 / peaks["tflops_sustained"],
+                            "frac_hbm": by / sec / 1e9 / peaks["hbm_gbs"]})
+            kernels[name] = ent
+        top = next(iter(kernels))
+        if top in work:
+            fl, by = work[top]
+            sec = kernels[top]["ms_per_launch"] * 1e-3
+            t_tensor, t_hbm = fl / (peaks["tflops_sustained"] * 1e12), by / (peaks["hbm_gbs"] * 1e9)
+            if t_tensor >= t_hbm:
+                roofline = {"kernel": top, "bound": "tensor", "achieved": fl / sec / 1e12, "peak": peaks["tflops_sustained"],
+                            "unit": "TFLOP/s", "frac": fl / sec / 1e12 / peaks["tflops_sustained"], "traffic": None}
+            else:
+                roofline = {"kernel": top, "bound": "hbm", "achieved": by / sec / 1e9, "peak": peaks["hbm_gbs"],
+                            "unit": "GB/s", "frac": by / sec / 1e9 / peaks["hbm_gbs"], "traffic": None}
+            roofline["peak_source"] = peaks["source"] + " (sustained bf16 GEMM / copy bandwidth)"
+            roofline["algorithmic_per_launch"] = {"flop": fl, "bytes": by}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        threads = os.cpu_count() or 1
+        sec = cpu_block_seconds(n, args.cpu_rows, 2, threads)
+        cpu = {"value": sec * 1e3, "unit": "ms", "cores": threads, "kind": "port",
+               "sample": f"{args.cpu_rows} of {n} rows of every sub-operation of one fp32 oracle block, scaled by "
+                         f"{n}/{args.cpu_rows}; median of 2 after 1 warm-up"}
+    if rank == 0:
+        line = {"metric": "pairformer_ms_per_block", "value": ms_block, "unit": "ms", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong",
+                "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "tflops": block_flops(n) / (ms_block * 1e-3) / 1e12,
+                "config": {"workload": f"Pairformer trunk, {nb} blocks, N={n}, c_z=128, c_s=384, bf16 operands / fp32 residual",
+                           "tokens": n, "blocks": nb, "parallelism": "single GPU" if world == 1 else f"row-sharded x{world}",
+                           "l2": "inputs larger than L2 (z fp32 = %d MiB)" % (n * n * C * 4 >> 20)},
+                "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "kernels": kernels,
+                "cpu_baseline": cpu}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -89,10 +89,35 @@ def stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+class KernelTimer:
+    """Optional per-entry-point timing with CUDA events on the launching stream (benchmarks)."""
+
+    def __init__(self) -> None:
+        self.events = []          # (name, start, end)
+
+    def summary(self):
+        torch.cuda.synchronize()
+        out = {}
+        for name, a, b in self.events:
+            ms, cnt = out.get(name, (0.0, 0))
+            out[name] = (ms + a.elapsed_time(b), cnt + 1)
+        return out
+
+
+timer: Optional[KernelTimer] = None
+
+
 def call(name: str, *args) -> None:
+    t = timer
+    if t is not None:
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
     rc = getattr(load(), name)(*args)
     if rc != 0:
         raise RuntimeError(f"{name} failed with status {rc}: {last_error()}")
+    if t is not None:
+        b.record()
+        t.events.append((name, a, b))
 
 
 def launch_count() -> int:
