@@ -104,43 +104,39 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def cpu_block_seconds(n: int, rows: int, repeats: int, threads: int):
-    """Row-sampled fp32 oracle timing of one block on the host cores (see oracle/sampled.py)."""
-    from oracle import sampled
+def cpu_block_seconds(n: int, threads: int, budget_s: float, max_steps: int, warmup: int):
+    """Seconds per block of the fp32 oracle (port of tt_bio/reference.py) on the host cores:
+    each step is one full block at n tokens, i.e. 1/64 of the trunk; stops early once budget_s is spent."""
+    from oracle import pairformer_oracle as orc
     from tt_boltz_b200 import synthetic
     torch.set_num_threads(threads)
     torch.set_float32_matmul_precision("highest")
     sd = synthetic.make_weights(1, seed=1)
     s, z = synthetic.make_inputs(n, seed=0)
     m, pm = synthetic.tail_padding_mask(n, 0)
-    times = []
-    for r in range(repeats + 1):            # first repeat is a warm-up
-        t = sampled.sampled_block_seconds(s[0], z[0], m[0], pm[0], sd, "layers.0.", rows, seed=r)
-        if r:
-            times.append(t["total"])
-    return statistics.median(times)
+    times, t_start = [], time.perf_counter()
+    with torch.no_grad():
+        for it in range(warmup + max_steps):
+            t0 = time.perf_counter()
+            orc.pairformer_layer(s[0], z[0], m[0], pm[0], sd, "layers.0.")
+            dt = time.perf_counter() - t0
+            if it >= warmup or (it == warmup - 1 and time.perf_counter() - t_start > budget_s):
+                times.append(dt)
+            if times and time.perf_counter() - t_start > budget_s:
+                break
+    return sum(times) / len(times), len(times)
 
 
 def run_reference(args, rank: int) -> None:
-    """Reference arm: the reference's CPU algorithm (oracle restatement) on the host cores."""
+    """Reference arm: the reference's CPU algorithm (oracle restatement) on all host cores."""
     if rank != 0:
         return
     threads = os.cpu_count() or 1
     n = args.n
-    from oracle import sampled
-    from tt_boltz_b200 import synthetic
-    torch.set_num_threads(threads)
-    sd = synthetic.make_weights(1, seed=1)
-    s, z = synthetic.make_inputs(n, seed=0)
-    m, pm = synthetic.tail_padding_mask(n, 0)
-    per_block = []
-    for it in range(args.warmup + args.steps):
-        t = sampled.sampled_block_seconds(s[0], z[0], m[0], pm[0], sd, "layers.0.", args.cpu_rows, seed=it)["total"]
-        if it >= args.warmup:
-            per_block.append(t)
-    ms = 1e3 * sum(per_block) / len(per_block)
-    sample = (f"{args.cpu_rows} of {n} rows of every sub-operation of one block, fp32 oracle (port of "
-              f"tt_bio/reference.py), scaled by {n}/{args.cpu_rows}; single track timed in full")
+    sec, done = cpu_block_seconds(n, threads, args.cpu_budget, args.steps, min(args.warmup, 1))
+    ms = sec * 1e3
+    sample = (f"{done} timed step(s), each one full fp32 block (1 of {args.blocks}) at N={n} through the oracle port of "
+              f"tt_bio/reference.py, {threads} threads; stops after {args.cpu_budget:.0f} s")
     line = {"impl": "reference", "metric": "pairformer_ms_per_block", "value": ms, "unit": "ms", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms * args.blocks, "higher_is_better": False,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -160,7 +156,7 @@ def main() -> None:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--n", type=int, default=1024, help="tokens")
     ap.add_argument("--blocks", type=int, default=64)
-    ap.add_argument("--cpu-rows", type=int, default=64, help="rows sampled by the CPU baseline")
+    ap.add_argument("--cpu-budget", type=float, default=150.0, help="seconds the CPU legs may spend")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -282,10 +278,10 @@ def main() -> None:
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         threads = os.cpu_count() or 1
-        sec = cpu_block_seconds(n, args.cpu_rows, 2, threads)
+        sec, done = cpu_block_seconds(n, threads, 30.0, 1, 0)
         cpu = {"value": sec * 1e3, "unit": "ms", "cores": threads, "kind": "port",
-               "sample": f"{args.cpu_rows} of {n} rows of every sub-operation of one fp32 oracle block, scaled by "
-                         f"{n}/{args.cpu_rows}; median of 2 after 1 warm-up"}
+               "sample": f"one full fp32 block (1 of {nb}) at N={n} through the oracle port of tt_bio/reference.py, "
+                         f"{threads} threads, no warm-up"}
     if rank == 0:
         line = {"metric": "pairformer_ms_per_block", "value": ms_block, "unit": "ms", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong",
