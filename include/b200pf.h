@@ -111,11 +111,20 @@ int b200pf_ln_proj_heads(const float* z, const float* gamma, const float* beta, 
  *         (q < 4) or b (q >= 4): their 32 p_in rows then their 32 g_in rows;  bias_pg: fp32 [512].
  *   incoming == 0: a[d][r][k] = u_a[r][k][d]  (plane rows = local z rows, cols = k)
  *   incoming != 0: a[d][c][r] = u_a[r][c][d]  (plane rows = z columns, cols = local z rows)
- *   value_mode 0 = bf16 planes (the only mode built so far; a_scales / b_scales unused). */
+ *   value_mode 0 = bf16 planes (the only mode built so far). */
+typedef struct b200pf_plane_out {
+    void*     ptr;            /* bf16 planes to write                                              */
+    long long plane_stride;   /* elements between channels                                         */
+    long long group_stride;   /* elements between groups of plane rows (unused when row_group <= 0) */
+    int       row_group;      /* plane rows per group; <= 0: one group (plain [d][row][col] planes) */
+} b200pf_plane_out;
+/* element (d, row, col) of an output operand is written to
+ *   ptr[(row / row_group) * group_stride + d * plane_stride + (row % row_group) * pitch + col];
+ * row groups let a rank lay its planes out as one contiguous block per destination rank. */
 int b200pf_trimul_producer(const float* z, const uint8_t* mask, const float* bias_pg,
-                           const b200pf_bf16* w_pg, void* a_planes, void* b_planes,
-                           void* a_scales, void* b_scales, long long plane_stride, int pitch,
-                           int rows, int n, int incoming, int value_mode, void* stream);
+                           const b200pf_bf16* w_pg, const b200pf_plane_out* a_out,
+                           const b200pf_plane_out* b_out, int pitch, int rows, int n, int incoming,
+                           int value_mode, void* stream);
 
 /* Operand description for the contraction: element (seg, d, row, col) of an operand lives at
  * ptr[seg*seg_stride + d*plane_stride + row*pitch + col]. */
@@ -151,27 +160,30 @@ int b200pf_trimul_epilogue(float* z, const b200pf_bf16* x, long long x_plane_str
 
 /* Triangle-attention producer: LN -> [q|k|v|g] projection and the 4-head triangle bias.
  * Replaces tt_bio/tenstorrent.py:545-567, 603-614 (reference.py:331-341, 99-120).
+ *   z is viewed as [rows][n][128] (a row shard, or a column shard stored [i][j_local][128]);
  *   w_qkvg: bf16 [528][128] = q rows (scaled by log2(e)/sqrt(32)), k, v, g rows, the 4 bias rows
  *           (scaled by log2(e)), 12 zero rows;  bias_qkvg: fp32 [528].
- * Outputs (bf16):
- *   q,k,v: [line][head][pos][32] where (line,pos) = (i,j) for the starting node and (j,i) for
- *          the ending node;
- *   g:     sigmoid(gate) in z layout [i][j][128];
- *   tri_bias: [head][q][k], row pitch bias_pitch, head stride bias_hs (elements);
- *          starting: (q,k) = (i,j); ending: (q,k) = (j,i). */
+ * A "line" is a row of the view (ending == 0, positions = its n columns) or a column of the view
+ * (ending != 0, positions = its `rows` rows).  Outputs (bf16):
+ *   q,k,v: [line][head][pos][32];
+ *   g:     sigmoid(gate) in the layout of the view, [rows][n][128];
+ *   tri_bias: element (head, line, pos) at tri_bias[head*bias_hs + line*bias_qs + pos]: the bias
+ *          of query `line` and key `pos` (for the ending node that is beta[row pos][col line]). */
 int b200pf_triatt_producer(const float* z, const b200pf_bf16* w_qkvg, const float* bias_qkvg,
                            b200pf_bf16* q, b200pf_bf16* k, b200pf_bf16* v, b200pf_bf16* g,
-                           b200pf_bf16* tri_bias, long long bias_hs, int bias_pitch,
+                           b200pf_bf16* tri_bias, long long bias_hs, long long bias_qs,
                            int rows, int n, int ending, void* stream);
 
 /* Fused flash-style triangle attention: for each line and head, softmax(q k^T + mask + bias) v
  * with online softmax in the log2 domain; logits never leave the SM.  Replaces the SDPA call at
  * tt_bio/tenstorrent.py:569-572 (reference.py:343-360, boltz2.py:790-810).
- *   mask byte for (line, key) = mask[line*mask_ls + key*mask_ks]; masked keys get -1e9.
- *   o is written in z layout: element (line, pos, c) at o[line*o_line_stride + pos*o_pos_stride + c].
+ *   n = queries = keys per line; q,k,v as written by the producer ([line][head][n][32]);
+ *   bias element (head, query, key) at bias[head*bias_hs + query*bias_qs + key], key < bias_cols;
+ *   mask byte for (line, key) = mask[line*mask_ls + key*mask_ks]; masked keys get -1e9;
+ *   o element (line, pos, c) at o[line*o_line_stride + pos*o_pos_stride + c];
  *   lines_per_cta: 1, 2 or 4 lines share one fetch of each bias tile (0 = default). */
 int b200pf_triatt_core(const b200pf_bf16* q, const b200pf_bf16* k, const b200pf_bf16* v,
-                       const b200pf_bf16* bias, long long bias_hs, int bias_pitch,
+                       const b200pf_bf16* bias, long long bias_hs, long long bias_qs, int bias_cols,
                        const uint8_t* mask, long long mask_ls, long long mask_ks,
                        b200pf_bf16* o, long long o_line_stride, long long o_pos_stride,
                        int lines, int n, int lines_per_cta, void* stream);

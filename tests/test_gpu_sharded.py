@@ -1,0 +1,72 @@
+"""Row-sharded trunk on 2 (or 4) GPUs over NCCL against the CPU oracle.  Skipped with one GPU."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import pairformer_oracle as orc
+from tt_boltz_b200 import synthetic
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as sk:
+        sk.bind(("127.0.0.1", 0))
+        return sk.getsockname()[1]
+
+
+def _worker(rank, world, port, n, blocks, out_q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from tt_boltz_b200 import _lib
+        from tt_boltz_b200.sharded import ShardedPairformerModule
+        sd = synthetic.make_weights(blocks, seed=1, std=0.05, affine_jitter=0.2)
+        s, z = synthetic.make_inputs(n, seed=0)
+        m, pm = synthetic.tail_padding_mask(n, 13)
+        mod = ShardedPairformerModule(384, 128, blocks, v2=True)
+        mod.load_state_dict(sd, strict=True)
+        so, zo = mod(s.to(dev), z.to(dev), m.to(dev), pm.to(dev))
+        torch.cuda.synchronize()
+        status = _lib.device_status()
+        out_q.put((rank, so.cpu(), zo.cpu() if rank == 0 else None, status, None))
+    except Exception as e:  # noqa: BLE001
+        out_q.put((rank, None, None, -1, repr(e)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_sharded_trunk_matches_oracle(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    n, blocks = 128 * world, 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, n, blocks, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = sorted((q.get(timeout=600) for _ in procs), key=lambda t: t[0])
+    for p in procs:
+        p.join(timeout=60)
+    for rank, so, zo, status, err in res:
+        assert err is None, f"rank {rank}: {err}"
+        assert status == 0
+    sd = synthetic.make_weights(blocks, seed=1, std=0.05, affine_jitter=0.2)
+    s, z = synthetic.make_inputs(n, seed=0)
+    m, pm = synthetic.tail_padding_mask(n, 13)
+    with torch.no_grad():
+        sr, zr = orc.pairformer_stack(s[0], z[0], m[0], pm[0], sd, blocks)
+    v = n - 13
+    zo, so = res[0][2][0], res[0][1][0]
+    assert float((zo[:v, :v] - zr[:v, :v]).norm() / zr[:v, :v].norm()) < 2e-2
+    assert float((so[:v] - sr[:v]).norm() / sr[:v].norm()) < 2e-2
+    for rank, so_r, _, _, _ in res[1:]:
+        assert torch.equal(so_r[0], so), "s must stay replicated bit for bit"

@@ -143,7 +143,11 @@ struct AttnArgs {
     float scale, inf_value;
 };
 
+template <int HD>
 __global__ void f32_attention_kernel(AttnArgs p) {
+    // One warp per (batch row r, head h, query q).  Lanes split the keys in all three passes:
+    // logits -> shared memory, exponentials, then each lane accumulates its keys' share of the
+    // output vector in registers and the warp reduces the HD partial sums with shuffles.
     extern __shared__ float smem[];
     int wid = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     float* logit = smem + (size_t)wid * p.n_k;
@@ -152,12 +156,22 @@ __global__ void f32_attention_kernel(AttnArgs p) {
         int qi = (int)(w % p.n_q);
         int h = (int)((w / p.n_q) % p.heads);
         long long r = w / ((long long)p.n_q * p.heads);
-        const float* qp = p.q + r * p.rs + (long long)qi * p.ps + h * p.hd;
+        const float* qp = p.q + r * p.rs + (long long)qi * p.ps + h * HD;
+        float qv[HD];
+#pragma unroll
+        for (int e = 0; e < HD; ++e) qv[e] = qp[e] * p.scale;
         float mx = -INFINITY;
         for (int kk = lane; kk < p.n_k; kk += 32) {
-            const float* kp = p.k + r * p.rs + (long long)kk * p.ps + h * p.hd;
+            const float4* kp = reinterpret_cast<const float4*>(p.k + r * p.rs + (long long)kk * p.ps + h * HD);
             float dot = 0.f;
-            for (int e = 0; e < p.hd; ++e) dot = fmaf(qp[e] * p.scale, kp[e], dot);
+#pragma unroll
+            for (int e4 = 0; e4 < HD / 4; ++e4) {
+                float4 kv = kp[e4];
+                dot = fmaf(qv[e4 * 4], kv.x, dot);
+                dot = fmaf(qv[e4 * 4 + 1], kv.y, dot);
+                dot = fmaf(qv[e4 * 4 + 2], kv.z, dot);
+                dot = fmaf(qv[e4 * 4 + 3], kv.w, dot);
+            }
             float mterm = 0.f;
             if (p.mask) mterm = -p.inf_value * (1.f - (float)p.mask[r * p.mask_rs + kk * p.mask_ks]);
             float bterm = p.bias ? p.bias[h * p.bias_hs + qi * p.bias_qs + kk * p.bias_ks] : 0.f;
@@ -167,21 +181,30 @@ __global__ void f32_attention_kernel(AttnArgs p) {
         }
         mx = warp_max(mx);
         float sum = 0.f;
+        float acc[HD];
+#pragma unroll
+        for (int e = 0; e < HD; ++e) acc[e] = 0.f;
         for (int kk = lane; kk < p.n_k; kk += 32) {
-            float e = expf(logit[kk] - mx);
-            logit[kk] = e;
-            sum += e;
+            float pe = expf(logit[kk] - mx);
+            sum += pe;
+            const float4* vp = reinterpret_cast<const float4*>(p.v + r * p.rs + (long long)kk * p.ps + h * HD);
+#pragma unroll
+            for (int e4 = 0; e4 < HD / 4; ++e4) {
+                float4 vv = vp[e4];
+                acc[e4 * 4] = fmaf(pe, vv.x, acc[e4 * 4]);
+                acc[e4 * 4 + 1] = fmaf(pe, vv.y, acc[e4 * 4 + 1]);
+                acc[e4 * 4 + 2] = fmaf(pe, vv.z, acc[e4 * 4 + 2]);
+                acc[e4 * 4 + 3] = fmaf(pe, vv.w, acc[e4 * 4 + 3]);
+            }
         }
-        sum = warp_sum(sum);
-        __syncwarp();
-        float inv = 1.f / sum;
-        for (int e = lane; e < p.hd; e += 32) {
-            float acc = 0.f;
-            const float* vp = p.v + r * p.rs + h * p.hd + e;
-            for (int kk = 0; kk < p.n_k; ++kk) acc = fmaf(logit[kk], vp[(long long)kk * p.ps], acc);
-            p.o[r * p.rs + (long long)qi * p.ps + h * p.hd + e] = acc * inv;
+        float inv = 1.f / warp_sum(sum);
+        float mine = 0.f;
+#pragma unroll
+        for (int e = 0; e < HD; ++e) {
+            float tot = warp_sum(acc[e]);
+            if (lane == e) mine = tot;
         }
-        __syncwarp();
+        if (lane < HD) p.o[r * p.rs + (long long)qi * p.ps + h * HD + lane] = mine * inv;
     }
 }
 
@@ -205,43 +228,91 @@ template <int HEADS>
 __global__ void __launch_bounds__(256)
 ln_proj_heads_kernel(const float* __restrict__ z, const float* __restrict__ gamma, const float* __restrict__ beta,
                      const float* __restrict__ w, float* __restrict__ out, long long out_hs, long long rows) {
+    // 8 lanes per row (16 channels each), 4 rows per pass, 32 rows per warp unit.  Head sums are
+    // reduced over the 8 lanes with a halving butterfly (HEADS -> HEADS/8 values per lane), staged
+    // in shared memory as [head][row] and written as 128-byte runs along the row index.
     constexpr int C = 128;
-    __shared__ float ws[HEADS][C];
-    __shared__ float cs[HEADS];            // sum_c beta[c]*w[h][c]
+    constexpr int PER = HEADS >= 8 ? HEADS / 8 : 1;      // heads a lane ends up owning
+    __shared__ float ws[HEADS][C + 4];
+    __shared__ float cs[HEADS];
+    __shared__ float stage[8][HEADS][32 + 1];
     for (int i = threadIdx.x; i < HEADS * C; i += blockDim.x) ws[i / C][i % C] = w[i] * gamma[i % C];
-    __syncthreads();
     if (threadIdx.x < HEADS) {
-        float s = 0.f;
-        for (int c = 0; c < C; ++c) s += w[threadIdx.x * C + c] * beta[c];
-        cs[threadIdx.x] = s;
+        float sacc = 0.f;
+        for (int c = 0; c < C; ++c) sacc += w[threadIdx.x * C + c] * beta[c];
+        cs[threadIdx.x] = sacc;
     }
     __syncthreads();
-    int lane = threadIdx.x & 31;
-    long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, sub = lane & 7, rq = lane >> 3;
+    long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + wid;
     long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
     for (long long base = warp * 32; base < rows; base += nwarps * 32) {
-        float res[HEADS];
+#pragma unroll 2
+        for (int it = 0; it < 8; ++it) {
+            long long row = base + it * 4 + rq;
+            float4 v[4];
 #pragma unroll
-        for (int h = 0; h < HEADS; ++h) res[h] = 0.f;
-        int cnt = (int)min((long long)32, rows - base);
-        for (int rr = 0; rr < cnt; ++rr) {
-            float4 xv = reinterpret_cast<const float4*>(z + (base + rr) * C)[lane];
-            float mean = warp_sum(xv.x + xv.y + xv.z + xv.w) * (1.f / C);
-            float d0 = xv.x - mean, d1 = xv.y - mean, d2 = xv.z - mean, d3 = xv.w - mean;
-            float rstd = rsqrtf(warp_sum(d0 * d0 + d1 * d1 + d2 * d2 + d3 * d3) * (1.f / C) + LN_EPS);
-            d0 *= rstd; d1 *= rstd; d2 *= rstd; d3 *= rstd;
+            for (int j = 0; j < 4; ++j)
+                v[j] = row < rows ? __ldg(reinterpret_cast<const float4*>(z + row * C) + j * 8 + sub) : make_float4(0.f, 0.f, 0.f, 0.f);
+            float sm = 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) sm += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+            sm += __shfl_xor_sync(0xffffffffu, sm, 1);
+            sm += __shfl_xor_sync(0xffffffffu, sm, 2);
+            sm += __shfl_xor_sync(0xffffffffu, sm, 4);
+            float mean = sm * (1.f / C), ss = 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                v[j].x -= mean; v[j].y -= mean; v[j].z -= mean; v[j].w -= mean;
+                ss += (v[j].x * v[j].x + v[j].y * v[j].y) + (v[j].z * v[j].z + v[j].w * v[j].w);
+            }
+            ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+            ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+            ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+            float rstd = rsqrtf(ss * (1.f / C) + LN_EPS);
+            float part[HEADS];
 #pragma unroll
             for (int h = 0; h < HEADS; ++h) {
-                const float* wr = &ws[h][lane * 4];
-                float pth = d0 * wr[0] + d1 * wr[1] + d2 * wr[2] + d3 * wr[3];
-                pth = warp_sum(pth) + cs[h];
-                if (lane == rr) res[h] = pth;
+                float a = 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float* wr = &ws[h][(j * 8 + sub) * 4];
+                    a += v[j].x * wr[0] + v[j].y * wr[1] + v[j].z * wr[2] + v[j].w * wr[3];
+                }
+                part[h] = a * rstd;
+            }
+            if (HEADS >= 8) {
+                // butterfly over lane bits 2, 1, 0: keep the half of the heads selected by the lane bit
+#pragma unroll
+                for (int step = 0; step < 3; ++step) {
+                    const int bit = 4 >> step, half = HEADS >> (step + 1);
+                    const bool upper = (sub & bit) != 0;
+#pragma unroll
+                    for (int h = 0; h < half; ++h) {
+                        float keep = upper ? part[h + half] : part[h];
+                        float send = upper ? part[h] : part[h + half];
+                        part[h] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
+                    }
+                }
+                // lane `sub` now owns heads: bits of sub select halves: head index = sub_bits-weighted
+                int hbase = ((sub >> 2) & 1) * (HEADS / 2) + ((sub >> 1) & 1) * (HEADS / 4) + (sub & 1) * (HEADS / 8);
+#pragma unroll
+                for (int h = 0; h < PER; ++h) stage[wid][hbase + h][it * 4 + rq] = part[h] + cs[hbase + h];
+            } else {
+#pragma unroll
+                for (int h = 0; h < HEADS; ++h) {
+                    float tsum = part[h];
+                    tsum += __shfl_xor_sync(0xffffffffu, tsum, 1);
+                    tsum += __shfl_xor_sync(0xffffffffu, tsum, 2);
+                    tsum += __shfl_xor_sync(0xffffffffu, tsum, 4);
+                    if (sub == h) stage[wid][h][it * 4 + rq] = tsum + cs[h];
+                }
             }
         }
-        if (lane < cnt) {
-#pragma unroll
-            for (int h = 0; h < HEADS; ++h) out[h * out_hs + base + lane] = res[h];
-        }
+        __syncwarp();
+        for (int h = 0; h < HEADS; ++h)
+            if (base + lane < rows) out[h * out_hs + base + lane] = stage[wid][h][lane];
+        __syncwarp();
     }
 }
 
@@ -309,11 +380,15 @@ int b200pf_f32_attention(const float* q, const float* k, const float* v, float* 
     int warps = 8;
     size_t smem = (size_t)warps * n_k * sizeof(float);
     B200PF_REQUIRE(smem <= 200 * 1024, B200PF_ERR_UNSUPPORTED, "f32_attention: n_k too large (%d)", n_k);
+    B200PF_REQUIRE(hd == 24 || hd == 32, B200PF_ERR_UNSUPPORTED, "f32_attention: head dim must be 24 or 32 (got %d)", hd);
+    B200PF_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && rs % 4 == 0 && ps % 4 == 0, B200PF_ERR_INVALID,
+                   "f32_attention: q/k/v must be 16-byte aligned with strides that are multiples of 4");
+    auto kern = hd == 24 ? f32_attention_kernel<24> : f32_attention_kernel<32>;
     if (smem > 48 * 1024)
-        B200PF_CUDA(cudaFuncSetAttribute(f32_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        B200PF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     long long total = (long long)batch * heads * n_q;
     unsigned blocks = (unsigned)min((long long)148 * 8, (total + warps - 1) / warps);
-    f32_attention_kernel<<<blocks, warps * 32, smem, (cudaStream_t)stream>>>(p);
+    kern<<<blocks, warps * 32, smem, (cudaStream_t)stream>>>(p);
     B200PF_LAUNCH_CHECK();
     return B200PF_OK;
 }

@@ -24,8 +24,8 @@ struct AttCoreArgs {
     const __nv_bfloat16 *q, *k, *v, *bias;
     const uint8_t* mask;
     __nv_bfloat16* o;
-    long long mask_ls, mask_ks, o_ls, o_ps, bias_hs;
-    int bias_pitch, lines, n;
+    long long mask_ls, mask_ks, o_ls, o_ps, bias_hs, bias_qs;
+    int bias_cols, lines, n;
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -75,8 +75,8 @@ __global__ void __launch_bounds__(256) triatt_core_kernel(AttCoreArgs p) {
         for (int i = 0; i < 4; ++i) {
             int idx = tid + i * 256, row = idx >> 3, c = idx & 7;
             int qrow = q0 + row, col = k0 + c * 8;
-            bool ok = qrow < n && col + 8 <= p.bias_pitch;
-            const __nv_bfloat16* src = p.bias + h * p.bias_hs + (long long)(ok ? qrow : 0) * p.bias_pitch + (ok ? col : 0);
+            bool ok = qrow < n && col + 8 <= p.bias_cols;
+            const __nv_bfloat16* src = p.bias + h * p.bias_hs + (long long)(ok ? qrow : 0) * p.bias_qs + (ok ? col : 0);
             cp_async16_zfill(st + bias_off(row, c), src, ok);
         }
         // K and V tiles: 64 rows x 4 chunks per line = one chunk per thread per operand
@@ -279,17 +279,17 @@ static int launch_core(const AttCoreArgs& p, cudaStream_t st) {
 using namespace b200pf;
 
 extern "C" int b200pf_triatt_core(const b200pf_bf16* q, const b200pf_bf16* k, const b200pf_bf16* v,
-                                  const b200pf_bf16* bias, long long bias_hs, int bias_pitch,
+                                  const b200pf_bf16* bias, long long bias_hs, long long bias_qs, int bias_cols,
                                   const uint8_t* mask, long long mask_ls, long long mask_ks,
                                   b200pf_bf16* o, long long o_line_stride, long long o_pos_stride,
                                   int lines, int n, int lines_per_cta, void* stream) {
     B200PF_REQUIRE(q && k && v && bias && mask && o && lines > 0 && n > 0, B200PF_ERR_INVALID, "triatt_core: bad argument");
     B200PF_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(bias) && aligned16(o), B200PF_ERR_INVALID,
                    "triatt_core: pointers must be 16-byte aligned");
-    B200PF_REQUIRE(bias_pitch % 8 == 0 && bias_pitch >= n && bias_hs % 8 == 0 && o_line_stride % 8 == 0 && o_pos_stride % 8 == 0,
+    B200PF_REQUIRE(bias_cols % 8 == 0 && bias_cols >= n && bias_hs % 8 == 0 && bias_qs % 8 == 0 && o_line_stride % 8 == 0 && o_pos_stride % 8 == 0,
                    B200PF_ERR_INVALID, "triatt_core: strides must be multiples of 8 elements");
     AttCoreArgs p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (const __nv_bfloat16*)bias,
-                  mask, (__nv_bfloat16*)o, mask_ls, mask_ks, o_line_stride, o_pos_stride, bias_hs, bias_pitch, lines, n};
+                  mask, (__nv_bfloat16*)o, mask_ls, mask_ks, o_line_stride, o_pos_stride, bias_hs, bias_qs, bias_cols, lines, n};
     cudaStream_t st = (cudaStream_t)stream;
     switch (lines_per_cta) {
         case 1: return launch_core<1>(p, st);

@@ -19,8 +19,8 @@ struct AttProducerArgs {
     const __nv_bfloat16* w;
     const float* wbias;
     __nv_bfloat16 *q, *k, *v, *g, *tri_bias;
-    long long bias_hs;
-    int bias_pitch, rows, n, ending;
+    long long bias_hs, bias_qs;
+    int rows, n, ending;              // z viewed as [rows][n][128]
 };
 
 __global__ void __launch_bounds__(WARPS * 32, 1) triatt_producer_kernel(AttProducerArgs p) {
@@ -35,7 +35,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) triatt_producer_kernel(AttProdu
     __syncthreads();
     const uint32_t w_addr = smem_u32(w_s), tile_addr = smem_u32(tile);
     const int n = p.n;
-    const int span = p.ending ? p.rows : n;
+    const int span = p.ending ? p.rows : n;          // positions along a line
     const int upl = (span + UNIT - 1) / UNIT;
     const long long units = (long long)(p.ending ? n : p.rows) * upl;
     const int g = lane >> 2, t = lane & 3;
@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) triatt_producer_kernel(AttProdu
                 } else {
                     __nv_bfloat16* dst = c < 2 ? p.q : (c < 4 ? p.k : p.v);
                     int head = (c & 1) * 2 + (piece >> 2);
-                    *reinterpret_cast<uint4*>(dst + (((long long)line * 4 + head) * n + pos0 + l) * 32 + (piece & 3) * 8) = v;
+                    *reinterpret_cast<uint4*>(dst + (((long long)line * 4 + head) * span + pos0 + l) * 32 + (piece & 3) * 8) = v;
                 }
             }
             __syncwarp();
@@ -104,7 +104,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) triatt_producer_kernel(AttProdu
 #pragma unroll
                         for (int e = 0; e < 2; ++e) {
                             int h = 2 * t + e;
-                            p.tri_bias[h * p.bias_hs + (long long)line * p.bias_pitch + pos0 + l] =
+                            p.tri_bias[h * p.bias_hs + (long long)line * p.bias_qs + pos0 + l] =
                                 __float2bfloat16(acc[mi][0][hh * 2 + e] + bias_s[512 + h]);
                         }
                     }
@@ -203,16 +203,15 @@ using namespace b200pf;
 
 extern "C" int b200pf_triatt_producer(const float* z, const b200pf_bf16* w_qkvg, const float* bias_qkvg,
                                       b200pf_bf16* q, b200pf_bf16* k, b200pf_bf16* v, b200pf_bf16* g,
-                                      b200pf_bf16* tri_bias, long long bias_hs, int bias_pitch,
+                                      b200pf_bf16* tri_bias, long long bias_hs, long long bias_qs,
                                       int rows, int n, int ending, void* stream) {
     B200PF_REQUIRE(z && w_qkvg && bias_qkvg && q && k && v && g && tri_bias, B200PF_ERR_INVALID, "triatt_producer: null pointer");
-    B200PF_REQUIRE(rows > 0 && n > 0 && rows <= n, B200PF_ERR_INVALID, "triatt_producer: bad rows/n");
-    B200PF_REQUIRE(bias_pitch >= n && bias_hs >= (long long)bias_pitch * n, B200PF_ERR_INVALID, "triatt_producer: bad bias pitch / head stride");
-    B200PF_REQUIRE(!ending || rows == n, B200PF_ERR_UNSUPPORTED, "triatt_producer: the ending node needs all rows locally");
+    B200PF_REQUIRE(rows > 0 && n > 0, B200PF_ERR_INVALID, "triatt_producer: bad rows/n");
+    B200PF_REQUIRE(bias_hs > 0 && bias_qs > 0, B200PF_ERR_INVALID, "triatt_producer: bad bias strides");
     B200PF_REQUIRE(aligned16(z) && aligned16(w_qkvg) && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(g),
                    B200PF_ERR_INVALID, "triatt_producer: pointers must be 16-byte aligned");
     AttProducerArgs p{z, (const __nv_bfloat16*)w_qkvg, bias_qkvg, (__nv_bfloat16*)q, (__nv_bfloat16*)k,
-                      (__nv_bfloat16*)v, (__nv_bfloat16*)g, (__nv_bfloat16*)tri_bias, bias_hs, bias_pitch, rows, n, ending};
+                      (__nv_bfloat16*)v, (__nv_bfloat16*)g, (__nv_bfloat16*)tri_bias, bias_hs, bias_qs, rows, n, ending};
     B200PF_CUDA(cudaFuncSetAttribute(triatt_producer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_PRODUCER_SMEM));
     int span = ending ? rows : n;
     long long units = (long long)(ending ? n : rows) * ((span + UNIT - 1) / UNIT);

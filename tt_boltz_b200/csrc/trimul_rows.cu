@@ -18,9 +18,10 @@ struct ProducerArgs {
     const uint8_t* mask;
     const __nv_bfloat16* w_pg;
     const float* bias_pg;
-    __nv_bfloat16* a_planes;
-    __nv_bfloat16* b_planes;
-    long long plane_stride;
+    __nv_bfloat16* planes[2];        // a, b
+    long long plane_stride[2];       // elements between channels
+    long long group_stride[2];       // elements between groups of plane rows
+    int row_group[2];                // plane rows per group (>= plane rows when ungrouped)
     int pitch, rows, n, incoming;
 };
 
@@ -82,14 +83,18 @@ __global__ void __launch_bounds__(WARPS * 32, 1) trimul_producer_kernel(Producer
                         stage[col * STAGE_PITCH + mi * 16 + g + (e >> 1) * 8] = __float2bfloat16(uv);
                     }
             __syncwarp();
-            __nv_bfloat16* planes = (q < 4 ? p.a_planes : p.b_planes) + (long long)((q & 3) * 32) * p.plane_stride;
+            const int op = q >> 2;
+            const long long ps = p.plane_stride[op];
+            __nv_bfloat16* planes = p.planes[op] + (long long)((q & 3) * 32) * ps +
+                                    (long long)(line / p.row_group[op]) * p.group_stride[op] +
+                                    (long long)(line % p.row_group[op]) * p.pitch;
 #pragma unroll
             for (int pass = 0; pass < 4; ++pass) {
                 int ch = pass * 8 + (lane >> 2), piece = lane & 3;
                 int col = pos0 + piece * 8;
                 if (col + 8 <= p.pitch) {
                     uint4 v = *reinterpret_cast<const uint4*>(stage + ch * STAGE_PITCH + piece * 8);
-                    *reinterpret_cast<uint4*>(planes + ch * p.plane_stride + (long long)line * p.pitch + col) = v;
+                    *reinterpret_cast<uint4*>(planes + ch * ps + col) = v;
                 }
             }
             __syncwarp();
@@ -224,20 +229,31 @@ static int grid_for(long long units) {
 using namespace b200pf;
 
 extern "C" int b200pf_trimul_producer(const float* z, const uint8_t* mask, const float* bias_pg,
-                                      const b200pf_bf16* w_pg, void* a_planes, void* b_planes,
-                                      void* a_scales, void* b_scales, long long plane_stride, int pitch,
-                                      int rows, int n, int incoming, int value_mode, void* stream) {
-    (void)a_scales; (void)b_scales;
-    B200PF_REQUIRE(z && mask && bias_pg && w_pg && a_planes && b_planes, B200PF_ERR_INVALID, "trimul_producer: null pointer");
+                                      const b200pf_bf16* w_pg, const b200pf_plane_out* a_out,
+                                      const b200pf_plane_out* b_out, int pitch, int rows, int n, int incoming,
+                                      int value_mode, void* stream) {
+    B200PF_REQUIRE(z && mask && bias_pg && w_pg && a_out && b_out && a_out->ptr && b_out->ptr, B200PF_ERR_INVALID,
+                   "trimul_producer: null pointer");
     B200PF_REQUIRE(rows > 0 && n > 0 && rows <= n, B200PF_ERR_INVALID, "trimul_producer: bad rows/n");
     B200PF_REQUIRE(value_mode == 0, B200PF_ERR_UNSUPPORTED, "trimul_producer: value mode %d is not built", value_mode);
     int cols = incoming ? rows : n, prow = incoming ? n : rows;
-    B200PF_REQUIRE(pitch % 8 == 0 && pitch >= cols && plane_stride >= (long long)pitch * prow && plane_stride % 8 == 0,
-                   B200PF_ERR_INVALID, "trimul_producer: bad pitch / plane stride");
-    B200PF_REQUIRE(aligned16(z) && aligned16(w_pg) && aligned16(a_planes) && aligned16(b_planes), B200PF_ERR_INVALID,
-                   "trimul_producer: pointers must be 16-byte aligned");
-    ProducerArgs p{z, mask, (const __nv_bfloat16*)w_pg, bias_pg, (__nv_bfloat16*)a_planes, (__nv_bfloat16*)b_planes,
-                   plane_stride, pitch, rows, n, incoming};
+    B200PF_REQUIRE(pitch % 8 == 0 && pitch >= cols, B200PF_ERR_INVALID, "trimul_producer: bad pitch");
+    ProducerArgs p;
+    p.z = z; p.mask = mask; p.w_pg = (const __nv_bfloat16*)w_pg; p.bias_pg = bias_pg;
+    const b200pf_plane_out* outs[2] = {a_out, b_out};
+    for (int i = 0; i < 2; ++i) {
+        const b200pf_plane_out* o = outs[i];
+        int rg = o->row_group > 0 ? o->row_group : prow;
+        B200PF_REQUIRE(o->plane_stride % 8 == 0 && o->plane_stride >= (long long)pitch * (rg < prow ? rg : prow),
+                       B200PF_ERR_INVALID, "trimul_producer: bad plane stride");
+        B200PF_REQUIRE(rg >= prow || (o->group_stride % 8 == 0 && o->group_stride > 0), B200PF_ERR_INVALID,
+                       "trimul_producer: bad group stride");
+        B200PF_REQUIRE(aligned16(o->ptr), B200PF_ERR_INVALID, "trimul_producer: planes must be 16-byte aligned");
+        p.planes[i] = (__nv_bfloat16*)o->ptr; p.plane_stride[i] = o->plane_stride;
+        p.group_stride[i] = o->group_stride; p.row_group[i] = rg;
+    }
+    B200PF_REQUIRE(aligned16(z) && aligned16(w_pg), B200PF_ERR_INVALID, "trimul_producer: pointers must be 16-byte aligned");
+    p.pitch = pitch; p.rows = rows; p.n = n; p.incoming = incoming;
     B200PF_CUDA(cudaFuncSetAttribute(trimul_producer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PRODUCER_SMEM));
     int span = incoming ? rows : n;
     long long units = (long long)(incoming ? n : rows) * ((span + UNIT - 1) / UNIT);

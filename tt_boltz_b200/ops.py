@@ -13,7 +13,7 @@ from typing import Dict, Optional
 import torch
 
 from . import _lib
-from ._lib import Planes, call, ptr, stream
+from ._lib import PlaneOut, Planes, call, ptr, stream
 
 C_Z = 128
 
@@ -44,8 +44,10 @@ def tri_mul_bf16(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Tens
     n = z.shape[0]
     a, b, x = ws.buf[0], ws.buf[1], ws.buf[2]
     st = stream()
-    call("b200pf_trimul_producer", ptr(z), ptr(mask_u8), ptr(w["bias_pg"]), ptr(w["w_pg"]), ptr(a), ptr(b),
-         None, None, ws.plane_stride, ws.pitch, n, n, int(incoming), 0, st)
+    oa = PlaneOut(ptr(a), ws.plane_stride, 0, 0)
+    ob = PlaneOut(ptr(b), ws.plane_stride, 0, 0)
+    call("b200pf_trimul_producer", ptr(z), ptr(mask_u8), ptr(w["bias_pg"]), ptr(w["w_pg"]), C.byref(oa), C.byref(ob),
+         ws.pitch, n, n, int(incoming), 0, st)
     pa = Planes(ptr(a), ws.plane_stride, 0, ws.pitch, n, n, 1, 0)
     pb = Planes(ptr(b), ws.plane_stride, 0, ws.pitch, n, n, 1, 0)
     call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), None, None, ptr(x), ws.plane_stride, ws.pitch,
@@ -59,14 +61,14 @@ def tri_att_bf16(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Tens
     n = z.shape[0]
     q, k, v, g, o = ws.buf
     st = stream()
-    bias_hs = n * ws.pitch
+    bias_hs, bias_qs = ws.pitch, 4 * ws.pitch          # layout [query][head][key]: a row shard is contiguous
     call("b200pf_triatt_producer", ptr(z), ptr(w["w_qkvg"]), ptr(w["bias_qkvg"]), ptr(q), ptr(k), ptr(v), ptr(g),
-         ptr(ws.tri_bias), bias_hs, ws.pitch, n, n, int(ending), st)
+         ptr(ws.tri_bias), bias_hs, bias_qs, n, n, int(ending), st)
     if ending:      # line = column j: mask(line, key) = M[key][line]; o element (line, pos) -> z position [pos][line]
         mask_ls, mask_ks, o_ls, o_ps = 1, n, C_Z, n * C_Z
     else:
         mask_ls, mask_ks, o_ls, o_ps = n, 1, n * C_Z, C_Z
-    call("b200pf_triatt_core", ptr(q), ptr(k), ptr(v), ptr(ws.tri_bias), bias_hs, ws.pitch, ptr(mask_u8),
+    call("b200pf_triatt_core", ptr(q), ptr(k), ptr(v), ptr(ws.tri_bias), bias_hs, bias_qs, ws.pitch, ptr(mask_u8),
          mask_ls, mask_ks, ptr(o), o_ls, o_ps, n, n, lines_per_cta, st)
     call("b200pf_triatt_epilogue", ptr(z), ptr(o), ptr(g), ptr(w["w_o"]), n * n, st)
 
