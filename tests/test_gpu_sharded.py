@@ -53,7 +53,7 @@ def test_sharded_trunk_matches_oracle(world):
     procs = [ctx.Process(target=_worker, args=(r, world, port, n, blocks, q)) for r in range(world)]
     for p in procs:
         p.start()
-    res = sorted((q.get(timeout=600) for _ in procs), key=lambda t: t[0])
+    res = sorted((q.get(timeout=150) for _ in procs), key=lambda t: t[0])
     for p in procs:
         p.join(timeout=60)
     for rank, so, zo, status, err in res:

@@ -168,12 +168,12 @@ def transition_f32(x_res: torch.Tensor, w: Dict[str, torch.Tensor]) -> None:
 
 
 def pair_bias_heads(z: torch.Tensor, w: Dict[str, torch.Tensor]) -> torch.Tensor:
-    """bias[h][i*N + j] of the single-track attention: one fp32 pass over z."""
-    n = z.shape[0]
+    """bias[h][i_local*N + j] of the single-track attention: one fp32 pass over the (local rows of) z."""
+    rows = z.shape[0] * z.shape[1]          # z may be a row shard [nr, N, 128]
     heads = w["proj_z.1.weight"].shape[0]
-    bias = torch.empty(heads, n * n, dtype=torch.float32, device=z.device)
+    bias = torch.empty(heads, rows, dtype=torch.float32, device=z.device)
     call("b200pf_ln_proj_heads", ptr(z), ptr(w["proj_z.0.weight"]), ptr(w["proj_z.0.bias"]),
-         ptr(w["proj_z.1.weight"]), ptr(bias), n * n, n * n, C_Z, heads, stream())
+         ptr(w["proj_z.1.weight"]), ptr(bias), rows, rows, C_Z, heads, stream())
     return bias
 
 
