@@ -200,6 +200,27 @@ int b200pf_triatt_epilogue(float* z, const b200pf_bf16* o, const b200pf_bf16* g,
 int b200pf_transition_z(float* z, const b200pf_bf16* w12, const float* bias12,
                         const b200pf_bf16* w3, long long n_rows_flat, void* stream);
 
+/* Triangle multiplication (producer -> contraction -> epilogue, bf16 tier) for callers that cannot
+ * allocate device memory.  No counterpart in the reference.
+ * Why it exists: the three stages pass their a / b / x planes through global memory, which the
+ * caller normally provides.  A host that runs inside a fixed memory budget, inside a callback
+ * where the allocator may not be entered, or in a server that forbids allocation after start-up
+ * has nowhere to get those planes from; here they live in a 12 MiB array that is part of the
+ * library image on every GPU that loads it (held until the process exits).
+ *   - limit: n <= 128 tokens; larger n is refused with B200PF_ERR_UNSUPPORTED and a message;
+ *   - z (fp32 [n][n][128]) is updated in place; mask is [n][n]; weights as for the three stage
+ *     entry points (w_pg [512][128], bias_pg [512], w_pout / w_gout [128][128], bias_* [128]);
+ *   - the call itself never calls cudaMalloc / cudaFree or any allocating routine;
+ *   - the first call on a device looks up the device address of the array
+ *     (cudaGetSymbolAddress); make that first call before starting any stream capture;
+ *   - all calls share the one array and it keeps the previous call's contents.  Nothing in it
+ *     has to start at zero (each stage overwrites everything the next one reads), but two calls
+ *     whose kernels overlap on the GPU (different streams) race on it: serialise them. */
+int b200pf_tri_mul_noalloc(float* z, const uint8_t* mask, const b200pf_bf16* w_pg, const float* bias_pg,
+                           const b200pf_bf16* w_pout, const b200pf_bf16* w_gout,
+                           const float* bias_pout, const float* bias_gout,
+                           int n, int incoming, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
