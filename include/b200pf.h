@@ -107,8 +107,10 @@ int b200pf_ln_proj_heads(const float* z, const float* gamma, const float* beta, 
 /* Triangle-multiplication producer: LN_in -> [p_in | g_in] projection -> p*sigmoid(g) -> mask
  * -> a/b written channel-major.  Replaces tt_bio/tenstorrent.py:410-452 (reference.py:456-464).
  *   z: fp32 [rows][n][128];  mask: [rows][n];
- *   w_pg: bf16 [512][128] in 8 chunks of 64 rows; chunk q = channels 32*(q%4)..+31 of operand a
- *         (q < 4) or b (q >= 4): their 32 p_in rows then their 32 g_in rows;  bias_pg: fp32 [512].
+ *   impl 0 (tcgen05 kernel): w_pg bf16 [512][128] = p_in rows of a, g_in rows of a, p_in rows of b,
+ *         g_in rows of b (128 each);  impl 1 (mma.sync cross-check): 8 chunks of 64 rows, chunk q =
+ *         channels 32*(q%4)..+31 of operand a (q < 4) or b (q >= 4): 32 p_in rows then 32 g_in rows;
+ *         bias_pg: fp32 [512] in the same order as w_pg.
  *   incoming == 0: a[d][r][k] = u_a[r][k][d]  (plane rows = local z rows, cols = k)
  *   incoming != 0: a[d][c][r] = u_a[r][c][d]  (plane rows = z columns, cols = local z rows)
  *   value_mode 0 = bf16 planes (the only mode built so far). */
@@ -124,7 +126,7 @@ typedef struct b200pf_plane_out {
 int b200pf_trimul_producer(const float* z, const uint8_t* mask, const float* bias_pg,
                            const b200pf_bf16* w_pg, const b200pf_plane_out* a_out,
                            const b200pf_plane_out* b_out, int pitch, int rows, int n, int incoming,
-                           int value_mode, void* stream);
+                           int value_mode, int impl, void* stream);
 
 /* Operand description for the contraction: element (seg, d, row, col) of an operand lives at
  * ptr[seg*seg_stride + d*plane_stride + row*pitch + col]. */
@@ -165,14 +167,16 @@ int b200pf_trimul_epilogue(float* z, const b200pf_bf16* x, long long x_plane_str
  *           (scaled by log2(e)), 12 zero rows;  bias_qkvg: fp32 [528].
  * A "line" is a row of the view (ending == 0, positions = its n columns) or a column of the view
  * (ending != 0, positions = its `rows` rows).  Outputs (bf16):
- *   q,k,v: [line][head][pos][32];
+ *   q,k: [line][head][pos][32];  v: the same when vt_pitch == 0, else transposed
+ *          [line][head][32][vt_pitch] (positions contiguous) as the tcgen05 attention core reads it;
  *   g:     sigmoid(gate) in the layout of the view, [rows][n][128];
  *   tri_bias: element (head, line, pos) at tri_bias[head*bias_hs + line*bias_qs + pos]: the bias
- *          of query `line` and key `pos` (for the ending node that is beta[row pos][col line]). */
+ *          of query `line` and key `pos` (for the ending node that is beta[row pos][col line]);
+ *   impl: 0 = tcgen05 kernel, 1 = mma.sync cross-check (same weights for both). */
 int b200pf_triatt_producer(const float* z, const b200pf_bf16* w_qkvg, const float* bias_qkvg,
                            b200pf_bf16* q, b200pf_bf16* k, b200pf_bf16* v, b200pf_bf16* g,
                            b200pf_bf16* tri_bias, long long bias_hs, long long bias_qs,
-                           int rows, int n, int ending, void* stream);
+                           int vt_pitch, int rows, int n, int ending, int impl, void* stream);
 
 /* Fused flash-style triangle attention: for each line and head, softmax(q k^T + mask + bias) v
  * with online softmax in the log2 domain; logits never leave the SM.  Replaces the SDPA call at
@@ -187,6 +191,18 @@ int b200pf_triatt_core(const b200pf_bf16* q, const b200pf_bf16* k, const b200pf_
                        const uint8_t* mask, long long mask_ls, long long mask_ks,
                        b200pf_bf16* o, long long o_line_stride, long long o_pos_stride,
                        int lines, int n, int lines_per_cta, void* stream);
+
+/* The same attention on tcgen05 / TMEM (the production core; b200pf_triatt_core is the mma.sync
+ * cross-check).  S = Q K^T and O = P V run as tcgen05.mma with accumulators in TMEM, operands come
+ * in by TMA, the bias tile is fetched once for two lines, softmax runs one thread per query row.
+ *   vt: v transposed [line][head][32][vt_pitch];  bias as above with bias_cols == n;
+ *   mask_lines: uint8 [lines][mask_pitch] (1 = attend), one contiguous row per line, mask_pitch a
+ *   multiple of 16 covering n rounded up to 64 (the host transposes the mask for the ending node). */
+int b200pf_triatt_core_tc(const b200pf_bf16* q, const b200pf_bf16* k, const b200pf_bf16* vt, int vt_pitch,
+                          const b200pf_bf16* bias, long long bias_hs, long long bias_qs,
+                          const uint8_t* mask_lines, int mask_pitch,
+                          b200pf_bf16* o, long long o_line_stride, long long o_pos_stride,
+                          int lines, int n, void* stream);
 
 /* Triangle-attention epilogue: z += (o * g) W_o^T  (g already passed through the sigmoid).
  * Replaces tt_bio/tenstorrent.py:580-591 and the residual :1013-1021 (reference.py:122-136). */
@@ -209,7 +225,7 @@ int b200pf_transition_z(float* z, const b200pf_bf16* w12, const float* bias12,
  * library image on every GPU that loads it (held until the process exits).
  *   - limit: n <= 128 tokens; larger n is refused with B200PF_ERR_UNSUPPORTED and a message;
  *   - z (fp32 [n][n][128]) is updated in place; mask is [n][n]; weights as for the three stage
- *     entry points (w_pg [512][128], bias_pg [512], w_pout / w_gout [128][128], bias_* [128]);
+ *     entry points with impl 0 (w_pg [512][128], bias_pg [512], w_pout / w_gout [128][128], bias_* [128]);
  *   - the call itself never calls cudaMalloc / cudaFree or any allocating routine;
  *   - the first call on a device looks up the device address of the array
  *     (cudaGetSymbolAddress); make that first call before starting any stream capture;

@@ -106,9 +106,9 @@ def test_sub_operations_bf16(dev, n):
          lambda zc: orc.tri_mul(zc, sd, "tri_mul_out", pm, False)),
         ("tri_mul_in", lambda zz: ops.tri_mul_bf16(zz, pm_u8, weights.pack_trimul(sd, "tri_mul_in.", dev), ws, True),
          lambda zc: orc.tri_mul(zc, sd, "tri_mul_in", pm, True)),
-        ("tri_att_start", lambda zz: ops.tri_att_bf16(zz, pm_u8, weights.pack_triatt(sd, "tri_att_start.", dev), ws, False),
+        ("tri_att_start", lambda zz: ops.tri_att_bf16(zz, ops.PairMasks(pm_u8), weights.pack_triatt(sd, "tri_att_start.", dev), ws, False),
          lambda zc: orc.tri_att(zc, sd, "tri_att_start", pm, False)),
-        ("tri_att_end", lambda zz: ops.tri_att_bf16(zz, pm_u8, weights.pack_triatt(sd, "tri_att_end.", dev), ws, True),
+        ("tri_att_end", lambda zz: ops.tri_att_bf16(zz, ops.PairMasks(pm_u8), weights.pack_triatt(sd, "tri_att_end.", dev), ws, True),
          lambda zc: orc.tri_att(zc, sd, "tri_att_end", pm, True)),
         ("transition_z", lambda zz: ops.transition_z_bf16(zz, weights.pack_transition_z(sd, "transition_z.", dev)),
          lambda zc: orc.transition(zc, sd, "transition_z")),
@@ -145,6 +145,29 @@ def test_contraction_tcgen05_matches_simt_and_einsum(dev):
         assert rel_l2(outs[0], ref) < 4e-3, n       # bf16 rounding of the stored result
         assert rel_l2(outs[1], ref) < 4e-3, n
         assert rel_l2(outs[0], outs[1]) < 1e-3, n
+
+
+@pytest.mark.parametrize("n", [50, 128, 200])
+def test_attention_tcgen05_core_matches_mma_sync_core(dev, n):
+    """The two attention cores (tcgen05 / TMEM and the mma.sync cross-check) see the same q, k, v, bias."""
+    from tt_boltz_b200 import _lib, ops, weights
+    sd = strip(synthetic.make_weights(1, seed=5, std=0.05, affine_jitter=0.3))
+    _, z = synthetic.make_inputs(n, seed=4, with_s=False)
+    g = torch.Generator().manual_seed(9)
+    pm = (torch.rand(n, n, generator=g) > 0.15).to(torch.uint8)
+    pm[3, :] = 0                       # one fully masked line
+    masks = ops.PairMasks(pm.to(dev))
+    ws = ops.Workspace(n, dev)
+    for ending in (False, True):
+        w = weights.pack_triatt(sd, "tri_att_end." if ending else "tri_att_start.", dev)
+        outs = []
+        for core in (0, 1):
+            zd = z[0].to(dev).clone()
+            ops.tri_att_bf16(zd, masks, w, ws, ending, core)
+            assert _lib.device_status() == 0
+            outs.append((zd.cpu() - z[0]))
+        assert torch.isfinite(outs[0]).all()
+        assert rel_l2(outs[0], outs[1]) < 5e-3, (n, ending)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -223,8 +246,9 @@ def test_cfg3_triatt_start_end_n768(dev):
         pm_u8 = (pm[0] != 0).to(torch.uint8).to(dev)
         ws = ops.Workspace(n, dev)
         zd = z[0].to(dev).clone()
-        ops.tri_att_bf16(zd, pm_u8, weights.pack_triatt(sd, "tri_att_start.", dev), ws, False)
-        ops.tri_att_bf16(zd, pm_u8, weights.pack_triatt(sd, "tri_att_end.", dev), ws, True)
+        masks = ops.PairMasks(pm_u8)
+        ops.tri_att_bf16(zd, masks, weights.pack_triatt(sd, "tri_att_start.", dev), ws, False)
+        ops.tri_att_bf16(zd, masks, weights.pack_triatt(sd, "tri_att_end.", dev), ws, True)
         z1 = z[0] + orc.tri_att(z[0], sd, "tri_att_start", pm[0], False)
         z2 = z1 + orc.tri_att(z1, sd, "tri_att_end", pm[0], True)
         v = n - 32

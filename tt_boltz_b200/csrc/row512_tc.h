@@ -1,0 +1,33 @@
+// Host-side interface of the tcgen05 "128 -> 512" producer kernels (row512_tc.cu).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200pf {
+namespace r512 {
+
+struct Args {
+    const float* z;
+    const uint8_t* mask;               // triangle multiplication: [rows][n]
+    const __nv_bfloat16* w;            // [512][128] packed weights
+    const float* wbias;                // [512] (triangle attention: [528])
+    // triangle-multiplication outputs
+    __nv_bfloat16* planes[2];
+    long long plane_stride[2], group_stride[2];
+    int row_group[2];
+    int pitch;
+    // triangle-attention outputs
+    __nv_bfloat16 *q, *k, *v, *g, *tri_bias;
+    const __nv_bfloat16* w_bias_rows;  // packed rows 512..515 (bf16), applied in fp32
+    long long bias_hs, bias_qs;
+    int vt_pitch;
+    // geometry: z viewed as [rows][n][128]; transposed != 0 walks columns (incoming / ending)
+    int rows, n, transposed;
+};
+
+int launch_trimul(const Args& a, cudaStream_t st);
+int launch_triatt(const Args& a, cudaStream_t st);
+
+}  // namespace r512
+}  // namespace b200pf

@@ -7,11 +7,13 @@
 // Host packing (tt_boltz_b200/weights.py): w_qkvg [528][128] = q (scaled by log2(e)/sqrt(32)),
 // k, v, g rows, then the 4 bias rows (scaled by log2(e)) and 12 zero rows, LN gain folded in;
 // bias_qkvg [528] = the matching LN-offset terms.
+#include "row512_tc.h"
 #include "rowtile.cuh"
 
 namespace b200pf {
 
 constexpr int QKVG_ROWS = 528;
+constexpr int HDIM = 32;
 constexpr int ST_PITCH = 72;     // staging: 64 columns + 8 pad (bf16 elements)
 
 struct AttProducerArgs {
@@ -20,6 +22,7 @@ struct AttProducerArgs {
     const float* wbias;
     __nv_bfloat16 *q, *k, *v, *g, *tri_bias;
     long long bias_hs, bias_qs;
+    int vt_pitch;                     // > 0: v is written transposed, [line][head][32][vt_pitch]
     int rows, n, ending;              // z viewed as [rows][n][128]
 };
 
@@ -73,6 +76,28 @@ __global__ void __launch_bounds__(WARPS * 32, 1) triatt_producer_kernel(AttProdu
                         *reinterpret_cast<uint32_t*>(stage + (mi * 16 + g + hh * 8) * ST_PITCH + col) = pack_bf16x2(v0, v1);
                     }
             __syncwarp();
+            if (p.vt_pitch > 0 && (c == 4 || c == 5)) {
+                // V transposed: for each (head, d) the unit's 32 positions are 64 contiguous bytes
+#pragma unroll
+                for (int pass = 0; pass < 8; ++pass) {
+                    int col = pass * 8 + (lane >> 2), piece = lane & 3;          // col = head_local*32 + d
+                    uint32_t w4[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        int l0 = piece * 8 + e * 2;
+                        uint32_t lo = *reinterpret_cast<const uint16_t*>(stage + l0 * ST_PITCH + col);
+                        uint32_t hi = *reinterpret_cast<const uint16_t*>(stage + (l0 + 1) * ST_PITCH + col);
+                        w4[e] = lo | (hi << 16);
+                    }
+                    int head = (c & 1) * 2 + (col >> 5), dd = col & 31;
+                    int pos = pos0 + piece * 8;
+                    if (pos + 8 <= p.vt_pitch)
+                        *reinterpret_cast<uint4*>(p.v + (((long long)line * 4 + head) * HDIM + dd) * p.vt_pitch + pos) =
+                            make_uint4(w4[0], w4[1], w4[2], w4[3]);
+                }
+                __syncwarp();
+                continue;
+            }
 #pragma unroll
             for (int pass = 0; pass < 8; ++pass) {
                 int l = pass * 4 + (lane >> 3), piece = lane & 7;
@@ -204,14 +229,26 @@ using namespace b200pf;
 extern "C" int b200pf_triatt_producer(const float* z, const b200pf_bf16* w_qkvg, const float* bias_qkvg,
                                       b200pf_bf16* q, b200pf_bf16* k, b200pf_bf16* v, b200pf_bf16* g,
                                       b200pf_bf16* tri_bias, long long bias_hs, long long bias_qs,
-                                      int rows, int n, int ending, void* stream) {
+                                      int vt_pitch, int rows, int n, int ending, int impl, void* stream) {
     B200PF_REQUIRE(z && w_qkvg && bias_qkvg && q && k && v && g && tri_bias, B200PF_ERR_INVALID, "triatt_producer: null pointer");
     B200PF_REQUIRE(rows > 0 && n > 0, B200PF_ERR_INVALID, "triatt_producer: bad rows/n");
     B200PF_REQUIRE(bias_hs > 0 && bias_qs > 0, B200PF_ERR_INVALID, "triatt_producer: bad bias strides");
+    B200PF_REQUIRE(vt_pitch == 0 || (vt_pitch % 8 == 0 && vt_pitch >= (ending ? rows : n)), B200PF_ERR_INVALID,
+                   "triatt_producer: vt_pitch must be 0 or a multiple of 8 covering the positions of a line");
     B200PF_REQUIRE(aligned16(z) && aligned16(w_qkvg) && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(g),
                    B200PF_ERR_INVALID, "triatt_producer: pointers must be 16-byte aligned");
     AttProducerArgs p{z, (const __nv_bfloat16*)w_qkvg, bias_qkvg, (__nv_bfloat16*)q, (__nv_bfloat16*)k,
-                      (__nv_bfloat16*)v, (__nv_bfloat16*)g, (__nv_bfloat16*)tri_bias, bias_hs, bias_qs, rows, n, ending};
+                      (__nv_bfloat16*)v, (__nv_bfloat16*)g, (__nv_bfloat16*)tri_bias, bias_hs, bias_qs, vt_pitch, rows, n, ending};
+    B200PF_REQUIRE(impl == 0 || impl == 1, B200PF_ERR_INVALID, "triatt_producer: impl must be 0 (tcgen05) or 1 (mma.sync)");
+    if (impl == 0) {
+        r512::Args a{};
+        a.z = z; a.w = (const __nv_bfloat16*)w_qkvg; a.wbias = bias_qkvg;
+        a.q = (__nv_bfloat16*)q; a.k = (__nv_bfloat16*)k; a.v = (__nv_bfloat16*)v; a.g = (__nv_bfloat16*)g;
+        a.tri_bias = (__nv_bfloat16*)tri_bias; a.w_bias_rows = (const __nv_bfloat16*)w_qkvg + 512 * 128;
+        a.bias_hs = bias_hs; a.bias_qs = bias_qs; a.vt_pitch = vt_pitch;
+        a.rows = rows; a.n = n; a.transposed = ending;
+        return r512::launch_triatt(a, (cudaStream_t)stream);
+    }
     B200PF_CUDA(cudaFuncSetAttribute(triatt_producer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_PRODUCER_SMEM));
     int span = ending ? rows : n;
     long long units = (long long)(ending ? n : rows) * ((span + UNIT - 1) / UNIT);

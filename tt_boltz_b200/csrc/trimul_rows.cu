@@ -7,6 +7,7 @@
 //   w_pg  [512][128]: 8 chunks of 64 rows; chunk q holds, for channels 32*(q%4) .. +31 of operand
 //         a (q < 4) or b (q >= 4), the 32 p_in rows followed by the 32 g_in rows, LN gain folded in;
 //   bias_pg [512]   : the matching LN-offset term (W beta), fp32, same order.
+#include "row512_tc.h"
 #include "rowtile.cuh"
 
 namespace b200pf {
@@ -231,7 +232,7 @@ using namespace b200pf;
 extern "C" int b200pf_trimul_producer(const float* z, const uint8_t* mask, const float* bias_pg,
                                       const b200pf_bf16* w_pg, const b200pf_plane_out* a_out,
                                       const b200pf_plane_out* b_out, int pitch, int rows, int n, int incoming,
-                                      int value_mode, void* stream) {
+                                      int value_mode, int impl, void* stream) {
     B200PF_REQUIRE(z && mask && bias_pg && w_pg && a_out && b_out && a_out->ptr && b_out->ptr, B200PF_ERR_INVALID,
                    "trimul_producer: null pointer");
     B200PF_REQUIRE(rows > 0 && n > 0 && rows <= n, B200PF_ERR_INVALID, "trimul_producer: bad rows/n");
@@ -254,6 +255,17 @@ extern "C" int b200pf_trimul_producer(const float* z, const uint8_t* mask, const
     }
     B200PF_REQUIRE(aligned16(z) && aligned16(w_pg), B200PF_ERR_INVALID, "trimul_producer: pointers must be 16-byte aligned");
     p.pitch = pitch; p.rows = rows; p.n = n; p.incoming = incoming;
+    B200PF_REQUIRE(impl == 0 || impl == 1, B200PF_ERR_INVALID, "trimul_producer: impl must be 0 (tcgen05) or 1 (mma.sync)");
+    if (impl == 0) {
+        r512::Args a{};
+        a.z = z; a.mask = mask; a.w = p.w_pg; a.wbias = bias_pg;
+        for (int i = 0; i < 2; ++i) {
+            a.planes[i] = p.planes[i]; a.plane_stride[i] = p.plane_stride[i];
+            a.group_stride[i] = p.group_stride[i]; a.row_group[i] = p.row_group[i];
+        }
+        a.pitch = pitch; a.rows = rows; a.n = n; a.transposed = incoming;
+        return r512::launch_trimul(a, (cudaStream_t)stream);
+    }
     B200PF_CUDA(cudaFuncSetAttribute(trimul_producer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PRODUCER_SMEM));
     int span = incoming ? rows : n;
     long long units = (long long)(incoming ? n : rows) * ((span + UNIT - 1) / UNIT);

@@ -22,6 +22,21 @@ def _round_up(x: int, m: int) -> int:
     return (x + m - 1) // m * m
 
 
+class PairMasks:
+    """uint8 forms of the pair mask: [N][N] for the triangle multiplication, and one contiguous,
+    64-padded row per attention line for the starting (rows) and ending (columns) node."""
+
+    def __init__(self, pair_mask_u8: torch.Tensor) -> None:
+        n = pair_mask_u8.shape[0]
+        self.n = n
+        self.pitch = _round_up(n, 64)
+        self.pm = pair_mask_u8.contiguous()
+        self.rows = torch.zeros(n, self.pitch, dtype=torch.uint8, device=pair_mask_u8.device)
+        self.rows[:, :n] = self.pm
+        self.cols = torch.zeros(n, self.pitch, dtype=torch.uint8, device=pair_mask_u8.device)
+        self.cols[:, :n] = self.pm.t()
+
+
 class Workspace:
     """bf16 scratch for one token count: five [N*pitch*128] buffers shared by the sub-operations
     (triangle multiplication uses three as a / b / x planes, triangle attention five as
@@ -39,15 +54,20 @@ class Workspace:
 # ------------------------------------------------------------------------------------------------
 # bf16 tier (fused kernels)
 # ------------------------------------------------------------------------------------------------
+def trimul_producer_weights(w: Dict[str, torch.Tensor], impl: int):
+    return (w["bias_pg_tc"], w["w_pg_tc"]) if impl == 0 else (w["bias_pg"], w["w_pg"])
+
+
 def tri_mul_bf16(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Tensor], ws: Workspace,
-                 incoming: bool, contract_variant: int = 0) -> None:
+                 incoming: bool, contract_variant: int = 0, row_impl: int = 0) -> None:
     n = z.shape[0]
     a, b, x = ws.buf[0], ws.buf[1], ws.buf[2]
     st = stream()
     oa = PlaneOut(ptr(a), ws.plane_stride, 0, 0)
     ob = PlaneOut(ptr(b), ws.plane_stride, 0, 0)
-    call("b200pf_trimul_producer", ptr(z), ptr(mask_u8), ptr(w["bias_pg"]), ptr(w["w_pg"]), C.byref(oa), C.byref(ob),
-         ws.pitch, n, n, int(incoming), 0, st)
+    bias_pg, w_pg = trimul_producer_weights(w, row_impl)
+    call("b200pf_trimul_producer", ptr(z), ptr(mask_u8), ptr(bias_pg), ptr(w_pg), C.byref(oa), C.byref(ob),
+         ws.pitch, n, n, int(incoming), 0, row_impl, st)
     pa = Planes(ptr(a), ws.plane_stride, 0, ws.pitch, n, n, 1, 0)
     pb = Planes(ptr(b), ws.plane_stride, 0, ws.pitch, n, n, 1, 0)
     call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), None, None, ptr(x), ws.plane_stride, ws.pitch,
@@ -56,20 +76,27 @@ def tri_mul_bf16(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Tens
          ptr(w["bias_pout"]), ptr(w["bias_gout"]), n, n, st)
 
 
-def tri_att_bf16(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Tensor], ws: Workspace,
-                 ending: bool, lines_per_cta: int = 0) -> None:
+def tri_att_bf16(z: torch.Tensor, masks: PairMasks, w: Dict[str, torch.Tensor], ws: Workspace,
+                 ending: bool, core: int = 0, lines_per_cta: int = 0, row_impl: int = 0) -> None:
+    """core 0 = tcgen05 attention core, 1 = mma.sync cross-check core."""
     n = z.shape[0]
     q, k, v, g, o = ws.buf
     st = stream()
     bias_hs, bias_qs = ws.pitch, 4 * ws.pitch          # layout [query][head][key]: a row shard is contiguous
     call("b200pf_triatt_producer", ptr(z), ptr(w["w_qkvg"]), ptr(w["bias_qkvg"]), ptr(q), ptr(k), ptr(v), ptr(g),
-         ptr(ws.tri_bias), bias_hs, bias_qs, n, n, int(ending), st)
-    if ending:      # line = column j: mask(line, key) = M[key][line]; o element (line, pos) -> z position [pos][line]
-        mask_ls, mask_ks, o_ls, o_ps = 1, n, C_Z, n * C_Z
+         ptr(ws.tri_bias), bias_hs, bias_qs, ws.pitch if core == 0 else 0, n, n, int(ending), row_impl, st)
+    if ending:      # line = column j: o element (line, pos) -> z position [pos][line]
+        o_ls, o_ps = C_Z, n * C_Z
     else:
-        mask_ls, mask_ks, o_ls, o_ps = n, 1, n * C_Z, C_Z
-    call("b200pf_triatt_core", ptr(q), ptr(k), ptr(v), ptr(ws.tri_bias), bias_hs, bias_qs, ws.pitch, ptr(mask_u8),
-         mask_ls, mask_ks, ptr(o), o_ls, o_ps, n, n, lines_per_cta, st)
+        o_ls, o_ps = n * C_Z, C_Z
+    if core == 0:
+        lines_mask = masks.cols if ending else masks.rows
+        call("b200pf_triatt_core_tc", ptr(q), ptr(k), ptr(v), ws.pitch, ptr(ws.tri_bias), bias_hs, bias_qs,
+             ptr(lines_mask), masks.pitch, ptr(o), o_ls, o_ps, n, n, st)
+    else:
+        mask_ls, mask_ks = (1, n) if ending else (n, 1)
+        call("b200pf_triatt_core", ptr(q), ptr(k), ptr(v), ptr(ws.tri_bias), bias_hs, bias_qs, ws.pitch, ptr(masks.pm),
+             mask_ls, mask_ks, ptr(o), o_ls, o_ps, n, n, lines_per_cta, st)
     call("b200pf_triatt_epilogue", ptr(z), ptr(o), ptr(g), ptr(w["w_o"]), n * n, st)
 
 

@@ -57,6 +57,8 @@ class B200PairformerLayer(nn.Module):
         self.token_s, self.token_z, self.num_heads = token_s, token_z, num_heads
         self.dropout, self.with_s, self.precision = dropout, with_s, precision
         self.contract_variant = 0      # 0 = tcgen05, 1 = SIMT cross-check
+        self.attention_core = 0        # 0 = tcgen05, 1 = mma.sync cross-check
+        self.row_impl = 0              # 0 = tcgen05 row-tile kernels, 1 = mma.sync cross-check
         self.lines_per_cta = 0
         for name, shape in layer_param_shapes(token_s, token_z, num_heads, pairwise_num_heads,
                                               pairwise_head_width, with_s):
@@ -89,20 +91,20 @@ class B200PairformerLayer(nn.Module):
         return pk
 
     def forward_inplace(self, s: Optional[torch.Tensor], z: torch.Tensor, tok_mask_u8: Optional[torch.Tensor],
-                        pair_mask_u8: torch.Tensor, ws: Optional[ops.Workspace]) -> None:
+                        masks: ops.PairMasks, ws: Optional[ops.Workspace]) -> None:
         """Update fp32 working copies z [N,N,128] and s [N,c_s] in place."""
         pk = self._pack(z.device)
         if self.precision == "bf16":
-            ops.tri_mul_bf16(z, pair_mask_u8, pk["tri_mul_out"], ws, False, self.contract_variant)
-            ops.tri_mul_bf16(z, pair_mask_u8, pk["tri_mul_in"], ws, True, self.contract_variant)
-            ops.tri_att_bf16(z, pair_mask_u8, pk["tri_att_start"], ws, False, self.lines_per_cta)
-            ops.tri_att_bf16(z, pair_mask_u8, pk["tri_att_end"], ws, True, self.lines_per_cta)
+            ops.tri_mul_bf16(z, masks.pm, pk["tri_mul_out"], ws, False, self.contract_variant, self.row_impl)
+            ops.tri_mul_bf16(z, masks.pm, pk["tri_mul_in"], ws, True, self.contract_variant, self.row_impl)
+            ops.tri_att_bf16(z, masks, pk["tri_att_start"], ws, False, self.attention_core, self.lines_per_cta, self.row_impl)
+            ops.tri_att_bf16(z, masks, pk["tri_att_end"], ws, True, self.attention_core, self.lines_per_cta, self.row_impl)
             ops.transition_z_bf16(z, pk["transition_z"])
         else:
-            ops.tri_mul_f32(z, pair_mask_u8, pk["tri_mul_out"], False)
-            ops.tri_mul_f32(z, pair_mask_u8, pk["tri_mul_in"], True)
-            ops.tri_att_f32(z, pair_mask_u8, pk["tri_att_start"], False)
-            ops.tri_att_f32(z, pair_mask_u8, pk["tri_att_end"], True)
+            ops.tri_mul_f32(z, masks.pm, pk["tri_mul_out"], False)
+            ops.tri_mul_f32(z, masks.pm, pk["tri_mul_in"], True)
+            ops.tri_att_f32(z, masks.pm, pk["tri_att_start"], False)
+            ops.tri_att_f32(z, masks.pm, pk["tri_att_end"], True)
             ops.transition_f32(z, pk["transition_z"])
         if self.with_s and s is not None:
             ops.single_track(s, z, tok_mask_u8, pk["pre_norm_s"], pk["attention"], pk["transition_s"], self.num_heads)
@@ -123,7 +125,7 @@ def _run_layers(layers, s, z, mask, pair_mask, ws_cache: Optional[dict] = None):
     with torch.cuda.device(z.device), torch.no_grad():
         zw = z[0].to(torch.float32).clone(memory_format=torch.contiguous_format)
         sw = None if s is None else s[0].to(torch.float32).clone(memory_format=torch.contiguous_format)
-        pm = _mask_u8(pair_mask, (n, n), z.device)
+        pm = ops.PairMasks(_mask_u8(pair_mask, (n, n), z.device))
         tm = _mask_u8(mask, (n,), z.device) if s is not None else None
         ws = None
         if any(l.precision == "bf16" for l in layers):

@@ -86,7 +86,7 @@ def _bf16(n_elems: int, dev) -> torch.Tensor:
 
 
 def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: torch.Tensor,
-                  tok_mask_u8: Optional[torch.Tensor], pair_mask_u8: torch.Tensor, rank: int, world: int,
+                  tok_mask_u8: Optional[torch.Tensor], masks: ops.PairMasks, rank: int, world: int,
                   group=None) -> torch.Tensor:
     """Update the local row shard z_loc [nr, N, 128] (returned; may be a new tensor) and s in place."""
     pk = layer._pack(z_loc.device)
@@ -97,14 +97,15 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
         raise RuntimeError("the sharded bf16 path needs N / P to be a multiple of 128 tokens")
     pn, pr = _ru8(n), _ru8(nr)
     st = stream()
-    mask_loc = pair_mask_u8[r0:r0 + nr]
+    mask_loc = masks.pm[r0:r0 + nr]
 
     # ---- triangle multiplication, outgoing -------------------------------------------------------
     w = pk["tri_mul_out"]
     a_loc, b_loc, x = _bf16(C_Z * nr * pn, dev), _bf16(C_Z * nr * pn, dev), _bf16(C_Z * nr * pn, dev)
     oa, ob = PlaneOut(ptr(a_loc), nr * pn, 0, 0), PlaneOut(ptr(b_loc), nr * pn, 0, 0)
-    call("b200pf_trimul_producer", ptr(z_loc), ptr(mask_loc), ptr(w["bias_pg"]), ptr(w["w_pg"]), C.byref(oa), C.byref(ob),
-         pn, nr, n, 0, 0, st)
+    bias_pg, w_pg = ops.trimul_producer_weights(w, layer.row_impl)
+    call("b200pf_trimul_producer", ptr(z_loc), ptr(mask_loc), ptr(bias_pg), ptr(w_pg), C.byref(oa), C.byref(ob),
+         pn, nr, n, 0, 0, layer.row_impl, st)
     b_all = all_gather_cat(b_loc, group)                                             # [P][D][nr][pn]
     pa = Planes(ptr(a_loc), nr * pn, 0, pn, nr, n, 1, 0)
     pb = Planes(ptr(b_all), nr * pn, C_Z * nr * pn, pn, nr, n, world, 0)
@@ -118,8 +119,9 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
     bt_loc = _bf16(C_Z * n * pr, dev)                                                # [D][j][k_local]
     oa = PlaneOut(ptr(at_send), nr * pr, C_Z * nr * pr, nr)
     ob = PlaneOut(ptr(bt_loc), n * pr, 0, 0)
-    call("b200pf_trimul_producer", ptr(z_loc), ptr(mask_loc), ptr(w["bias_pg"]), ptr(w["w_pg"]), C.byref(oa), C.byref(ob),
-         pr, nr, n, 1, 0, st)
+    bias_pg, w_pg = ops.trimul_producer_weights(w, layer.row_impl)
+    call("b200pf_trimul_producer", ptr(z_loc), ptr(mask_loc), ptr(bias_pg), ptr(w_pg), C.byref(oa), C.byref(ob),
+         pr, nr, n, 1, 0, layer.row_impl, st)
     at_recv = all_to_all_blocks(at_send.view(world, -1), group)                      # [src][D][i_local][k_local of src]
     bt_all = all_gather_cat(bt_loc, group)                                           # [src][D][j][k_local of src]
     pa = Planes(ptr(at_recv), nr * pr, C_Z * nr * pr, pr, nr, nr, world, 1)
@@ -134,20 +136,20 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
     q, k, v, g, o = (_bf16(nr * n * C_Z, dev) for _ in range(5))
     bias_loc = _bf16(nr * 4 * pn, dev)
     call("b200pf_triatt_producer", ptr(z_loc), ptr(w["w_qkvg"]), ptr(w["bias_qkvg"]), ptr(q), ptr(k), ptr(v), ptr(g),
-         ptr(bias_loc), pn, 4 * pn, nr, n, 0, st)
+         ptr(bias_loc), pn, 4 * pn, pn, nr, n, 0, layer.row_impl, st)
     bias_all = all_gather_cat(bias_loc, group)                                       # [query][head][key]
-    call("b200pf_triatt_core", ptr(q), ptr(k), ptr(v), ptr(bias_all), pn, 4 * pn, pn, ptr(mask_loc), n, 1,
-         ptr(o), n * C_Z, C_Z, nr, n, layer.lines_per_cta, st)
+    call("b200pf_triatt_core_tc", ptr(q), ptr(k), ptr(v), pn, ptr(bias_all), pn, 4 * pn, ptr(masks.rows[r0:r0 + nr]),
+         masks.pitch, ptr(o), n * C_Z, C_Z, nr, n, st)
     call("b200pf_triatt_epilogue", ptr(z_loc), ptr(o), ptr(g), ptr(w["w_o"]), nr * n, st)
 
     # ---- triangle attention, ending node (lines = local columns of the column shard) ------------
     w = pk["tri_att_end"]
     zc = rows_to_cols(z_loc, group)                                                  # [N][nr][128] fp32
     call("b200pf_triatt_producer", ptr(zc), ptr(w["w_qkvg"]), ptr(w["bias_qkvg"]), ptr(q), ptr(k), ptr(v), ptr(g),
-         ptr(bias_loc), pn, 4 * pn, n, nr, 1, st)
+         ptr(bias_loc), pn, 4 * pn, pn, n, nr, 1, layer.row_impl, st)
     bias_all = all_gather_cat(bias_loc, group)
-    call("b200pf_triatt_core", ptr(q), ptr(k), ptr(v), ptr(bias_all), pn, 4 * pn, pn, pair_mask_u8.data_ptr() + r0, 1, n,
-         ptr(o), C_Z, nr * C_Z, nr, n, layer.lines_per_cta, st)
+    call("b200pf_triatt_core_tc", ptr(q), ptr(k), ptr(v), pn, ptr(bias_all), pn, 4 * pn, ptr(masks.cols[r0:r0 + nr]),
+         masks.pitch, ptr(o), C_Z, nr * C_Z, nr, n, st)
     call("b200pf_triatt_epilogue", ptr(zc), ptr(o), ptr(g), ptr(w["w_o"]), n * nr, st)
     z_loc = cols_to_rows(zc, group)
     del q, k, v, g, o, zc, bias_loc, bias_all
@@ -197,7 +199,7 @@ class ShardedPairformerModule(nn.Module):
         rank, world = dist.get_rank(self.group), dist.get_world_size(self.group)
         n = z_loc.shape[1]
         with torch.cuda.device(z_loc.device), torch.no_grad():
-            pm = _mask_u8(pair_mask, (n, n), z_loc.device)
+            pm = ops.PairMasks(_mask_u8(pair_mask, (n, n), z_loc.device))
             tm = _mask_u8(mask, (n,), z_loc.device)
             sw = s.to(torch.float32).clone()
             for layer in self.layers:

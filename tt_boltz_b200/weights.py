@@ -34,11 +34,14 @@ def pack_trimul(sd: Dict[str, torch.Tensor], pre: str, device) -> Dict[str, torc
         ch0 = (q // 4) * d + (q % 4) * 32
         rows += [f["p_in.weight"][ch0:ch0 + 32], f["g_in.weight"][ch0:ch0 + 32]]
     w_pg, bias_pg = _fold(torch.cat(rows, 0), f["norm_in.weight"], f["norm_in.bias"])
+    # tcgen05 producer: [p_a | g_a | p_b | g_b], 128 rows each
+    rows_tc = [f["p_in.weight"][:d], f["g_in.weight"][:d], f["p_in.weight"][d:], f["g_in.weight"][d:]]
+    w_pg_tc, bias_pg_tc = _fold(torch.cat(rows_tc, 0), f["norm_in.weight"], f["norm_in.bias"])
     w_pout, bias_pout = _fold(f["p_out.weight"], f["norm_out.weight"], f["norm_out.bias"])
     w_gout, bias_gout = _fold(f["g_out.weight"], f["norm_in.weight"], f["norm_in.bias"])
     bf = lambda t: t.to(device=device, dtype=torch.bfloat16).contiguous()
     fp = lambda t: t.to(device=device, dtype=torch.float32).contiguous()
-    return {"w_pg": bf(w_pg), "bias_pg": fp(bias_pg), "w_pout": bf(w_pout), "bias_pout": fp(bias_pout),
+    return {"w_pg": bf(w_pg), "bias_pg": fp(bias_pg), "w_pg_tc": bf(w_pg_tc), "bias_pg_tc": fp(bias_pg_tc), "w_pout": bf(w_pout), "bias_pout": fp(bias_pout),
             "w_gout": bf(w_gout), "bias_gout": fp(bias_gout)}
 
 
