@@ -107,10 +107,12 @@ int b200pf_ln_proj_heads(const float* z, const float* gamma, const float* beta, 
 /* Triangle-multiplication producer: LN_in -> [p_in | g_in] projection -> p*sigmoid(g) -> mask
  * -> a/b written channel-major.  Replaces tt_bio/tenstorrent.py:410-452 (reference.py:456-464).
  *   z: fp32 [rows][n][128];  mask: [rows][n];
- *   impl 0 (tcgen05 kernel): w_pg bf16 [512][128] = p_in rows of a, g_in rows of a, p_in rows of b,
- *         g_in rows of b (128 each);  impl 1 (mma.sync cross-check): 8 chunks of 64 rows, chunk q =
- *         channels 32*(q%4)..+31 of operand a (q < 4) or b (q >= 4): 32 p_in rows then 32 g_in rows;
- *         bias_pg: fp32 [512] in the same order as w_pg.
+ *   impl 0 (tcgen05 kernel): the LayerNorm affine (ln_gamma, ln_beta: fp32 [128]) is applied in the
+ *         kernel; w_pg bf16 [512][128] = 0.5 * (p_in rows of a, g_in rows of a, p_in rows of b, g_in
+ *         rows of b), 128 each (the halves turn p*sigmoid(g) into p' + p'*tanh(g')); bias_pg unused.
+ *   impl 1 (mma.sync cross-check): LN gain folded into w_pg, 8 chunks of 64 rows, chunk q = channels
+ *         32*(q%4)..+31 of operand a (q < 4) or b (q >= 4): 32 p_in rows then 32 g_in rows;
+ *         bias_pg: fp32 [512] LN-offset term in the same order; ln_gamma / ln_beta unused.
  *   incoming == 0: a[d][r][k] = u_a[r][k][d]  (plane rows = local z rows, cols = k)
  *   incoming != 0: a[d][c][r] = u_a[r][c][d]  (plane rows = z columns, cols = local z rows)
  *   value_mode 0 = bf16 planes (the only mode built so far). */
@@ -123,8 +125,8 @@ typedef struct b200pf_plane_out {
 /* element (d, row, col) of an output operand is written to
  *   ptr[(row / row_group) * group_stride + d * plane_stride + (row % row_group) * pitch + col];
  * row groups let a rank lay its planes out as one contiguous block per destination rank. */
-int b200pf_trimul_producer(const float* z, const uint8_t* mask, const float* bias_pg,
-                           const b200pf_bf16* w_pg, const b200pf_plane_out* a_out,
+int b200pf_trimul_producer(const float* z, const uint8_t* mask, const float* ln_gamma, const float* ln_beta,
+                           const float* bias_pg, const b200pf_bf16* w_pg, const b200pf_plane_out* a_out,
                            const b200pf_plane_out* b_out, int pitch, int rows, int n, int incoming,
                            int value_mode, int impl, void* stream);
 
@@ -163,17 +165,21 @@ int b200pf_trimul_epilogue(float* z, const b200pf_bf16* x, long long x_plane_str
 /* Triangle-attention producer: LN -> [q|k|v|g] projection and the 4-head triangle bias.
  * Replaces tt_bio/tenstorrent.py:545-567, 603-614 (reference.py:331-341, 99-120).
  *   z is viewed as [rows][n][128] (a row shard, or a column shard stored [i][j_local][128]);
- *   w_qkvg: bf16 [528][128] = q rows (scaled by log2(e)/sqrt(32)), k, v, g rows, the 4 bias rows
- *           (scaled by log2(e)), 12 zero rows;  bias_qkvg: fp32 [528].
+ *   impl 1 (mma.sync): w_qkvg bf16 [528][128] = q rows (scaled by log2(e)/sqrt(32)), k, v, g rows,
+ *           the 4 bias rows (scaled by log2(e)), 12 zero rows, LN gain folded; bias_qkvg: fp32 [528];
+ *   impl 0 (tcgen05): LN affine from ln_gamma / ln_beta; w_qkvg bf16 [512][128] = q (scaled), k,
+ *           0.5 * g, v rows; w_bias_f32: fp32 [4][128] bias rows times log2(e); v is written
+ *           transposed (vt_pitch > 0 required); bias_qkvg unused.
  * A "line" is a row of the view (ending == 0, positions = its n columns) or a column of the view
  * (ending != 0, positions = its `rows` rows).  Outputs (bf16):
- *   q,k: [line][head][pos][32];  v: the same when vt_pitch == 0, else transposed
+ *   q,k: impl 0 [line][pos][head][32], impl 1 [line][head][pos][32];  v: like q when vt_pitch == 0, else transposed
  *          [line][head][32][vt_pitch] (positions contiguous) as the tcgen05 attention core reads it;
  *   g:     sigmoid(gate) in the layout of the view, [rows][n][128];
  *   tri_bias: element (head, line, pos) at tri_bias[head*bias_hs + line*bias_qs + pos]: the bias
  *          of query `line` and key `pos` (for the ending node that is beta[row pos][col line]);
  *   impl: 0 = tcgen05 kernel, 1 = mma.sync cross-check (same weights for both). */
-int b200pf_triatt_producer(const float* z, const b200pf_bf16* w_qkvg, const float* bias_qkvg,
+int b200pf_triatt_producer(const float* z, const float* ln_gamma, const float* ln_beta, const float* w_bias_f32,
+                           const b200pf_bf16* w_qkvg, const float* bias_qkvg,
                            b200pf_bf16* q, b200pf_bf16* k, b200pf_bf16* v, b200pf_bf16* g,
                            b200pf_bf16* tri_bias, long long bias_hs, long long bias_qs,
                            int vt_pitch, int rows, int n, int ending, int impl, void* stream);
@@ -195,7 +201,8 @@ int b200pf_triatt_core(const b200pf_bf16* q, const b200pf_bf16* k, const b200pf_
 /* The same attention on tcgen05 / TMEM (the production core; b200pf_triatt_core is the mma.sync
  * cross-check).  S = Q K^T and O = P V run as tcgen05.mma with accumulators in TMEM, operands come
  * in by TMA, the bias tile is fetched once for two lines, softmax runs one thread per query row.
- *   vt: v transposed [line][head][32][vt_pitch];  bias as above with bias_cols == n;
+ *   q, k: [line][pos][head][32] (as written by the impl-0 producer); vt: v transposed
+ *   [line][head][32][vt_pitch];  bias as above with bias_cols == n;
  *   mask_lines: uint8 [lines][mask_pitch] (1 = attend), one contiguous row per line, mask_pitch a
  *   multiple of 16 covering n rounded up to 64 (the host transposes the mask for the ending node). */
 int b200pf_triatt_core_tc(const b200pf_bf16* q, const b200pf_bf16* k, const b200pf_bf16* vt, int vt_pitch,
@@ -225,14 +232,15 @@ int b200pf_transition_z(float* z, const b200pf_bf16* w12, const float* bias12,
  * library image on every GPU that loads it (held until the process exits).
  *   - limit: n <= 128 tokens; larger n is refused with B200PF_ERR_UNSUPPORTED and a message;
  *   - z (fp32 [n][n][128]) is updated in place; mask is [n][n]; weights as for the three stage
- *     entry points with impl 0 (w_pg [512][128], bias_pg [512], w_pout / w_gout [128][128], bias_* [128]);
+ *     entry points with impl 0 (ln_gamma / ln_beta [128], w_pg [512][128], w_pout / w_gout [128][128], bias_* [128]);
  *   - the call itself never calls cudaMalloc / cudaFree or any allocating routine;
  *   - the first call on a device looks up the device address of the array
  *     (cudaGetSymbolAddress); make that first call before starting any stream capture;
  *   - all calls share the one array and it keeps the previous call's contents.  Nothing in it
  *     has to start at zero (each stage overwrites everything the next one reads), but two calls
  *     whose kernels overlap on the GPU (different streams) race on it: serialise them. */
-int b200pf_tri_mul_noalloc(float* z, const uint8_t* mask, const b200pf_bf16* w_pg, const float* bias_pg,
+int b200pf_tri_mul_noalloc(float* z, const uint8_t* mask, const float* ln_gamma, const float* ln_beta,
+                           const b200pf_bf16* w_pg,
                            const b200pf_bf16* w_pout, const b200pf_bf16* w_gout,
                            const float* bias_pout, const float* bias_gout,
                            int n, int incoming, void* stream);

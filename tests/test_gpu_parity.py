@@ -147,6 +147,18 @@ def test_contraction_tcgen05_matches_simt_and_einsum(dev):
         assert rel_l2(outs[0], outs[1]) < 1e-3, n
 
 
+def test_tcgen05_kernels_match_mma_sync_cross_checks(dev):
+    """One layer with every tcgen05 kernel against the same layer on the mma.sync / SIMT cross-check kernels."""
+    n = 136
+    sd = synthetic.make_weights(1, seed=1, std=0.05, affine_jitter=0.3)
+    s, z = synthetic.make_inputs(n, seed=0)
+    m, pm = synthetic.tail_padding_mask(n, 11)
+    _, z_tc = run_module(sd, 1, s, z, m, pm, dev, "bf16")
+    _, z_x = run_module(sd, 1, s, z, m, pm, dev, "bf16", row_impl=1, attention_core=1, contract_variant=1)
+    v = n - 11
+    assert rel_l2((z_tc - z)[0, :v, :v], (z_x - z)[0, :v, :v]) < 8e-3
+
+
 @pytest.mark.parametrize("n", [50, 128, 200])
 def test_attention_tcgen05_core_matches_mma_sync_core(dev, n):
     """The two attention cores (tcgen05 / TMEM and the mma.sync cross-check) see the same q, k, v, bias."""

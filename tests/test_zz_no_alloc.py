@@ -37,7 +37,7 @@ def test_noalloc_matches_stage_entry_points_twice_in_a_row():
         ops.tri_mul_bf16(z_ref, pm, w, ops.Workspace(n, dev), incoming)
         z_new = z[0].to(dev).clone()
         before = torch.cuda.memory_allocated(dev)
-        call("b200pf_tri_mul_noalloc", ptr(z_new), ptr(pm), ptr(w["w_pg_tc"]), ptr(w["bias_pg_tc"]), ptr(w["w_pout"]),
+        call("b200pf_tri_mul_noalloc", ptr(z_new), ptr(pm), ptr(w["ln_in_gamma"]), ptr(w["ln_in_beta"]), ptr(w["w_pg_tc"]), ptr(w["w_pout"]),
              ptr(w["w_gout"]), ptr(w["bias_pout"]), ptr(w["bias_gout"]), n, int(incoming), stream())
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated(dev) == before
@@ -53,6 +53,6 @@ def test_noalloc_rejects_sizes_beyond_its_scratch():
     dev = torch.device("cuda:0")
     z = torch.zeros(8, device=dev)
     lib = _lib.load()
-    rc = lib.b200pf_tri_mul_noalloc(z.data_ptr(), None, None, None, None, None, None, None, 129, 0, None)
+    rc = lib.b200pf_tri_mul_noalloc(z.data_ptr(), None, None, None, None, None, None, None, None, 129, 0, None)
     assert rc == -2
     assert "exceeds the built-in scratch" in _lib.last_error()

@@ -43,15 +43,15 @@ SIGNATURES = {
                              _ll, _ll, _f, _f, _i, _vp],
     "b200pf_f32_transpose01": [_vp, _vp, _i, _i, _i, _vp],
     "b200pf_ln_proj_heads": [_vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _vp],
-    "b200pf_trimul_producer": [_vp, _vp, _vp, _vp, C.POINTER(PlaneOut), C.POINTER(PlaneOut), _i, _i, _i, _i, _i, _i, _vp],
+    "b200pf_trimul_producer": [_vp, _vp, _vp, _vp, _vp, _vp, C.POINTER(PlaneOut), C.POINTER(PlaneOut), _i, _i, _i, _i, _i, _i, _vp],
     "b200pf_trimul_contract": [C.POINTER(Planes), C.POINTER(Planes), _vp, _vp, _vp, _ll, _i, _i, _i, _vp],
     "b200pf_trimul_epilogue": [_vp, _vp, _ll, _i, _vp, _vp, _vp, _vp, _i, _i, _vp],
-    "b200pf_triatt_producer": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _vp],
+    "b200pf_triatt_producer": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _vp],
     "b200pf_triatt_core_tc": [_vp, _vp, _vp, _i, _vp, _ll, _ll, _vp, _i, _vp, _ll, _ll, _i, _i, _vp],
     "b200pf_triatt_core": [_vp, _vp, _vp, _vp, _ll, _ll, _i, _vp, _ll, _ll, _vp, _ll, _ll, _i, _i, _i, _vp],
     "b200pf_triatt_epilogue": [_vp, _vp, _vp, _vp, _ll, _vp],
     "b200pf_transition_z": [_vp, _vp, _vp, _vp, _ll, _vp],
-    "b200pf_tri_mul_noalloc": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
+    "b200pf_tri_mul_noalloc": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
 }
 _RESTYPES = {"b200pf_last_error": C.c_char_p, "b200pf_launch_count": _ll}
 

@@ -1,16 +1,27 @@
-// The two "128 -> 512" producers on tcgen05: LayerNorm -> one [128 x 128] x [128 x 512] GEMM per tile
-// of 128 pair positions -> element-wise epilogue straight out of TMEM.
+// The two "128 -> 512" producers on tcgen05: LayerNorm (with its affine) -> GEMMs of one tile of 128
+// pair positions against 512 weight rows kept in shared memory -> thin epilogue out of TMEM.
 //
-//   MODE_TRIMUL : [p_a | g_a] [p_b | g_b] -> p * sigmoid(g) * mask -> a / b planes (channel-major)
-//   MODE_TRIATT : [q | k] [v | g]          -> q, k rows per head, v transposed, sigmoid(g) in z layout;
-//                 the 4 triangle-bias heads are dotted on the CUDA cores by the loader warps (fp32)
-//
-// Roles (416 threads): warps 0-7 LayerNorm loaders (16 rows each), warp 8 MMA issuer, warps 9-12
-// epilogue (thread = row = TMEM lane).  The 512 output columns are two halves of 256 that live in
-// the two halves of TMEM, so the epilogue of one half overlaps the MMAs of the next; the A tile is
-// double buffered so the loaders run a tile ahead.  Weights stay in shared memory (128 KB).
+// The orientation of each GEMM is chosen so that the epilogue thread already holds the values
+// in the order they are stored, and nothing is transposed through shared memory:
+//   MODE_TRIMUL : D[channel][position] = W x^T for the four groups p_a, g_a, p_b, g_b (M = 128
+//                 channels, N = 128 positions): thread = channel, 32 consecutive positions per
+//                 tcgen05.ld = 64 contiguous bytes of a plane row.  u = p*sigmoid(g) costs one
+//                 MUFU and one FMA per element: the host halves W_p and W_g, so with
+//                 p' = p/2, t = tanh(g/2):  p*sigmoid(g) = p' + p'*t.  Masked / out-of-range
+//                 positions are zero rows of x, which makes p' (and u) exactly zero.
+//   MODE_TRIATT : D[position][q|k] = x W^T and D[position][g] = x W_g^T (thread = position:
+//                 64-byte head rows and z-layout gate rows), D[v-channel][position] = W_v x^T
+//                 (thread = channel: rows of the transposed V).  The 4 triangle-bias heads are
+//                 dotted in fp32 by the loader warps.
+// Output goes TMEM -> registers -> a swizzled staging tile -> TMA stores, so that global memory
+// only ever sees full, contiguous lines (thread-per-row 16-byte stores were 3x slower).
+// Roles (416 threads): warps 0-3 LayerNorm loaders (32 rows each), warp 4 MMA issuer, warps 5-12
+// epilogue (two warps per TMEM lane quarter, each taking half of the columns).  TMEM is used as
+// two halves of 256 columns so the epilogue of one half overlaps the MMAs of the next, and the x
+// tile is double buffered so the loaders run a tile ahead.
 #include "row512_tc.h"
 #include "rowtc.cuh"
+#include "tmap.cuh"
 
 namespace b200pf {
 namespace r512 {
@@ -18,15 +29,16 @@ namespace r512 {
 using namespace rtc;
 
 constexpr int MODE_TRIMUL = 0, MODE_TRIATT = 1;
-constexpr int LOAD_WARPS = 8, EPI_WARP0 = 9, THREADS = 13 * 32;
-constexpr int W_BYTES = 512 * 128 * 2;                 // 131072 (two k-blocks of [512][128 B])
+constexpr int LOAD_WARPS = 4, MMA_WARP = 4, EPI_WARP0 = 5, EPI_WARPS = 8, THREADS = 13 * 32;
+constexpr int W_BYTES = 512 * 128 * 2;                 // two k-blocks of [512][128 B]
+constexpr int W_KB = 512 * 128;
 constexpr int OFF_A = W_BYTES;                          // 2 stages x 32 KB
-constexpr int OFF_STAGE = OFF_A + 2 * A_TILE_BYTES;     // per epilogue warp: [32][40] bf16 = 2560 B
-constexpr int STG_PITCH = 40;
-constexpr int OFF_BIAS = OFF_STAGE + 4 * 32 * STG_PITCH * 2;   // 512 fp32
-constexpr int OFF_WB = OFF_BIAS + 512 * 4;              // triangle-bias rows [4][128] fp32 + 4 offsets
-constexpr int OFF_BAR = OFF_WB + (4 * 128 + 4) * 4;
-constexpr int SMEM_BYTES = OFF_BAR + 128 + 1024;
+constexpr int OFF_STG = OFF_A + 2 * A_TILE_BYTES;       // output staging: 2 boxes of [128 rows][128 B], 128-byte swizzle
+constexpr int STG_BOX = 128 * 128;
+constexpr int OFF_WB = OFF_STG + 2 * STG_BOX;           // triangle-bias rows [4][128] fp32
+constexpr int OFF_BAR = OFF_WB + 4 * 128 * 4;
+constexpr int SMEM_BYTES = OFF_BAR + 128;               // 231,552: the dynamic window must start 1024-byte aligned
+constexpr int EPI_BAR_ID = 1;
 
 struct Bars {
     uint64_t a_full[2], a_empty[2], acc_full[2], acc_empty[2];
@@ -34,14 +46,36 @@ struct Bars {
     int abort_flag;
 };
 
-template <int MODE>
-__global__ void __launch_bounds__(THREADS, 1) row512_kernel(Args p, unsigned int* status) {
+// D[tmem] = A(rows a_row0.. of `a_addr` tile set, M = 128) * B(rows b_row0 .. + n_cols)^T over K = 128.
+__device__ __forceinline__ void gemm_k128(uint32_t tmem_d, uint32_t a_addr, uint32_t a_kb, uint32_t b_addr, uint32_t b_kb,
+                                          uint32_t idesc) {
     using namespace sm100;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+        const uint32_t kb = ks >> 2, kk = ks & 3;
+        umma_bf16(tmem_d, make_desc_k_sw128(a_addr + kb * a_kb + kk * 32), make_desc_k_sw128(b_addr + kb * b_kb + kk * 32),
+                  idesc, ks ? 1u : 0u);
+    }
+}
+
+__device__ __forceinline__ float tanh_approx(float x) {
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x));
+    return t;
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(THREADS, 1)
+row512_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
+              const __grid_constant__ CUtensorMap map2, const __grid_constant__ CUtensorMap map3, Args p, unsigned int* status) {
+    using namespace sm100;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    if ((smem_u32(smem) & 1023u) != 0) {       // swizzled tiles need 1024-byte alignment; there is no slack to fix it up
+        if (threadIdx.x == 0) atomicOr(status, DEV_STATUS_BAD_INDEX);
+        return;
+    }
     Bars* B = reinterpret_cast<Bars*>(smem + OFF_BAR);
     volatile int* abort_flag = &B->abort_flag;
-    float* bias_s = reinterpret_cast<float*>(smem + OFF_BIAS);
     float* wb_s = reinterpret_cast<float*>(smem + OFF_WB);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
 
@@ -53,19 +87,16 @@ __global__ void __launch_bounds__(THREADS, 1) row512_kernel(Args p, unsigned int
     if (tid == 0) {
         for (int i = 0; i < 2; ++i) {
             mbar_init(&B->a_full[i], LOAD_WARPS); mbar_init(&B->a_empty[i], 1);
-            mbar_init(&B->acc_full[i], 1); mbar_init(&B->acc_empty[i], 4);
+            mbar_init(&B->acc_full[i], 1); mbar_init(&B->acc_empty[i], EPI_WARPS);
         }
         B->abort_flag = 0;
         fence_barrier_init();
     }
     load_weights_sw128(smem, p.w, 512, tid, THREADS);
-    for (int i = tid; i < 512; i += THREADS) bias_s[i] = p.wbias[i];
-    if (MODE == MODE_TRIATT) {
-        for (int i = tid; i < 4 * 128; i += THREADS) wb_s[i] = __bfloat162float(p.w_bias_rows[i]);
-        if (tid < 4) wb_s[512 + tid] = p.wbias[512 + tid];
-    }
+    if (MODE == MODE_TRIATT)
+        for (int i = tid; i < 4 * 128; i += THREADS) wb_s[i] = p.w_bias_f32[i];
     fence_proxy_async();
-    if (warp == 8) { tmem_alloc(&B->tmem_slot, 512); tmem_relinquish(); }
+    if (warp == MMA_WARP) { tmem_alloc(&B->tmem_slot, 512); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -78,6 +109,13 @@ __global__ void __launch_bounds__(THREADS, 1) row512_kernel(Args p, unsigned int
 
     if (warp < LOAD_WARPS) {
         // ---------------------------- LayerNorm loaders ----------------------------
+        const int sub = lane & 7, rq = lane >> 3;
+        float4 gam[4], bet[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            gam[j] = __ldg(reinterpret_cast<const float4*>(p.ln_gamma) + j * 8 + sub);
+            bet[j] = __ldg(reinterpret_cast<const float4*>(p.ln_beta) + j * 8 + sub);
+        }
         uint32_t it = 0;
         bool ok = true;
         for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
@@ -86,10 +124,53 @@ __global__ void __launch_bounds__(THREADS, 1) row512_kernel(Args p, unsigned int
             ok = mbar_wait(&B->a_empty[stage], ph ^ 1, abort_flag);
             if (!ok) break;
             uint8_t* a_tile = smem + OFF_A + stage * A_TILE_BYTES;
-            ln_rows16_to_sw128(
-                [&](int r) -> const float* { long long f = flat_of(line, pos0 + r); return f < 0 ? nullptr : p.z + f * KC; },
-                a_tile, warp * 16, lane,
-                [&](int r, const float4 (&v)[4]) {
+#pragma unroll 1
+            for (int pass = 0; pass < 2; ++pass) {
+                const int row0 = warp * 32 + pass * 16;
+                float4 v[4][4];
+                long long fl[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    fl[i] = flat_of(line, pos0 + row0 + i * 4 + rq);
+                    const float4* src = reinterpret_cast<const float4*>(p.z + (fl[i] < 0 ? 0 : fl[i]) * KC);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) v[i][j] = (fl[i] < 0 || (p.debug & 1)) ? make_float4(0.f, 0.f, 0.f, float(j)) : __ldg(src + j * 8 + sub);
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int row = row0 + i * 4 + rq;
+                    float s = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) s += (v[i][j].x + v[i][j].y) + (v[i][j].z + v[i][j].w);
+                    s += __shfl_xor_sync(0xffffffffu, s, 1);
+                    s += __shfl_xor_sync(0xffffffffu, s, 2);
+                    s += __shfl_xor_sync(0xffffffffu, s, 4);
+                    const float mean = s * (1.f / KC);
+                    float ss = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        v[i][j].x -= mean; v[i][j].y -= mean; v[i][j].z -= mean; v[i][j].w -= mean;
+                        ss += (v[i][j].x * v[i][j].x + v[i][j].y * v[i][j].y) + (v[i][j].z * v[i][j].z + v[i][j].w * v[i][j].w);
+                    }
+                    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+                    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+                    ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+                    const float rstd = rsqrtf(ss * (1.f / KC) + LN_EPS);
+                    bool keep = fl[i] >= 0;
+                    if (MODE == MODE_TRIMUL) keep = keep && p.mask[fl[i] < 0 ? 0 : fl[i]] != 0;
+                    const float kz = keep ? 1.f : 0.f;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        v[i][j].x = fmaf(v[i][j].x * rstd, gam[j].x, bet[j].x) * kz;
+                        v[i][j].y = fmaf(v[i][j].y * rstd, gam[j].y, bet[j].y) * kz;
+                        v[i][j].z = fmaf(v[i][j].z * rstd, gam[j].z, bet[j].z) * kz;
+                        v[i][j].w = fmaf(v[i][j].w * rstd, gam[j].w, bet[j].w) * kz;
+                        uint2 o;
+                        o.x = pack_bf16x2(v[i][j].x, v[i][j].y);
+                        o.y = pack_bf16x2(v[i][j].z, v[i][j].w);
+                        const int chunk = (j & 1) * 4 + (sub >> 1);
+                        *reinterpret_cast<uint2*>(a_tile + (j >> 1) * A_KB_BYTES + sw128(row, chunk) + (sub & 1) * 8) = o;
+                    }
                     if (MODE == MODE_TRIATT) {
                         float acc[4];
 #pragma unroll
@@ -97,30 +178,30 @@ __global__ void __launch_bounds__(THREADS, 1) row512_kernel(Args p, unsigned int
                             float a = 0.f;
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
-                                const float4 wv = *reinterpret_cast<const float4*>(wb_s + h * 128 + (j * 8 + (lane & 7)) * 4);
-                                a += v[j].x * wv.x + v[j].y * wv.y + v[j].z * wv.z + v[j].w * wv.w;
+                                const float4 wv = *reinterpret_cast<const float4*>(wb_s + h * 128 + (j * 8 + sub) * 4);
+                                a += v[i][j].x * wv.x + v[i][j].y * wv.y + v[i][j].z * wv.z + v[i][j].w * wv.w;
                             }
                             a += __shfl_xor_sync(0xffffffffu, a, 1);
                             a += __shfl_xor_sync(0xffffffffu, a, 2);
                             a += __shfl_xor_sync(0xffffffffu, a, 4);
                             acc[h] = a;
                         }
-                        const int sub = lane & 7;
-                        if (sub < 4 && pos0 + r < span) {
+                        if (sub < 4 && fl[i] >= 0) {
                             float val = sub == 0 ? acc[0] : (sub == 1 ? acc[1] : (sub == 2 ? acc[2] : acc[3]));
-                            p.tri_bias[sub * p.bias_hs + (long long)line * p.bias_qs + pos0 + r] = __float2bfloat16(val + wb_s[512 + sub]);
+                            p.tri_bias[sub * p.bias_hs + (long long)line * p.bias_qs + pos0 + row] = __float2bfloat16(val);
                         }
                     }
-                });
+                }
+            }
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(&B->a_full[stage]);
         }
         if (!ok && lane == 0) atomicOr(status, DEV_STATUS_MBAR_TIMEOUT);
-    } else if (warp == 8) {
+    } else if (warp == MMA_WARP) {
         if (lane == 0) {
             // ---------------------------- MMA issuer ----------------------------
-            constexpr uint32_t idesc = make_idesc_bf16(TM, 256);
+            constexpr uint32_t idesc128 = make_idesc_bf16(TM, 128), idesc256 = make_idesc_bf16(TM, 256);
             const uint32_t w_addr = smem_u32(smem);
             uint32_t it = 0, acc_cnt[2] = {0, 0};
             bool ok = true;
@@ -129,13 +210,23 @@ __global__ void __launch_bounds__(THREADS, 1) row512_kernel(Args p, unsigned int
                 ok = mbar_wait(&B->a_full[stage], ph, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t a_addr = smem_u32(smem + OFF_A + stage * A_TILE_BYTES);
+                const uint32_t x_addr = smem_u32(smem + OFF_A + stage * A_TILE_BYTES);
                 for (int half = 0; half < 2 && ok; ++half) {
                     ok = mbar_wait(&B->acc_empty[half], (acc_cnt[half] & 1) ^ 1, abort_flag);
                     if (!ok) break;
                     ++acc_cnt[half];
                     tc_fence_after();
-                    issue_gemm_k128(tmem_base + half * 256, a_addr, w_addr, 512, half * 256, idesc);
+                    const uint32_t d = tmem_base + half * 256;
+                    if (MODE == MODE_TRIMUL) {
+                        // channels on the lanes: A = 128 weight rows, B = the x tile (positions)
+                        gemm_k128(d, w_addr + (half * 256) * 128, W_KB, x_addr, A_KB_BYTES, idesc128);
+                        gemm_k128(d + 128, w_addr + (half * 256 + 128) * 128, W_KB, x_addr, A_KB_BYTES, idesc128);
+                    } else if (half == 0) {
+                        gemm_k128(d, x_addr, A_KB_BYTES, w_addr, W_KB, idesc256);                    // [q | k]
+                    } else {
+                        gemm_k128(d, x_addr, A_KB_BYTES, w_addr + 256 * 128, W_KB, idesc128);        // g
+                        gemm_k128(d + 128, w_addr + 384 * 128, W_KB, x_addr, A_KB_BYTES, idesc128);  // v^T
+                    }
                     umma_commit(&B->acc_full[half]);
                 }
                 if (ok) umma_commit(&B->a_empty[stage]);
@@ -144,119 +235,147 @@ __global__ void __launch_bounds__(THREADS, 1) row512_kernel(Args p, unsigned int
         }
     } else {
         // ---------------------------- epilogue ----------------------------
-        const int quarter = warp & 3;
-        const int row = quarter * 32 + lane;
+        // Each round moves one [128 x 128] bf16 block out: TMEM -> registers -> swizzled staging tile
+        // -> two TMA stores of [128 rows x 64 elements], so global memory only sees full lines.
+        const int quarter = warp & 3, chalf = (warp - EPI_WARP0) >> 2;
+        const int epi_tid = threadIdx.x - EPI_WARP0 * 32;
+        const int lrow = quarter * 32 + lane;                     // TMEM lane of this thread = staging row
         const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
-        __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem + OFF_STAGE) + (warp - EPI_WARP0) * 32 * STG_PITCH;
+        uint8_t* stg = smem + OFF_STG;
         uint32_t acc_cnt = 0;
         bool ok = true;
-        for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+        // tanh_mode: 0 = copy, 1 = p' + p' * tanh(g')  (gate columns at +128), 2 = 0.5 + 0.5 * tanh(x)
+        auto load64 = [&](uint32_t taddr, int tanh_mode, uint4 (&o)[8]) {
+            uint32_t r[2][32];
+            tmem_ld_32x32(taddr, r[0]);
+            tmem_ld_32x32(taddr + 32, r[1]);
+            uint32_t gq[2][32];
+            if (tanh_mode == 1) {
+                tmem_ld_32x32(taddr + 128, gq[0]);
+                tmem_ld_32x32(taddr + 160, gq[1]);
+            }
+            tmem_ld_wait();
+            uint32_t* w = reinterpret_cast<uint32_t*>(o);
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+                float v0 = __uint_as_float(r[e >> 4][(2 * e) & 31]), v1 = __uint_as_float(r[e >> 4][(2 * e + 1) & 31]);
+                if (tanh_mode == 1) {
+                    v0 = fmaf(v0, tanh_approx(__uint_as_float(gq[e >> 4][(2 * e) & 31])), v0);
+                    v1 = fmaf(v1, tanh_approx(__uint_as_float(gq[e >> 4][(2 * e + 1) & 31])), v1);
+                } else if (tanh_mode == 2) {
+                    v0 = fmaf(0.5f, tanh_approx(v0), 0.5f);
+                    v1 = fmaf(0.5f, tanh_approx(v1), 0.5f);
+                }
+                w[e] = pack_bf16x2(v0, v1);
+            }
+        };
+        auto store_round = [&](const uint4 (&o)[8], const CUtensorMap* map, int c0, int c1, int c2, int c3) {
+            if (epi_tid == 0) bulk_wait_read0();               // the previous round's stores have read the staging tile
+            named_bar_sync(EPI_BAR_ID, EPI_WARPS * 32);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) *reinterpret_cast<uint4*>(stg + chalf * STG_BOX + sw128(lrow, j)) = o[j];
+            fence_proxy_async();
+            named_bar_sync(EPI_BAR_ID, EPI_WARPS * 32);
+            if (epi_tid == 0 && !(p.debug & 2)) {
+                tma_store_4d(map, stg, c0, c1, c2, c3);
+                tma_store_4d(map, stg + STG_BOX, c0 + 64, c1, c2, c3);
+                bulk_commit();
+            }
+        };
+        for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++acc_cnt) {
             const int line = (int)(t / tpl), pos0 = (int)(t % tpl) * TM;
-            const long long flat = flat_of(line, pos0 + row);
-            float mk = 1.f;
-            if (MODE == MODE_TRIMUL) mk = flat < 0 ? 0.f : (float)p.mask[flat];
             for (int half = 0; half < 2 && ok; ++half) {
                 ok = mbar_wait(&B->acc_full[half], acc_cnt & 1, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t tbase = tmem_base + lane_off + half * 256;
+                uint4 o[8];
                 if (MODE == MODE_TRIMUL) {
-                    // columns [0,128) = p, [128,256) = g of operand `half`; 32 channels per step
-#pragma unroll 1
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t pr[32], gr[32];
-                        tmem_ld_32x32(tbase + c * 32, pr);
-                        tmem_ld_32x32(tbase + 128 + c * 32, gr);
-                        tmem_ld_wait();
-                        const float* bp = bias_s + half * 256 + c * 32;
-#pragma unroll
-                        for (int e = 0; e < 32; ++e) {
-                            float u = (__uint_as_float(pr[e]) + bp[e]) * sigmoid_tanh(__uint_as_float(gr[e]) + bp[128 + e]) * mk;
-                            stg[e * STG_PITCH + lane] = __float2bfloat16(u);
-                        }
-                        __syncwarp();
-                        const long long ps = p.plane_stride[half];
-                        __nv_bfloat16* planes = p.planes[half] + (long long)(c * 32) * ps +
-                                                (long long)(line / p.row_group[half]) * p.group_stride[half] +
-                                                (long long)(line % p.row_group[half]) * p.pitch;
-#pragma unroll
-                        for (int pass = 0; pass < 4; ++pass) {
-                            int ch = pass * 8 + (lane >> 2), piece = lane & 3;
-                            int col = pos0 + quarter * 32 + piece * 8;
-                            if (col + 8 <= p.pitch)
-                                *reinterpret_cast<uint4*>(planes + ch * ps + col) =
-                                    *reinterpret_cast<const uint4*>(stg + ch * STG_PITCH + piece * 8);
-                        }
-                        __syncwarp();
-                    }
+                    // lane = channel of operand `half`, columns = positions; this warp's 64 positions = box `chalf`
+                    load64(tbase + chalf * 64, 1, o);
+                    const int rg = p.row_group[half];
+                    store_round(o, half == 0 ? &map0 : &map1, pos0, line % rg, 0, line / rg);
+                } else if (half == 0) {
+                    // lane = position, columns = channels of q then k; box `chalf` = channels 64*chalf ..
+                    load64(tbase + chalf * 64, 0, o);
+                    store_round(o, &map0, 0, pos0, line, 0);
+                    load64(tbase + 128 + chalf * 64, 0, o);
+                    store_round(o, &map1, 0, pos0, line, 0);
                 } else {
-                    // half 0: [q | k], half 1: [v | g]; 32 columns = one head
-#pragma unroll 1
-                    for (int c = 0; c < 8; ++c) {
-                        uint32_t r[32];
-                        tmem_ld_32x32(tbase + c * 32, r);
-                        tmem_ld_wait();
-                        const float* bp = bias_s + half * 256 + c * 32;
-                        const int head = c & 3;
-                        const bool is_gate = half == 1 && c >= 4;
-                        const bool is_vt = half == 1 && c < 4 && p.vt_pitch > 0;
-                        if (is_vt) {
-#pragma unroll
-                            for (int e = 0; e < 32; ++e) stg[e * STG_PITCH + lane] = __float2bfloat16(__uint_as_float(r[e]) + bp[e]);
-                            __syncwarp();
-#pragma unroll
-                            for (int pass = 0; pass < 4; ++pass) {
-                                int dd = pass * 8 + (lane >> 2), piece = lane & 3;
-                                int col = pos0 + quarter * 32 + piece * 8;
-                                if (col + 8 <= p.vt_pitch)
-                                    *reinterpret_cast<uint4*>(p.v + (((long long)line * 4 + head) * 32 + dd) * p.vt_pitch + col) =
-                                        *reinterpret_cast<const uint4*>(stg + dd * STG_PITCH + piece * 8);
-                            }
-                            __syncwarp();
-                        } else if (flat >= 0) {
-                            uint4 o[4];
-                            uint32_t* ow = reinterpret_cast<uint32_t*>(o);
-#pragma unroll
-                            for (int e = 0; e < 16; ++e) {
-                                float v0 = __uint_as_float(r[2 * e]) + bp[2 * e], v1 = __uint_as_float(r[2 * e + 1]) + bp[2 * e + 1];
-                                if (is_gate) { v0 = sigmoid_tanh(v0); v1 = sigmoid_tanh(v1); }
-                                ow[e] = pack_bf16x2(v0, v1);
-                            }
-                            __nv_bfloat16* dst;
-                            if (is_gate) dst = p.g + flat * KC + head * 32;
-                            else {
-                                __nv_bfloat16* base = half == 0 ? (c < 4 ? p.q : p.k) : p.v;
-                                dst = base + (((long long)line * 4 + head) * span + pos0 + row) * 32;
-                            }
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) reinterpret_cast<uint4*>(dst)[e] = o[e];
-                        }
-                    }
+                    load64(tbase + chalf * 64, 2, o);                       // gate: sigmoid
+                    if (p.transposed) store_round(o, &map2, 0, line, pos0, 0);
+                    else store_round(o, &map2, 0, pos0, line, 0);
+                    load64(tbase + 128 + chalf * 64, 0, o);                 // v^T: lane = v channel, columns = positions
+                    store_round(o, &map3, pos0, 0, line, 0);
                 }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&B->acc_empty[half]);
             }
-            ++acc_cnt;
         }
+        if (epi_tid == 0) bulk_wait0();
         if (!ok && lane == 0) atomicOr(status, DEV_STATUS_MBAR_TIMEOUT);
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 8) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+    if (warp == MMA_WARP) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+static int make_maps(int mode, const Args& a, CUtensorMap (&m)[4]) {
+    const CUtensorMapDataType bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    const int span = a.transposed ? a.rows : a.n, lines = a.transposed ? a.n : a.rows;
+    int rc;
+    if (mode == MODE_TRIMUL) {
+        for (int i = 0; i < 2; ++i) {
+            const int rg = a.row_group[i], groups = (lines + rg - 1) / rg;
+            cuuint64_t dims[4] = {(cuuint64_t)a.pitch, (cuuint64_t)(rg < lines ? rg : lines), 128, (cuuint64_t)groups};
+            cuuint64_t str[3] = {(cuuint64_t)a.pitch * 2, (cuuint64_t)a.plane_stride[i] * 2,
+                                 (cuuint64_t)(groups > 1 ? a.group_stride[i] : a.plane_stride[i] * 128) * 2};
+            cuuint32_t box[4] = {64, 1, 128, 1};
+            if ((rc = tmap_encode(&m[i], bf, a.planes[i], 4, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, "planes")) != B200PF_OK) return rc;
+        }
+        m[2] = m[0];
+        m[3] = m[0];
+        return B200PF_OK;
+    }
+    {   // q, k: [line][pos][128]
+        cuuint64_t dims[4] = {128, (cuuint64_t)span, (cuuint64_t)lines, 1};
+        cuuint64_t str[3] = {256, (cuuint64_t)span * 256, (cuuint64_t)span * 256 * lines};
+        cuuint32_t box[4] = {64, 128, 1, 1};
+        if ((rc = tmap_encode(&m[0], bf, a.q, 4, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, "q")) != B200PF_OK) return rc;
+        if ((rc = tmap_encode(&m[1], bf, a.k, 4, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, "k")) != B200PF_OK) return rc;
+    }
+    {   // g in the layout of the z view [rows][n][128]
+        cuuint64_t dims[4] = {128, (cuuint64_t)a.n, (cuuint64_t)a.rows, 1};
+        cuuint64_t str[3] = {256, (cuuint64_t)a.n * 256, (cuuint64_t)a.n * 256 * a.rows};
+        cuuint32_t box_rows[4] = {64, 128, 1, 1}, box_cols[4] = {64, 1, 128, 1};
+        if ((rc = tmap_encode(&m[2], bf, a.g, 4, dims, str, a.transposed ? box_cols : box_rows, CU_TENSOR_MAP_SWIZZLE_128B, "g")) != B200PF_OK) return rc;
+    }
+    {   // v transposed: [line][head*32 + d][vt_pitch]
+        cuuint64_t dims[4] = {(cuuint64_t)a.vt_pitch, 128, (cuuint64_t)lines, 1};
+        cuuint64_t str[3] = {(cuuint64_t)a.vt_pitch * 2, (cuuint64_t)a.vt_pitch * 256, (cuuint64_t)a.vt_pitch * 256 * lines};
+        cuuint32_t box[4] = {64, 128, 1, 1};
+        if ((rc = tmap_encode(&m[3], bf, a.v, 4, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, "vt")) != B200PF_OK) return rc;
+    }
+    return B200PF_OK;
 }
 
 template <int MODE>
 static int launch(const Args& a, cudaStream_t st) {
     unsigned int* status = device_status_word();
     B200PF_REQUIRE(status, B200PF_ERR_CUDA, "row512: no device status word");
+    B200PF_REQUIRE(a.ln_gamma && a.ln_beta && aligned16(a.ln_gamma) && aligned16(a.ln_beta), B200PF_ERR_INVALID,
+                   "row512: LayerNorm gain / offset must be given and 16-byte aligned");
     B200PF_CUDA(cudaFuncSetAttribute(row512_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     int dev = 0, sms = 148;
     B200PF_CUDA(cudaGetDevice(&dev));
     B200PF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     int span = a.transposed ? a.rows : a.n, lines = a.transposed ? a.n : a.rows;
     long long tiles = (long long)lines * ((span + TM - 1) / TM);
-    row512_kernel<MODE><<<(unsigned)(tiles < sms ? tiles : sms), THREADS, SMEM_BYTES, st>>>(a, status);
+    CUtensorMap m[4];
+    int rc = make_maps(MODE, a, m);
+    if (rc != B200PF_OK) return rc;
+    row512_kernel<MODE><<<(unsigned)(tiles < sms ? tiles : sms), THREADS, SMEM_BYTES, st>>>(m[0], m[1], m[2], m[3], a, status);
     B200PF_LAUNCH_CHECK();
     return B200PF_OK;
 }

@@ -9,9 +9,10 @@ namespace r512 {
 
 struct Args {
     const float* z;
+    const float* ln_gamma;             // [128] LayerNorm gain, applied by the loader warps
+    const float* ln_beta;              // [128] LayerNorm offset
     const uint8_t* mask;               // triangle multiplication: [rows][n]
-    const __nv_bfloat16* w;            // [512][128] packed weights
-    const float* wbias;                // [512] (triangle attention: [528])
+    const __nv_bfloat16* w;            // [512][128] weights (layout per mode, see row512_tc.cu)
     // triangle-multiplication outputs
     __nv_bfloat16* planes[2];
     long long plane_stride[2], group_stride[2];
@@ -19,11 +20,12 @@ struct Args {
     int pitch;
     // triangle-attention outputs
     __nv_bfloat16 *q, *k, *v, *g, *tri_bias;
-    const __nv_bfloat16* w_bias_rows;  // packed rows 512..515 (bf16), applied in fp32
+    const float* w_bias_f32;           // [4][128] triangle-bias rows (already times log2 e)
     long long bias_hs, bias_qs;
     int vt_pitch;
     // geometry: z viewed as [rows][n][128]; transposed != 0 walks columns (incoming / ending)
     int rows, n, transposed;
+    int debug;                         // timing experiments only: 1 = loaders skip loads, 2 = epilogue skips stores, 4 = epilogue skips math
 };
 
 int launch_trimul(const Args& a, cudaStream_t st);

@@ -154,7 +154,7 @@ triatt_core_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 if (!ok) break;
                 mbar_arrive_expect_tx(&B->q_full, 2 * Q_BYTES);
                 for (int w = 0; w < 2; ++w)
-                    tma_load_4d(smem + OFF_Q + w * Q_BYTES, &map_q, &B->q_full, 0, qt * AQ, h, clamp_line(line0 + w));
+                    tma_load_4d(smem + OFF_Q + w * Q_BYTES, &map_q, &B->q_full, 0, h, qt * AQ, clamp_line(line0 + w));
                 for (int j = 0; j < T; ++j, ++g) {
                     uint32_t stage = g % ST, phase = (g / ST) & 1;
                     ok = mbar_wait(&B->kv_empty[stage], phase ^ 1, abort_flag);
@@ -164,7 +164,7 @@ triatt_core_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     tma_load_3d(st, &map_bias, &B->kv_full[stage], j * AK, h, qt * AQ);
                     for (int w = 0; w < 2; ++w) {
                         int line = clamp_line(line0 + w);
-                        tma_load_4d(st + BIAS_BYTES + w * K_BYTES, &map_k, &B->kv_full[stage], 0, j * AK, h, line);
+                        tma_load_4d(st + BIAS_BYTES + w * K_BYTES, &map_k, &B->kv_full[stage], 0, h, j * AK, line);
                         tma_load_4d(st + BIAS_BYTES + 2 * K_BYTES + w * VT_BYTES, &map_vt, &B->kv_full[stage], j * AK, 0, h, line);
                     }
                 }
@@ -415,10 +415,10 @@ extern "C" int b200pf_triatt_core_tc(const b200pf_bf16* q, const b200pf_bf16* k,
     B200PF_REQUIRE(o_line_stride % 8 == 0 && o_pos_stride % 8 == 0, B200PF_ERR_INVALID, "triatt_core_tc: bad o strides");
     CUtensorMap mq, mk, mvt, mb;
     int rc;
-    {
-        cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)n, 4, (cuuint64_t)lines};
-        cuuint64_t str[3] = {(cuuint64_t)HD * 2, (cuuint64_t)n * HD * 2, (cuuint64_t)4 * n * HD * 2};
-        cuuint32_t boxq[4] = {HD, AQ, 1, 1}, boxk[4] = {HD, AK, 1, 1};
+    {   // q, k: [line][pos][head][32]; coordinates (d, head, pos, line)
+        cuuint64_t dims[4] = {(cuuint64_t)HD, 4, (cuuint64_t)n, (cuuint64_t)lines};
+        cuuint64_t str[3] = {(cuuint64_t)HD * 2, (cuuint64_t)4 * HD * 2, (cuuint64_t)n * 4 * HD * 2};
+        cuuint32_t boxq[4] = {HD, 1, AQ, 1}, boxk[4] = {HD, 1, AK, 1};
         if ((rc = encode(&mq, q, 4, dims, str, boxq, CU_TENSOR_MAP_SWIZZLE_64B, "q")) != B200PF_OK) return rc;
         if ((rc = encode(&mk, k, 4, dims, str, boxk, CU_TENSOR_MAP_SWIZZLE_64B, "k")) != B200PF_OK) return rc;
     }

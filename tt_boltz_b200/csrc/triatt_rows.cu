@@ -226,11 +226,14 @@ static int grid_for_units(long long units, int ctas_per_sm) {
 
 using namespace b200pf;
 
-extern "C" int b200pf_triatt_producer(const float* z, const b200pf_bf16* w_qkvg, const float* bias_qkvg,
+extern "C" int b200pf_triatt_producer(const float* z, const float* ln_gamma, const float* ln_beta, const float* w_bias_f32,
+                                      const b200pf_bf16* w_qkvg, const float* bias_qkvg,
                                       b200pf_bf16* q, b200pf_bf16* k, b200pf_bf16* v, b200pf_bf16* g,
                                       b200pf_bf16* tri_bias, long long bias_hs, long long bias_qs,
                                       int vt_pitch, int rows, int n, int ending, int impl, void* stream) {
-    B200PF_REQUIRE(z && w_qkvg && bias_qkvg && q && k && v && g && tri_bias, B200PF_ERR_INVALID, "triatt_producer: null pointer");
+    B200PF_REQUIRE(z && w_qkvg && q && k && v && g && tri_bias, B200PF_ERR_INVALID, "triatt_producer: null pointer");
+    B200PF_REQUIRE(impl == 0 ? (ln_gamma && ln_beta && w_bias_f32 && vt_pitch > 0) : (bias_qkvg != nullptr), B200PF_ERR_INVALID,
+                   "triatt_producer: impl 0 needs ln_gamma / ln_beta / w_bias_f32 and vt_pitch > 0, impl 1 needs bias_qkvg");
     B200PF_REQUIRE(rows > 0 && n > 0, B200PF_ERR_INVALID, "triatt_producer: bad rows/n");
     B200PF_REQUIRE(bias_hs > 0 && bias_qs > 0, B200PF_ERR_INVALID, "triatt_producer: bad bias strides");
     B200PF_REQUIRE(vt_pitch == 0 || (vt_pitch % 8 == 0 && vt_pitch >= (ending ? rows : n)), B200PF_ERR_INVALID,
@@ -242,9 +245,9 @@ extern "C" int b200pf_triatt_producer(const float* z, const b200pf_bf16* w_qkvg,
     B200PF_REQUIRE(impl == 0 || impl == 1, B200PF_ERR_INVALID, "triatt_producer: impl must be 0 (tcgen05) or 1 (mma.sync)");
     if (impl == 0) {
         r512::Args a{};
-        a.z = z; a.w = (const __nv_bfloat16*)w_qkvg; a.wbias = bias_qkvg;
+        a.z = z; a.w = (const __nv_bfloat16*)w_qkvg; a.ln_gamma = ln_gamma; a.ln_beta = ln_beta; a.w_bias_f32 = w_bias_f32;
         a.q = (__nv_bfloat16*)q; a.k = (__nv_bfloat16*)k; a.v = (__nv_bfloat16*)v; a.g = (__nv_bfloat16*)g;
-        a.tri_bias = (__nv_bfloat16*)tri_bias; a.w_bias_rows = (const __nv_bfloat16*)w_qkvg + 512 * 128;
+        a.tri_bias = (__nv_bfloat16*)tri_bias;
         a.bias_hs = bias_hs; a.bias_qs = bias_qs; a.vt_pitch = vt_pitch;
         a.rows = rows; a.n = n; a.transposed = ending;
         return r512::launch_triatt(a, (cudaStream_t)stream);

@@ -45,7 +45,8 @@ static int scratch_address(__nv_bfloat16** out) {
 
 using namespace b200pf;
 
-extern "C" int b200pf_tri_mul_noalloc(float* z, const uint8_t* mask, const b200pf_bf16* w_pg, const float* bias_pg,
+extern "C" int b200pf_tri_mul_noalloc(float* z, const uint8_t* mask, const float* ln_gamma, const float* ln_beta,
+                                      const b200pf_bf16* w_pg,
                                       const b200pf_bf16* w_pout, const b200pf_bf16* w_gout,
                                       const float* bias_pout, const float* bias_gout,
                                       int n, int incoming, void* stream) {
@@ -64,7 +65,7 @@ extern "C" int b200pf_tri_mul_noalloc(float* z, const uint8_t* mask, const b200p
     // The producer writes every element the contraction reads and the contraction every element
     // the epilogue reads (padding columns included), so nothing has to be cleared between calls.
     b200pf_plane_out oa{a, plane_stride, 0, 0}, ob{b, plane_stride, 0, 0};
-    rc = b200pf_trimul_producer(z, mask, bias_pg, w_pg, &oa, &ob, pitch, n, n, incoming, 0, 0, stream);
+    rc = b200pf_trimul_producer(z, mask, ln_gamma, ln_beta, nullptr, w_pg, &oa, &ob, pitch, n, n, incoming, 0, 0, stream);
     if (rc != B200PF_OK) return rc;
     b200pf_planes pa{a, plane_stride, 0, pitch, n, n, 1, 0}, pb{b, plane_stride, 0, pitch, n, n, 1, 0};
     rc = b200pf_trimul_contract(&pa, &pb, nullptr, nullptr, reinterpret_cast<b200pf_bf16*>(x), plane_stride, pitch,

@@ -7,6 +7,8 @@
 //   w_pg  [512][128]: 8 chunks of 64 rows; chunk q holds, for channels 32*(q%4) .. +31 of operand
 //         a (q < 4) or b (q >= 4), the 32 p_in rows followed by the 32 g_in rows, LN gain folded in;
 //   bias_pg [512]   : the matching LN-offset term (W beta), fp32, same order.
+#include <stdlib.h>
+
 #include "row512_tc.h"
 #include "rowtile.cuh"
 
@@ -229,12 +231,14 @@ static int grid_for(long long units) {
 
 using namespace b200pf;
 
-extern "C" int b200pf_trimul_producer(const float* z, const uint8_t* mask, const float* bias_pg,
-                                      const b200pf_bf16* w_pg, const b200pf_plane_out* a_out,
+extern "C" int b200pf_trimul_producer(const float* z, const uint8_t* mask, const float* ln_gamma, const float* ln_beta,
+                                      const float* bias_pg, const b200pf_bf16* w_pg, const b200pf_plane_out* a_out,
                                       const b200pf_plane_out* b_out, int pitch, int rows, int n, int incoming,
                                       int value_mode, int impl, void* stream) {
-    B200PF_REQUIRE(z && mask && bias_pg && w_pg && a_out && b_out && a_out->ptr && b_out->ptr, B200PF_ERR_INVALID,
+    B200PF_REQUIRE(z && mask && w_pg && a_out && b_out && a_out->ptr && b_out->ptr, B200PF_ERR_INVALID,
                    "trimul_producer: null pointer");
+    B200PF_REQUIRE(impl == 0 ? (ln_gamma && ln_beta) : (bias_pg != nullptr), B200PF_ERR_INVALID,
+                   "trimul_producer: impl 0 needs ln_gamma / ln_beta, impl 1 needs bias_pg");
     B200PF_REQUIRE(rows > 0 && n > 0 && rows <= n, B200PF_ERR_INVALID, "trimul_producer: bad rows/n");
     B200PF_REQUIRE(value_mode == 0, B200PF_ERR_UNSUPPORTED, "trimul_producer: value mode %d is not built", value_mode);
     int cols = incoming ? rows : n, prow = incoming ? n : rows;
@@ -258,12 +262,13 @@ extern "C" int b200pf_trimul_producer(const float* z, const uint8_t* mask, const
     B200PF_REQUIRE(impl == 0 || impl == 1, B200PF_ERR_INVALID, "trimul_producer: impl must be 0 (tcgen05) or 1 (mma.sync)");
     if (impl == 0) {
         r512::Args a{};
-        a.z = z; a.mask = mask; a.w = p.w_pg; a.wbias = bias_pg;
+        a.z = z; a.mask = mask; a.w = p.w_pg; a.ln_gamma = ln_gamma; a.ln_beta = ln_beta;
         for (int i = 0; i < 2; ++i) {
             a.planes[i] = p.planes[i]; a.plane_stride[i] = p.plane_stride[i];
             a.group_stride[i] = p.group_stride[i]; a.row_group[i] = p.row_group[i];
         }
         a.pitch = pitch; a.rows = rows; a.n = n; a.transposed = incoming;
+        { const char* dbg = getenv("B200PF_DEBUG_ROW512"); a.debug = dbg ? atoi(dbg) : 0; }
         return r512::launch_trimul(a, (cudaStream_t)stream);
     }
     B200PF_CUDA(cudaFuncSetAttribute(trimul_producer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PRODUCER_SMEM));

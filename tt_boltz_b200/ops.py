@@ -55,7 +55,17 @@ class Workspace:
 # bf16 tier (fused kernels)
 # ------------------------------------------------------------------------------------------------
 def trimul_producer_weights(w: Dict[str, torch.Tensor], impl: int):
-    return (w["bias_pg_tc"], w["w_pg_tc"]) if impl == 0 else (w["bias_pg"], w["w_pg"])
+    """(ln_gamma, ln_beta, bias_pg, w_pg) pointers for the chosen producer implementation."""
+    if impl == 0:
+        return ptr(w["ln_in_gamma"]), ptr(w["ln_in_beta"]), None, ptr(w["w_pg_tc"])
+    return None, None, ptr(w["bias_pg"]), ptr(w["w_pg"])
+
+
+def triatt_producer_weights(w: Dict[str, torch.Tensor], impl: int):
+    """(ln_gamma, ln_beta, w_bias_f32, w, bias) pointers for the chosen producer implementation."""
+    if impl == 0:
+        return ptr(w["ln_gamma"]), ptr(w["ln_beta"]), ptr(w["w_bias_f32"]), ptr(w["w_qkgv_tc"]), None
+    return None, None, None, ptr(w["w_qkvg"]), ptr(w["bias_qkvg"])
 
 
 def tri_mul_bf16(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Tensor], ws: Workspace,
@@ -65,8 +75,7 @@ def tri_mul_bf16(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Tens
     st = stream()
     oa = PlaneOut(ptr(a), ws.plane_stride, 0, 0)
     ob = PlaneOut(ptr(b), ws.plane_stride, 0, 0)
-    bias_pg, w_pg = trimul_producer_weights(w, row_impl)
-    call("b200pf_trimul_producer", ptr(z), ptr(mask_u8), ptr(bias_pg), ptr(w_pg), C.byref(oa), C.byref(ob),
+    call("b200pf_trimul_producer", ptr(z), ptr(mask_u8), *trimul_producer_weights(w, row_impl), C.byref(oa), C.byref(ob),
          ws.pitch, n, n, int(incoming), 0, row_impl, st)
     pa = Planes(ptr(a), ws.plane_stride, 0, ws.pitch, n, n, 1, 0)
     pb = Planes(ptr(b), ws.plane_stride, 0, ws.pitch, n, n, 1, 0)
@@ -83,7 +92,9 @@ def tri_att_bf16(z: torch.Tensor, masks: PairMasks, w: Dict[str, torch.Tensor], 
     q, k, v, g, o = ws.buf
     st = stream()
     bias_hs, bias_qs = ws.pitch, 4 * ws.pitch          # layout [query][head][key]: a row shard is contiguous
-    call("b200pf_triatt_producer", ptr(z), ptr(w["w_qkvg"]), ptr(w["bias_qkvg"]), ptr(q), ptr(k), ptr(v), ptr(g),
+    if core != 0:
+        row_impl = 1          # the mma.sync core reads v untransposed, which only the mma.sync producer writes
+    call("b200pf_triatt_producer", ptr(z), *triatt_producer_weights(w, row_impl), ptr(q), ptr(k), ptr(v), ptr(g),
          ptr(ws.tri_bias), bias_hs, bias_qs, ws.pitch if core == 0 else 0, n, n, int(ending), row_impl, st)
     if ending:      # line = column j: o element (line, pos) -> z position [pos][line]
         o_ls, o_ps = C_Z, n * C_Z

@@ -103,9 +103,8 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
     w = pk["tri_mul_out"]
     a_loc, b_loc, x = _bf16(C_Z * nr * pn, dev), _bf16(C_Z * nr * pn, dev), _bf16(C_Z * nr * pn, dev)
     oa, ob = PlaneOut(ptr(a_loc), nr * pn, 0, 0), PlaneOut(ptr(b_loc), nr * pn, 0, 0)
-    bias_pg, w_pg = ops.trimul_producer_weights(w, layer.row_impl)
-    call("b200pf_trimul_producer", ptr(z_loc), ptr(mask_loc), ptr(bias_pg), ptr(w_pg), C.byref(oa), C.byref(ob),
-         pn, nr, n, 0, 0, layer.row_impl, st)
+    call("b200pf_trimul_producer", ptr(z_loc), ptr(mask_loc), *ops.trimul_producer_weights(w, layer.row_impl),
+         C.byref(oa), C.byref(ob), pn, nr, n, 0, 0, layer.row_impl, st)
     b_all = all_gather_cat(b_loc, group)                                             # [P][D][nr][pn]
     pa = Planes(ptr(a_loc), nr * pn, 0, pn, nr, n, 1, 0)
     pb = Planes(ptr(b_all), nr * pn, C_Z * nr * pn, pn, nr, n, world, 0)
@@ -119,9 +118,8 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
     bt_loc = _bf16(C_Z * n * pr, dev)                                                # [D][j][k_local]
     oa = PlaneOut(ptr(at_send), nr * pr, C_Z * nr * pr, nr)
     ob = PlaneOut(ptr(bt_loc), n * pr, 0, 0)
-    bias_pg, w_pg = ops.trimul_producer_weights(w, layer.row_impl)
-    call("b200pf_trimul_producer", ptr(z_loc), ptr(mask_loc), ptr(bias_pg), ptr(w_pg), C.byref(oa), C.byref(ob),
-         pr, nr, n, 1, 0, layer.row_impl, st)
+    call("b200pf_trimul_producer", ptr(z_loc), ptr(mask_loc), *ops.trimul_producer_weights(w, layer.row_impl),
+         C.byref(oa), C.byref(ob), pr, nr, n, 1, 0, layer.row_impl, st)
     at_recv = all_to_all_blocks(at_send.view(world, -1), group)                      # [src][D][i_local][k_local of src]
     bt_all = all_gather_cat(bt_loc, group)                                           # [src][D][j][k_local of src]
     pa = Planes(ptr(at_recv), nr * pr, C_Z * nr * pr, pr, nr, nr, world, 1)
@@ -135,7 +133,7 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
     w = pk["tri_att_start"]
     q, k, v, g, o = (_bf16(nr * n * C_Z, dev) for _ in range(5))
     bias_loc = _bf16(nr * 4 * pn, dev)
-    call("b200pf_triatt_producer", ptr(z_loc), ptr(w["w_qkvg"]), ptr(w["bias_qkvg"]), ptr(q), ptr(k), ptr(v), ptr(g),
+    call("b200pf_triatt_producer", ptr(z_loc), *ops.triatt_producer_weights(w, layer.row_impl), ptr(q), ptr(k), ptr(v), ptr(g),
          ptr(bias_loc), pn, 4 * pn, pn, nr, n, 0, layer.row_impl, st)
     bias_all = all_gather_cat(bias_loc, group)                                       # [query][head][key]
     call("b200pf_triatt_core_tc", ptr(q), ptr(k), ptr(v), pn, ptr(bias_all), pn, 4 * pn, ptr(masks.rows[r0:r0 + nr]),
@@ -145,7 +143,7 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
     # ---- triangle attention, ending node (lines = local columns of the column shard) ------------
     w = pk["tri_att_end"]
     zc = rows_to_cols(z_loc, group)                                                  # [N][nr][128] fp32
-    call("b200pf_triatt_producer", ptr(zc), ptr(w["w_qkvg"]), ptr(w["bias_qkvg"]), ptr(q), ptr(k), ptr(v), ptr(g),
+    call("b200pf_triatt_producer", ptr(zc), *ops.triatt_producer_weights(w, layer.row_impl), ptr(q), ptr(k), ptr(v), ptr(g),
          ptr(bias_loc), pn, 4 * pn, pn, n, nr, 1, layer.row_impl, st)
     bias_all = all_gather_cat(bias_loc, group)
     call("b200pf_triatt_core_tc", ptr(q), ptr(k), ptr(v), pn, ptr(bias_all), pn, 4 * pn, ptr(masks.cols[r0:r0 + nr]),

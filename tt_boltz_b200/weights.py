@@ -34,14 +34,14 @@ def pack_trimul(sd: Dict[str, torch.Tensor], pre: str, device) -> Dict[str, torc
         ch0 = (q // 4) * d + (q % 4) * 32
         rows += [f["p_in.weight"][ch0:ch0 + 32], f["g_in.weight"][ch0:ch0 + 32]]
     w_pg, bias_pg = _fold(torch.cat(rows, 0), f["norm_in.weight"], f["norm_in.bias"])
-    # tcgen05 producer: [p_a | g_a | p_b | g_b], 128 rows each
-    rows_tc = [f["p_in.weight"][:d], f["g_in.weight"][:d], f["p_in.weight"][d:], f["g_in.weight"][d:]]
-    w_pg_tc, bias_pg_tc = _fold(torch.cat(rows_tc, 0), f["norm_in.weight"], f["norm_in.bias"])
+    # tcgen05 producer: 0.5 * [p_a | g_a | p_b | g_b], 128 rows each, LayerNorm affine applied in the kernel
+    w_pg_tc = 0.5 * torch.cat([f["p_in.weight"][:d], f["g_in.weight"][:d], f["p_in.weight"][d:], f["g_in.weight"][d:]], 0)
     w_pout, bias_pout = _fold(f["p_out.weight"], f["norm_out.weight"], f["norm_out.bias"])
     w_gout, bias_gout = _fold(f["g_out.weight"], f["norm_in.weight"], f["norm_in.bias"])
     bf = lambda t: t.to(device=device, dtype=torch.bfloat16).contiguous()
     fp = lambda t: t.to(device=device, dtype=torch.float32).contiguous()
-    return {"w_pg": bf(w_pg), "bias_pg": fp(bias_pg), "w_pg_tc": bf(w_pg_tc), "bias_pg_tc": fp(bias_pg_tc), "w_pout": bf(w_pout), "bias_pout": fp(bias_pout),
+    return {"w_pg": bf(w_pg), "bias_pg": fp(bias_pg), "w_pg_tc": bf(w_pg_tc),
+            "ln_in_gamma": fp(f["norm_in.weight"]), "ln_in_beta": fp(f["norm_in.bias"]), "w_pout": bf(w_pout), "bias_pout": fp(bias_pout),
             "w_gout": bf(w_gout), "bias_gout": fp(bias_gout)}
 
 
@@ -55,7 +55,14 @@ def pack_triatt(sd: Dict[str, torch.Tensor], pre: str, device) -> Dict[str, torc
                       f["mha.linear_v.weight"], f["mha.linear_g.weight"], f["linear.weight"] * LOG2E,
                       torch.zeros(12, C_Z)], 0)
     w, b = _fold(rows, f["layer_norm.weight"], f["layer_norm.bias"])
-    return {"w_qkvg": w.to(device=device, dtype=torch.bfloat16).contiguous(),
+    # tcgen05 producer: [q (scaled) | k | 0.5 g | v], LayerNorm affine and the bias heads applied in fp32 in the kernel
+    w_tc = torch.cat([f["mha.linear_q.weight"] * (LOG2E / math.sqrt(TRI_HEAD_DIM)), f["mha.linear_k.weight"],
+                      0.5 * f["mha.linear_g.weight"], f["mha.linear_v.weight"]], 0)
+    return {"w_qkgv_tc": w_tc.to(device=device, dtype=torch.bfloat16).contiguous(),
+            "w_bias_f32": (f["linear.weight"] * LOG2E).to(device=device, dtype=torch.float32).contiguous(),
+            "ln_gamma": f["layer_norm.weight"].to(device=device, dtype=torch.float32).contiguous(),
+            "ln_beta": f["layer_norm.bias"].to(device=device, dtype=torch.float32).contiguous(),
+            "w_qkvg": w.to(device=device, dtype=torch.bfloat16).contiguous(),
             "bias_qkvg": b.to(device=device, dtype=torch.float32).contiguous(),
             "w_o": f["mha.linear_o.weight"].to(device=device, dtype=torch.bfloat16).contiguous()}
 
