@@ -162,6 +162,17 @@ int b200pf_trimul_epilogue(float* z, const b200pf_bf16* x, long long x_plane_str
                            const float* bias_pout, const float* bias_gout,
                            int rows, int n, void* stream);
 
+/* The same epilogue on tcgen05 (production path).  x is multiplied RAW as an MN-major operand
+ * straight from its planes; the LayerNorm over the channels of x is applied after the GEMM per
+ * position (mean / rstd from the tile), the update leaves through TMA reduce-add into z.
+ *   w_pout: bf16 [128][128] = 0.5 * W_pout * gamma_out;  wsum: fp32 [128] row sums of that bf16 matrix;
+ *   wb: fp32 [128] = 0.5 * W_pout beta_out;  w_gout: bf16 [128][128] = 0.5 * W_gout;
+ *   ln_in_gamma / ln_in_beta: fp32 [128] LayerNorm of z for the gate, applied in the kernel. */
+int b200pf_trimul_epilogue_tc(float* z, const b200pf_bf16* x, long long x_plane_stride, int x_pitch,
+                              const float* ln_in_gamma, const float* ln_in_beta,
+                              const b200pf_bf16* w_pout, const b200pf_bf16* w_gout,
+                              const float* wsum, const float* wb, int rows, int n, void* stream);
+
 /* Triangle-attention producer: LN -> [q|k|v|g] projection and the 4-head triangle bias.
  * Replaces tt_bio/tenstorrent.py:545-567, 603-614 (reference.py:331-341, 99-120).
  *   z is viewed as [rows][n][128] (a row shard, or a column shard stored [i][j_local][128]);
@@ -232,7 +243,8 @@ int b200pf_transition_z(float* z, const b200pf_bf16* w12, const float* bias12,
  * library image on every GPU that loads it (held until the process exits).
  *   - limit: n <= 128 tokens; larger n is refused with B200PF_ERR_UNSUPPORTED and a message;
  *   - z (fp32 [n][n][128]) is updated in place; mask is [n][n]; weights as for the three stage
- *     entry points with impl 0 (ln_gamma / ln_beta [128], w_pg [512][128], w_pout / w_gout [128][128], bias_* [128]);
+ *     tcgen05 stage entry points (ln_gamma / ln_beta [128], w_pg [512][128], and w_pout / w_gout / wsum / wb as
+ *     for b200pf_trimul_epilogue_tc);
  *   - the call itself never calls cudaMalloc / cudaFree or any allocating routine;
  *   - the first call on a device looks up the device address of the array
  *     (cudaGetSymbolAddress); make that first call before starting any stream capture;
@@ -242,7 +254,7 @@ int b200pf_transition_z(float* z, const b200pf_bf16* w12, const float* bias12,
 int b200pf_tri_mul_noalloc(float* z, const uint8_t* mask, const float* ln_gamma, const float* ln_beta,
                            const b200pf_bf16* w_pg,
                            const b200pf_bf16* w_pout, const b200pf_bf16* w_gout,
-                           const float* bias_pout, const float* bias_gout,
+                           const float* wsum, const float* wb,
                            int n, int incoming, void* stream);
 
 #ifdef __cplusplus

@@ -37,8 +37,8 @@ def test_noalloc_matches_stage_entry_points_twice_in_a_row():
         ops.tri_mul_bf16(z_ref, pm, w, ops.Workspace(n, dev), incoming)
         z_new = z[0].to(dev).clone()
         before = torch.cuda.memory_allocated(dev)
-        call("b200pf_tri_mul_noalloc", ptr(z_new), ptr(pm), ptr(w["ln_in_gamma"]), ptr(w["ln_in_beta"]), ptr(w["w_pg_tc"]), ptr(w["w_pout"]),
-             ptr(w["w_gout"]), ptr(w["bias_pout"]), ptr(w["bias_gout"]), n, int(incoming), stream())
+        call("b200pf_tri_mul_noalloc", ptr(z_new), ptr(pm), ptr(w["ln_in_gamma"]), ptr(w["ln_in_beta"]), ptr(w["w_pg_tc"]), ptr(w["w_pout_tc"]),
+             ptr(w["w_gout_tc"]), ptr(w["wsum_tc"]), ptr(w["wb_tc"]), n, int(incoming), stream())
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated(dev) == before
         assert _lib.device_status() == 0

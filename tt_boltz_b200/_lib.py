@@ -46,6 +46,7 @@ SIGNATURES = {
     "b200pf_trimul_producer": [_vp, _vp, _vp, _vp, _vp, _vp, C.POINTER(PlaneOut), C.POINTER(PlaneOut), _i, _i, _i, _i, _i, _i, _vp],
     "b200pf_trimul_contract": [C.POINTER(Planes), C.POINTER(Planes), _vp, _vp, _vp, _ll, _i, _i, _i, _vp],
     "b200pf_trimul_epilogue": [_vp, _vp, _ll, _i, _vp, _vp, _vp, _vp, _i, _i, _vp],
+    "b200pf_trimul_epilogue_tc": [_vp, _vp, _ll, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "b200pf_triatt_producer": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _vp],
     "b200pf_triatt_core_tc": [_vp, _vp, _vp, _i, _vp, _ll, _ll, _vp, _i, _vp, _ll, _ll, _i, _i, _vp],
     "b200pf_triatt_core": [_vp, _vp, _vp, _vp, _ll, _ll, _i, _vp, _ll, _ll, _vp, _ll, _ll, _i, _i, _i, _vp],

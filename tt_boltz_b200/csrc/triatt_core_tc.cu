@@ -49,6 +49,7 @@ struct Bars {
     uint64_t s_full[2][2], s_empty[2][2];
     uint64_t p_full[2], pv_full[2];
     uint64_t q_full, q_empty;
+    uint64_t turn[2];            // exp-phase hand-off between the two softmax groups (ping-pong)
     uint32_t tmem_slot;
     int abort_flag;
 };
@@ -111,6 +112,8 @@ triatt_core_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         }
         mbar_init(&B->q_full, 1);
         mbar_init(&B->q_empty, 1);
+        mbar_init(&B->turn[0], 4);
+        mbar_init(&B->turn[1], 4);
         B->abort_flag = 0;
         fence_barrier_init();
     }
@@ -246,7 +249,7 @@ triatt_core_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const int row = quarter * 32 + lane;
         const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
         uint8_t* p_tile = smem + OFF_P + w * P_BYTES;
-        uint32_t g = 0, s_cnt = 0, pv_cnt = 0;
+        uint32_t g = 0, s_cnt = 0, pv_cnt = 0, turn_cnt = 0;
         bool ok = true;
         for (long long it = blockIdx.x; it < items && ok; it += gridDim.x) {
             int qt, h, line0;
@@ -288,8 +291,15 @@ triatt_core_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 for (int e = 0; e < 64; ++e) s[e] = __uint_as_float(sr[e >> 5][e & 31]);
                 float mx = m_run;
                 if (fast) {
+                    float m4[4] = {mx, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                    for (int e = 0; e < 64; e += 2) mx = max3(mx, s[e], s[e + 1]);
+                    for (int e = 0; e < 64; e += 8) {
+                        m4[0] = max3(m4[0], s[e], s[e + 1]);
+                        m4[1] = max3(m4[1], s[e + 2], s[e + 3]);
+                        m4[2] = max3(m4[2], s[e + 4], s[e + 5]);
+                        m4[3] = max3(m4[3], s[e + 6], s[e + 7]);
+                    }
+                    mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
                 } else {
 #pragma unroll
                     for (int e = 0; e < 64; ++e) {
@@ -316,7 +326,11 @@ triatt_core_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     for (int e = 0; e < HD; ++e) o_acc[e] = (o_acc[e] + __uint_as_float(pv[e])) * scale;
                     l_run = (l_run + __uint_as_float(ps)) * scale;
                 }
-                // probabilities -> P tile (bf16, 128-byte swizzled rows)
+                // probabilities -> P tile (bf16, 128-byte swizzled rows).  The two groups take turns on the
+                // exponential (MUFU) phase so that one group's loads / waits overlap the other's exponentials.
+                ok = mbar_wait(&B->turn[w], (turn_cnt & 1) ^ (w == 0 ? 1u : 0u), abort_flag);
+                if (!ok) break;
+                ++turn_cnt;
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
                     uint4 pk;
@@ -329,7 +343,7 @@ triatt_core_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 fence_proxy_async();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&B->p_full[w]);
+                if (lane == 0) { mbar_arrive(&B->turn[w ^ 1]); mbar_arrive(&B->p_full[w]); }
             }
             if (!ok) break;
             // last tile's P V, normalise, store

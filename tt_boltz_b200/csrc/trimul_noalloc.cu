@@ -48,7 +48,7 @@ using namespace b200pf;
 extern "C" int b200pf_tri_mul_noalloc(float* z, const uint8_t* mask, const float* ln_gamma, const float* ln_beta,
                                       const b200pf_bf16* w_pg,
                                       const b200pf_bf16* w_pout, const b200pf_bf16* w_gout,
-                                      const float* bias_pout, const float* bias_gout,
+                                      const float* wsum, const float* wb,
                                       int n, int incoming, void* stream) {
     B200PF_REQUIRE(n > 0, B200PF_ERR_INVALID, "tri_mul_noalloc: n must be positive");
     B200PF_REQUIRE(n <= NOALLOC_MAX_N, B200PF_ERR_UNSUPPORTED,
@@ -71,6 +71,6 @@ extern "C" int b200pf_tri_mul_noalloc(float* z, const uint8_t* mask, const float
     rc = b200pf_trimul_contract(&pa, &pb, nullptr, nullptr, reinterpret_cast<b200pf_bf16*>(x), plane_stride, pitch,
                                 NOALLOC_CH, 0, stream);
     if (rc != B200PF_OK) return rc;
-    return b200pf_trimul_epilogue(z, reinterpret_cast<const b200pf_bf16*>(x), plane_stride, pitch, w_pout, w_gout,
-                                  bias_pout, bias_gout, n, n, stream);
+    return b200pf_trimul_epilogue_tc(z, reinterpret_cast<const b200pf_bf16*>(x), plane_stride, pitch, ln_gamma, ln_beta,
+                                     w_pout, w_gout, wsum, wb, n, n, stream);
 }

@@ -68,6 +68,15 @@ def triatt_producer_weights(w: Dict[str, torch.Tensor], impl: int):
     return None, None, None, ptr(w["w_qkvg"]), ptr(w["bias_qkvg"])
 
 
+def trimul_epilogue(z, x, plane_stride, pitch, w, rows, n, impl: int) -> None:
+    if impl == 0:
+        call("b200pf_trimul_epilogue_tc", ptr(z), ptr(x), plane_stride, pitch, ptr(w["ln_in_gamma"]), ptr(w["ln_in_beta"]),
+             ptr(w["w_pout_tc"]), ptr(w["w_gout_tc"]), ptr(w["wsum_tc"]), ptr(w["wb_tc"]), rows, n, stream())
+    else:
+        call("b200pf_trimul_epilogue", ptr(z), ptr(x), plane_stride, pitch, ptr(w["w_pout"]), ptr(w["w_gout"]),
+             ptr(w["bias_pout"]), ptr(w["bias_gout"]), rows, n, stream())
+
+
 def tri_mul_bf16(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Tensor], ws: Workspace,
                  incoming: bool, contract_variant: int = 0, row_impl: int = 0) -> None:
     n = z.shape[0]
@@ -81,8 +90,7 @@ def tri_mul_bf16(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Tens
     pb = Planes(ptr(b), ws.plane_stride, 0, ws.pitch, n, n, 1, 0)
     call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), None, None, ptr(x), ws.plane_stride, ws.pitch,
          C_Z, contract_variant, st)
-    call("b200pf_trimul_epilogue", ptr(z), ptr(x), ws.plane_stride, ws.pitch, ptr(w["w_pout"]), ptr(w["w_gout"]),
-         ptr(w["bias_pout"]), ptr(w["bias_gout"]), n, n, st)
+    trimul_epilogue(z, x, ws.plane_stride, ws.pitch, w, n, n, row_impl)
 
 
 def tri_att_bf16(z: torch.Tensor, masks: PairMasks, w: Dict[str, torch.Tensor], ws: Workspace,

@@ -109,8 +109,7 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
     pa = Planes(ptr(a_loc), nr * pn, 0, pn, nr, n, 1, 0)
     pb = Planes(ptr(b_all), nr * pn, C_Z * nr * pn, pn, nr, n, world, 0)
     call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), None, None, ptr(x), nr * pn, pn, C_Z, layer.contract_variant, st)
-    call("b200pf_trimul_epilogue", ptr(z_loc), ptr(x), nr * pn, pn, ptr(w["w_pout"]), ptr(w["w_gout"]),
-         ptr(w["bias_pout"]), ptr(w["bias_gout"]), nr, n, st)
+    ops.trimul_epilogue(z_loc, x, nr * pn, pn, w, nr, n, layer.row_impl)
 
     # ---- triangle multiplication, incoming -------------------------------------------------------
     w = pk["tri_mul_in"]
@@ -125,8 +124,7 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
     pa = Planes(ptr(at_recv), nr * pr, C_Z * nr * pr, pr, nr, nr, world, 1)
     pb = Planes(ptr(bt_all), n * pr, C_Z * n * pr, pr, n, nr, world, 1)
     call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), None, None, ptr(x), nr * pn, pn, C_Z, layer.contract_variant, st)
-    call("b200pf_trimul_epilogue", ptr(z_loc), ptr(x), nr * pn, pn, ptr(w["w_pout"]), ptr(w["w_gout"]),
-         ptr(w["bias_pout"]), ptr(w["bias_gout"]), nr, n, st)
+    ops.trimul_epilogue(z_loc, x, nr * pn, pn, w, nr, n, layer.row_impl)
     del a_loc, b_loc, b_all, at_send, at_recv, bt_loc, bt_all, x
 
     # ---- triangle attention, starting node (lines = local rows) ---------------------------------

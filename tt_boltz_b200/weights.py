@@ -38,9 +38,15 @@ def pack_trimul(sd: Dict[str, torch.Tensor], pre: str, device) -> Dict[str, torc
     w_pg_tc = 0.5 * torch.cat([f["p_in.weight"][:d], f["g_in.weight"][:d], f["p_in.weight"][d:], f["g_in.weight"][d:]], 0)
     w_pout, bias_pout = _fold(f["p_out.weight"], f["norm_out.weight"], f["norm_out.bias"])
     w_gout, bias_gout = _fold(f["g_out.weight"], f["norm_in.weight"], f["norm_in.bias"])
+    # tcgen05 epilogue: raw-x GEMM with 0.5 * W_pout * gamma_out, LayerNorm over channels applied after the GEMM
+    w_pout_tc = (0.5 * f["p_out.weight"] * f["norm_out.weight"][None, :]).to(torch.bfloat16)
+    wsum_tc = w_pout_tc.float().sum(1)
+    wb_tc = 0.5 * (f["p_out.weight"] @ f["norm_out.bias"])
+    w_gout_tc = 0.5 * f["g_out.weight"]
     bf = lambda t: t.to(device=device, dtype=torch.bfloat16).contiguous()
     fp = lambda t: t.to(device=device, dtype=torch.float32).contiguous()
-    return {"w_pg": bf(w_pg), "bias_pg": fp(bias_pg), "w_pg_tc": bf(w_pg_tc),
+    return {"w_pg": bf(w_pg), "bias_pg": fp(bias_pg), "w_pg_tc": bf(w_pg_tc), "w_pout_tc": bf(w_pout_tc), "wsum_tc": fp(wsum_tc), "wb_tc": fp(wb_tc),
+            "w_gout_tc": bf(w_gout_tc),
             "ln_in_gamma": fp(f["norm_in.weight"]), "ln_in_beta": fp(f["norm_in.bias"]), "w_pout": bf(w_pout), "bias_pout": fp(bias_pout),
             "w_gout": bf(w_gout), "bias_gout": fp(bias_gout)}
 
