@@ -38,6 +38,9 @@ int         b200pf_version(void);
 const char* b200pf_last_error(void);
 /* Number of kernels this library has launched in the calling process (for benchmarks). */
 long long   b200pf_launch_count(void);
+/* Profiling aid: copies and clears the cycle counters the tcgen05 attention core accumulates when
+ * the environment variable B200PF_ATT_DEBUG is set (per-phase cycles of one softmax warp).  Synchronises. */
+int         b200pf_debug_counters(long long* host_out, int n);
 /* Reads (and clears) the device status word kernels set when a bounded wait runs out.
  * Synchronises `stream`.  0 = clean. */
 int         b200pf_device_status(void* stream);

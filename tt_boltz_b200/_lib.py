@@ -35,6 +35,7 @@ SIGNATURES = {
     "b200pf_last_error": [],
     "b200pf_launch_count": [],
     "b200pf_device_status": [_vp],
+    "b200pf_debug_counters": [C.POINTER(_ll), _i],
     "b200pf_f32_layernorm": [_vp, _vp, _vp, _vp, _ll, _i, _vp],
     "b200pf_f32_linear": [_vp, _vp, _vp, _vp, _ll, _i, _i, _i, _vp],
     "b200pf_f32_gate": [_vp, _vp, _vp, _vp, _ll, _i, _i, _vp],

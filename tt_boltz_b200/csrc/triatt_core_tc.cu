@@ -1,19 +1,23 @@
 // Fused triangle attention on tcgen05 / TMEM (the production attention core).
 //
 // One CTA works on (head, 128-query tile, a PAIR of lines) at a time and walks the keys in tiles
-// of 64.  Roles (320 threads):
+// of 64.  Roles (352 threads):
 //   warps 0-3  softmax group 0  -> line l        (thread = query row = TMEM lane)
 //   warps 4-7  softmax group 1  -> line l + 1
 //   warp  8    TMA producer     (bias tile shared by both lines, K and V^T tiles per line)
-//   warp  9    MMA issuer       (S = Q K^T into TMEM, then O_tile = P V with P read from smem)
+//   warps 9,10 MMA issuers      (one per group: S = Q K^T + bias into TMEM, then O_tile = P V)
 // Per key tile and group:  S (128 x 64 fp32, TMEM) (the bf16 bias tile, fetched once for both lines, is added inside the same
 // MMA chain by multiplying it with an identity tile) -> mask -> running max -> p = exp2(s - m) (fp32 ex2.approx, packed to bf16)
-// -> P tile in shared memory (128-byte swizzled A operand) -> tcgen05.mma with V^T.
+// -> packed bf16 pairs written back to TENSOR memory (tcgen05.st) and used from there as the A
+// operand of tcgen05.mma with V^T: the probabilities never touch shared memory, whose bandwidth
+// is the scarce resource of this kernel (Q, K, V^T and the bias tile are re-read every tile).
 // V^T carries an extra row of ones, so column 32 of the PV result is the row sum of exactly the
 // bf16 probabilities that were multiplied: no separate summation.  The running output stays in
 // registers (32 fp32 per thread) and is rescaled when the maximum moves.
 // Scores are in the log2 domain (host folds log2(e)/sqrt(32) into W_q and log2(e) into the bias).
 // Every wait is bounded; a wait that runs out raises the status word and the CTA unwinds.
+#include <stdlib.h>
+
 #include "sm100.cuh"
 
 namespace b200pf {
@@ -28,12 +32,11 @@ constexpr int STAGE_BYTES = BIAS_BYTES + 2 * K_BYTES + 2 * VT_BYTES;     // 3686
 constexpr int Q_BYTES = AQ * HD * 2;             // 8192 per line, SW64
 constexpr int P_BYTES = AQ * AK * 2;             // 16384 per group, SW128
 constexpr int OFF_Q = ST * STAGE_BYTES;
-constexpr int OFF_P = OFF_Q + 2 * Q_BYTES;
-constexpr int OFF_IDENT = OFF_P + 2 * P_BYTES;     // [64 keys][64] bf16 identity, SW128: adds the bias tile inside the MMA
+constexpr int OFF_IDENT = OFF_Q + 4 * Q_BYTES;     // [64 keys][64] bf16 identity, SW128: adds the bias tile inside the MMA
 constexpr int IDENT_BYTES = AK * AK * 2;
 constexpr int OFF_BAR = OFF_IDENT + IDENT_BYTES;
 constexpr int SMEM_BYTES = OFF_BAR + 512 + 1024;
-constexpr int THREADS = 320;
+constexpr int THREADS = 352;
 constexpr uint32_t TX_STAGE = BIAS_BYTES + 2 * K_BYTES + 2 * VT_TMA_BYTES;
 constexpr float MASKED_SCORE = -1.0e9f * 1.4426950408889634f;
 
@@ -42,13 +45,17 @@ struct Args {
     __nv_bfloat16* o;
     long long o_ls, o_ps;
     int mask_pitch, lines, n;
+    int debug;                  // non-zero: accumulate cycle counters (profiling aid)
 };
+
+// Cycle counters of softmax group 0 / warp 0 / lane 0 of CTA 0 (profiling aid, read by b200pf_debug_counters).
+__device__ long long g_att_cycles[16];
 
 struct Bars {
     uint64_t kv_full[ST], kv_empty[ST];
     uint64_t s_full[2][2], s_empty[2][2];
     uint64_t p_full[2], pv_full[2];
-    uint64_t q_full, q_empty;
+    uint64_t q_full[2], q_empty[2];
     uint64_t turn[2];            // exp-phase hand-off between the two softmax groups (ping-pong)
     uint32_t tmem_slot;
     int abort_flag;
@@ -110,8 +117,7 @@ triatt_core_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             mbar_init(&B->p_full[w], 4);
             mbar_init(&B->pv_full[w], 1);
         }
-        mbar_init(&B->q_full, 1);
-        mbar_init(&B->q_empty, 1);
+        for (int i = 0; i < 2; ++i) { mbar_init(&B->q_full[i], 1); mbar_init(&B->q_empty[i], 2); }
         mbar_init(&B->turn[0], 4);
         mbar_init(&B->turn[1], 4);
         B->abort_flag = 0;
@@ -153,11 +159,12 @@ triatt_core_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             for (long long it = blockIdx.x; it < items && ok; it += gridDim.x, ++qn) {
                 int qt, h, line0;
                 decode(it, qt, h, line0);
-                ok = mbar_wait(&B->q_empty, (qn & 1) ^ 1, abort_flag);
+                const uint32_t qb = qn & 1, qph = (qn >> 1) & 1;           // Q tiles are double buffered across items
+                ok = mbar_wait(&B->q_empty[qb], qph ^ 1, abort_flag);
                 if (!ok) break;
-                mbar_arrive_expect_tx(&B->q_full, 2 * Q_BYTES);
+                mbar_arrive_expect_tx(&B->q_full[qb], 2 * Q_BYTES);
                 for (int w = 0; w < 2; ++w)
-                    tma_load_4d(smem + OFF_Q + w * Q_BYTES, &map_q, &B->q_full, 0, h, qt * AQ, clamp_line(line0 + w));
+                    tma_load_4d(smem + OFF_Q + (qb * 2 + w) * Q_BYTES, &map_q, &B->q_full[qb], 0, h, qt * AQ, clamp_line(line0 + w));
                 for (int j = 0; j < T; ++j, ++g) {
                     uint32_t stage = g % ST, phase = (g / ST) & 1;
                     ok = mbar_wait(&B->kv_empty[stage], phase ^ 1, abort_flag);
@@ -178,17 +185,19 @@ triatt_core_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
             }
         }
-    } else if (warp == 9) {
+    } else if (warp == 9 || warp == 10) {
         if (lane == 0) {
-            // ------------------------------ MMA issuer ------------------------------
+            // ------------------------------ MMA issuer of softmax group w ------------------------------
+            // One issuing thread per group: S of the next key tile goes out a full iteration ahead of
+            // the group that consumes it, and the two groups do not wait on each other's P tiles.
+            const int w = warp - 9;
             constexpr uint32_t idesc_s = make_idesc_bf16(AQ, AK);
             constexpr uint32_t idesc_pv = make_idesc_bf16(AQ, PV_N);
-            const uint32_t q_addr = smem_u32(smem + OFF_Q), p_addr = smem_u32(smem + OFF_P), ident_addr = smem_u32(smem + OFF_IDENT);
-            uint32_t g = 0, qn = 0;
-            uint32_t s_cnt[2] = {0, 0}, p_cnt[2] = {0, 0};
+            const uint32_t ident_addr = smem_u32(smem + OFF_IDENT);
+            uint32_t g = 0, qn = 0, s_cnt = 0, p_cnt = 0;
             bool ok = true;
-            auto issue_s = [&](int w, uint32_t stage) -> bool {
-                uint32_t b = s_cnt[w] & 1, ph = (s_cnt[w] >> 1) & 1;
+            auto issue_s = [&](uint32_t stage, uint32_t q_addr) -> bool {
+                uint32_t b = s_cnt & 1, ph = (s_cnt >> 1) & 1;
                 if (!mbar_wait(&B->s_empty[w][b], ph ^ 1, abort_flag)) return false;
                 tc_fence_after();
                 uint32_t bias_addr = smem_u32(smem + stage * STAGE_BYTES);
@@ -196,49 +205,45 @@ triatt_core_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 uint32_t d = tmem_base + (uint32_t)((w * 2 + b) * AK);
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk)
-                    umma_bf16(d, desc_sw64(q_addr + w * Q_BYTES + kk * 32), desc_sw64(k_addr + kk * 32), idesc_s, kk ? 1u : 0u);
+                    umma_bf16(d, desc_sw64(q_addr + kk * 32), desc_sw64(k_addr + kk * 32), idesc_s, kk ? 1u : 0u);
 #pragma unroll
                 for (int kk = 0; kk < AK / 16; ++kk)
                     umma_bf16(d, make_desc_k_sw128(bias_addr + kk * 32), make_desc_k_sw128(ident_addr + kk * 32), idesc_s, 1u);
                 umma_commit(&B->s_full[w][b]);
-                ++s_cnt[w];
+                ++s_cnt;
                 return true;
             };
             for (long long it = blockIdx.x; it < items && ok; it += gridDim.x, ++qn) {
-                ok = mbar_wait(&B->q_full, qn & 1, abort_flag);
-                if (!ok) break;
-                ok = mbar_wait(&B->kv_full[g % ST], (g / ST) & 1, abort_flag);
+                const uint32_t qb = qn & 1, qph = (qn >> 1) & 1;
+                const uint32_t q_addr = smem_u32(smem + OFF_Q + (qb * 2 + w) * Q_BYTES);
+                ok = mbar_wait(&B->q_full[qb], qph, abort_flag) && mbar_wait(&B->kv_full[g % ST], (g / ST) & 1, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-                ok = issue_s(0, g % ST) && issue_s(1, g % ST);
-                if (ok && T == 1) umma_commit(&B->q_empty);
+                ok = issue_s(g % ST, q_addr);
+                if (ok && T == 1) umma_commit(&B->q_empty[qb]);
                 for (int j = 0; j < T && ok; ++j, ++g) {
-                    uint32_t stage = g % ST;
+                    const uint32_t stage = g % ST;
                     if (j + 1 < T) {
-                        uint32_t g1 = g + 1;
+                        const uint32_t g1 = g + 1;
                         ok = mbar_wait(&B->kv_full[g1 % ST], (g1 / ST) & 1, abort_flag);
                         if (!ok) break;
                         tc_fence_after();
-                    }
-                    for (int w = 0; w < 2 && ok; ++w) {
-                        if (j + 1 < T) {
-                            ok = issue_s(w, (g + 1) % ST);
-                            if (!ok) break;
-                            if (j + 2 == T && w == 1) umma_commit(&B->q_empty);
-                        }
-                        ok = mbar_wait(&B->p_full[w], p_cnt[w] & 1, abort_flag);
+                        ok = issue_s(g1 % ST, q_addr);
                         if (!ok) break;
-                        ++p_cnt[w];
-                        tc_fence_after();
-                        uint32_t vt_addr = smem_u32(smem + stage * STAGE_BYTES + BIAS_BYTES + 2 * K_BYTES + w * VT_BYTES);
-                        uint32_t d = tmem_base + 256u + (uint32_t)(w * 64);
-#pragma unroll
-                        for (int kk = 0; kk < AK / 16; ++kk)
-                            umma_bf16(d, make_desc_k_sw128(p_addr + w * P_BYTES + kk * 32), make_desc_k_sw128(vt_addr + kk * 32),
-                                      idesc_pv, kk ? 1u : 0u);
-                        umma_commit(&B->pv_full[w]);
-                        umma_commit(&B->kv_empty[stage]);
+                        if (j + 2 == T) umma_commit(&B->q_empty[qb]);
                     }
+                    ok = mbar_wait(&B->p_full[w], p_cnt & 1, abort_flag);
+                    if (!ok) break;
+                    ++p_cnt;
+                    tc_fence_after();
+                    const uint32_t vt_addr = smem_u32(smem + stage * STAGE_BYTES + BIAS_BYTES + 2 * K_BYTES + w * VT_BYTES);
+                    const uint32_t d = tmem_base + 256u + (uint32_t)(w * 64);
+#pragma unroll
+                    for (int kk = 0; kk < AK / 16; ++kk)
+                        umma_bf16_ts(d, tmem_base + 384u + (uint32_t)(w * 32 + kk * 8), make_desc_k_sw128(vt_addr + kk * 32),
+                                     idesc_pv, kk ? 1u : 0u);
+                    umma_commit(&B->pv_full[w]);
+                    umma_commit(&B->kv_empty[stage]);
                 }
             }
             if (!ok) atomicOr(status, DEV_STATUS_MBAR_TIMEOUT);
@@ -248,7 +253,6 @@ triatt_core_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const int w = warp >> 2, quarter = warp & 3;
         const int row = quarter * 32 + lane;
         const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
-        uint8_t* p_tile = smem + OFF_P + w * P_BYTES;
         uint32_t g = 0, s_cnt = 0, pv_cnt = 0, turn_cnt = 0;
         bool ok = true;
         for (long long it = blockIdx.x; it < items && ok; it += gridDim.x) {
@@ -262,6 +266,7 @@ triatt_core_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             float m_run = -INFINITY, l_run = 0.f;
             for (int j = 0; j < T && ok; ++j, ++g) {
                 const uint32_t stage = g % ST;
+                long long c0 = clock64();
                 // mask bytes of this key tile (same for every thread of the group)
                 uint32_t mw[16];
 #pragma unroll
@@ -275,10 +280,12 @@ triatt_core_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 const bool fast = (all == 0x01010101u) && (j * AK + AK <= n);
                 // scores
                 uint32_t b = s_cnt & 1, ph = (s_cnt >> 1) & 1;
+                long long c1 = clock64();
                 ok = mbar_wait(&B->s_full[w][b], ph, abort_flag);
                 if (!ok) break;
                 ++s_cnt;
                 tc_fence_after();
+                long long c2 = clock64();
                 uint32_t sr[2][32];
                 tmem_ld_32x32(tmem_base + lane_off + (uint32_t)((w * 2 + b) * AK), sr[0]);
                 tmem_ld_32x32(tmem_base + lane_off + (uint32_t)((w * 2 + b) * AK + 32), sr[1]);
@@ -286,6 +293,7 @@ triatt_core_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&B->s_empty[w][b]);
+                long long c3 = clock64();
                 float s[64];
 #pragma unroll
                 for (int e = 0; e < 64; ++e) s[e] = __uint_as_float(sr[e >> 5][e & 31]);
@@ -311,12 +319,14 @@ triatt_core_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 }
                 const float scale = ex2_f32(m_run - mx);                // first tile: exp2(-inf) = 0
                 m_run = mx;
+                long long c4 = clock64(), c5 = c4, c6 = c4;
                 // fold in the previous tile's P V (computed with the previous maximum), then rescale
                 if (j > 0) {
                     ok = mbar_wait(&B->pv_full[w], pv_cnt & 1, abort_flag);
                     if (!ok) break;
                     ++pv_cnt;
                     tc_fence_after();
+                    c5 = clock64();
                     uint32_t pv[32], ps;
                     tmem_ld_32x32(tmem_base + lane_off + 256u + (uint32_t)(w * 64), pv);
                     tmem_ld_x1(tmem_base + lane_off + 256u + (uint32_t)(w * 64 + HD), ps);
@@ -325,25 +335,32 @@ triatt_core_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 #pragma unroll
                     for (int e = 0; e < HD; ++e) o_acc[e] = (o_acc[e] + __uint_as_float(pv[e])) * scale;
                     l_run = (l_run + __uint_as_float(ps)) * scale;
+                    c6 = clock64();
                 }
-                // probabilities -> P tile (bf16, 128-byte swizzled rows).  The two groups take turns on the
-                // exponential (MUFU) phase so that one group's loads / waits overlap the other's exponentials.
-                ok = mbar_wait(&B->turn[w], (turn_cnt & 1) ^ (w == 0 ? 1u : 0u), abort_flag);
-                if (!ok) break;
-                ++turn_cnt;
+                // probabilities -> packed bf16 pairs in tensor memory: the A operand of the P V product
+                long long c7 = clock64();
+                {
+                    uint32_t pw[32];
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    uint4 pk;
-                    pk.x = ex2_bf16x2(s[c * 8 + 0] - mx, s[c * 8 + 1] - mx);
-                    pk.y = ex2_bf16x2(s[c * 8 + 2] - mx, s[c * 8 + 3] - mx);
-                    pk.z = ex2_bf16x2(s[c * 8 + 4] - mx, s[c * 8 + 5] - mx);
-                    pk.w = ex2_bf16x2(s[c * 8 + 6] - mx, s[c * 8 + 7] - mx);
-                    *reinterpret_cast<uint4*>(p_tile + row * 128 + ((c ^ (row & 7)) << 4)) = pk;
+                    for (int e = 0; e < 32; ++e) pw[e] = ex2_bf16x2(s[2 * e] - mx, s[2 * e + 1] - mx);
+                    tmem_st_32x32(tmem_base + lane_off + 384u + (uint32_t)(w * 32), pw);
+                    tmem_st_wait();
                 }
-                fence_proxy_async();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) { mbar_arrive(&B->turn[w ^ 1]); mbar_arrive(&B->p_full[w]); }
+                if (lane == 0) mbar_arrive(&B->p_full[w]);
+                if (p.debug && blockIdx.x == 0 && warp == 0 && lane == 0) {
+                    long long c8 = clock64();
+                    g_att_cycles[0] += c1 - c0;   // mask loads
+                    g_att_cycles[1] += c2 - c1;   // wait S
+                    g_att_cycles[2] += c3 - c2;   // tcgen05.ld S
+                    g_att_cycles[3] += c4 - c3;   // max + scale
+                    g_att_cycles[4] += c5 - c4;   // wait PV
+                    g_att_cycles[5] += c6 - c5;   // ld PV + O update
+                    g_att_cycles[6] += c7 - c6;   // wait turn
+                    g_att_cycles[7] += c8 - c7;   // exp + P store + fences
+                    g_att_cycles[8] += 1;
+                }
             }
             if (!ok) break;
             // last tile's P V, normalise, store
@@ -455,8 +472,20 @@ extern "C" int b200pf_triatt_core_tc(const b200pf_bf16* q, const b200pf_bf16* k,
     B200PF_CUDA(cudaGetDevice(&dev));
     B200PF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     long long items = (long long)((lines + 1) / 2) * 4 * ((n + AQ - 1) / AQ);
-    Args a{mask_lines, (__nv_bfloat16*)o, o_line_stride, o_pos_stride, mask_pitch, lines, n};
+    Args a{mask_lines, (__nv_bfloat16*)o, o_line_stride, o_pos_stride, mask_pitch, lines, n, getenv("B200PF_ATT_DEBUG") != nullptr};
     triatt_core_tc_kernel<<<(unsigned)(items < sms ? items : sms), THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(mq, mk, mvt, mb, a, status);
     B200PF_LAUNCH_CHECK();
+    return B200PF_OK;
+}
+
+// Profiling aid: copies (and clears) the attention kernel's cycle counters; synchronises the device.
+extern "C" int b200pf_debug_counters(long long* host_out, int n) {
+    B200PF_REQUIRE(host_out && n > 0 && n <= 16, B200PF_ERR_INVALID, "debug_counters: bad argument");
+    long long tmp[16] = {0};
+    B200PF_CUDA(cudaDeviceSynchronize());
+    B200PF_CUDA(cudaMemcpyFromSymbol(tmp, atc::g_att_cycles, sizeof(tmp)));
+    for (int i = 0; i < n; ++i) host_out[i] = tmp[i];
+    long long zero[16] = {0};
+    B200PF_CUDA(cudaMemcpyToSymbol(atc::g_att_cycles, zero, sizeof(zero)));
     return B200PF_OK;
 }
