@@ -237,6 +237,15 @@ int b200pf_triatt_epilogue(float* z, const b200pf_bf16* o, const b200pf_bf16* g,
 int b200pf_transition_z(float* z, const b200pf_bf16* w12, const float* bias12,
                         const b200pf_bf16* w3, long long n_rows_flat, void* stream);
 
+/* The same transition on tcgen05 (production path): GEMM1 per 64-channel chunk of the hidden layer into
+ * TMEM, SwiGLU in registers, hidden activations written back to TMEM as the A operand of GEMM2,
+ * update through TMA reduce-add into z; weights streamed from L2 by TMA.
+ *   ln_gamma / ln_beta: fp32 [128], applied in the kernel;
+ *   w12: bf16 [8][128][128]: per chunk c the rows 0.5 * fc1[64c .. 64c+63] then fc2[64c .. 64c+63];
+ *   w3:  bf16 [8][128][64]: per chunk the matching 64 columns of fc3. */
+int b200pf_transition_z_tc(float* z, const float* ln_gamma, const float* ln_beta,
+                           const b200pf_bf16* w12, const b200pf_bf16* w3, long long n_rows_flat, void* stream);
+
 /* Triangle multiplication (producer -> contraction -> epilogue, bf16 tier) for callers that cannot
  * allocate device memory.  No counterpart in the reference.
  * Why it exists: the three stages pass their a / b / x planes through global memory, which the

@@ -53,6 +53,7 @@ SIGNATURES = {
     "b200pf_triatt_core": [_vp, _vp, _vp, _vp, _ll, _ll, _i, _vp, _ll, _ll, _vp, _ll, _ll, _i, _i, _i, _vp],
     "b200pf_triatt_epilogue": [_vp, _vp, _vp, _vp, _ll, _vp],
     "b200pf_transition_z": [_vp, _vp, _vp, _vp, _ll, _vp],
+    "b200pf_transition_z_tc": [_vp, _vp, _vp, _vp, _vp, _ll, _vp],
     "b200pf_tri_mul_noalloc": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
 }
 _RESTYPES = {"b200pf_last_error": C.c_char_p, "b200pf_launch_count": _ll}

@@ -119,9 +119,12 @@ def tri_att_bf16(z: torch.Tensor, masks: PairMasks, w: Dict[str, torch.Tensor], 
     call("b200pf_triatt_epilogue", ptr(z), ptr(o), ptr(g), ptr(w["w_o"]), n * n, st)
 
 
-def transition_z_bf16(z: torch.Tensor, w: Dict[str, torch.Tensor]) -> None:
-    n = z.shape[0]
-    call("b200pf_transition_z", ptr(z), ptr(w["w12"]), ptr(w["bias12"]), ptr(w["w3"]), n * n, stream())
+def transition_z_bf16(z: torch.Tensor, w: Dict[str, torch.Tensor], impl: int = 0) -> None:
+    rows = z.shape[0] * z.shape[1]
+    if impl == 0:
+        call("b200pf_transition_z_tc", ptr(z), ptr(w["ln_gamma"]), ptr(w["ln_beta"]), ptr(w["w12_tc"]), ptr(w["w3"]), rows, stream())
+    else:
+        call("b200pf_transition_z", ptr(z), ptr(w["w12"]), ptr(w["bias12"]), ptr(w["w3"]), rows, stream())
 
 
 # ------------------------------------------------------------------------------------------------

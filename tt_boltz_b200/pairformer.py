@@ -99,7 +99,7 @@ class B200PairformerLayer(nn.Module):
             ops.tri_mul_bf16(z, masks.pm, pk["tri_mul_in"], ws, True, self.contract_variant, self.row_impl)
             ops.tri_att_bf16(z, masks, pk["tri_att_start"], ws, False, self.attention_core, self.lines_per_cta, self.row_impl)
             ops.tri_att_bf16(z, masks, pk["tri_att_end"], ws, True, self.attention_core, self.lines_per_cta, self.row_impl)
-            ops.transition_z_bf16(z, pk["transition_z"])
+            ops.transition_z_bf16(z, pk["transition_z"], self.row_impl)
         else:
             ops.tri_mul_f32(z, masks.pm, pk["tri_mul_out"], False)
             ops.tri_mul_f32(z, masks.pm, pk["tri_mul_in"], True)

@@ -151,8 +151,7 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
     del q, k, v, g, o, zc, bias_loc, bias_all
 
     # ---- pair transition ---------------------------------------------------------------------------
-    w = pk["transition_z"]
-    call("b200pf_transition_z", ptr(z_loc), ptr(w["w12"]), ptr(w["bias12"]), ptr(w["w3"]), nr * n, st)
+    ops.transition_z_bf16(z_loc, pk["transition_z"], layer.row_impl)
 
     # ---- single track: attention for the local query rows, the rest replicated --------------------
     if layer.with_s and s is not None:

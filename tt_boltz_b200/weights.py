@@ -83,9 +83,15 @@ def pack_transition_z(sd: Dict[str, torch.Tensor], pre: str, device) -> Dict[str
         rows += [f["fc1.weight"][grp * 16:(grp + 1) * 16], f["fc2.weight"][grp * 16:(grp + 1) * 16]]
     w12, bias12 = _fold(torch.cat(rows, 0), f["norm.weight"], f["norm.bias"])
     w3 = torch.stack([f["fc3.weight"][:, st * 64:(st + 1) * 64] for st in range(hidden // 64)], 0)   # [8][128][64]
+    # tcgen05 kernel: per 64-channel chunk [0.5 * fc1 rows | fc2 rows], LayerNorm affine applied in the kernel
+    w12_tc = torch.stack([torch.cat([0.5 * f["fc1.weight"][c * 64:(c + 1) * 64], f["fc2.weight"][c * 64:(c + 1) * 64]], 0)
+                          for c in range(hidden // 64)], 0)
     return {"w12": w12.to(device=device, dtype=torch.bfloat16).contiguous(),
             "bias12": bias12.to(device=device, dtype=torch.float32).contiguous(),
-            "w3": w3.to(device=device, dtype=torch.bfloat16).contiguous()}
+            "w3": w3.to(device=device, dtype=torch.bfloat16).contiguous(),
+            "w12_tc": w12_tc.to(device=device, dtype=torch.bfloat16).contiguous(),
+            "ln_gamma": f["norm.weight"].to(device=device, dtype=torch.float32).contiguous(),
+            "ln_beta": f["norm.bias"].to(device=device, dtype=torch.float32).contiguous()}
 
 
 def to_device_f32(sd: Dict[str, torch.Tensor], pre: str, device) -> Dict[str, torch.Tensor]:
