@@ -45,12 +45,24 @@ def kernel_work(n: int):
         "b200pf_trimul_producer": (2 * n * n * C * 512, 8 * e),
         "b200pf_trimul_contract": (2 * n ** 3 * C, 6 * e),
         "b200pf_trimul_epilogue": (2 * n * n * C * 256, 10 * e),
+        "b200pf_trimul_epilogue_tc": (2 * n * n * C * 256, 10 * e),
         "b200pf_triatt_producer": (2 * n * n * C * 516, 12 * e),
         "b200pf_triatt_core": (4 * n ** 3 * C, 8 * e + 2 * 4 * n * n),
+        "b200pf_triatt_core_tc": (4 * n ** 3 * C, 8 * e + 2 * 4 * n * n),
         "b200pf_triatt_epilogue": (2 * n * n * C * C, 12 * e),
         "b200pf_transition_z": (6 * n * n * C * 4 * C, 8 * e),
+        "b200pf_transition_z_tc": (6 * n * n * C * 4 * C, 8 * e),
         "b200pf_ln_proj_heads": (2 * n * n * C * 16, 4 * e + 4 * 16 * n * n),
     }
+
+
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per launch divided by the algorithmic bytes, from one
+# `ncu --set full` capture at N = 768 (profiles/tcgen05_kernels_n768_ncu_full.md); traffic grows with N^2 * 128, so
+# the full-size figure is this ratio times the algorithmic bytes at the benchmark's N.
+NCU_TRAFFIC_RATIO = {
+    "b200pf_trimul_contract": 0.92, "b200pf_trimul_producer": 0.92, "b200pf_trimul_epilogue_tc": 0.92,
+    "b200pf_triatt_producer": 0.94, "b200pf_triatt_core_tc": 0.98, "b200pf_triatt_epilogue": 0.95,
+}
 
 
 def measured_peaks():
@@ -245,6 +257,16 @@ def main() -> None:
     # ---- per-kernel pass (one extra, untimed-for-the-metric step with CUDA events per launch) ----
     peaks = measured_peaks()
     kernels, roofline = {}, None
+    if world > 1 and rank == 0:
+        _lib.timer = _lib.KernelTimer()
+    if world > 1:
+        step_dev()
+        if rank == 0:
+            summ = _lib.timer.summary()
+            _lib.timer = None
+            for name, (ms, cnt) in sorted(summ.items(), key=lambda kv: -kv[1][0]):
+                kernels[name] = {"launches": cnt, "ms_per_launch": ms / cnt, "ms_per_block": ms / nb}
+            kernels["_sum_ms_per_block"] = sum(v[0] for v in summ.values()) / nb
     if world == 1:
         _lib.timer = _lib.KernelTimer()
         step_dev()
@@ -257,6 +279,8 @@ def main() -> None:
             if name in work:
                 fl, by = work[name]
                 sec = ms / cnt * 1e-3
+                if name in NCU_TRAFFIC_RATIO:
+                    ent["traffic"] = NCU_TRAFFIC_RATIO[name] * by
                 ent.update({"tflops": fl / sec / 1e12, "gbs": by / sec / 1e9,
                             "frac_tensor": fl / sec / 1e12 / peaks["tflops_sustained"],
                             "frac_hbm": by / sec / 1e9 / peaks["hbm_gbs"]})
@@ -268,10 +292,11 @@ def main() -> None:
             t_tensor, t_hbm = fl / (peaks["tflops_sustained"] * 1e12), by / (peaks["hbm_gbs"] * 1e9)
             if t_tensor >= t_hbm:
                 roofline = {"kernel": top, "bound": "tensor", "achieved": fl / sec / 1e12, "peak": peaks["tflops_sustained"],
-                            "unit": "TFLOP/s", "frac": fl / sec / 1e12 / peaks["tflops_sustained"], "traffic": None}
+                            "unit": "TFLOP/s", "frac": fl / sec / 1e12 / peaks["tflops_sustained"],
+                            "traffic": kernels[top].get("traffic")}
             else:
                 roofline = {"kernel": top, "bound": "hbm", "achieved": by / sec / 1e9, "peak": peaks["hbm_gbs"],
-                            "unit": "GB/s", "frac": by / sec / 1e9 / peaks["hbm_gbs"], "traffic": None}
+                            "unit": "GB/s", "frac": by / sec / 1e9 / peaks["hbm_gbs"], "traffic": kernels[top].get("traffic")}
             roofline["peak_source"] = peaks["source"] + " (sustained bf16 GEMM / copy bandwidth)"
             roofline["algorithmic_per_launch"] = {"flop": fl, "bytes": by}
 
