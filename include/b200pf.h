@@ -86,6 +86,24 @@ int b200pf_f32_attention(const float* q, const float* k, const float* v, float* 
                          long long rs, long long ps, float scale, float inf_value, int order,
                          void* stream);
 
+/* Linear with the result written transposed: yt[n][r] = sum_k x[r][k] w[n][k] (+ bias[n]), rows of yt are
+ * yt_pitch floats apart.  Used to lay K and V out key-contiguous for the single-track attention. */
+int b200pf_f32_linear_t(const float* x, const float* w, const float* bias, float* yt, long long yt_pitch,
+                        long long rows, int k, int n_out, void* stream);
+
+/* b200pf_f32_gate (modes 0-2, no row mask) on operands with separate row pitches (in floats). */
+int b200pf_f32_gate_strided(const float* a, long long a_pitch, const float* b, long long b_pitch, float* y, long long y_pitch,
+                            long long rows, int c, int mode, void* stream);
+
+/* Single-track attention of AttentionPairBias (tt_bio/boltz2.py:357-366) in fp32, head dim 24:
+ *   o[q][h] = sigmoid(g[q][h]) * softmax_k( scale * <q[q][h], k[k][h]> + bias[h][q][k] - inf * (1 - mask[k]) ) v[k][h]
+ * q, g, o are row-major with their own pitches (head h at columns h*24 ..); k and v come transposed,
+ * kt[(h*24 + e)][key] with kt_pitch floats per row (as b200pf_f32_linear_t writes them); g may be NULL. */
+int b200pf_f32_sattention(const float* q, long long q_pitch, const float* g, long long g_pitch,
+                          const float* kt, const float* vt, long long kt_pitch, float* o, long long o_pitch,
+                          const float* bias, long long bias_hs, long long bias_qs, const uint8_t* mask,
+                          int n_q, int n_k, int heads, int hd, float scale, float inf_value, void* stream);
+
 /* dst[j][i][:] (+)= src[i][j][:] for an [n][n][c] tensor (tt_bio/reference.py:326-328, 362-363). */
 int b200pf_f32_transpose01(const float* src, float* dst, int n, int c, int accumulate, void* stream);
 

@@ -43,6 +43,9 @@ SIGNATURES = {
     "b200pf_f32_attention": [_vp, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _i, _i, _i, _i, _i,
                              _ll, _ll, _f, _f, _i, _vp],
     "b200pf_f32_transpose01": [_vp, _vp, _i, _i, _i, _vp],
+    "b200pf_f32_linear_t": [_vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _vp],
+    "b200pf_f32_gate_strided": [_vp, _ll, _vp, _ll, _vp, _ll, _ll, _i, _i, _vp],
+    "b200pf_f32_sattention": [_vp, _ll, _vp, _ll, _vp, _vp, _ll, _vp, _ll, _vp, _ll, _ll, _vp, _i, _i, _i, _i, _f, _f, _vp],
     "b200pf_ln_proj_heads": [_vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _vp],
     "b200pf_trimul_producer": [_vp, _vp, _vp, _vp, _vp, _vp, C.POINTER(PlaneOut), C.POINTER(PlaneOut), _i, _i, _i, _i, _i, _i, _vp],
     "b200pf_trimul_contract": [C.POINTER(Planes), C.POINTER(Planes), _vp, _vp, _vp, _ll, _i, _i, _i, _vp],

@@ -31,7 +31,7 @@ __global__ void f32_layernorm_kernel(const float* __restrict__ x, const float* _
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 f32_linear_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
-                  float* __restrict__ y, long long m, int k, int n, int accumulate) {
+                  float* __restrict__ y, long long m, int k, int n, int accumulate, long long yt_pitch) {
     __shared__ float xs[16][64 + 4];
     __shared__ float ws[16][64 + 4];
     int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
@@ -73,7 +73,7 @@ f32_linear_kernel(const float* __restrict__ x, const float* __restrict__ w, cons
             int c = n0 + tx * 4 + j;
             if (c >= n) continue;
             float v = acc[i][j] + (bias ? bias[c] : 0.f);
-            long long idx = r * n + c;
+            long long idx = yt_pitch > 0 ? (long long)c * yt_pitch + r : r * n + c;      // transposed: y^T[c][r]
             y[idx] = accumulate ? y[idx] + v : v;
         }
     }
@@ -84,18 +84,21 @@ f32_linear_kernel(const float* __restrict__ x, const float* __restrict__ w, cons
 // ------------------------------------------------------------------------------------------
 __global__ void f32_gate_kernel(const float* __restrict__ a, const float* __restrict__ b,
                                 const uint8_t* __restrict__ row_mask, float* __restrict__ y,
-                                long long total, int c, int mode) {
+                                long long total, int c, int mode, long long pa, long long pb, long long py) {
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     long long stride = (long long)gridDim.x * blockDim.x;
     for (; i < total; i += stride) {
-        float av = a[i], bv = b[i];
+        long long r = i / c;
+        int col = (int)(i - r * c);
+        float av = a[r * pa + col], bv = b[r * pb + col];
+        float* yp = y + r * py + col;
         if (mode == 0) {
-            float mk = row_mask ? (float)row_mask[i / c] : 1.f;
-            y[i] = av * sigmoid_precise(bv) * mk;
+            float mk = row_mask ? (float)row_mask[r] : 1.f;
+            *yp = av * sigmoid_precise(bv) * mk;
         } else if (mode == 1) {
-            y[i] = av * sigmoid_precise(av) * bv;
+            *yp = av * sigmoid_precise(av) * bv;
         } else {
-            y[i] += av * sigmoid_precise(bv);
+            *yp += av * sigmoid_precise(bv);
         }
     }
 }
@@ -205,6 +208,101 @@ __global__ void f32_attention_kernel(AttnArgs p) {
             if (lane == e) mine = tot;
         }
         if (lane < HD) p.o[r * p.rs + (long long)qi * p.ps + h * HD + lane] = mine * inv;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Single-track attention, fp32, with K and V given transposed ([head*HD + e][key], keys contiguous):
+// a block owns one head and 32 queries (8 warps x 4 queries), lanes split the keys, so every
+// K / V load is one coalesced line shared by four queries.  Two passes over the keys: row
+// maxima first, then exponentials, the P V partial sums and the row sums; the gate
+// sigmoid(g) is applied before the store.
+// ------------------------------------------------------------------------------------------
+struct SAttnArgs {
+    const float *q, *g, *kt, *vt, *bias;
+    float* o;
+    const uint8_t* mask;
+    long long q_pitch, g_pitch, o_pitch, kt_pitch, bias_hs, bias_qs;
+    int n_q, n_k, heads;
+    float scale, inf_value;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(256) f32_sattention_kernel(SAttnArgs p) {
+    constexpr int QB = 4;
+    __shared__ float qs[8][HD][QB];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qblocks = (p.n_q + 31) / 32;
+    const int h = blockIdx.x / qblocks, q0 = (blockIdx.x % qblocks) * 32 + warp * QB;
+    if (q0 >= p.n_q) return;
+    for (int i = lane; i < HD * QB; i += 32) {
+        int e = i / QB, qb = i % QB;
+        int qi = min(q0 + qb, p.n_q - 1);
+        qs[warp][e][qb] = p.q[(long long)qi * p.q_pitch + h * HD + e] * p.scale;
+    }
+    __syncwarp();
+    const float* kt = p.kt + (long long)h * HD * p.kt_pitch;
+    const float* vt = p.vt + (long long)h * HD * p.kt_pitch;
+    auto logits = [&](int kk, float (&l)[QB]) {
+#pragma unroll
+        for (int qb = 0; qb < QB; ++qb) l[qb] = 0.f;
+#pragma unroll
+        for (int e = 0; e < HD; ++e) {
+            const float kv = kt[(long long)e * p.kt_pitch + kk];
+            const float4 qv = *reinterpret_cast<const float4*>(&qs[warp][e][0]);
+            l[0] = fmaf(qv.x, kv, l[0]); l[1] = fmaf(qv.y, kv, l[1]); l[2] = fmaf(qv.z, kv, l[2]); l[3] = fmaf(qv.w, kv, l[3]);
+        }
+        const float mterm = p.mask ? -p.inf_value * (1.f - (float)p.mask[kk]) : 0.f;
+#pragma unroll
+        for (int qb = 0; qb < QB; ++qb) {
+            int qi = min(q0 + qb, p.n_q - 1);
+            l[qb] = (l[qb] + p.bias[h * p.bias_hs + qi * p.bias_qs + kk]) + mterm;
+        }
+    };
+    float mx[QB];
+#pragma unroll
+    for (int qb = 0; qb < QB; ++qb) mx[qb] = -INFINITY;
+    for (int kk = lane; kk < p.n_k; kk += 32) {
+        float l[QB];
+        logits(kk, l);
+#pragma unroll
+        for (int qb = 0; qb < QB; ++qb) mx[qb] = fmaxf(mx[qb], l[qb]);
+    }
+#pragma unroll
+    for (int qb = 0; qb < QB; ++qb) mx[qb] = warp_max(mx[qb]);
+    float sum[QB], acc[QB][HD];
+#pragma unroll
+    for (int qb = 0; qb < QB; ++qb) {
+        sum[qb] = 0.f;
+#pragma unroll
+        for (int e = 0; e < HD; ++e) acc[qb][e] = 0.f;
+    }
+    for (int kk = lane; kk < p.n_k; kk += 32) {
+        float l[QB];
+        logits(kk, l);
+#pragma unroll
+        for (int qb = 0; qb < QB; ++qb) { l[qb] = expf(l[qb] - mx[qb]); sum[qb] += l[qb]; }
+#pragma unroll
+        for (int e = 0; e < HD; ++e) {
+            const float vv = vt[(long long)e * p.kt_pitch + kk];
+#pragma unroll
+            for (int qb = 0; qb < QB; ++qb) acc[qb][e] = fmaf(l[qb], vv, acc[qb][e]);
+        }
+    }
+#pragma unroll
+    for (int qb = 0; qb < QB; ++qb) {
+        const float inv = 1.f / warp_sum(sum[qb]);
+        float mine = 0.f;
+#pragma unroll
+        for (int e = 0; e < HD; ++e) {
+            float tot = warp_sum(acc[qb][e]);
+            if (lane == e) mine = tot;
+        }
+        const int qi = q0 + qb;
+        if (qi < p.n_q && lane < HD) {
+            float gate = p.g ? sigmoid_precise(p.g[(long long)qi * p.g_pitch + h * HD + lane]) : 1.f;
+            p.o[(long long)qi * p.o_pitch + h * HD + lane] = mine * inv * gate;
+        }
     }
 }
 
@@ -337,7 +435,18 @@ int b200pf_f32_linear(const float* x, const float* w, const float* bias, float* 
     B200PF_REQUIRE(x && w && y && rows >= 0 && k > 0 && n_out > 0, B200PF_ERR_INVALID, "f32_linear: bad argument");
     if (rows == 0) return B200PF_OK;
     dim3 grid((unsigned)((rows + 63) / 64), (unsigned)((n_out + 63) / 64));
-    f32_linear_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(x, w, bias, y, rows, k, n_out, accumulate);
+    f32_linear_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(x, w, bias, y, rows, k, n_out, accumulate, 0);
+    B200PF_LAUNCH_CHECK();
+    return B200PF_OK;
+}
+
+int b200pf_f32_linear_t(const float* x, const float* w, const float* bias, float* yt, long long yt_pitch,
+                        long long rows, int k, int n_out, void* stream) {
+    B200PF_REQUIRE(x && w && yt && rows >= 0 && k > 0 && n_out > 0 && yt_pitch >= rows, B200PF_ERR_INVALID,
+                   "f32_linear_t: bad argument");
+    if (rows == 0) return B200PF_OK;
+    dim3 grid((unsigned)((rows + 63) / 64), (unsigned)((n_out + 63) / 64));
+    f32_linear_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(x, w, bias, yt, rows, k, n_out, 0, yt_pitch);
     B200PF_LAUNCH_CHECK();
     return B200PF_OK;
 }
@@ -349,7 +458,19 @@ int b200pf_f32_gate(const float* a, const float* b, const uint8_t* row_mask, flo
     long long total = rows * c;
     if (total == 0) return B200PF_OK;
     unsigned blocks = (unsigned)min((long long)148 * 16, (total + 255) / 256);
-    f32_gate_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(a, b, row_mask, y, total, c, mode);
+    f32_gate_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(a, b, row_mask, y, total, c, mode, c, c, c);
+    B200PF_LAUNCH_CHECK();
+    return B200PF_OK;
+}
+
+int b200pf_f32_gate_strided(const float* a, long long a_pitch, const float* b, long long b_pitch, float* y, long long y_pitch,
+                            long long rows, int c, int mode, void* stream) {
+    B200PF_REQUIRE(a && b && y && rows >= 0 && c > 0 && mode >= 0 && mode <= 2 && a_pitch >= c && b_pitch >= c && y_pitch >= c,
+                   B200PF_ERR_INVALID, "f32_gate_strided: bad argument");
+    long long total = rows * c;
+    if (total == 0) return B200PF_OK;
+    unsigned blocks = (unsigned)min((long long)148 * 16, (total + 255) / 256);
+    f32_gate_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(a, b, nullptr, y, total, c, mode, a_pitch, b_pitch, y_pitch);
     B200PF_LAUNCH_CHECK();
     return B200PF_OK;
 }
@@ -412,6 +533,20 @@ int b200pf_ln_proj_heads(const float* z, const float* gamma, const float* beta, 
         ln_proj_heads_kernel<4><<<blocks, 256, 0, (cudaStream_t)stream>>>(z, gamma, beta, w, out, out_hs, rows);
     else
         ln_proj_heads_kernel<16><<<blocks, 256, 0, (cudaStream_t)stream>>>(z, gamma, beta, w, out, out_hs, rows);
+    B200PF_LAUNCH_CHECK();
+    return B200PF_OK;
+}
+
+int b200pf_f32_sattention(const float* q, long long q_pitch, const float* g, long long g_pitch,
+                          const float* kt, const float* vt, long long kt_pitch, float* o, long long o_pitch,
+                          const float* bias, long long bias_hs, long long bias_qs, const uint8_t* mask,
+                          int n_q, int n_k, int heads, int hd, float scale, float inf_value, void* stream) {
+    B200PF_REQUIRE(q && kt && vt && o && bias && n_q > 0 && n_k > 0 && heads > 0, B200PF_ERR_INVALID, "f32_sattention: bad argument");
+    B200PF_REQUIRE(hd == 24, B200PF_ERR_UNSUPPORTED, "f32_sattention: built for head dim 24 (got %d)", hd);
+    B200PF_REQUIRE(kt_pitch >= n_k, B200PF_ERR_INVALID, "f32_sattention: kt_pitch must cover the keys");
+    SAttnArgs p{q, g, kt, vt, bias, o, mask, q_pitch, g_pitch, o_pitch, kt_pitch, bias_hs, bias_qs, n_q, n_k, heads, scale, inf_value};
+    unsigned blocks = (unsigned)(heads * ((n_q + 31) / 32));
+    f32_sattention_kernel<24><<<blocks, 256, 0, (cudaStream_t)stream>>>(p);
     B200PF_LAUNCH_CHECK();
     return B200PF_OK;
 }

@@ -226,20 +226,56 @@ def pair_bias_heads(z: torch.Tensor, w: Dict[str, torch.Tensor]) -> torch.Tensor
     return bias
 
 
+def pack_single_track(w_att: Dict[str, torch.Tensor], w_trans: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+    """Concatenated fp32 weights so that q|g, k|v and fc1|fc2 are one GEMM launch each."""
+    cs = w_att["proj_q.weight"].shape[0]
+    return {
+        "w_qg": torch.cat([w_att["proj_q.weight"], w_att["proj_g.weight"]], 0).contiguous(),
+        "b_qg": torch.cat([w_att["proj_q.bias"], torch.zeros(cs, device=w_att["proj_q.bias"].device)], 0).contiguous(),
+        "w_kv": torch.cat([w_att["proj_k.weight"], w_att["proj_v.weight"]], 0).contiguous(),
+        "w_12": torch.cat([w_trans["fc1.weight"], w_trans["fc2.weight"]], 0).contiguous(),
+    }
+
+
+def single_track_local(s: torch.Tensor, z_rows: torch.Tensor, tok_mask_u8: torch.Tensor, w_norm: Dict[str, torch.Tensor],
+                       w_att: Dict[str, torch.Tensor], fused: Dict[str, torch.Tensor], num_heads: int,
+                       r0: int = 0) -> torch.Tensor:
+    """Gated attention output sigmoid(g) * softmax(...) v for the query rows [r0, r0 + z_rows.shape[0]) (fp32)."""
+    n, cs = s.shape
+    nq = z_rows.shape[0]
+    hd = cs // num_heads
+    st = stream()
+    sn = f32_layernorm(s, w_norm["weight"], w_norm["bias"])
+    qg = f32_linear(sn[r0:r0 + nq], fused["w_qg"], fused["b_qg"])                       # [nq, 2 cs]: q | g
+    pitch = _round_up(n, 4)
+    kvt = torch.empty(2 * cs, pitch, dtype=torch.float32, device=s.device)              # [k rows | v rows][key]
+    call("b200pf_f32_linear_t", ptr(sn), ptr(fused["w_kv"]), None, ptr(kvt), pitch, n, cs, 2 * cs, st)
+    bias = pair_bias_heads(z_rows, w_att)                                                # [heads][nq * n]
+    o = torch.empty(nq, cs, dtype=torch.float32, device=s.device)
+    call("b200pf_f32_sattention", ptr(qg), 2 * cs, qg.data_ptr() + 4 * cs, 2 * cs, ptr(kvt), kvt.data_ptr() + 4 * cs * pitch, pitch,
+         ptr(o), cs, ptr(bias), nq * n, n, ptr(tok_mask_u8), nq, n, num_heads, hd, 1.0 / math.sqrt(hd), 1e6, st)
+    return o
+
+
+def single_track_finish(s: torch.Tensor, og_all: torch.Tensor, w_att: Dict[str, torch.Tensor],
+                        w_trans: Dict[str, torch.Tensor], fused: Dict[str, torch.Tensor]) -> None:
+    """s += proj_o(gated attention output); s += Transition(s) (tt_bio/reference.py:906-911)."""
+    n, cs = s.shape
+    f32_linear(og_all, w_att["proj_o.weight"], out=s, accumulate=True)
+    x = f32_layernorm(s, w_trans["norm.weight"], w_trans["norm.bias"])
+    h12 = f32_linear(x, fused["w_12"])                                                  # [n, 8 cs]: fc1 | fc2
+    hidden = h12.shape[1] // 2
+    h = torch.empty(n, hidden, dtype=torch.float32, device=s.device)
+    call("b200pf_f32_gate_strided", ptr(h12), 2 * hidden, h12.data_ptr() + 4 * hidden, 2 * hidden, ptr(h), hidden,
+         n, hidden, 1, stream())
+    f32_linear(h, w_trans["fc3.weight"], out=s, accumulate=True)
+
+
 def single_track(s: torch.Tensor, z: torch.Tensor, tok_mask_u8: torch.Tensor, w_norm: Dict[str, torch.Tensor],
                  w_att: Dict[str, torch.Tensor], w_trans: Dict[str, torch.Tensor], num_heads: int,
-                 bias: Optional[torch.Tensor] = None) -> None:
+                 fused: Optional[Dict[str, torch.Tensor]] = None) -> None:
     """s += AttentionPairBias(LN(s), z); s += Transition(s) in fp32 (tt_bio/reference.py:906-912)."""
-    n, cs = s.shape
-    hd = cs // num_heads
-    sn = f32_layernorm(s, w_norm["weight"], w_norm["bias"])
-    q = f32_linear(sn, w_att["proj_q.weight"], w_att["proj_q.bias"])
-    k = f32_linear(sn, w_att["proj_k.weight"])
-    v = f32_linear(sn, w_att["proj_v.weight"])
-    g = f32_linear(sn, w_att["proj_g.weight"])
-    if bias is None:
-        bias = pair_bias_heads(z, w_att)
-    o = _attention_f32(q, k, v, bias, (n * n, n, 1), tok_mask_u8, (0, 1), 1, n, n, num_heads, hd, 0, cs,
-                       1.0 / math.sqrt(hd), 1e6, 1)
-    f32_linear(f32_gate(o, g, 0), w_att["proj_o.weight"], out=s, accumulate=True)
-    transition_f32(s, w_trans)
+    if fused is None:
+        fused = pack_single_track(w_att, w_trans)
+    og = single_track_local(s, z, tok_mask_u8, w_norm, w_att, fused, num_heads)
+    single_track_finish(s, og, w_att, w_trans, fused)

@@ -87,6 +87,7 @@ class B200PairformerLayer(nn.Module):
             pk["pre_norm_s"] = weights.to_device_f32(sd, "pre_norm_s.", device)
             pk["attention"] = weights.to_device_f32(sd, "attention.", device)
             pk["transition_s"] = weights.to_device_f32(sd, "transition_s.", device)
+            pk["s_fused"] = ops.pack_single_track(pk["attention"], pk["transition_s"])
         self._packed = pk
         return pk
 
@@ -107,7 +108,8 @@ class B200PairformerLayer(nn.Module):
             ops.tri_att_f32(z, masks.pm, pk["tri_att_end"], True)
             ops.transition_f32(z, pk["transition_z"])
         if self.with_s and s is not None:
-            ops.single_track(s, z, tok_mask_u8, pk["pre_norm_s"], pk["attention"], pk["transition_s"], self.num_heads)
+            ops.single_track(s, z, tok_mask_u8, pk["pre_norm_s"], pk["attention"], pk["transition_s"], self.num_heads,
+                             pk["s_fused"])
 
     def forward(self, s: Optional[torch.Tensor], z: torch.Tensor, mask: Optional[torch.Tensor] = None,
                 pair_mask: Optional[torch.Tensor] = None, chunk_size_tri_attn: Optional[int] = None,

@@ -158,20 +158,10 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
 
     # ---- single track: attention for the local query rows, the rest replicated --------------------
     if layer.with_s and s is not None:
-        wa, cs = pk["attention"], s.shape[1]
-        hd = cs // layer.num_heads
-        sn = ops.f32_layernorm(s, pk["pre_norm_s"]["weight"], pk["pre_norm_s"]["bias"])
-        qs = ops.f32_linear(sn[r0:r0 + nr], wa["proj_q.weight"], wa["proj_q.bias"])
-        gs = ops.f32_linear(sn[r0:r0 + nr], wa["proj_g.weight"])
-        ks = ops.f32_linear(sn, wa["proj_k.weight"])
-        vs = ops.f32_linear(sn, wa["proj_v.weight"])
-        bias = ops.pair_bias_heads(z_loc, wa)                                        # [16][nr * N]
-        o_loc = torch.empty_like(qs)
-        call("b200pf_f32_attention", ptr(qs), ptr(ks), ptr(vs), ptr(o_loc), ptr(bias), nr * n, n, 1, ptr(tok_mask_u8), 0, 1,
-             1, nr, n, layer.num_heads, hd, 0, cs, 1.0 / math.sqrt(hd), 1e6, 1, st)
-        og_all = all_gather_cat(ops.f32_gate(o_loc, gs, 0), group).view(n, cs)
-        ops.f32_linear(og_all, wa["proj_o.weight"], out=s, accumulate=True)
-        ops.transition_f32(s, pk["transition_s"])
+        og_loc = ops.single_track_local(s, z_loc, tok_mask_u8, pk["pre_norm_s"], pk["attention"], pk["s_fused"],
+                                        layer.num_heads, r0)
+        og_all = all_gather_cat(og_loc, group).view(n, s.shape[1])
+        ops.single_track_finish(s, og_all, pk["attention"], pk["transition_s"], pk["s_fused"])
     return z_loc
 
 
