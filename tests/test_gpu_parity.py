@@ -284,6 +284,19 @@ def test_stack_depth_bf16(dev):
     assert rel_l2(so[0], sr) < 2e-2
 
 
+def test_stack_64_blocks_bf16(dev):
+    """The full trunk depth (64 blocks, independent N(0, 0.02) weights) stays inside the bf16 tier."""
+    n, nb = 48, 64
+    sd = synthetic.make_weights(nb, seed=1)
+    s, z = synthetic.make_inputs(n, seed=0)
+    m, pm = synthetic.tail_padding_mask(n, 5)
+    so, zo = run_module(sd, nb, s, z, m, pm, dev, "bf16")
+    sr, zr = orc.pairformer_stack(s[0], z[0], m[0], pm[0], sd, nb)
+    v = n - 5
+    assert rel_l2(zo[0][:v, :v], zr[:v, :v]) < 2e-2
+    assert rel_l2(so[0][:v], sr[:v]) < 2e-2
+
+
 def test_layer_forward_signature(dev):
     """PairformerLayer.forward(s, z, mask, pair_mask, chunk_size_tri_attn, use_kernels) returns new tensors."""
     n = 32

@@ -134,7 +134,7 @@ row512_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ 
                     fl[i] = flat_of(line, pos0 + row0 + i * 4 + rq);
                     const float4* src = reinterpret_cast<const float4*>(p.z + (fl[i] < 0 ? 0 : fl[i]) * KC);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) v[i][j] = (fl[i] < 0 || (p.debug & 1)) ? make_float4(0.f, 0.f, 0.f, float(j)) : __ldg(src + j * 8 + sub);
+                    for (int j = 0; j < 4; ++j) v[i][j] = fl[i] < 0 ? make_float4(0.f, 0.f, 0.f, 0.f) : __ldg(src + j * 8 + sub);
                 }
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -276,7 +276,7 @@ row512_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ 
             for (int j = 0; j < 8; ++j) *reinterpret_cast<uint4*>(stg + chalf * STG_BOX + sw128(lrow, j)) = o[j];
             fence_proxy_async();
             named_bar_sync(EPI_BAR_ID, EPI_WARPS * 32);
-            if (epi_tid == 0 && !(p.debug & 2)) {
+            if (epi_tid == 0) {
                 tma_store_4d(map, stg, c0, c1, c2, c3);
                 tma_store_4d(map, stg + STG_BOX, c0 + 64, c1, c2, c3);
                 bulk_commit();

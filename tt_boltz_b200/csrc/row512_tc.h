@@ -25,7 +25,6 @@ struct Args {
     int vt_pitch;
     // geometry: z viewed as [rows][n][128]; transposed != 0 walks columns (incoming / ending)
     int rows, n, transposed;
-    int debug;                         // timing experiments only: 1 = loaders skip loads, 2 = epilogue skips stores, 4 = epilogue skips math
 };
 
 int launch_trimul(const Args& a, cudaStream_t st);

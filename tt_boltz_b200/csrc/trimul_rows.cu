@@ -7,8 +7,6 @@
 //   w_pg  [512][128]: 8 chunks of 64 rows; chunk q holds, for channels 32*(q%4) .. +31 of operand
 //         a (q < 4) or b (q >= 4), the 32 p_in rows followed by the 32 g_in rows, LN gain folded in;
 //   bias_pg [512]   : the matching LN-offset term (W beta), fp32, same order.
-#include <stdlib.h>
-
 #include "row512_tc.h"
 #include "rowtile.cuh"
 
@@ -268,7 +266,6 @@ extern "C" int b200pf_trimul_producer(const float* z, const uint8_t* mask, const
             a.group_stride[i] = p.group_stride[i]; a.row_group[i] = p.row_group[i];
         }
         a.pitch = pitch; a.rows = rows; a.n = n; a.transposed = incoming;
-        { const char* dbg = getenv("B200PF_DEBUG_ROW512"); a.debug = dbg ? atoi(dbg) : 0; }
         return r512::launch_trimul(a, (cudaStream_t)stream);
     }
     B200PF_CUDA(cudaFuncSetAttribute(trimul_producer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PRODUCER_SMEM));
