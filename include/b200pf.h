@@ -168,11 +168,32 @@ typedef struct b200pf_planes {
  * the triangle multiplication as a batched K-major GEMM (tcgen05 + TMEM, TMA-fed).
  * Replaces the per-chunk ttnn.matmul at tt_bio/tenstorrent.py:453-460 (reference.py:467, 556).
  * x is bf16 planes x[d][i][j] with pitch x_pitch.  variant 0 = tcgen05 bf16, 1 = SIMT bf16
- * (debug cross-check of variant 0). */
+ * (debug cross-check of variant 0), 2 = tcgen05 block-scaled MXFP8: a / b are byte planes of e4m3
+ * values (pitch, plane_stride in bytes, multiples of 16; nseg 1) and a_scales / b_scales their e8m0
+ * scale blocks as written by b200pf_trimul_producer_mx.  The scales are ignored by variants 0, 1. */
 int b200pf_trimul_contract(const b200pf_planes* a, const b200pf_planes* b,
                            const void* a_scales, const void* b_scales,
                            b200pf_bf16* x, long long x_plane_stride, int x_pitch,
                            int channels, int variant, void* stream);
+
+/* MXFP8 form of the producer (the counterpart of the reference's block-fp8 "fast" mode,
+ * tt_bio/tenstorrent.py:178-181, 432-452): same computation as b200pf_trimul_producer impl 0, but
+ * a / b are quantised straight from fp32 to e4m3 with one e8m0 scale per 32 elements along the
+ * contraction index (scale = smallest power of two with amax / scale <= 448).
+ *   a_out / b_out: byte planes [128][plane rows][pitch] (pitch, plane_stride in bytes, multiples of 16);
+ *   a_scales / b_scales: b200pf_mx_scale_bytes(plane rows, plane cols, 128) bytes each, zeroed once by
+ *   the caller; 512-byte blocks, block = (d * ceil(cols/128) + k/128) * row_blocks + row/128 with
+ *   row_blocks = 2*ceil(rows/256), byte in block = (row%32)*16 + ((row%128)/32)*4 + (k/32)%4. */
+long long b200pf_mx_scale_bytes(int rows, int cols, int channels);
+int b200pf_trimul_producer_mx(const float* z, const uint8_t* mask, const float* ln_gamma, const float* ln_beta,
+                              const b200pf_bf16* w_pg, uint8_t* a_out, uint8_t* b_out, uint8_t* a_scales,
+                              uint8_t* b_scales, long long plane_stride, int pitch, int rows, int n, int incoming,
+                              void* stream);
+/* Expand MXFP8 planes to bf16 planes (exact).  Cross-check of variant 2 and a way to feed MXFP8
+ * operands to consumers that want bf16. */
+int b200pf_mx_dequant(const uint8_t* planes, const uint8_t* scales, b200pf_bf16* out, long long plane_stride,
+                      int pitch, long long out_plane_stride, int out_pitch, int rows, int cols, int channels,
+                      void* stream);
 
 /* Triangle-multiplication epilogue: z += (LN_out(x) W_pout^T) * sigmoid(LN_in(z) W_gout^T).
  * Replaces tt_bio/tenstorrent.py:463-502 plus the residual add :1007-1011.

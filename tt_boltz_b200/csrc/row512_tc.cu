@@ -19,6 +19,7 @@
 // epilogue (two warps per TMEM lane quarter, each taking half of the columns).  TMEM is used as
 // two halves of 256 columns so the epilogue of one half overlaps the MMAs of the next, and the x
 // tile is double buffered so the loaders run a tile ahead.
+#include "mxfp8.cuh"
 #include "row512_tc.h"
 #include "rowtc.cuh"
 #include "tmap.cuh"
@@ -28,7 +29,7 @@ namespace r512 {
 
 using namespace rtc;
 
-constexpr int MODE_TRIMUL = 0, MODE_TRIATT = 1;
+constexpr int MODE_TRIMUL = 0, MODE_TRIATT = 1, MODE_TRIMUL_MX = 2;   // MX: e4m3 planes + e8m0 scales (mxfp8.cuh)
 constexpr int LOAD_WARPS = 4, MMA_WARP = 4, EPI_WARP0 = 5, EPI_WARPS = 8, THREADS = 13 * 32;
 constexpr int W_BYTES = 512 * 128 * 2;                 // two k-blocks of [512][128 B]
 constexpr int W_KB = 512 * 128;
@@ -157,7 +158,7 @@ row512_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ 
                     ss += __shfl_xor_sync(0xffffffffu, ss, 4);
                     const float rstd = rsqrtf(ss * (1.f / KC) + LN_EPS);
                     bool keep = fl[i] >= 0;
-                    if (MODE == MODE_TRIMUL) keep = keep && p.mask[fl[i] < 0 ? 0 : fl[i]] != 0;
+                    if (MODE != MODE_TRIATT) keep = keep && p.mask[fl[i] < 0 ? 0 : fl[i]] != 0;
                     const float kz = keep ? 1.f : 0.f;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
@@ -217,7 +218,7 @@ row512_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ 
                     ++acc_cnt[half];
                     tc_fence_after();
                     const uint32_t d = tmem_base + half * 256;
-                    if (MODE == MODE_TRIMUL) {
+                    if (MODE != MODE_TRIATT) {
                         // channels on the lanes: A = 128 weight rows, B = the x tile (positions)
                         gemm_k128(d, w_addr + (half * 256) * 128, W_KB, x_addr, A_KB_BYTES, idesc128);
                         gemm_k128(d + 128, w_addr + (half * 256 + 128) * 128, W_KB, x_addr, A_KB_BYTES, idesc128);
@@ -290,7 +291,45 @@ row512_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ 
                 tc_fence_after();
                 const uint32_t tbase = tmem_base + lane_off + half * 256;
                 uint4 o[8];
-                if (MODE == MODE_TRIMUL) {
+                if (MODE == MODE_TRIMUL_MX) {
+                    // lane = channel of operand `half`; this warp's 64 positions are two scale blocks
+                    uint32_t sc = 0;
+#pragma unroll
+                    for (int blk = 0; blk < 2; ++blk) {
+                        uint32_t pr[32], gr[32];
+                        tmem_ld_32x32(tbase + chalf * 64 + blk * 32, pr);
+                        tmem_ld_32x32(tbase + 128 + chalf * 64 + blk * 32, gr);
+                        tmem_ld_wait();
+                        float amax = 0.f;
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) {
+                            const float pv = __uint_as_float(pr[e]);
+                            const float u = fmaf(pv, tanh_approx(__uint_as_float(gr[e])), pv);
+                            pr[e] = __float_as_uint(u);
+                            amax = fmaxf(amax, fabsf(u));
+                        }
+                        const uint32_t eb = mx::scale_byte(amax);
+                        const float inv = mx::inv_scale(eb);
+                        sc |= eb << (8 * blk);
+                        uint32_t* w = reinterpret_cast<uint32_t*>(&o[blk * 2]);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e)
+                            w[e] = mx::pack_e4m3x4(__uint_as_float(pr[4 * e]) * inv, __uint_as_float(pr[4 * e + 1]) * inv,
+                                                   __uint_as_float(pr[4 * e + 2]) * inv, __uint_as_float(pr[4 * e + 3]) * inv);
+                    }
+                    *reinterpret_cast<uint16_t*>(p.scales[half] + mx::scale_offset(lrow, line, (pos0 >> 5) + chalf * 2,
+                                                                                   p.sf_kgroups, p.sf_row_blocks)) = (uint16_t)sc;
+                    if (epi_tid == 0) bulk_wait_read0();
+                    named_bar_sync(EPI_BAR_ID, EPI_WARPS * 32);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(stg + sw128(lrow, chalf * 4 + j)) = o[j];
+                    fence_proxy_async();
+                    named_bar_sync(EPI_BAR_ID, EPI_WARPS * 32);
+                    if (epi_tid == 0) {
+                        tma_store_4d(half == 0 ? &map0 : &map1, stg, pos0, line, 0, 0);
+                        bulk_commit();
+                    }
+                } else if (MODE == MODE_TRIMUL) {
                     // lane = channel of operand `half`, columns = positions; this warp's 64 positions = box `chalf`
                     load64(tbase + chalf * 64, 1, o);
                     const int rg = p.row_group[half];
@@ -325,6 +364,18 @@ static int make_maps(int mode, const Args& a, CUtensorMap (&m)[4]) {
     const CUtensorMapDataType bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     const int span = a.transposed ? a.rows : a.n, lines = a.transposed ? a.n : a.rows;
     int rc;
+    if (mode == MODE_TRIMUL_MX) {
+        for (int i = 0; i < 2; ++i) {     // byte planes [d][line][pitch]
+            cuuint64_t dims[4] = {(cuuint64_t)a.pitch, (cuuint64_t)lines, 128, 1};
+            cuuint64_t str[3] = {(cuuint64_t)a.pitch, (cuuint64_t)a.plane_stride[i], (cuuint64_t)a.plane_stride[i] * 128};
+            cuuint32_t box[4] = {128, 1, 128, 1};
+            if ((rc = tmap_encode(&m[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, a.planes[i], 4, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                                  "mx planes")) != B200PF_OK) return rc;
+        }
+        m[2] = m[0];
+        m[3] = m[0];
+        return B200PF_OK;
+    }
     if (mode == MODE_TRIMUL) {
         for (int i = 0; i < 2; ++i) {
             const int rg = a.row_group[i], groups = (lines + rg - 1) / rg;
@@ -381,6 +432,7 @@ static int launch(const Args& a, cudaStream_t st) {
 }
 
 int launch_trimul(const Args& a, cudaStream_t st) { return launch<MODE_TRIMUL>(a, st); }
+int launch_trimul_mx(const Args& a, cudaStream_t st) { return launch<MODE_TRIMUL_MX>(a, st); }
 int launch_triatt(const Args& a, cudaStream_t st) { return launch<MODE_TRIATT>(a, st); }
 
 }  // namespace r512

@@ -18,6 +18,9 @@ struct Args {
     long long plane_stride[2], group_stride[2];
     int row_group[2];
     int pitch;
+    // MXFP8 planes (launch_trimul_mx): `planes` are byte planes, pitch / plane_stride in bytes
+    uint8_t* scales[2];
+    int sf_kgroups, sf_row_blocks;
     // triangle-attention outputs
     __nv_bfloat16 *q, *k, *v, *g, *tri_bias;
     const float* w_bias_f32;           // [4][128] triangle-bias rows (already times log2 e)
@@ -28,6 +31,7 @@ struct Args {
 };
 
 int launch_trimul(const Args& a, cudaStream_t st);
+int launch_trimul_mx(const Args& a, cudaStream_t st);
 int launch_triatt(const Args& a, cudaStream_t st);
 
 }  // namespace r512

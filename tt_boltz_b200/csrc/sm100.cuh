@@ -179,5 +179,42 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// ---- block-scaled fp8 (MXFP8: e4m3 values, one e8m0 scale per 32 elements along K) --------------
+// Untiled bulk copy global -> shared (both addresses and the size multiples of 16 bytes).
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+// Descriptor of one 512-byte scale block in shared memory: 32 rows of 16 bytes, no swizzle
+// (8-row core matrices 128 bytes apart).
+__device__ __forceinline__ uint64_t make_desc_scale_block(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;                               // leading byte offset: a single 16-byte column, unused
+    d |= (uint64_t)(128 >> 4) << 32;                      // 8 rows x 16 bytes per core matrix
+    d |= (uint64_t)1 << 46;
+    return d;
+}
+// Copy one scale block into 4 consecutive tensor-memory columns: lane i (of every 32-lane
+// quarter) receives the 16 bytes of row i.  Issued by ONE thread; ordered with later MMAs.
+__device__ __forceinline__ void tmem_cp_scale_block(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+// Instruction descriptor: e4m3 x e4m3 -> fp32 with e8m0 scales, both operands K-major; sf_a / sf_b
+// pick which of the 4 scale bytes of a tensor-memory column belongs to this K = 32 step.
+__host__ __device__ constexpr uint32_t make_idesc_mxf8(int m, int n, uint32_t sf_a, uint32_t sf_b) {
+    return (sf_b << 4) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((uint32_t)(m >> 4) << 24) | (sf_a << 29);
+}
+// D[tmem] (+)= (A * 2^sfa)[smem] * (B * 2^sfb)[smem]; K = 32 per instruction.
+__device__ __forceinline__ void umma_mxf8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb) : "memory");
+}
+
 }  // namespace sm100
 }  // namespace b200pf

@@ -264,6 +264,11 @@ static int check_planes(const b200pf_planes* p, const char* what) {
     return B200PF_OK;
 }
 
+namespace gemm_mx {   // block-scaled fp8 kernel, trimul_gemm_mx.cu
+int launch_contract(const b200pf_planes* a, const b200pf_planes* b, const void* a_scales, const void* b_scales,
+                    b200pf_bf16* x, long long x_plane_stride, int x_pitch, int channels, cudaStream_t st);
+}
+
 }  // namespace b200pf
 
 using namespace b200pf;
@@ -272,7 +277,9 @@ extern "C" int b200pf_trimul_contract(const b200pf_planes* a, const b200pf_plane
                                       const void* a_scales, const void* b_scales,
                                       b200pf_bf16* x, long long x_plane_stride, int x_pitch,
                                       int channels, int variant, void* stream) {
-    (void)a_scales; (void)b_scales;
+    if (variant == 2)
+        return gemm_mx::launch_contract(a, b, a_scales, b_scales, x, x_plane_stride, x_pitch, channels,
+                                        static_cast<cudaStream_t>(stream));
     int rc;
     if ((rc = check_planes(a, "A")) != B200PF_OK) return rc;
     if ((rc = check_planes(b, "B")) != B200PF_OK) return rc;

@@ -49,6 +49,14 @@ class Workspace:
         elems = C_Z * self.plane_stride
         self.buf = [torch.empty(elems, dtype=torch.bfloat16, device=device) for _ in range(5)]
         self.tri_bias = torch.empty(4 * n * self.pitch, dtype=torch.bfloat16, device=device)
+        self._mx_scales = None
+
+    def mx_scales(self):
+        """Two zero-initialised e8m0 scale buffers (a and b operand) for the MXFP8 triangle multiplication."""
+        if self._mx_scales is None:
+            nbytes = _lib.load().b200pf_mx_scale_bytes(self.n, self.n, C_Z)
+            self._mx_scales = [torch.zeros(nbytes, dtype=torch.uint8, device=self.buf[0].device) for _ in range(2)]
+        return self._mx_scales
 
 
 # ------------------------------------------------------------------------------------------------
@@ -91,6 +99,37 @@ def tri_mul_bf16(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Tens
     call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), None, None, ptr(x), ws.plane_stride, ws.pitch,
          C_Z, contract_variant, st)
     trimul_epilogue(z, x, ws.plane_stride, ws.pitch, w, n, n, row_impl)
+
+
+def tri_mul_mxfp8(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Tensor], ws: Workspace,
+                  incoming: bool, contract_variant: int = 2) -> None:
+    """Triangle multiplication with MXFP8 operands (e4m3 values, e8m0 scale per 32 along k).
+
+    contract_variant 2 = block-scaled tcgen05 contraction; 0 / 1 = expand the operands to bf16
+    (exactly) and run the bf16 contraction: the cross-check of variant 2.
+    """
+    n = z.shape[0]
+    st = stream()
+    pitch8 = _round_up(n, 16)
+    stride8 = n * pitch8
+    a8, b8 = ws.buf[3].view(torch.uint8), ws.buf[4].view(torch.uint8)
+    sa, sb = ws.mx_scales()
+    x = ws.buf[2]
+    call("b200pf_trimul_producer_mx", ptr(z), ptr(mask_u8), ptr(w["ln_in_gamma"]), ptr(w["ln_in_beta"]), ptr(w["w_pg_tc"]),
+         ptr(a8), ptr(b8), ptr(sa), ptr(sb), stride8, pitch8, n, n, int(incoming), st)
+    if contract_variant == 2:
+        pa = Planes(ptr(a8), stride8, 0, pitch8, n, n, 1, 0)
+        pb = Planes(ptr(b8), stride8, 0, pitch8, n, n, 1, 0)
+        call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), ptr(sa), ptr(sb), ptr(x), ws.plane_stride, ws.pitch, C_Z, 2, st)
+    else:
+        a, b = ws.buf[0], ws.buf[1]
+        for src, sc, dst in ((a8, sa, a), (b8, sb, b)):
+            call("b200pf_mx_dequant", ptr(src), ptr(sc), ptr(dst), stride8, pitch8, ws.plane_stride, ws.pitch, n, n, C_Z, st)
+        pa = Planes(ptr(a), ws.plane_stride, 0, ws.pitch, n, n, 1, 0)
+        pb = Planes(ptr(b), ws.plane_stride, 0, ws.pitch, n, n, 1, 0)
+        call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), None, None, ptr(x), ws.plane_stride, ws.pitch,
+             C_Z, contract_variant, st)
+    trimul_epilogue(z, x, ws.plane_stride, ws.pitch, w, n, n, 0)
 
 
 def tri_att_bf16(z: torch.Tensor, masks: PairMasks, w: Dict[str, torch.Tensor], ws: Workspace,

@@ -13,8 +13,11 @@ Parameters carry the reference's state-dict key names, so ``load_state_dict`` of
 checkpoint slice works unchanged (tt_bio/tenstorrent.py:2179-2180 does the same for its backend).
 
 Inference only (eval-mode semantics: dropout masks are 1).  Inputs must be CUDA tensors; there
-is no CPU path.  ``precision``: "bf16" (fused tensor-core kernels, fp32 residual stream) or
-"fp32" (un-fused fp32 kernels, the validation tier).
+is no CPU path.  ``precision``: "bf16" (fused tensor-core kernels, fp32 residual stream),
+"mxfp8" (as bf16, but the triangle-multiplication operands a / b are MXFP8: e4m3 values with one
+e8m0 scale per 32 elements along the contraction index, contracted by the block-scaled tensor-core
+instruction - the counterpart of the reference's block-fp8 fast mode, tt_bio/tenstorrent.py:178-181)
+or "fp32" (un-fused fp32 kernels, the validation tier).
 """
 from __future__ import annotations
 
@@ -52,11 +55,13 @@ class B200PairformerLayer(nn.Module):
         super().__init__()
         if post_layer_norm:
             raise NotImplementedError("post_layer_norm=True is not used by Boltz-2 and is not built")
-        if precision not in ("bf16", "fp32"):
-            raise ValueError("precision must be 'bf16' or 'fp32'")
+        if precision not in ("bf16", "mxfp8", "fp32"):
+            raise ValueError("precision must be 'bf16', 'mxfp8' or 'fp32'")
         self.token_s, self.token_z, self.num_heads = token_s, token_z, num_heads
         self.dropout, self.with_s, self.precision = dropout, with_s, precision
+        self.fused = precision != "fp32"
         self.contract_variant = 0      # 0 = tcgen05, 1 = SIMT cross-check
+        self.mx_contract_variant = 2   # 2 = block-scaled tcgen05, 0 = expand to bf16 + bf16 contraction (cross-check)
         self.attention_core = 0        # 0 = tcgen05, 1 = mma.sync cross-check
         self.row_impl = 0              # 0 = tcgen05 row-tile kernels, 1 = mma.sync cross-check
         self.lines_per_cta = 0
@@ -76,12 +81,12 @@ class B200PairformerLayer(nn.Module):
         sd = {k: v for k, v in self.state_dict().items()}
         pk: Dict[str, Dict[str, torch.Tensor]] = {"_device": device}
         for name in ("tri_mul_out", "tri_mul_in"):
-            pk[name] = (weights.pack_trimul(sd, name + ".", device) if self.precision == "bf16"
+            pk[name] = (weights.pack_trimul(sd, name + ".", device) if self.fused
                         else weights.to_device_f32(sd, name + ".", device))
         for name in ("tri_att_start", "tri_att_end"):
-            pk[name] = (weights.pack_triatt(sd, name + ".", device) if self.precision == "bf16"
+            pk[name] = (weights.pack_triatt(sd, name + ".", device) if self.fused
                         else weights.to_device_f32(sd, name + ".", device))
-        pk["transition_z"] = (weights.pack_transition_z(sd, "transition_z.", device) if self.precision == "bf16"
+        pk["transition_z"] = (weights.pack_transition_z(sd, "transition_z.", device) if self.fused
                               else weights.to_device_f32(sd, "transition_z.", device))
         if self.with_s:
             pk["pre_norm_s"] = weights.to_device_f32(sd, "pre_norm_s.", device)
@@ -95,9 +100,13 @@ class B200PairformerLayer(nn.Module):
                         masks: ops.PairMasks, ws: Optional[ops.Workspace]) -> None:
         """Update fp32 working copies z [N,N,128] and s [N,c_s] in place."""
         pk = self._pack(z.device)
-        if self.precision == "bf16":
-            ops.tri_mul_bf16(z, masks.pm, pk["tri_mul_out"], ws, False, self.contract_variant, self.row_impl)
-            ops.tri_mul_bf16(z, masks.pm, pk["tri_mul_in"], ws, True, self.contract_variant, self.row_impl)
+        if self.fused:
+            if self.precision == "mxfp8":
+                ops.tri_mul_mxfp8(z, masks.pm, pk["tri_mul_out"], ws, False, self.mx_contract_variant)
+                ops.tri_mul_mxfp8(z, masks.pm, pk["tri_mul_in"], ws, True, self.mx_contract_variant)
+            else:
+                ops.tri_mul_bf16(z, masks.pm, pk["tri_mul_out"], ws, False, self.contract_variant, self.row_impl)
+                ops.tri_mul_bf16(z, masks.pm, pk["tri_mul_in"], ws, True, self.contract_variant, self.row_impl)
             ops.tri_att_bf16(z, masks, pk["tri_att_start"], ws, False, self.attention_core, self.lines_per_cta, self.row_impl)
             ops.tri_att_bf16(z, masks, pk["tri_att_end"], ws, True, self.attention_core, self.lines_per_cta, self.row_impl)
             ops.transition_z_bf16(z, pk["transition_z"], self.row_impl)
@@ -130,7 +139,7 @@ def _run_layers(layers, s, z, mask, pair_mask, ws_cache: Optional[dict] = None):
         pm = ops.PairMasks(_mask_u8(pair_mask, (n, n), z.device))
         tm = _mask_u8(mask, (n,), z.device) if s is not None else None
         ws = None
-        if any(l.precision == "bf16" for l in layers):
+        if any(l.fused for l in layers):
             key = (n, z.device)
             if ws_cache is not None and key in ws_cache:
                 ws = ws_cache[key]
