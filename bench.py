@@ -43,12 +43,14 @@ def kernel_work(n: int):
     e = n * n * C
     return {
         "b200pf_trimul_producer": (2 * n * n * C * 512, 8 * e),
+        "b200pf_trimul_producer_mx": (2 * n * n * C * 512, 6 * e + e // 16),
         "b200pf_trimul_contract": (2 * n ** 3 * C, 6 * e),
         "b200pf_trimul_epilogue": (2 * n * n * C * 256, 10 * e),
         "b200pf_trimul_epilogue_tc": (2 * n * n * C * 256, 10 * e),
         "b200pf_triatt_producer": (2 * n * n * C * 516, 12 * e),
         "b200pf_triatt_core": (4 * n ** 3 * C, 8 * e + 2 * 4 * n * n),
         "b200pf_triatt_core_tc": (4 * n ** 3 * C, 8 * e + 2 * 4 * n * n),
+        "b200pf_triatt_core_tc4": (4 * n ** 3 * C, 8 * e + 2 * 4 * n * n),
         "b200pf_triatt_epilogue": (2 * n * n * C * C, 12 * e),
         "b200pf_transition_z": (6 * n * n * C * 4 * C, 8 * e),
         "b200pf_transition_z_tc": (6 * n * n * C * 4 * C, 8 * e),
@@ -171,6 +173,8 @@ def main() -> None:
     ap.add_argument("--cpu-budget", type=float, default=150.0, help="seconds the CPU legs may spend")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "mxfp8"],
+                    help="bf16 = the headline tier; mxfp8 = triangle-multiplication operands in MXFP8 (1 GPU only)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -195,9 +199,11 @@ def main() -> None:
     m_cpu, pm_cpu = synthetic.tail_padding_mask(n, 0)
     if world > 1:
         from tt_boltz_b200.sharded import ShardedPairformerModule
+        if args.precision != "bf16":
+            raise SystemExit("--precision mxfp8 is built for one GPU only")
         mod = ShardedPairformerModule(384, 128, nb, v2=True, precision="bf16")
     else:
-        mod = B200PairformerModule(384, 128, nb, v2=True, precision="bf16")
+        mod = B200PairformerModule(384, 128, nb, v2=True, precision=args.precision)
     mod.load_state_dict(sd, strict=True)
     del sd
     s_pin, z_pin = s_cpu.pin_memory(), z_cpu.pin_memory()
@@ -310,7 +316,8 @@ def main() -> None:
     if rank == 0:
         line = {"metric": "pairformer_ms_per_block", "value": ms_block, "unit": "ms", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong",
-                "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "vs_baseline": None, "dtype": "bf16" if args.precision == "bf16" else "mxfp8 (tri-mul operands) + bf16",
+                "data": "synthetic",
                 "tflops": block_flops(n) / (ms_block * 1e-3) / 1e12,
                 "config": {"workload": f"Pairformer trunk, {nb} blocks, N={n}, c_z=128, c_s=384, bf16 operands / fp32 residual",
                            "tokens": n, "blocks": nb, "parallelism": "single GPU" if world == 1 else f"row-sharded x{world}",

@@ -263,6 +263,14 @@ int b200pf_triatt_core_tc(const b200pf_bf16* q, const b200pf_bf16* k, const b200
                           const uint8_t* mask_lines, int mask_pitch,
                           b200pf_bf16* o, long long o_line_stride, long long o_pos_stride,
                           int lines, int n, void* stream);
+/* Same arguments and result; four lines per CTA (four softmax groups in flight, the bias tile
+ * fetched and multiplied once per pair of lines, running output kept in TMEM with a rescale only
+ * when a row maximum has grown by more than 2^8). */
+int b200pf_triatt_core_tc4(const b200pf_bf16* q, const b200pf_bf16* k, const b200pf_bf16* vt, int vt_pitch,
+                           const b200pf_bf16* bias, long long bias_hs, long long bias_qs,
+                           const uint8_t* mask_lines, int mask_pitch,
+                           b200pf_bf16* o, long long o_line_stride, long long o_pos_stride,
+                           int lines, int n, void* stream);
 
 /* Triangle-attention epilogue: z += (o * g) W_o^T  (g already passed through the sigmoid).
  * Replaces tt_bio/tenstorrent.py:580-591 and the residual :1013-1021 (reference.py:122-136). */

@@ -159,9 +159,10 @@ def test_tcgen05_kernels_match_mma_sync_cross_checks(dev):
     assert rel_l2((z_tc - z)[0, :v, :v], (z_x - z)[0, :v, :v]) < 8e-3
 
 
-@pytest.mark.parametrize("n", [50, 128, 200])
+@pytest.mark.parametrize("n", [50, 128, 200, 330])
 def test_attention_tcgen05_core_matches_mma_sync_core(dev, n):
-    """The two attention cores (tcgen05 / TMEM and the mma.sync cross-check) see the same q, k, v, bias."""
+    """The attention cores (tcgen05 / TMEM with two and with four lines per CTA, and the mma.sync cross-check)
+    see the same q, k, v, bias."""
     from tt_boltz_b200 import _lib, ops, weights
     sd = strip(synthetic.make_weights(1, seed=5, std=0.05, affine_jitter=0.3))
     _, z = synthetic.make_inputs(n, seed=4, with_s=False)
@@ -173,13 +174,14 @@ def test_attention_tcgen05_core_matches_mma_sync_core(dev, n):
     for ending in (False, True):
         w = weights.pack_triatt(sd, "tri_att_end." if ending else "tri_att_start.", dev)
         outs = []
-        for core in (0, 1):
+        for core in (0, 1, 2):
             zd = z[0].to(dev).clone()
             ops.tri_att_bf16(zd, masks, w, ws, ending, core)
             assert _lib.device_status() == 0
             outs.append((zd.cpu() - z[0]))
-        assert torch.isfinite(outs[0]).all()
+        assert torch.isfinite(outs[0]).all() and torch.isfinite(outs[2]).all()
         assert rel_l2(outs[0], outs[1]) < 5e-3, (n, ending)
+        assert rel_l2(outs[2], outs[1]) < 5e-3, (n, ending)
 
 
 # ---------------------------------------------------------------------------------------------

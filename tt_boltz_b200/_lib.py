@@ -56,6 +56,7 @@ SIGNATURES = {
     "b200pf_trimul_epilogue_tc": [_vp, _vp, _ll, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "b200pf_triatt_producer": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _vp],
     "b200pf_triatt_core_tc": [_vp, _vp, _vp, _i, _vp, _ll, _ll, _vp, _i, _vp, _ll, _ll, _i, _i, _vp],
+    "b200pf_triatt_core_tc4": [_vp, _vp, _vp, _i, _vp, _ll, _ll, _vp, _i, _vp, _ll, _ll, _i, _i, _vp],
     "b200pf_triatt_core": [_vp, _vp, _vp, _vp, _ll, _ll, _i, _vp, _ll, _ll, _vp, _ll, _ll, _i, _i, _i, _vp],
     "b200pf_triatt_epilogue": [_vp, _vp, _vp, _vp, _ll, _vp],
     "b200pf_transition_z": [_vp, _vp, _vp, _vp, _ll, _vp],

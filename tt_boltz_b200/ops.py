@@ -134,22 +134,23 @@ def tri_mul_mxfp8(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Ten
 
 def tri_att_bf16(z: torch.Tensor, masks: PairMasks, w: Dict[str, torch.Tensor], ws: Workspace,
                  ending: bool, core: int = 0, lines_per_cta: int = 0, row_impl: int = 0) -> None:
-    """core 0 = tcgen05 attention core, 1 = mma.sync cross-check core."""
+    """core 0 = tcgen05 attention core (four lines per CTA, the production kernel), 2 = the earlier tcgen05
+    core with two lines per CTA, 1 = mma.sync core (the last two are cross-checks)."""
     n = z.shape[0]
     q, k, v, g, o = ws.buf
     st = stream()
     bias_hs, bias_qs = ws.pitch, 4 * ws.pitch          # layout [query][head][key]: a row shard is contiguous
-    if core != 0:
+    if core == 1:
         row_impl = 1          # the mma.sync core reads v untransposed, which only the mma.sync producer writes
     call("b200pf_triatt_producer", ptr(z), *triatt_producer_weights(w, row_impl), ptr(q), ptr(k), ptr(v), ptr(g),
-         ptr(ws.tri_bias), bias_hs, bias_qs, ws.pitch if core == 0 else 0, n, n, int(ending), row_impl, st)
+         ptr(ws.tri_bias), bias_hs, bias_qs, ws.pitch if core != 1 else 0, n, n, int(ending), row_impl, st)
     if ending:      # line = column j: o element (line, pos) -> z position [pos][line]
         o_ls, o_ps = C_Z, n * C_Z
     else:
         o_ls, o_ps = n * C_Z, C_Z
-    if core == 0:
+    if core != 1:
         lines_mask = masks.cols if ending else masks.rows
-        call("b200pf_triatt_core_tc", ptr(q), ptr(k), ptr(v), ws.pitch, ptr(ws.tri_bias), bias_hs, bias_qs,
+        call("b200pf_triatt_core_tc4" if core == 0 else "b200pf_triatt_core_tc", ptr(q), ptr(k), ptr(v), ws.pitch, ptr(ws.tri_bias), bias_hs, bias_qs,
              ptr(lines_mask), masks.pitch, ptr(o), o_ls, o_ps, n, n, st)
     else:
         mask_ls, mask_ks = (1, n) if ending else (n, 1)

@@ -62,7 +62,7 @@ class B200PairformerLayer(nn.Module):
         self.fused = precision != "fp32"
         self.contract_variant = 0      # 0 = tcgen05, 1 = SIMT cross-check
         self.mx_contract_variant = 2   # 2 = block-scaled tcgen05, 0 = expand to bf16 + bf16 contraction (cross-check)
-        self.attention_core = 0        # 0 = tcgen05, 1 = mma.sync cross-check
+        self.attention_core = 0        # 0 = tcgen05 (four lines per CTA); cross-checks: 2 = tcgen05 two lines per CTA, 1 = mma.sync
         self.row_impl = 0              # 0 = tcgen05 row-tile kernels, 1 = mma.sync cross-check
         self.lines_per_cta = 0
         for name, shape in layer_param_shapes(token_s, token_z, num_heads, pairwise_num_heads,

@@ -137,7 +137,7 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
     call("b200pf_triatt_producer", ptr(z_loc), *ops.triatt_producer_weights(w, layer.row_impl), ptr(q), ptr(k), ptr(v), ptr(g),
          ptr(bias_loc), pn, 4 * pn, pn, nr, n, 0, layer.row_impl, st)
     bias_all = all_gather_cat(bias_loc, group)                                       # [query][head][key]
-    call("b200pf_triatt_core_tc", ptr(q), ptr(k), ptr(v), pn, ptr(bias_all), pn, 4 * pn, ptr(masks.rows[r0:r0 + nr]),
+    call("b200pf_triatt_core_tc4", ptr(q), ptr(k), ptr(v), pn, ptr(bias_all), pn, 4 * pn, ptr(masks.rows[r0:r0 + nr]),
          masks.pitch, ptr(o), n * C_Z, C_Z, nr, n, st)
     call("b200pf_triatt_epilogue", ptr(z_loc), ptr(o), ptr(g), ptr(w["w_o"]), nr * n, st)
 
@@ -147,7 +147,7 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
     call("b200pf_triatt_producer", ptr(zc), *ops.triatt_producer_weights(w, layer.row_impl), ptr(q), ptr(k), ptr(v), ptr(g),
          ptr(bias_loc), pn, 4 * pn, pn, n, nr, 1, layer.row_impl, st)
     bias_all = all_gather_cat(bias_loc, group)
-    call("b200pf_triatt_core_tc", ptr(q), ptr(k), ptr(v), pn, ptr(bias_all), pn, 4 * pn, ptr(masks.cols[r0:r0 + nr]),
+    call("b200pf_triatt_core_tc4", ptr(q), ptr(k), ptr(v), pn, ptr(bias_all), pn, 4 * pn, ptr(masks.cols[r0:r0 + nr]),
          masks.pitch, ptr(o), C_Z, nr * C_Z, nr, n, st)
     call("b200pf_triatt_epilogue", ptr(zc), ptr(o), ptr(g), ptr(w["w_o"]), n * nr, st)
     z_loc = cols_to_rows(zc, group)
