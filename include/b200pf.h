@@ -167,13 +167,19 @@ typedef struct b200pf_planes {
 /* x[d][i][j] = sum_k A[d][i][k] * B[d][j][k] for d < channels: the N x N x N contraction of
  * the triangle multiplication as a batched K-major GEMM (tcgen05 + TMEM, TMA-fed).
  * Replaces the per-chunk ttnn.matmul at tt_bio/tenstorrent.py:453-460 (reference.py:467, 556).
- * x is bf16 planes x[d][i][j] with pitch x_pitch.  variant 0 = tcgen05 bf16, 1 = SIMT bf16
+ * x is bf16 planes x[d][i][j] with pitch x_pitch; with x_row_group > 0 the output rows are written
+ * in groups, element (d, i, j) at (i / x_row_group) * x_group_stride + d * x_plane_stride +
+ * (i % x_row_group) * x_pitch + j, so that a rank that contracts a slice of the channels for every
+ * row can send each owner of output rows one contiguous block.  Both operands may be segmented
+ * along rows or along the contraction index (segments of 128-row multiples / 64-column multiples).
+ * variant 0 = tcgen05 bf16, 1 = SIMT bf16
  * (debug cross-check of variant 0), 2 = tcgen05 block-scaled MXFP8: a / b are byte planes of e4m3
  * values (pitch, plane_stride in bytes, multiples of 16; nseg 1) and a_scales / b_scales their e8m0
  * scale blocks as written by b200pf_trimul_producer_mx.  The scales are ignored by variants 0, 1. */
 int b200pf_trimul_contract(const b200pf_planes* a, const b200pf_planes* b,
                            const void* a_scales, const void* b_scales,
                            b200pf_bf16* x, long long x_plane_stride, int x_pitch,
+                           int x_row_group, long long x_group_stride,
                            int channels, int variant, void* stream);
 
 /* MXFP8 form of the producer (the counterpart of the reference's block-fp8 "fast" mode,
@@ -315,6 +321,17 @@ int b200pf_tri_mul_noalloc(float* z, const uint8_t* mask, const float* ln_gamma,
                            const b200pf_bf16* w_pout, const b200pf_bf16* w_gout,
                            const float* wsum, const float* wb,
                            int n, int incoming, void* stream);
+
+/* All-to-all of equal blocks over peer mappings (multi-GPU path, no counterpart in the reference, whose
+ * cards do not exchange data: tt_bio/distributed.py fans whole jobs out).  Block t of `send` (world blocks
+ * of block_bytes) is written to slot `rank` of rank t's receive buffer; recv_ptrs is a HOST array of the
+ * world receive-buffer addresses as mapped in this process (symmetric memory, no multicast).  One launch per
+ * rank; the caller puts a cross-rank barrier between this and the consumers of the receive buffer. */
+int b200pf_peer_scatter(const void* send, const unsigned long long* recv_ptrs, long long block_bytes,
+                        int rank, int world, void* stream);
+/* All-gather form of the same: `send` is ONE block, written to slot `rank` of every rank's receive buffer. */
+int b200pf_peer_broadcast(const void* send, const unsigned long long* recv_ptrs, long long block_bytes,
+                          int rank, int world, void* stream);
 
 #ifdef __cplusplus
 }

@@ -14,12 +14,33 @@ def _gated(z, w, pre, mask):
     return x, u
 
 
+def _channel_parallel_contract(a_pl, b_pl, world, contract_rows):
+    """a_pl, b_pl: channel-major planes [D][plane rows][plane cols] of this rank's shard.  All-to-all to channel
+    shards, contract D/P channels for every row, all-to-all the result back to row shards: [D][nr][N]."""
+    d = a_pl.shape[0]
+    cl = d // world
+    a_ch = all_to_all_blocks(a_pl.reshape(world, -1)).view(world, cl, a_pl.shape[1], a_pl.shape[2])   # [src][cl][rows][cols]
+    b_ch = all_to_all_blocks(b_pl.reshape(world, -1)).view(world, cl, b_pl.shape[1], b_pl.shape[2])
+    if contract_rows:      # incoming: the source rank owns a block of the contraction index (plane columns)
+        a_f = a_ch.permute(1, 2, 0, 3).reshape(cl, a_pl.shape[1], -1)       # [cl][i][k]
+        b_f = b_ch.permute(1, 2, 0, 3).reshape(cl, b_pl.shape[1], -1)
+    else:                  # outgoing: the source rank owns a block of the operand's rows
+        a_f = a_ch.permute(1, 0, 2, 3).reshape(cl, -1, a_pl.shape[2])       # [cl][i][k]
+        b_f = b_ch.permute(1, 0, 2, 3).reshape(cl, -1, b_pl.shape[2])
+    x = torch.einsum("cik,cjk->cij", a_f, b_f)                               # [cl][N][N]
+    n = x.shape[1]
+    nr = n // world
+    send = x.view(cl, world, nr, n).permute(1, 0, 2, 3).contiguous()         # [dest][cl][nr][N]
+    return all_to_all_blocks(send.view(world, -1)).view(d, nr, n)            # [src * cl + c][nr][N]
+
+
 def _tri_mul_out(z_loc, w, pre, mask_loc, world):
     nr, n, _ = z_loc.shape
     x, u = _gated(z_loc, w, pre, mask_loc)
     d = u.shape[-1] // 2
-    b_all = all_gather_cat(u[..., d:].contiguous()).view(n, n, d)
-    t = torch.einsum("ikc,jkc->ijc", u[..., :d], b_all)
+    a_pl = u[..., :d].permute(2, 0, 1).contiguous()                           # [D][i local][k]
+    b_pl = u[..., d:].permute(2, 0, 1).contiguous()                           # [D][j local][k]
+    t = _channel_parallel_contract(a_pl, b_pl, world, False).permute(1, 2, 0)
     return z_loc + orc._lin(orc._ln(t, w, pre + ".norm_out"), w, pre + ".p_out") * torch.sigmoid(orc._lin(x, w, pre + ".g_out"))
 
 
@@ -27,11 +48,9 @@ def _tri_mul_in(z_loc, w, pre, mask_loc, world):
     nr, n, _ = z_loc.shape
     x, u = _gated(z_loc, w, pre, mask_loc)
     d = u.shape[-1] // 2
-    a_loc = u[..., :d]                                                        # [k local][i][c]
-    send = a_loc.view(nr, world, nr, d).permute(1, 0, 2, 3)                   # [dest][k local][i local][c]
-    a_cols = all_to_all_blocks(send).view(n, nr, d)                           # [k][i local][c]
-    b_all = all_gather_cat(u[..., d:].contiguous()).view(n, n, d)             # [k][j][c]
-    t = torch.einsum("kic,kjc->ijc", a_cols, b_all)
+    a_pl = u[..., :d].permute(2, 1, 0).contiguous()                           # [D][i][k local]
+    b_pl = u[..., d:].permute(2, 1, 0).contiguous()                           # [D][j][k local]
+    t = _channel_parallel_contract(a_pl, b_pl, world, True).permute(1, 2, 0)
     return z_loc + orc._lin(orc._ln(t, w, pre + ".norm_out"), w, pre + ".p_out") * torch.sigmoid(orc._lin(x, w, pre + ".g_out"))
 
 
@@ -92,7 +111,7 @@ def sharded_block_cpu(w, pre, s, z_loc, mask, pm, rank, world, num_heads=16):
     bias = orc._lin(orc._ln(z_loc, w, ap + ".proj_z.0"), w, ap + ".proj_z.1").permute(2, 0, 1)
     att = torch.einsum("ihd,jhd->hij", q, k) / (hd ** 0.5) + bias + ((1 - mask) * -orc.S_ATT_INF)[None, None, :]
     o = torch.einsum("hij,jhd->ihd", att.softmax(-1), v).reshape(nr, cs)
-    og_all = all_gather_cat((g * o).contiguous()).view(n, cs)
-    s = s + orc._lin(og_all, w, ap + ".proj_o")
-    s = s + orc.transition(s, w, pre + "transition_s")
+    s_loc = s[r0:r0 + nr] + orc._lin((g * o).contiguous(), w, ap + ".proj_o")
+    s_loc = s_loc + orc.transition(s_loc, w, pre + "transition_s")
+    s = all_gather_cat(s_loc.contiguous()).view(n, cs)
     return s, z_loc

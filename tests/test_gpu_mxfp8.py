@@ -128,7 +128,7 @@ def test_block_scaled_contraction(dev, n):
     pa = Planes(ptr(ops_dev[0]), n * pitch8, 0, pitch8, n, n, 1, 0)
     pb = Planes(ptr(ops_dev[1]), n * pitch8, 0, pitch8, n, n, 1, 0)
     call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), ptr(scales_dev[0]), ptr(scales_dev[1]), ptr(x2), n * pitch, pitch,
-         128, 2, stream())
+         0, 0, 128, 2, stream())
     # expand to bf16 (exact) and contract with the bf16 kernel
     exp = [torch.zeros(128, n, pitch, dtype=torch.bfloat16, device=dev) for _ in range(2)]
     for i in range(2):
@@ -137,7 +137,7 @@ def test_block_scaled_contraction(dev, n):
     x0 = torch.zeros(128, n, pitch, dtype=torch.bfloat16, device=dev)
     pa0 = Planes(ptr(exp[0]), n * pitch, 0, pitch, n, n, 1, 0)
     pb0 = Planes(ptr(exp[1]), n * pitch, 0, pitch, n, n, 1, 0)
-    call("b200pf_trimul_contract", C.byref(pa0), C.byref(pb0), None, None, ptr(x0), n * pitch, pitch, 128, 0, stream())
+    call("b200pf_trimul_contract", C.byref(pa0), C.byref(pb0), None, None, ptr(x0), n * pitch, pitch, 0, 0, 128, 0, stream())
     torch.cuda.synchronize()
     assert _lib.device_status() == 0
     for i in range(2):

@@ -138,13 +138,47 @@ def test_contraction_tcgen05_matches_simt_and_einsum(dev):
             x = torch.zeros(128, n, pitch, dtype=torch.bfloat16, device=dev)
             pa = Planes(ptr(ad), ps, 0, pitch, n, n, 1, 0)
             pb = Planes(ptr(bd), ps, 0, pitch, n, n, 1, 0)
-            call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), None, None, ptr(x), ps, pitch, 128, variant, stream())
+            call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), None, None, ptr(x), ps, pitch, 0, 0, 128, variant, stream())
             assert _lib.device_status() == 0
             outs.append(x[:, :, :n].float().cpu())
         ref = torch.einsum("dik,djk->dij", a[:, :, :n].float(), b[:, :, :n].float())
         assert rel_l2(outs[0], ref) < 4e-3, n       # bf16 rounding of the stored result
         assert rel_l2(outs[1], ref) < 4e-3, n
         assert rel_l2(outs[0], outs[1]) < 1e-3, n
+
+
+@pytest.mark.parametrize("seg_is_k", [0, 1])
+def test_contraction_segmented_operands_and_grouped_output(dev, seg_is_k):
+    """The operand / result layouts of the channel-parallel sharded triangle multiplication: both operands split in
+    P segments (blocks of rows, or blocks of the contraction index), the result written in P groups of output rows."""
+    from tt_boltz_b200._lib import Planes, call, ptr, stream
+    from tt_boltz_b200 import _lib
+    world, cl, n = 2, 16, 256
+    nr = n // world
+    g = torch.Generator().manual_seed(31 + seg_is_k)
+    a = torch.randn(cl, n, n, generator=g).bfloat16()          # [c][i][k]
+    b = torch.randn(cl, n, n, generator=g).bfloat16()          # [c][j][k]
+    if seg_is_k:    # segment s holds k in [s*nr, (s+1)*nr): [s][c][row][k local]
+        a_seg = a.view(cl, n, world, nr).permute(2, 0, 1, 3).contiguous()
+        b_seg = b.view(cl, n, world, nr).permute(2, 0, 1, 3).contiguous()
+        rows, cols = n, nr
+    else:           # segment s holds rows [s*nr, (s+1)*nr): [s][c][row local][k]
+        a_seg = a.view(cl, world, nr, n).permute(1, 0, 2, 3).contiguous()
+        b_seg = b.view(cl, world, nr, n).permute(1, 0, 2, 3).contiguous()
+        rows, cols = nr, n
+    ad, bd = a_seg.to(dev), b_seg.to(dev)
+    ref = torch.einsum("cik,cjk->cij", a.float(), b.float())
+    outs = []
+    for variant in (0, 1):
+        x = torch.zeros(world, cl, nr, n, dtype=torch.bfloat16, device=dev)        # [group = i / nr][c][i local][j]
+        pa = Planes(ptr(ad), rows * cols, cl * rows * cols, cols, rows, cols, world, seg_is_k)
+        pb = Planes(ptr(bd), rows * cols, cl * rows * cols, cols, rows, cols, world, seg_is_k)
+        call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), None, None, ptr(x), nr * n, n, nr, cl * nr * n, cl, variant, stream())
+        assert _lib.device_status() == 0
+        outs.append(x.permute(1, 0, 2, 3).reshape(cl, n, n).float().cpu())
+    assert rel_l2(outs[0], ref) < 4e-3
+    assert rel_l2(outs[1], ref) < 4e-3
+    assert rel_l2(outs[0], outs[1]) < 1e-3
 
 
 def test_tcgen05_kernels_match_mma_sync_cross_checks(dev):

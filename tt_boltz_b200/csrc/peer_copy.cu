@@ -1,0 +1,81 @@
+// All-to-all of equal blocks written straight into the destination ranks' memory.
+//
+// Every rank holds a receive buffer that its peers have mapped into their own address space
+// (symmetric memory: plain peer mappings over NVLink, no multicast).  Block t of this rank's send
+// buffer goes to slot `rank` of rank t's receive buffer, so one launch on every rank is the whole
+// exchange: 16-byte loads from local memory, 16-byte stores to local or peer memory, all SMs.  The
+// caller orders it against the consumers with a cross-rank barrier afterwards; nothing here waits
+// on another GPU.
+#include "common.cuh"
+
+namespace b200pf {
+
+constexpr int PEER_MAX_RANKS = 16;
+struct PeerPtrs {
+    unsigned long long recv[PEER_MAX_RANKS];     // receive buffer of rank t as mapped on this device
+};
+
+__global__ void __launch_bounds__(256)
+peer_scatter_kernel(const uint4* __restrict__ send, PeerPtrs peers, long long block_vec, int rank, int world) {
+    const long long total = block_vec * world;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        // start every rank on a different destination so that no receiver is hit by all senders at once
+        const long long slot = i / block_vec, off = i - slot * block_vec;
+        const int t = (int)((slot + rank) % world);
+        uint4* dst = reinterpret_cast<uint4*>(peers.recv[t]) + (long long)rank * block_vec + off;
+        *dst = __ldg(send + (long long)t * block_vec + off);
+    }
+}
+
+// All-gather form: the one block of this rank goes to slot `rank` of every rank's receive buffer.
+__global__ void __launch_bounds__(256)
+peer_broadcast_kernel(const uint4* __restrict__ send, PeerPtrs peers, long long block_vec, int rank, int world) {
+    const long long total = block_vec * world;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const long long slot = i / block_vec, off = i - slot * block_vec;
+        const int t = (int)((slot + rank) % world);
+        uint4* dst = reinterpret_cast<uint4*>(peers.recv[t]) + (long long)rank * block_vec + off;
+        *dst = __ldg(send + off);
+    }
+}
+
+}  // namespace b200pf
+
+using namespace b200pf;
+
+static int peer_launch(bool broadcast, const void* send, const unsigned long long* recv_ptrs, long long block_bytes,
+                       int rank, int world, void* stream) {
+    B200PF_REQUIRE(send && recv_ptrs && world > 0 && world <= PEER_MAX_RANKS && rank >= 0 && rank < world, B200PF_ERR_INVALID,
+                   "peer_scatter: bad argument (at most %d ranks)", PEER_MAX_RANKS);
+    B200PF_REQUIRE(block_bytes > 0 && block_bytes % 16 == 0 && aligned16(send), B200PF_ERR_INVALID,
+                   "peer_scatter: blocks must be 16-byte multiples and 16-byte aligned");
+    PeerPtrs p{};
+    for (int t = 0; t < world; ++t) {
+        B200PF_REQUIRE(recv_ptrs[t] != 0 && recv_ptrs[t] % 16 == 0, B200PF_ERR_INVALID, "peer_scatter: bad receive pointer of rank %d", t);
+        p.recv[t] = recv_ptrs[t];
+    }
+    int dev = 0, sms = 148;
+    B200PF_CUDA(cudaGetDevice(&dev));
+    B200PF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const long long vec = block_bytes / 16;
+    long long blocks = (vec * world + 255) / 256;
+    if (blocks > (long long)sms * 8) blocks = (long long)sms * 8;
+    if (broadcast)
+        peer_broadcast_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(static_cast<const uint4*>(send), p, vec, rank, world);
+    else
+        peer_scatter_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(static_cast<const uint4*>(send), p, vec, rank, world);
+    B200PF_LAUNCH_CHECK();
+    return B200PF_OK;
+}
+
+extern "C" int b200pf_peer_scatter(const void* send, const unsigned long long* recv_ptrs, long long block_bytes,
+                                   int rank, int world, void* stream) {
+    return peer_launch(false, send, recv_ptrs, block_bytes, rank, world, stream);
+}
+
+extern "C" int b200pf_peer_broadcast(const void* send, const unsigned long long* recv_ptrs, long long block_bytes,
+                                     int rank, int world, void* stream) {
+    return peer_launch(true, send, recv_ptrs, block_bytes, rank, world, stream);
+}

@@ -21,11 +21,19 @@ struct GemmShape {
     int k_total;         // contraction length over all k segments
     int a_kseg_cols;     // columns per k segment of A (== k_total when unsegmented)
     int b_kseg_cols;
-    int b_rowseg_rows;   // rows per row segment of B (== n_rows when unsegmented)
+    int a_rowseg_rows;   // rows per row segment of A (> m_rows when unsegmented)
+    int b_rowseg_rows;   // rows per row segment of B (> n_rows when unsegmented)
     int channels;
     int x_pitch;
     long long x_plane_stride;
+    int x_row_group;     // output rows per group (> m_rows when the output is plain planes)
+    long long x_group_stride;
 };
+// Output element (d, row, col) lives at (row / x_row_group) * x_group_stride + d * x_plane_stride + (row % x_row_group) * x_pitch + col.
+__device__ __forceinline__ long long x_row_offset(const GemmShape& s, int d, int row) {
+    const int grp = row / s.x_row_group;
+    return (long long)grp * s.x_group_stride + (long long)d * s.x_plane_stride + (long long)(row - grp * s.x_row_group) * s.x_pitch;
+}
 
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 trimul_contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -76,7 +84,7 @@ trimul_contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                 uint8_t* sb = sa + A_BYTES;
                 mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
                 int k0 = kb * BK;
-                tma_load_4d(sa, &map_a, &full[stage], k0 % s.a_kseg_cols, m0, d, k0 / s.a_kseg_cols);
+                tma_load_4d(sa, &map_a, &full[stage], k0 % s.a_kseg_cols, m0 % s.a_rowseg_rows, d, m0 / s.a_rowseg_rows + k0 / s.a_kseg_cols);
                 int kseg_b = k0 / s.b_kseg_cols, kin_b = k0 % s.b_kseg_cols;
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
@@ -136,7 +144,7 @@ trimul_contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             if (!ok) break;
             tc_fence_after();
             int row = m0 + quarter * 32 + lane;
-            __nv_bfloat16* xrow = x + (long long)d * s.x_plane_stride + (long long)row * s.x_pitch;
+            __nv_bfloat16* xrow = x + x_row_offset(s, d, row < s.m_rows ? row : 0);
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 int col = n0 + c * 32;
@@ -208,7 +216,7 @@ trimul_contract_simt_kernel(PlaneView a, PlaneView b, __nv_bfloat16* __restrict_
         for (int v = 0; v < 4; ++v) {
             int i = i0 + ty * 4 + u, j = j0 + tx * 4 + v;
             if (i < s.m_rows && j < s.n_rows)
-                x[d * s.x_plane_stride + (long long)i * s.x_pitch + j] = __float2bfloat16(acc[u][v]);
+                x[x_row_offset(s, d, i) + j] = __float2bfloat16(acc[u][v]);
         }
 }
 
@@ -276,30 +284,39 @@ using namespace b200pf;
 extern "C" int b200pf_trimul_contract(const b200pf_planes* a, const b200pf_planes* b,
                                       const void* a_scales, const void* b_scales,
                                       b200pf_bf16* x, long long x_plane_stride, int x_pitch,
+                                      int x_row_group, long long x_group_stride,
                                       int channels, int variant, void* stream) {
-    if (variant == 2)
+    if (variant == 2) {
+        B200PF_REQUIRE(x_row_group <= 0, B200PF_ERR_UNSUPPORTED, "trimul_contract: variant 2 writes plain planes only");
         return gemm_mx::launch_contract(a, b, a_scales, b_scales, x, x_plane_stride, x_pitch, channels,
                                         static_cast<cudaStream_t>(stream));
+    }
     int rc;
     if ((rc = check_planes(a, "A")) != B200PF_OK) return rc;
     if ((rc = check_planes(b, "B")) != B200PF_OK) return rc;
     B200PF_REQUIRE(x && aligned16(x) && channels > 0, B200PF_ERR_INVALID, "trimul_contract: bad output");
-    B200PF_REQUIRE(!(a->nseg > 1 && !a->seg_is_k), B200PF_ERR_UNSUPPORTED, "trimul_contract: A cannot be row-segmented");
     GemmShape s;
-    s.m_rows = a->rows;
+    s.m_rows = (a->nseg > 1 && !a->seg_is_k) ? a->rows * a->nseg : a->rows;
     s.n_rows = (b->nseg > 1 && !b->seg_is_k) ? b->rows * b->nseg : b->rows;
-    int ka = (a->nseg > 1) ? a->cols * a->nseg : a->cols;
+    int ka = (a->nseg > 1 && a->seg_is_k) ? a->cols * a->nseg : a->cols;
     int kb = (b->nseg > 1 && b->seg_is_k) ? b->cols * b->nseg : b->cols;
     B200PF_REQUIRE(ka == kb, B200PF_ERR_INVALID, "trimul_contract: contraction lengths differ (%d vs %d)", ka, kb);
     s.k_total = ka;
-    s.a_kseg_cols = a->nseg > 1 ? a->cols : (ka + BK);          // never reached by k0 when unsegmented
+    s.a_kseg_cols = (a->nseg > 1 && a->seg_is_k) ? a->cols : (ka + BK);          // never reached by k0 when unsegmented
+    s.a_rowseg_rows = (a->nseg > 1 && !a->seg_is_k) ? a->rows : (s.m_rows + BM);
     s.b_kseg_cols = (b->nseg > 1 && b->seg_is_k) ? b->cols : (kb + BK);
     s.b_rowseg_rows = (b->nseg > 1 && !b->seg_is_k) ? b->rows : (s.n_rows + BN);
     s.channels = channels;
     s.x_pitch = x_pitch;
     s.x_plane_stride = x_plane_stride;
-    B200PF_REQUIRE(x_pitch % 8 == 0 && x_pitch >= s.n_rows && x_plane_stride >= (long long)x_pitch * s.m_rows,
+    const bool grouped = x_row_group > 0 && x_row_group < s.m_rows;
+    s.x_row_group = grouped ? x_row_group : s.m_rows + BM;
+    s.x_group_stride = grouped ? x_group_stride : 0;
+    B200PF_REQUIRE(x_pitch % 8 == 0 && x_pitch >= s.n_rows &&
+                       x_plane_stride >= (long long)x_pitch * (grouped ? x_row_group : s.m_rows) && x_plane_stride % 8 == 0,
                    B200PF_ERR_INVALID, "trimul_contract: bad x pitch / plane stride");
+    B200PF_REQUIRE(!grouped || (x_group_stride % 8 == 0 && x_group_stride >= x_plane_stride * channels), B200PF_ERR_INVALID,
+                   "trimul_contract: bad x group stride");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (variant == 1) {
         PlaneView va{(const __nv_bfloat16*)a->ptr, a->plane_stride, a->seg_stride, a->pitch, a->rows, a->cols, a->nseg, a->seg_is_k};

@@ -69,7 +69,7 @@ extern "C" int b200pf_tri_mul_noalloc(float* z, const uint8_t* mask, const float
     if (rc != B200PF_OK) return rc;
     b200pf_planes pa{a, plane_stride, 0, pitch, n, n, 1, 0}, pb{b, plane_stride, 0, pitch, n, n, 1, 0};
     rc = b200pf_trimul_contract(&pa, &pb, nullptr, nullptr, reinterpret_cast<b200pf_bf16*>(x), plane_stride, pitch,
-                                NOALLOC_CH, 0, stream);
+                                0, 0, NOALLOC_CH, 0, stream);
     if (rc != B200PF_OK) return rc;
     return b200pf_trimul_epilogue_tc(z, reinterpret_cast<const b200pf_bf16*>(x), plane_stride, pitch, ln_gamma, ln_beta,
                                      w_pout, w_gout, wsum, wb, n, n, stream);

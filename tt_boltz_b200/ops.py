@@ -97,7 +97,7 @@ def tri_mul_bf16(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Tens
     pa = Planes(ptr(a), ws.plane_stride, 0, ws.pitch, n, n, 1, 0)
     pb = Planes(ptr(b), ws.plane_stride, 0, ws.pitch, n, n, 1, 0)
     call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), None, None, ptr(x), ws.plane_stride, ws.pitch,
-         C_Z, contract_variant, st)
+         0, 0, C_Z, contract_variant, st)
     trimul_epilogue(z, x, ws.plane_stride, ws.pitch, w, n, n, row_impl)
 
 
@@ -120,7 +120,7 @@ def tri_mul_mxfp8(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Ten
     if contract_variant == 2:
         pa = Planes(ptr(a8), stride8, 0, pitch8, n, n, 1, 0)
         pb = Planes(ptr(b8), stride8, 0, pitch8, n, n, 1, 0)
-        call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), ptr(sa), ptr(sb), ptr(x), ws.plane_stride, ws.pitch, C_Z, 2, st)
+        call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), ptr(sa), ptr(sb), ptr(x), ws.plane_stride, ws.pitch, 0, 0, C_Z, 2, st)
     else:
         a, b = ws.buf[0], ws.buf[1]
         for src, sc, dst in ((a8, sa, a), (b8, sb, b)):
@@ -128,7 +128,7 @@ def tri_mul_mxfp8(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Ten
         pa = Planes(ptr(a), ws.plane_stride, 0, ws.pitch, n, n, 1, 0)
         pb = Planes(ptr(b), ws.plane_stride, 0, ws.pitch, n, n, 1, 0)
         call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), None, None, ptr(x), ws.plane_stride, ws.pitch,
-             C_Z, contract_variant, st)
+             0, 0, C_Z, contract_variant, st)
     trimul_epilogue(z, x, ws.plane_stride, ws.pitch, w, n, n, 0)
 
 

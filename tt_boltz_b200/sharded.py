@@ -4,13 +4,14 @@ One process per GPU (``torch.distributed``, backend NCCL over NVLink / NVSwitch)
 rows R_r = [r*nr, (r+1)*nr) of the fp32 pair tensor, nr = N / P; the single representation s is
 replicated.  Exchanges per block (everything else is row-local):
 
-  tri_mul_out    all-gather of the k-side operand b (bf16 planes)
-  tri_mul_in     all-to-all of a^T blocks (destination = owner of the output rows) and
-                 all-gather of b^T; the contraction index arrives split in P segments
+  tri_mul_out/in all-to-all of the a and b planes from row shards to CHANNEL shards (each rank
+                 contracts 128/P channels for all rows; the operands arrive split in P row
+                 segments (outgoing) or P segments of the contraction index (incoming)), and the
+                 all-to-all of the result back to row shards
   tri_att_start  all-gather of the triangle bias [query][head][key] (8 MiB at N = 1024)
   tri_att_end    all-to-all row shard -> column shard of z (fp32), bias all-gather, and the
                  all-to-all back of the updated column shard
-  single track   all-gather of the gated attention output of the local query rows
+  single track   attention, output projection and transition for the local rows, all-gather of s
 
 The plumbing helpers below work on CPU tensors with the gloo backend as well, which is how the
 partition / index logic is tested without GPUs.
@@ -19,6 +20,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import os
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -35,20 +37,68 @@ C_Z = 128
 # ------------------------------------------------------------------------------------------------
 # plumbing (backend-agnostic)
 # ------------------------------------------------------------------------------------------------
-def all_gather_cat(x: torch.Tensor, group=None) -> torch.Tensor:
-    """[P, *x.shape]: slot s holds rank s's tensor."""
+def all_gather_cat(x: torch.Tensor, group=None, tag: Optional[str] = None) -> torch.Tensor:
+    """[P, *x.shape]: slot s holds rank s's tensor.  With a ``tag`` on CUDA: peer writes (see all_to_all_blocks)."""
     world = dist.get_world_size(group)
+    x = x.contiguous()
+    nbytes = x.numel() * x.element_size()
+    if x.is_cuda and tag is not None and _PEER_COPY["enabled"] and nbytes % 16 == 0:
+        rank = dist.get_rank(group)
+        recv, hdl, ptrs = _symm_buffer(tag, world * x.numel(), x.dtype, x.device, group)
+        call("b200pf_peer_broadcast", ptr(x), ptrs, nbytes, rank, world, stream())
+        hdl.barrier(channel=0, timeout_ms=_BARRIER_TIMEOUT_MS)
+        return recv.view((world,) + tuple(x.shape))
     out = torch.empty((world,) + tuple(x.shape), dtype=x.dtype, device=x.device)
     if x.is_cuda:
-        dist.all_gather_into_tensor(out, x.contiguous(), group=group)      # one NCCL call, no staging copies
+        dist.all_gather_into_tensor(out, x, group=group)      # one NCCL call, no staging copies
     else:
-        dist.all_gather(list(out.unbind(0)), x.contiguous(), group=group)
+        dist.all_gather(list(out.unbind(0)), x, group=group)
     return out
 
 
-def all_to_all_blocks(send: torch.Tensor, group=None) -> torch.Tensor:
-    """send[t] goes to rank t; recv[s] is what rank s sent to this rank."""
+# The receive buffers are plain peer mappings; nothing here uses NVLink multicast, so the allocator is told
+# not to bind a multicast object to them (a rank that dies while bound can fault its peers' links).
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+
+# Symmetric (peer-mapped) receive buffers of the peer-write all-to-all: two per call site and size, used in turn.
+_SYMM: Dict[tuple, tuple] = {}
+_SYMM_TURN: Dict[tuple, int] = {}
+_PEER_COPY = {"enabled": os.environ.get("B200PF_PEER_COPY", "1") != "0"}       # "0": every exchange through NCCL
+_BARRIER_TIMEOUT_MS = 20000           # a rank that never arrives ends the wait with an error instead of a hang
+
+
+def _symm_buffer(tag: str, numel: int, dtype: torch.dtype, device: torch.device, group):
+    key = (tag, numel, dtype, device.index)
+    turn = _SYMM_TURN.get(key, 0)
+    _SYMM_TURN[key] = turn ^ 1
+    key = key + (turn,)
+    if key not in _SYMM:
+        import torch.distributed._symmetric_memory as symm
+        buf = symm.empty(numel, dtype=dtype, device=device)
+        hdl = symm.rendezvous(buf, group if group is not None else dist.group.WORLD)
+        ptrs = (C.c_ulonglong * hdl.world_size)(*[int(p) for p in hdl.buffer_ptrs])
+        _SYMM[key] = (buf, hdl, ptrs)
+    return _SYMM[key]
+
+
+def all_to_all_blocks(send: torch.Tensor, group=None, tag: Optional[str] = None) -> torch.Tensor:
+    """send[t] goes to rank t; recv[s] is what rank s sent to this rank.
+
+    On CUDA with a ``tag`` (one per call site) every rank writes its blocks straight into the destination
+    ranks' symmetric receive buffers over NVLink with one kernel (``b200pf_peer_scatter``), followed by one
+    device-side barrier that says every block has landed.  Each call site alternates between two receive
+    buffers: a rank can only pass the barrier of exchange k+1 after every rank has enqueued it, i.e. after
+    their consumers of exchange k in stream order, so exchange k+2 may overwrite buffer k without another
+    barrier.  The returned tensor is the receive buffer: valid until the second-next exchange of the same
+    tag and size.  Otherwise (CPU / gloo, no tag, or B200PF_PEER_COPY=0) it is ``all_to_all_single``.
+    """
     send = send.contiguous()
+    if send.is_cuda and tag is not None and _PEER_COPY["enabled"]:
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        recv, hdl, ptrs = _symm_buffer(tag, send.numel(), send.dtype, send.device, group)
+        call("b200pf_peer_scatter", ptr(send), ptrs, send.numel() * send.element_size() // world, rank, world, stream())
+        hdl.barrier(channel=0, timeout_ms=_BARRIER_TIMEOUT_MS)
+        return recv.view(send.shape)
     recv = torch.empty_like(send)
     dist.all_to_all_single(recv, send, group=group)
     return recv
@@ -59,14 +109,14 @@ def rows_to_cols(z_loc: torch.Tensor, group=None) -> torch.Tensor:
     world = dist.get_world_size(group)
     nr, n, c = z_loc.shape
     send = z_loc.view(nr, world, nr, c).permute(1, 0, 2, 3)      # [dest t][i_local][j_local][c]
-    return all_to_all_blocks(send, group).view(n, nr, c)         # [src s * nr + i_local][j_local][c]
+    return all_to_all_blocks(send, group, "z_rows_to_cols").view(n, nr, c)   # [src s * nr + i_local][j_local][c]
 
 
 def cols_to_rows(zc: torch.Tensor, group=None) -> torch.Tensor:
     """Inverse of rows_to_cols: column shard [N, nr, C] -> row shard [nr, N, C]."""
     world = dist.get_world_size(group)
     n, nr, c = zc.shape
-    recv = all_to_all_blocks(zc.view(world, nr, nr, c), group)   # recv[s] = rows R_r, cols R_s
+    recv = all_to_all_blocks(zc.view(world, nr, nr, c), group, "z_cols_to_rows")   # recv[s] = rows R_r, cols R_s
     return recv.permute(1, 0, 2, 3).reshape(nr, n, c).contiguous()
 
 
@@ -102,33 +152,36 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
     st = stream()
     mask_loc = masks.pm[r0:r0 + nr]
 
-    # ---- triangle multiplication, outgoing -------------------------------------------------------
-    w = pk["tri_mul_out"]
-    a_loc, b_loc, x = _bf16(C_Z * nr * pn, dev), _bf16(C_Z * nr * pn, dev), _bf16(C_Z * nr * pn, dev)
-    oa, ob = PlaneOut(ptr(a_loc), nr * pn, 0, 0), PlaneOut(ptr(b_loc), nr * pn, 0, 0)
-    call("b200pf_trimul_producer", ptr(z_loc), ptr(mask_loc), *ops.trimul_producer_weights(w, layer.row_impl),
-         C.byref(oa), C.byref(ob), pn, nr, n, 0, 0, layer.row_impl, st)
-    b_all = all_gather_cat(b_loc, group)                                             # [P][D][nr][pn]
-    pa = Planes(ptr(a_loc), nr * pn, 0, pn, nr, n, 1, 0)
-    pb = Planes(ptr(b_all), nr * pn, C_Z * nr * pn, pn, nr, n, world, 0)
-    call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), None, None, ptr(x), nr * pn, pn, C_Z, layer.contract_variant, st)
-    ops.trimul_epilogue(z_loc, x, nr * pn, pn, w, nr, n, layer.row_impl)
-
-    # ---- triangle multiplication, incoming -------------------------------------------------------
-    w = pk["tri_mul_in"]
-    at_send = _bf16(world * C_Z * nr * pr, dev)                                      # [dest][D][i_local][k_local]
-    bt_loc = _bf16(C_Z * n * pr, dev)                                                # [D][j][k_local]
-    oa = PlaneOut(ptr(at_send), nr * pr, C_Z * nr * pr, nr)
-    ob = PlaneOut(ptr(bt_loc), n * pr, 0, 0)
-    call("b200pf_trimul_producer", ptr(z_loc), ptr(mask_loc), *ops.trimul_producer_weights(w, layer.row_impl),
-         C.byref(oa), C.byref(ob), pr, nr, n, 1, 0, layer.row_impl, st)
-    at_recv = all_to_all_blocks(at_send.view(world, -1), group)                      # [src][D][i_local][k_local of src]
-    bt_all = all_gather_cat(bt_loc, group)                                           # [src][D][j][k_local of src]
-    pa = Planes(ptr(at_recv), nr * pr, C_Z * nr * pr, pr, nr, nr, world, 1)
-    pb = Planes(ptr(bt_all), n * pr, C_Z * n * pr, pr, n, nr, world, 1)
-    call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), None, None, ptr(x), nr * pn, pn, C_Z, layer.contract_variant, st)
-    ops.trimul_epilogue(z_loc, x, nr * pn, pn, w, nr, n, layer.row_impl)
-    del a_loc, b_loc, b_all, at_send, at_recv, bt_loc, bt_all, x
+    # ---- triangle multiplication (both directions): channel-parallel contraction --------------------
+    # The contraction is independent per channel, so instead of gathering a whole operand on every rank,
+    # each rank contracts C/P channels for ALL rows: the producer's channel-major planes are already one
+    # contiguous block per destination rank (all-to-all), and the contraction writes its result in groups
+    # of output rows, one contiguous block per owner (all-to-all back).  Per rank and direction this moves
+    # 3 * (P-1)/P of one local operand instead of (P-1) of them.
+    if C_Z % world:
+        raise RuntimeError("the sharded triangle multiplication needs the rank count to divide 128 channels")
+    cl = C_Z // world                                                                # channels contracted here
+    x_send, x_loc = _bf16(world * cl * nr * pn, dev), None
+    for incoming in (0, 1):
+        w = pk["tri_mul_in" if incoming else "tri_mul_out"]
+        # outgoing: planes [D][local row i or j][k], k = all N columns; incoming: [D][column i or j][local row k]
+        prow, pcol, pitch = (n, nr, pr) if incoming else (nr, n, pn)
+        a_loc, b_loc = _bf16(C_Z * prow * pitch, dev), _bf16(C_Z * prow * pitch, dev)
+        oa, ob = PlaneOut(ptr(a_loc), prow * pitch, 0, 0), PlaneOut(ptr(b_loc), prow * pitch, 0, 0)
+        call("b200pf_trimul_producer", ptr(z_loc), ptr(mask_loc), *ops.trimul_producer_weights(w, layer.row_impl),
+             C.byref(oa), C.byref(ob), pitch, nr, n, incoming, 0, layer.row_impl, st)
+        a_ch = all_to_all_blocks(a_loc.view(world, -1), group, "trimul_a")           # [src][cl][prow][pitch]
+        b_ch = all_to_all_blocks(b_loc.view(world, -1), group, "trimul_b")
+        seg = cl * prow * pitch
+        # outgoing: the source rank owns a block of ROWS of the operand; incoming: a block of the contraction index
+        pa = Planes(ptr(a_ch), prow * pitch, seg, pitch, prow, pcol, world, incoming)
+        pb = Planes(ptr(b_ch), prow * pitch, seg, pitch, prow, pcol, world, incoming)
+        call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), None, None, ptr(x_send), nr * pn, pn,
+             nr, cl * nr * pn, cl, layer.contract_variant, st)                      # x[dest][cl][nr][pn]
+        x_loc = all_to_all_blocks(x_send.view(world, -1), group, "trimul_x")         # [src = channel block][cl][nr][pn] = [D][nr][pn]
+        ops.trimul_epilogue(z_loc, x_loc, nr * pn, pn, w, nr, n, layer.row_impl)
+        del a_loc, b_loc, a_ch, b_ch
+    del x_send, x_loc
 
     # ---- triangle attention, starting node (lines = local rows) ---------------------------------
     w = pk["tri_att_start"]
@@ -136,7 +189,7 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
     bias_loc = _bf16(nr * 4 * pn, dev)
     call("b200pf_triatt_producer", ptr(z_loc), *ops.triatt_producer_weights(w, layer.row_impl), ptr(q), ptr(k), ptr(v), ptr(g),
          ptr(bias_loc), pn, 4 * pn, pn, nr, n, 0, layer.row_impl, st)
-    bias_all = all_gather_cat(bias_loc, group)                                       # [query][head][key]
+    bias_all = all_gather_cat(bias_loc, group, "tri_bias")                           # [query][head][key]
     call("b200pf_triatt_core_tc4", ptr(q), ptr(k), ptr(v), pn, ptr(bias_all), pn, 4 * pn, ptr(masks.rows[r0:r0 + nr]),
          masks.pitch, ptr(o), n * C_Z, C_Z, nr, n, st)
     call("b200pf_triatt_epilogue", ptr(z_loc), ptr(o), ptr(g), ptr(w["w_o"]), nr * n, st)
@@ -146,7 +199,7 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
     zc = rows_to_cols(z_loc, group)                                                  # [N][nr][128] fp32
     call("b200pf_triatt_producer", ptr(zc), *ops.triatt_producer_weights(w, layer.row_impl), ptr(q), ptr(k), ptr(v), ptr(g),
          ptr(bias_loc), pn, 4 * pn, pn, n, nr, 1, layer.row_impl, st)
-    bias_all = all_gather_cat(bias_loc, group)
+    bias_all = all_gather_cat(bias_loc, group, "tri_bias")
     call("b200pf_triatt_core_tc4", ptr(q), ptr(k), ptr(v), pn, ptr(bias_all), pn, 4 * pn, ptr(masks.cols[r0:r0 + nr]),
          masks.pitch, ptr(o), C_Z, nr * C_Z, nr, n, st)
     call("b200pf_triatt_epilogue", ptr(zc), ptr(o), ptr(g), ptr(w["w_o"]), n * nr, st)
@@ -160,8 +213,10 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
     if layer.with_s and s is not None:
         og_loc = ops.single_track_local(s, z_loc, tok_mask_u8, pk["pre_norm_s"], pk["attention"], pk["s_fused"],
                                         layer.num_heads, r0)
-        og_all = all_gather_cat(og_loc, group).view(n, s.shape[1])
-        ops.single_track_finish(s, og_all, pk["attention"], pk["transition_s"], pk["s_fused"])
+        # output projection and transition are per row: run them on the local rows, then gather s
+        s_loc = s[r0:r0 + nr]
+        ops.single_track_finish(s_loc, og_loc, pk["attention"], pk["transition_s"], pk["s_fused"])
+        s.copy_(all_gather_cat(s_loc, group, "s_rows").view(n, s.shape[1]))
     return z_loc
 
 
