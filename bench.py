@@ -58,12 +58,14 @@ def kernel_work(n: int):
     }
 
 
-# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per launch divided by the algorithmic bytes, from one
-# `ncu --set full` capture at N = 768 (profiles/tcgen05_kernels_n768_ncu_full.md); traffic grows with N^2 * 128, so
-# the full-size figure is this ratio times the algorithmic bytes at the benchmark's N.
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per launch divided by the algorithmic bytes, from
+# `ncu --set full` captures at N = 768 (profiles/tcgen05_kernels_n768_ncu_full.md, triatt_core_tc4_n768_ncu_full.md,
+# trimul_mxfp8_n768_ncu_full.md); traffic grows with N^2 * 128, so the full-size figure is this ratio times the
+# algorithmic bytes at the benchmark's N.
 NCU_TRAFFIC_RATIO = {
     "b200pf_trimul_contract": 0.92, "b200pf_trimul_producer": 0.92, "b200pf_trimul_epilogue_tc": 0.92,
-    "b200pf_triatt_producer": 0.94, "b200pf_triatt_core_tc": 0.98, "b200pf_triatt_epilogue": 0.95,
+    "b200pf_triatt_producer": 0.94, "b200pf_triatt_core_tc": 0.98, "b200pf_triatt_core_tc4": 0.98,
+    "b200pf_triatt_epilogue": 0.95, "b200pf_trimul_producer_mx": 0.93,
 }
 
 

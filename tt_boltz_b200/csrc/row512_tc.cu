@@ -125,6 +125,19 @@ row512_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ 
             ok = mbar_wait(&B->a_empty[stage], ph ^ 1, abort_flag);
             if (!ok) break;
             uint8_t* a_tile = smem + OFF_A + stage * A_TILE_BYTES;
+            // this warp's 32 rows of the NEXT tile: one lane per row asks L2 for its four 128-byte lines, so the
+            // loads of the next round find them there instead of paying the DRAM latency with only 4 warps in flight
+            {
+                const long long tn = t + gridDim.x;
+                if (tn < tiles) {
+                    const long long f = flat_of((int)(tn / tpl), (int)(tn % tpl) * TM + warp * 32 + lane);
+                    if (f >= 0) {
+                        const char* rowp = reinterpret_cast<const char*>(p.z + f * KC);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) asm volatile("prefetch.global.L2 [%0];" ::"l"(rowp + j * 128));
+                    }
+                }
+            }
 #pragma unroll 1
             for (int pass = 0; pass < 2; ++pass) {
                 const int row0 = warp * 32 + pass * 16;

@@ -123,6 +123,14 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_w12, const __grid_c
             ok = mbar_wait(&B->a_empty[stage], ph ^ 1, abort_flag);
             if (!ok) break;
             uint8_t* a_tile = smem + OFF_A + stage * A_TILE_BYTES;
+            {   // ask L2 for this warp's 32 rows of the NEXT tile (one lane per row, four 128-byte lines)
+                const long long fn = (t + gridDim.x) * TM + warp * 32 + lane;
+                if (t + gridDim.x < tiles && fn < p.rows_flat) {
+                    const char* rowp = reinterpret_cast<const char*>(p.z + fn * KC);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) asm volatile("prefetch.global.L2 [%0];" ::"l"(rowp + j * 128));
+                }
+            }
 #pragma unroll 1
             for (int pass = 0; pass < 2; ++pass) {
                 const int row0 = warp * 32 + pass * 16;

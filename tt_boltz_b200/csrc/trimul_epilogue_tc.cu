@@ -123,6 +123,15 @@ trimul_epilogue_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
             ok = mbar_wait(&B->in_empty[stage], ph ^ 1, abort_flag) && mbar_wait(&B->acc_empty[stage], ph ^ 1, abort_flag);
             if (!ok) break;
             uint8_t* a_tile = smem + OFF_AZ + stage * A_TILE_BYTES;
+            {   // ask L2 for this warp's 32 rows of the NEXT tile (one lane per row, four 128-byte lines)
+                const long long tn = t + gridDim.x;
+                const int posn = (int)(tn % tpl) * TM + warp * 32 + lane;
+                if (tn < tiles && posn < p.n) {
+                    const char* rowp = reinterpret_cast<const char*>(p.z + ((tn / tpl) * p.n + posn) * KC);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) asm volatile("prefetch.global.L2 [%0];" ::"l"(rowp + j * 128));
+                }
+            }
 #pragma unroll 1
             for (int pass = 0; pass < 2; ++pass) {
                 const int row0 = warp * 32 + pass * 16;
