@@ -198,12 +198,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) triatt_epilogue_kernel(AttEpilo
                     if (f >= p.rows_flat) continue;
                     float* zr = p.z + f * KC + c * 64 + 2 * t;
 #pragma unroll
-                    for (int nt = 0; nt < 8; ++nt) {
-                        float2 zv = *reinterpret_cast<float2*>(zr + nt * 8);
-                        zv.x += acc[mi][nt][hh * 2];
-                        zv.y += acc[mi][nt][hh * 2 + 1];
-                        *reinterpret_cast<float2*>(zr + nt * 8) = zv;
-                    }
+                    for (int nt = 0; nt < 8; ++nt)      // residual add done by L2 (no load to wait for)
+                        asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(zr + nt * 8), "f"(acc[mi][nt][hh * 2]),
+                                     "f"(acc[mi][nt][hh * 2 + 1]) : "memory");
                 }
         }
         __syncwarp();
