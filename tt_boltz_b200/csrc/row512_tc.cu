@@ -150,59 +150,87 @@ row512_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ 
 #pragma unroll
                     for (int j = 0; j < 4; ++j) v[i][j] = fl[i] < 0 ? make_float4(0.f, 0.f, 0.f, 0.f) : __ldg(src + j * 8 + sub);
                 }
+                // The four rows of a pass are worked on stage by stage (all sums, then all shuffles, ...), not row by
+                // row: one loader warp per scheduler has nothing else to hide a dependent chain behind.
+                float kz[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const int row = row0 + i * 4 + rq;
+                    bool keep = fl[i] >= 0;
+                    if (MODE != MODE_TRIATT) keep = keep && __ldg(p.mask + (fl[i] < 0 ? 0 : fl[i])) != 0;
+                    kz[i] = keep ? 1.f : 0.f;
+                }
+                float s4[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
                     float s = 0.f;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) s += (v[i][j].x + v[i][j].y) + (v[i][j].z + v[i][j].w);
-                    s += __shfl_xor_sync(0xffffffffu, s, 1);
-                    s += __shfl_xor_sync(0xffffffffu, s, 2);
-                    s += __shfl_xor_sync(0xffffffffu, s, 4);
-                    const float mean = s * (1.f / KC);
+                    s4[i] = s;
+                }
+#pragma unroll
+                for (int step = 1; step < 8; step <<= 1)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) s4[i] += __shfl_xor_sync(0xffffffffu, s4[i], step);
+                float ss4[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float mean = s4[i] * (1.f / KC);
                     float ss = 0.f;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         v[i][j].x -= mean; v[i][j].y -= mean; v[i][j].z -= mean; v[i][j].w -= mean;
                         ss += (v[i][j].x * v[i][j].x + v[i][j].y * v[i][j].y) + (v[i][j].z * v[i][j].z + v[i][j].w * v[i][j].w);
                     }
-                    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
-                    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
-                    ss += __shfl_xor_sync(0xffffffffu, ss, 4);
-                    const float rstd = rsqrtf(ss * (1.f / KC) + LN_EPS);
-                    bool keep = fl[i] >= 0;
-                    if (MODE != MODE_TRIATT) keep = keep && p.mask[fl[i] < 0 ? 0 : fl[i]] != 0;
-                    const float kz = keep ? 1.f : 0.f;
+                    ss4[i] = ss;
+                }
+#pragma unroll
+                for (int step = 1; step < 8; step <<= 1)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) ss4[i] += __shfl_xor_sync(0xffffffffu, ss4[i], step);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int row = row0 + i * 4 + rq;
+                    const float rstd = rsqrtf(ss4[i] * (1.f / KC) + LN_EPS);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        v[i][j].x = fmaf(v[i][j].x * rstd, gam[j].x, bet[j].x) * kz;
-                        v[i][j].y = fmaf(v[i][j].y * rstd, gam[j].y, bet[j].y) * kz;
-                        v[i][j].z = fmaf(v[i][j].z * rstd, gam[j].z, bet[j].z) * kz;
-                        v[i][j].w = fmaf(v[i][j].w * rstd, gam[j].w, bet[j].w) * kz;
+                        v[i][j].x = fmaf(v[i][j].x * rstd, gam[j].x, bet[j].x) * kz[i];
+                        v[i][j].y = fmaf(v[i][j].y * rstd, gam[j].y, bet[j].y) * kz[i];
+                        v[i][j].z = fmaf(v[i][j].z * rstd, gam[j].z, bet[j].z) * kz[i];
+                        v[i][j].w = fmaf(v[i][j].w * rstd, gam[j].w, bet[j].w) * kz[i];
                         uint2 o;
                         o.x = pack_bf16x2(v[i][j].x, v[i][j].y);
                         o.y = pack_bf16x2(v[i][j].z, v[i][j].w);
                         const int chunk = (j & 1) * 4 + (sub >> 1);
                         *reinterpret_cast<uint2*>(a_tile + (j >> 1) * A_KB_BYTES + sw128(row, chunk) + (sub & 1) * 8) = o;
                     }
-                    if (MODE == MODE_TRIATT) {
-                        float acc[4];
+                }
+                if (MODE == MODE_TRIATT) {
+                    float acc[4][4];      // [row i][head]
 #pragma unroll
-                        for (int h = 0; h < 4; ++h) {
+                    for (int h = 0; h < 4; ++h) {
+                        float4 wv[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) wv[j] = *reinterpret_cast<const float4*>(wb_s + h * 128 + (j * 8 + sub) * 4);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
                             float a = 0.f;
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const float4 wv = *reinterpret_cast<const float4*>(wb_s + h * 128 + (j * 8 + sub) * 4);
-                                a += v[i][j].x * wv.x + v[i][j].y * wv.y + v[i][j].z * wv.z + v[i][j].w * wv.w;
-                            }
-                            a += __shfl_xor_sync(0xffffffffu, a, 1);
-                            a += __shfl_xor_sync(0xffffffffu, a, 2);
-                            a += __shfl_xor_sync(0xffffffffu, a, 4);
-                            acc[h] = a;
+                            for (int j = 0; j < 4; ++j)
+                                a += v[i][j].x * wv[j].x + v[i][j].y * wv[j].y + v[i][j].z * wv[j].z + v[i][j].w * wv[j].w;
+                            acc[i][h] = a;
                         }
+                    }
+#pragma unroll
+                    for (int step = 1; step < 8; step <<= 1)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+#pragma unroll
+                            for (int h = 0; h < 4; ++h) acc[i][h] += __shfl_xor_sync(0xffffffffu, acc[i][h], step);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
                         if (sub < 4 && fl[i] >= 0) {
-                            float val = sub == 0 ? acc[0] : (sub == 1 ? acc[1] : (sub == 2 ? acc[2] : acc[3]));
-                            p.tri_bias[sub * p.bias_hs + (long long)line * p.bias_qs + pos0 + row] = __float2bfloat16(val);
+                            const float val = sub == 0 ? acc[i][0] : (sub == 1 ? acc[i][1] : (sub == 2 ? acc[i][2] : acc[i][3]));
+                            p.tri_bias[sub * p.bias_hs + (long long)line * p.bias_qs + pos0 + row0 + i * 4 + rq] = __float2bfloat16(val);
                         }
                     }
                 }
