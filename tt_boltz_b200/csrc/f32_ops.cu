@@ -414,6 +414,108 @@ ln_proj_heads_kernel(const float* __restrict__ z, const float* __restrict__ gamm
     }
 }
 
+// The same for 16 heads on the tensor cores, still at fp32 accuracy: mma.sync m16n8k8 with the
+// 3xTF32 split (x = hi + lo in tf32; hi*hi + lo*hi + hi*lo, fp32 accumulation: error ~2^-19 per
+// product).  A warp takes 16 rows per step: lane (g, t) = (lane / 4, lane % 4) holds channels
+// [32 t, 32 t + 32) of rows g and g + 8.  K step ks uses channels 32 t + 2 ks (+1) of every lane,
+// which is the k <-> channel map the weights are laid out with in shared memory.
+__device__ __forceinline__ uint32_t to_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ void mma_tf32(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(256)
+ln_proj_heads16_mma_kernel(const float* __restrict__ z, const float* __restrict__ gamma, const float* __restrict__ beta,
+                           const float* __restrict__ w, float* __restrict__ out, long long out_hs, long long rows) {
+    constexpr int C = 128, HEADS = 16;
+    __shared__ uint2 w_hi[16][2][32], w_lo[16][2][32];       // [k step][n tile][lane] -> (b0, b1)
+    __shared__ float cs[HEADS];
+    for (int i = threadIdx.x; i < 16 * 2 * 32; i += blockDim.x) {
+        const int ln = i & 31, nt = (i >> 5) & 1, ks = i >> 6;
+        const int g = ln >> 2, t = ln & 3, h = nt * 8 + g, c0 = 32 * t + 2 * ks;
+        const float v0 = w[h * C + c0] * gamma[c0], v1 = w[h * C + c0 + 1] * gamma[c0 + 1];
+        const uint32_t h0 = to_tf32(v0), h1 = to_tf32(v1);
+        w_hi[ks][nt][ln] = make_uint2(h0, h1);
+        w_lo[ks][nt][ln] = make_uint2(to_tf32(v0 - __uint_as_float(h0)), to_tf32(v1 - __uint_as_float(h1)));
+    }
+    if (threadIdx.x < HEADS) {
+        float sacc = 0.f;
+        for (int c = 0; c < C; ++c) sacc += w[threadIdx.x * C + c] * beta[c];
+        cs[threadIdx.x] = sacc;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+    for (long long base = warp * 16; base < rows; base += nwarps * 16) {
+        float x[2][32];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const long long row = base + g + 8 * r;
+            const float4* src = reinterpret_cast<const float4*>(z + (row < rows ? row : 0) * C + 32 * t);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const float4 v = row < rows ? __ldg(src + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+                x[r][4 * q] = v.x; x[r][4 * q + 1] = v.y; x[r][4 * q + 2] = v.z; x[r][4 * q + 3] = v.w;
+            }
+        }
+        float sm[2], ss[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            float a = 0.f;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) a += x[r][e];
+            sm[r] = a;
+        }
+#pragma unroll
+        for (int st = 1; st < 4; st <<= 1)
+#pragma unroll
+            for (int r = 0; r < 2; ++r) sm[r] += __shfl_xor_sync(0xffffffffu, sm[r], st);
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const float mean = sm[r] * (1.f / C);
+            float a = 0.f;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) { x[r][e] -= mean; a = fmaf(x[r][e], x[r][e], a); }
+            ss[r] = a;
+        }
+#pragma unroll
+        for (int st = 1; st < 4; st <<= 1)
+#pragma unroll
+            for (int r = 0; r < 2; ++r) ss[r] += __shfl_xor_sync(0xffffffffu, ss[r], st);
+        const float rstd0 = rsqrtf(ss[0] * (1.f / C) + LN_EPS), rstd1 = rsqrtf(ss[1] * (1.f / C) + LN_EPS);
+        float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int ks = 0; ks < 16; ++ks) {
+            const float v0 = x[0][2 * ks] * rstd0, v1 = x[1][2 * ks] * rstd1, v2 = x[0][2 * ks + 1] * rstd0, v3 = x[1][2 * ks + 1] * rstd1;
+            const uint32_t a0 = to_tf32(v0), a1 = to_tf32(v1), a2 = to_tf32(v2), a3 = to_tf32(v3);
+            const uint32_t l0 = to_tf32(v0 - __uint_as_float(a0)), l1 = to_tf32(v1 - __uint_as_float(a1));
+            const uint32_t l2 = to_tf32(v2 - __uint_as_float(a2)), l3 = to_tf32(v3 - __uint_as_float(a3));
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                const uint2 bh = w_hi[ks][nt][lane], bl = w_lo[ks][nt][lane];
+                mma_tf32(acc[nt], l0, l1, l2, l3, bh.x, bh.y);
+                mma_tf32(acc[nt], a0, a1, a2, a3, bl.x, bl.y);
+                mma_tf32(acc[nt], a0, a1, a2, a3, bh.x, bh.y);
+            }
+        }
+        // c0: (row g, head 2t), c1: (row g, head 2t + 1), c2 / c3: the same for row g + 8
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const long long row = base + g + 8 * (e >> 1);
+                const int h = nt * 8 + 2 * t + (e & 1);
+                if (row < rows) out[h * out_hs + row] = acc[nt][e] + cs[h];
+            }
+    }
+}
+
 }  // namespace b200pf
 
 using namespace b200pf;
@@ -532,7 +634,8 @@ int b200pf_ln_proj_heads(const float* z, const float* gamma, const float* beta, 
     if (heads == 4)
         ln_proj_heads_kernel<4><<<blocks, 256, 0, (cudaStream_t)stream>>>(z, gamma, beta, w, out, out_hs, rows);
     else
-        ln_proj_heads_kernel<16><<<blocks, 256, 0, (cudaStream_t)stream>>>(z, gamma, beta, w, out, out_hs, rows);
+        ln_proj_heads16_mma_kernel<<<(unsigned)min((long long)148 * 4, (rows + 127) / 128), 256, 0, (cudaStream_t)stream>>>(
+            z, gamma, beta, w, out, out_hs, rows);
     B200PF_LAUNCH_CHECK();
     return B200PF_OK;
 }

@@ -47,15 +47,15 @@ struct Bars {
     int abort_flag;
 };
 
-// D[tmem] = A(rows a_row0.. of `a_addr` tile set, M = 128) * B(rows b_row0 .. + n_cols)^T over K = 128.
-__device__ __forceinline__ void gemm_k128(uint32_t tmem_d, uint32_t a_addr, uint32_t a_kb, uint32_t b_addr, uint32_t b_kb,
-                                          uint32_t idesc) {
+// D[tmem] = A (M = 128 rows) * B^T over K = 128: two k-blocks of 64, each four K = 16 steps.  Operands are given as
+// ready descriptors of their first k-block (address field in 16-byte units) plus the k-block distance in the same
+// units: the issuing thread must not spend longer per instruction than the ~64 cycles it occupies the tensor pipe.
+__device__ __forceinline__ void gemm_k128(uint32_t tmem_d, uint64_t da, uint32_t a_kb16, uint64_t db, uint32_t b_kb16, uint32_t idesc) {
     using namespace sm100;
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
         const uint32_t kb = ks >> 2, kk = ks & 3;
-        umma_bf16(tmem_d, make_desc_k_sw128(a_addr + kb * a_kb + kk * 32), make_desc_k_sw128(b_addr + kb * b_kb + kk * 32),
-                  idesc, ks ? 1u : 0u);
+        umma_bf16(tmem_d, da + kb * a_kb16 + kk * 2, db + kb * b_kb16 + kk * 2, idesc, ks ? 1u : 0u);
     }
 }
 
@@ -244,7 +244,9 @@ row512_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ 
         if (lane == 0) {
             // ---------------------------- MMA issuer ----------------------------
             constexpr uint32_t idesc128 = make_idesc_bf16(TM, 128), idesc256 = make_idesc_bf16(TM, 256);
-            const uint32_t w_addr = smem_u32(smem);
+            const uint64_t d_w = make_desc_k_sw128(smem_u32(smem));            // weight row r starts 8 r units further
+            const uint64_t d_x0 = make_desc_k_sw128(smem_u32(smem + OFF_A));
+            constexpr uint32_t W_KB16 = W_KB >> 4, A_KB16 = A_KB_BYTES >> 4;
             uint32_t it = 0, acc_cnt[2] = {0, 0};
             bool ok = true;
             for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
@@ -252,7 +254,7 @@ row512_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ 
                 ok = mbar_wait(&B->a_full[stage], ph, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t x_addr = smem_u32(smem + OFF_A + stage * A_TILE_BYTES);
+                const uint64_t d_x = d_x0 + stage * (uint64_t)(A_TILE_BYTES >> 4);
                 for (int half = 0; half < 2 && ok; ++half) {
                     ok = mbar_wait(&B->acc_empty[half], (acc_cnt[half] & 1) ^ 1, abort_flag);
                     if (!ok) break;
@@ -261,13 +263,13 @@ row512_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ 
                     const uint32_t d = tmem_base + half * 256;
                     if (MODE != MODE_TRIATT) {
                         // channels on the lanes: A = 128 weight rows, B = the x tile (positions)
-                        gemm_k128(d, w_addr + (half * 256) * 128, W_KB, x_addr, A_KB_BYTES, idesc128);
-                        gemm_k128(d + 128, w_addr + (half * 256 + 128) * 128, W_KB, x_addr, A_KB_BYTES, idesc128);
+                        gemm_k128(d, d_w + (half * 256) * 8, W_KB16, d_x, A_KB16, idesc128);
+                        gemm_k128(d + 128, d_w + (half * 256 + 128) * 8, W_KB16, d_x, A_KB16, idesc128);
                     } else if (half == 0) {
-                        gemm_k128(d, x_addr, A_KB_BYTES, w_addr, W_KB, idesc256);                    // [q | k]
+                        gemm_k128(d, d_x, A_KB16, d_w, W_KB16, idesc256);                          // [q | k]
                     } else {
-                        gemm_k128(d, x_addr, A_KB_BYTES, w_addr + 256 * 128, W_KB, idesc128);        // g
-                        gemm_k128(d + 128, w_addr + 384 * 128, W_KB, x_addr, A_KB_BYTES, idesc128);  // v^T
+                        gemm_k128(d, d_x, A_KB16, d_w + 256 * 8, W_KB16, idesc128);                // g
+                        gemm_k128(d + 128, d_w + 384 * 8, W_KB16, d_x, A_KB16, idesc128);          // v^T
                     }
                     umma_commit(&B->acc_full[half]);
                 }

@@ -209,11 +209,18 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_w12, const __grid_c
             constexpr uint32_t idesc = make_idesc_bf16(TM, 128);
             uint32_t it = 0, g = 0, h_cnt[2] = {0, 0};
             bool ok = true;
-            auto gemm1 = [&](uint32_t a_addr, uint32_t w_addr, uint32_t buf) {
+            // A tcgen05.mma of this size occupies the tensor pipe for ~64 cycles; building two descriptors from
+            // addresses costs the issuing thread more than that, so they are a precomputed base plus constants
+            // (the descriptor's address field counts 16-byte units).
+            const uint64_t d_a0 = make_desc_k_sw128(smem_u32(smem + OFF_A));
+            const uint64_t d_w0 = make_desc_k_sw128(smem_u32(smem + OFF_W));
+            const uint64_t d_w3_0 = make_desc_k_sw128(smem_u32(smem + OFF_W + W12_BYTES));
+            auto gemm1 = [&](uint32_t a_stage, uint32_t w_stage, uint32_t buf) {
+                const uint64_t da = d_a0 + a_stage * (uint64_t)(A_TILE_BYTES >> 4), dw = d_w0 + w_stage * (uint64_t)(WSTAGE >> 4);
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)
-                    umma_bf16(tmem_base + COL_D1 + buf * 128, make_desc_k_sw128(a_addr + (ks >> 2) * A_KB_BYTES + (ks & 3) * 32),
-                              make_desc_k_sw128(w_addr + (ks >> 2) * (128 * 128) + (ks & 3) * 32), idesc, ks ? 1u : 0u);
+                    umma_bf16(tmem_base + COL_D1 + buf * 128, da + (ks >> 2) * (A_KB_BYTES >> 4) + (ks & 3) * 2,
+                              dw + (ks >> 2) * ((128 * 128) >> 4) + (ks & 3) * 2, idesc, ks ? 1u : 0u);
                 umma_commit(&B->d1_full[buf]);
             };
             for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
@@ -221,8 +228,7 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_w12, const __grid_c
                 ok = mbar_wait(&B->a_full[stage], ph, abort_flag) && mbar_wait(&B->w_full[g & 1], (g >> 1) & 1, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t a_addr = smem_u32(smem + OFF_A + stage * A_TILE_BYTES);
-                gemm1(a_addr, smem_u32(smem + OFF_W + (g & 1) * WSTAGE), 0);
+                gemm1(stage, g & 1, 0);
                 for (int c = 0; c < CHUNKS && ok; ++c, ++g) {
                     const uint32_t buf = c & 1, ws = g & 1;
                     if (c + 1 < CHUNKS) {
@@ -230,7 +236,7 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_w12, const __grid_c
                         ok = mbar_wait(&B->w_full[g1 & 1], (g1 >> 1) & 1, abort_flag);
                         if (!ok) break;
                         tc_fence_after();
-                        gemm1(a_addr, smem_u32(smem + OFF_W + (g1 & 1) * WSTAGE), buf ^ 1);
+                        gemm1(stage, g1 & 1, buf ^ 1);
                     } else {
                         umma_commit(&B->a_empty[stage]);         // all GEMM1 of this tile issued: the A tile is free once they finish
                     }
@@ -242,11 +248,10 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_w12, const __grid_c
                         if (!ok) break;
                     }
                     tc_fence_after();
-                    const uint32_t w3_addr = smem_u32(smem + OFF_W + ws * WSTAGE + W12_BYTES);
+                    const uint64_t dw3 = d_w3_0 + ws * (uint64_t)(WSTAGE >> 4);
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)               // 64 hidden = 4 k-steps; h: 8 TMEM columns per step
-                        umma_bf16_ts(tmem_base + COL_D2, tmem_base + COL_H + buf * 32 + kk * 8, make_desc_k_sw128(w3_addr + kk * 32),
-                                     idesc, (c | kk) ? 1u : 0u);
+                        umma_bf16_ts(tmem_base + COL_D2, tmem_base + COL_H + buf * 32 + kk * 8, dw3 + kk * 2, idesc, (c | kk) ? 1u : 0u);
                     umma_commit(&B->w_empty[ws]);
                 }
                 if (ok) umma_commit(&B->d2_full);

@@ -103,6 +103,7 @@ trimul_contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer ----------------
         constexpr uint32_t idesc = make_idesc_bf16(BM, BN);
+        const uint64_t d_a0 = make_desc_k_sw128(smem_u32(smem)), d_b0 = make_desc_k_sw128(smem_u32(smem + A_BYTES));
         uint32_t stage = 0, phase = 0;
         bool ok = true;
         long long it = 0;
@@ -116,14 +117,9 @@ trimul_contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                 ok = mbar_wait(&full[stage], phase, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-                uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
-                uint32_t sb = sa + A_BYTES;
+                const uint64_t so = stage * (uint64_t)(STAGE_BYTES >> 4);      // descriptors: precomputed base + 16-byte units
 #pragma unroll
-                for (int kk = 0; kk < BK / 16; ++kk) {
-                    uint64_t da = make_desc_k_sw128(sa + kk * 32);
-                    uint64_t db = make_desc_k_sw128(sb + kk * 32);
-                    umma_bf16(tmem_d, da, db, idesc, (kb | kk) ? 1u : 0u);
-                }
+                for (int kk = 0; kk < BK / 16; ++kk) umma_bf16(tmem_d, d_a0 + so + kk * 2, d_b0 + so + kk * 2, idesc, (kb | kk) ? 1u : 0u);
                 umma_commit(&empty[stage]);
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
