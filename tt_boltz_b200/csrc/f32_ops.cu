@@ -516,6 +516,82 @@ ln_proj_heads16_mma_kernel(const float* __restrict__ z, const float* __restrict_
     }
 }
 
+// Linear on the tensor cores at fp32 accuracy (3xTF32, see above): y[M][N] (+)= x[M][K] w[N][K]^T (+ bias), or the
+// transposed result y^T[N][yt_pitch].  64 x 64 tile per CTA of 4 warps (each 32 x 32), K walked in steps of 32 with
+// the next step's global loads in flight while the current one is multiplied.  Needs K % 4 == 0 and 16-byte rows.
+__global__ void __launch_bounds__(128)
+f32_linear_mma_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
+                      float* __restrict__ y, long long m, int k, int n, int accumulate, long long yt_pitch) {
+    constexpr int BM = 64, BN = 64, BK = 32, LD = BK + 4;
+    __shared__ float xs[BM][LD], ws[BN][LD];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+    const long long m0 = (long long)blockIdx.x * BM;
+    const int n0 = blockIdx.y * BN;
+    const int lr = tid >> 3, lk = (tid & 7) * 4;              // this thread's load slot: rows lr + 16 e, k offset lk
+    float4 px[4], pw[4];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const long long r = m0 + lr + 16 * e;
+            const int c = n0 + lr + 16 * e;
+            const bool kin = k0 + lk < k;
+            px[e] = (r < m && kin) ? __ldg(reinterpret_cast<const float4*>(x + r * k + k0 + lk)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            pw[e] = (c < n && kin) ? __ldg(reinterpret_cast<const float4*>(w + (long long)c * k + k0 + lk)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    };
+    float acc[2][4][4] = {};
+    fetch(0);
+    for (int k0 = 0; k0 < k; k0 += BK) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            *reinterpret_cast<float4*>(&xs[lr + 16 * e][lk]) = px[e];
+            *reinterpret_cast<float4*>(&ws[lr + 16 * e][lk]) = pw[e];
+        }
+        __syncthreads();
+        if (k0 + BK < k) fetch(k0 + BK);
+#pragma unroll
+        for (int k8 = 0; k8 < BK; k8 += 8) {
+            uint32_t ah[2][4], al[2][4], bh[4][2], bl[4][2];
+#pragma unroll
+            for (int mi = 0; mi < 2; ++mi) {
+                const float v[4] = {xs[wm + 16 * mi + g][k8 + t], xs[wm + 16 * mi + g + 8][k8 + t],
+                                    xs[wm + 16 * mi + g][k8 + t + 4], xs[wm + 16 * mi + g + 8][k8 + t + 4]};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) { ah[mi][q] = to_tf32(v[q]); al[mi][q] = to_tf32(v[q] - __uint_as_float(ah[mi][q])); }
+            }
+#pragma unroll
+            for (int ni = 0; ni < 4; ++ni) {
+                const float v[2] = {ws[wn + 8 * ni + g][k8 + t], ws[wn + 8 * ni + g][k8 + t + 4]};
+#pragma unroll
+                for (int q = 0; q < 2; ++q) { bh[ni][q] = to_tf32(v[q]); bl[ni][q] = to_tf32(v[q] - __uint_as_float(bh[ni][q])); }
+            }
+#pragma unroll
+            for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+                for (int ni = 0; ni < 4; ++ni) {
+                    mma_tf32(acc[mi][ni], al[mi][0], al[mi][1], al[mi][2], al[mi][3], bh[ni][0], bh[ni][1]);
+                    mma_tf32(acc[mi][ni], ah[mi][0], ah[mi][1], ah[mi][2], ah[mi][3], bl[ni][0], bl[ni][1]);
+                    mma_tf32(acc[mi][ni], ah[mi][0], ah[mi][1], ah[mi][2], ah[mi][3], bh[ni][0], bh[ni][1]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+        for (int ni = 0; ni < 4; ++ni)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const long long r = m0 + wm + 16 * mi + g + 8 * (e >> 1);
+                const int c = n0 + wn + 8 * ni + 2 * t + (e & 1);
+                if (r >= m || c >= n) continue;
+                const float v = acc[mi][ni][e] + (bias ? bias[c] : 0.f);
+                const long long idx = yt_pitch > 0 ? (long long)c * yt_pitch + r : r * n + c;      // transposed: y^T[c][r]
+                y[idx] = accumulate ? y[idx] + v : v;
+            }
+}
+
 }  // namespace b200pf
 
 using namespace b200pf;
@@ -537,7 +613,10 @@ int b200pf_f32_linear(const float* x, const float* w, const float* bias, float* 
     B200PF_REQUIRE(x && w && y && rows >= 0 && k > 0 && n_out > 0, B200PF_ERR_INVALID, "f32_linear: bad argument");
     if (rows == 0) return B200PF_OK;
     dim3 grid((unsigned)((rows + 63) / 64), (unsigned)((n_out + 63) / 64));
-    f32_linear_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(x, w, bias, y, rows, k, n_out, accumulate, 0);
+    if (k % 4 == 0 && aligned16(x) && aligned16(w))
+        f32_linear_mma_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(x, w, bias, y, rows, k, n_out, accumulate, 0);
+    else
+        f32_linear_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(x, w, bias, y, rows, k, n_out, accumulate, 0);
     B200PF_LAUNCH_CHECK();
     return B200PF_OK;
 }
@@ -548,7 +627,10 @@ int b200pf_f32_linear_t(const float* x, const float* w, const float* bias, float
                    "f32_linear_t: bad argument");
     if (rows == 0) return B200PF_OK;
     dim3 grid((unsigned)((rows + 63) / 64), (unsigned)((n_out + 63) / 64));
-    f32_linear_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(x, w, bias, yt, rows, k, n_out, 0, yt_pitch);
+    if (k % 4 == 0 && aligned16(x) && aligned16(w))
+        f32_linear_mma_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(x, w, bias, yt, rows, k, n_out, 0, yt_pitch);
+    else
+        f32_linear_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(x, w, bias, yt, rows, k, n_out, 0, yt_pitch);
     B200PF_LAUNCH_CHECK();
     return B200PF_OK;
 }
