@@ -9,7 +9,7 @@
 // update leaves through TMA reduce-add into z.  silu uses one MUFU: the host halves fc1, so with
 // a = f1/2:  silu(f1) = a + a*tanh(a).
 // Weights (384 KB bf16) do not fit in shared memory: a dedicated warp streams the chunk pair
-// (32 KB + 16 KB) from L2 with TMA through a two-stage ring.
+// (32 KB + 16 KB) from L2 with TMA through a three-stage ring.
 // Roles (448 threads): warps 0-3 LayerNorm loaders, warp 4 MMA issuer, warp 5 weight TMA, warps 6-13 epilogue.
 #include "rowtc.cuh"
 #include "tmap.cuh"
@@ -25,11 +25,13 @@ constexpr int W12_BYTES = 128 * 128 * 2;                  // [128 rows][128 K]: 
 constexpr int W3_BYTES = 128 * 64 * 2;                    // [128 out][64 hidden]
 constexpr int WSTAGE = W12_BYTES + W3_BYTES;              // 49,152
 constexpr int OFF_W = 0;                                  // 2 stages
-constexpr int OFF_A = 2 * WSTAGE;                         // 2 stages x 32 KB
-constexpr int OFF_STG = OFF_A + 2 * A_TILE_BYTES;         // staging: 2 boxes of [128 pos][32 fp32]
+constexpr int WSTAGES = 3;                                // the weight stream comes from L2 for every tile: the MMA
+                                                          // issuer waited ~6.4 k clocks per tile on it with 2 stages
+constexpr int OFF_A = WSTAGES * WSTAGE;                   // 2 stages x 32 KB
+constexpr int OFF_STG = OFF_A + 2 * A_TILE_BYTES;         // staging: one box of [128 pos][32 fp32]
 constexpr int STG_BOX = 128 * 128;
-constexpr int OFF_BAR = OFF_STG + 2 * STG_BOX;
-constexpr int SMEM_BYTES = OFF_BAR + 256;                 // 196,864
+constexpr int OFF_BAR = OFF_STG + STG_BOX;
+constexpr int SMEM_BYTES = OFF_BAR + 256;                 // 229,632
 constexpr int EPI_BAR_ID = 1;
 // TMEM columns
 constexpr uint32_t COL_D1 = 0, COL_D2 = 256, COL_H = 384;
@@ -42,7 +44,7 @@ struct Args {
 };
 
 struct Bars {
-    uint64_t w_full[2], w_empty[2], a_full[2], a_empty[2], d1_full[2], h_full[2], d2_full, d2_empty;
+    uint64_t w_full[WSTAGES], w_empty[WSTAGES], a_full[2], a_empty[2], d1_full[2], h_full[2], d2_full, d2_empty;
     uint32_t tmem_slot;
     int abort_flag;
 };
@@ -90,8 +92,8 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_w12, const __grid_c
     const long long tiles = (p.rows_flat + TM - 1) / TM;
 
     if (tid == 0) {
+        for (int i = 0; i < WSTAGES; ++i) { mbar_init(&B->w_full[i], 1); mbar_init(&B->w_empty[i], 1); }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(&B->w_full[i], 1); mbar_init(&B->w_empty[i], 1);
             mbar_init(&B->a_full[i], LOAD_WARPS); mbar_init(&B->a_empty[i], 1);
             mbar_init(&B->d1_full[i], 1); mbar_init(&B->h_full[i], EPI_WARPS);
         }
@@ -187,7 +189,7 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_w12, const __grid_c
             bool ok = true;
             for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
                 for (int c = 0; c < CHUNKS; ++c, ++g) {
-                    const uint32_t stage = g & 1, ph = (g >> 1) & 1;
+                    const uint32_t stage = g % WSTAGES, ph = (g / WSTAGES) & 1;
                     ok = mbar_wait(&B->w_empty[stage], ph ^ 1, abort_flag);
                     if (!ok) break;
                     uint8_t* ws = smem + OFF_W + stage * WSTAGE;
@@ -225,18 +227,18 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_w12, const __grid_c
             };
             for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
                 const uint32_t stage = it & 1, ph = (it >> 1) & 1;
-                ok = mbar_wait(&B->a_full[stage], ph, abort_flag) && mbar_wait(&B->w_full[g & 1], (g >> 1) & 1, abort_flag);
+                ok = mbar_wait(&B->a_full[stage], ph, abort_flag) && mbar_wait(&B->w_full[g % WSTAGES], (g / WSTAGES) & 1, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-                gemm1(stage, g & 1, 0);
+                gemm1(stage, g % WSTAGES, 0);
                 for (int c = 0; c < CHUNKS && ok; ++c, ++g) {
-                    const uint32_t buf = c & 1, ws = g & 1;
+                    const uint32_t buf = c & 1, ws = g % WSTAGES;
                     if (c + 1 < CHUNKS) {
                         const uint32_t g1 = g + 1;
-                        ok = mbar_wait(&B->w_full[g1 & 1], (g1 >> 1) & 1, abort_flag);
+                        ok = mbar_wait(&B->w_full[g1 % WSTAGES], (g1 / WSTAGES) & 1, abort_flag);
                         if (!ok) break;
                         tc_fence_after();
-                        gemm1(stage, g1 & 1, buf ^ 1);
+                        gemm1(stage, g1 % WSTAGES, buf ^ 1);
                     } else {
                         umma_commit(&B->a_empty[stage]);         // all GEMM1 of this tile issued: the A tile is free once they finish
                     }
@@ -306,20 +308,21 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_w12, const __grid_c
             if (lane == 0) mbar_arrive(&B->d2_empty);
             const long long base = t * TM;
 #pragma unroll
-            for (int rd = 0; rd < 2; ++rd) {
-                // round rd stores channels [64 eh + 32 rd, +32) of both warp halves: box eh
+            for (int rd = 0; rd < 4; ++rd) {
+                // round rd stores channels [32 rd, +32): they are held by the warps with eh == rd / 2 (register half rd % 2)
                 if (epi_tid == 0) bulk_wait_read0();
                 named_bar_sync(EPI_BAR_ID, EPI_WARPS * 32);
+                if (eh == (rd >> 1)) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    uint4 v = make_uint4(d[rd][4 * j], d[rd][4 * j + 1], d[rd][4 * j + 2], d[rd][4 * j + 3]);
-                    *reinterpret_cast<uint4*>(smem + OFF_STG + eh * STG_BOX + sw128(lrow, j)) = v;
+                    for (int j = 0; j < 8; ++j) {
+                        uint4 v = make_uint4(d[rd & 1][4 * j], d[rd & 1][4 * j + 1], d[rd & 1][4 * j + 2], d[rd & 1][4 * j + 3]);
+                        *reinterpret_cast<uint4*>(smem + OFF_STG + sw128(lrow, j)) = v;
+                    }
                 }
                 fence_proxy_async();
                 named_bar_sync(EPI_BAR_ID, EPI_WARPS * 32);
                 if (epi_tid == 0) {
                     tma_reduce_add_4d(&map_z, smem + OFF_STG, rd * 32, (int)(base & 0x7fffffff), 0, 0);
-                    tma_reduce_add_4d(&map_z, smem + OFF_STG + STG_BOX, 64 + rd * 32, (int)(base & 0x7fffffff), 0, 0);
                     bulk_commit();
                 }
             }
