@@ -214,8 +214,11 @@ def test_attention_tcgen05_core_matches_mma_sync_core(dev, n):
             assert _lib.device_status() == 0
             outs.append((zd.cpu() - z[0]))
         assert torch.isfinite(outs[0]).all() and torch.isfinite(outs[2]).all()
-        assert rel_l2(outs[0], outs[1]) < 5e-3, (n, ending)
-        assert rel_l2(outs[2], outs[1]) < 5e-3, (n, ending)
+        # the tcgen05 producer takes the four bias heads from the bf16-rounded normalised rows, the mma.sync
+        # producer from fp32 rows: a little more spread between the two than between the cores alone
+        assert rel_l2(outs[0], outs[1]) < 7e-3, (n, ending)
+        assert rel_l2(outs[2], outs[1]) < 7e-3, (n, ending)
+        assert rel_l2(outs[0], outs[2]) < 3e-3, (n, ending)          # same producer, different cores
 
 
 # ---------------------------------------------------------------------------------------------

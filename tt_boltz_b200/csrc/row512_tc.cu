@@ -12,7 +12,9 @@
 //   MODE_TRIATT : D[position][q|k] = x W^T and D[position][g] = x W_g^T (thread = position:
 //                 64-byte head rows and z-layout gate rows), D[v-channel][position] = W_v x^T
 //                 (thread = channel: rows of the transposed V).  The 4 triangle-bias heads are
-//                 dotted in fp32 by the loader warps.
+//                 dotted by the epilogue warps (fp32 weights and accumulation) from the normalised
+//                 bf16 rows of the A tile: on the loader warps, one per scheduler, the same work
+//                 doubled the time of the whole kernel.
 // Output goes TMEM -> registers -> a swizzled staging tile -> TMA stores, so that global memory
 // only ever sees full, contiguous lines (thread-per-row 16-byte stores were 3x slower).
 // Roles (416 threads): warps 0-3 LayerNorm loaders (32 rows each), warp 4 MMA issuer, warps 5-12
@@ -87,7 +89,7 @@ row512_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ 
 
     if (tid == 0) {
         for (int i = 0; i < 2; ++i) {
-            mbar_init(&B->a_full[i], LOAD_WARPS); mbar_init(&B->a_empty[i], 1);
+            mbar_init(&B->a_full[i], LOAD_WARPS); mbar_init(&B->a_empty[i], MODE == MODE_TRIATT ? 1 + EPI_WARPS : 1);
             mbar_init(&B->acc_full[i], 1); mbar_init(&B->acc_empty[i], EPI_WARPS);
         }
         B->abort_flag = 0;
@@ -202,36 +204,6 @@ row512_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ 
                         o.y = pack_bf16x2(v[i][j].z, v[i][j].w);
                         const int chunk = (j & 1) * 4 + (sub >> 1);
                         *reinterpret_cast<uint2*>(a_tile + (j >> 1) * A_KB_BYTES + sw128(row, chunk) + (sub & 1) * 8) = o;
-                    }
-                }
-                if (MODE == MODE_TRIATT) {
-                    float acc[4][4];      // [row i][head]
-#pragma unroll
-                    for (int h = 0; h < 4; ++h) {
-                        float4 wv[4];
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) wv[j] = *reinterpret_cast<const float4*>(wb_s + h * 128 + (j * 8 + sub) * 4);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            float a = 0.f;
-#pragma unroll
-                            for (int j = 0; j < 4; ++j)
-                                a += v[i][j].x * wv[j].x + v[i][j].y * wv[j].y + v[i][j].z * wv[j].z + v[i][j].w * wv[j].w;
-                            acc[i][h] = a;
-                        }
-                    }
-#pragma unroll
-                    for (int step = 1; step < 8; step <<= 1)
-#pragma unroll
-                        for (int i = 0; i < 4; ++i)
-#pragma unroll
-                            for (int h = 0; h < 4; ++h) acc[i][h] += __shfl_xor_sync(0xffffffffu, acc[i][h], step);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        if (sub < 4 && fl[i] >= 0) {
-                            const float val = sub == 0 ? acc[i][0] : (sub == 1 ? acc[i][1] : (sub == 2 ? acc[i][2] : acc[i][3]));
-                            p.tri_bias[sub * p.bias_hs + (long long)line * p.bias_qs + pos0 + row0 + i * 4 + rq] = __float2bfloat16(val);
-                        }
                     }
                 }
             }
@@ -378,6 +350,37 @@ row512_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ 
                     const int rg = p.row_group[half];
                     store_round(o, half == 0 ? &map0 : &map1, pos0, line % rg, 0, line / rg);
                 } else if (half == 0) {
+                    {   // The 4 triangle-bias heads of this tile, from the normalised bf16 rows still in the A tile (the
+                        // accumulator being ready means the loaders' writes are visible): thread = position `lrow`,
+                        // this warp's two heads 2 chalf, 2 chalf + 1; fp32 weights, fp32 accumulation.
+                        const uint32_t stage = acc_cnt & 1;
+                        const uint8_t* a_row = smem + OFF_A + stage * A_TILE_BYTES + lrow * 128;
+                        const float* w0 = wb_s + (2 * chalf) * 128;
+                        float b0 = 0.f, b1 = 0.f;
+#pragma unroll
+                        for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+                            for (int c = 0; c < 8; ++c) {
+                                const uint4 xv = *reinterpret_cast<const uint4*>(a_row + kb * A_KB_BYTES + ((c ^ (lrow & 7)) << 4));
+                                const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+                                for (int q = 0; q < 2; ++q) {
+                                    const float4 wa = *reinterpret_cast<const float4*>(w0 + kb * 64 + c * 8 + q * 4);
+                                    const float4 wc = *reinterpret_cast<const float4*>(w0 + 128 + kb * 64 + c * 8 + q * 4);
+                                    const float x0 = __uint_as_float(xw[2 * q] << 16), x1 = __uint_as_float(xw[2 * q] & 0xffff0000u);
+                                    const float x2 = __uint_as_float(xw[2 * q + 1] << 16), x3 = __uint_as_float(xw[2 * q + 1] & 0xffff0000u);
+                                    b0 = fmaf(x0, wa.x, fmaf(x1, wa.y, fmaf(x2, wa.z, fmaf(x3, wa.w, b0))));
+                                    b1 = fmaf(x0, wc.x, fmaf(x1, wc.y, fmaf(x2, wc.z, fmaf(x3, wc.w, b1))));
+                                }
+                            }
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&B->a_empty[stage]);          // the A tile may be overwritten
+                        if (pos0 + lrow < span) {
+                            __nv_bfloat16* bp = p.tri_bias + (long long)line * p.bias_qs + pos0 + lrow;
+                            bp[(2 * chalf) * p.bias_hs] = __float2bfloat16(b0);
+                            bp[(2 * chalf + 1) * p.bias_hs] = __float2bfloat16(b1);
+                        }
+                    }
                     // lane = position, columns = channels of q then k; box `chalf` = channels 64*chalf ..
                     load64(tbase + chalf * 64, 0, o);
                     store_round(o, &map0, 0, pos0, line, 0);
