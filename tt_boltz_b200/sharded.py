@@ -43,11 +43,12 @@ def all_gather_cat(x: torch.Tensor, group=None, tag: Optional[str] = None) -> to
     x = x.contiguous()
     nbytes = x.numel() * x.element_size()
     if x.is_cuda and tag is not None and _PEER_COPY["enabled"] and nbytes % 16 == 0:
-        rank = dist.get_rank(group)
-        recv, hdl, ptrs = _symm_buffer(tag, world * x.numel(), x.dtype, x.device, group)
-        call("b200pf_peer_broadcast", ptr(x), ptrs, nbytes, rank, world, stream())
-        hdl.barrier(channel=0, timeout_ms=_BARRIER_TIMEOUT_MS)
-        return recv.view((world,) + tuple(x.shape))
+        peer = _peer_buffers(tag, world * x.numel(), x.dtype, x.device, group)
+        if peer is not None:
+            recv, hdl, ptrs = peer
+            call("b200pf_peer_broadcast", ptr(x), ptrs, nbytes, dist.get_rank(group), world, stream())
+            hdl.barrier(channel=0, timeout_ms=_BARRIER_TIMEOUT_MS)
+            return recv.view((world,) + tuple(x.shape))
     out = torch.empty((world,) + tuple(x.shape), dtype=x.dtype, device=x.device)
     if x.is_cuda:
         dist.all_gather_into_tensor(out, x, group=group)      # one NCCL call, no staging copies
@@ -81,6 +82,20 @@ def _symm_buffer(tag: str, numel: int, dtype: torch.dtype, device: torch.device,
     return _SYMM[key]
 
 
+def _peer_buffers(tag: str, numel: int, dtype: torch.dtype, device: torch.device, group):
+    """Receive buffer, handle and peer pointers, or None when symmetric memory cannot be set up on this system
+    (the allocation and the rendezvous are collective, so every rank takes the same branch): the exchange then
+    goes through NCCL for the rest of the process."""
+    try:
+        return _symm_buffer(tag, numel, dtype, device, group)
+    except (RuntimeError, ImportError, AttributeError) as exc:        # no peer mapping / API missing in this torch
+        if _PEER_COPY["enabled"]:
+            _PEER_COPY["enabled"] = False
+            if dist.get_rank(group) == 0:
+                print(f"b200pf: symmetric memory unavailable ({exc}); exchanges go through NCCL", flush=True)
+        return None
+
+
 def all_to_all_blocks(send: torch.Tensor, group=None, tag: Optional[str] = None) -> torch.Tensor:
     """send[t] goes to rank t; recv[s] is what rank s sent to this rank.
 
@@ -95,10 +110,12 @@ def all_to_all_blocks(send: torch.Tensor, group=None, tag: Optional[str] = None)
     send = send.contiguous()
     if send.is_cuda and tag is not None and _PEER_COPY["enabled"]:
         world, rank = dist.get_world_size(group), dist.get_rank(group)
-        recv, hdl, ptrs = _symm_buffer(tag, send.numel(), send.dtype, send.device, group)
-        call("b200pf_peer_scatter", ptr(send), ptrs, send.numel() * send.element_size() // world, rank, world, stream())
-        hdl.barrier(channel=0, timeout_ms=_BARRIER_TIMEOUT_MS)
-        return recv.view(send.shape)
+        peer = _peer_buffers(tag, send.numel(), send.dtype, send.device, group)
+        if peer is not None:
+            recv, hdl, ptrs = peer
+            call("b200pf_peer_scatter", ptr(send), ptrs, send.numel() * send.element_size() // world, rank, world, stream())
+            hdl.barrier(channel=0, timeout_ms=_BARRIER_TIMEOUT_MS)
+            return recv.view(send.shape)
     recv = torch.empty_like(send)
     dist.all_to_all_single(recv, send, group=group)
     return recv
