@@ -81,14 +81,13 @@ trimul_epilogue_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
     volatile int* abort_flag = &B->abort_flag;
     float* wsum_s = reinterpret_cast<float*>(smem + OFF_CONST);
     float* wb_s = wsum_s + 128;
-    float2* stats_s = reinterpret_cast<float2*>(smem + OFF_STATS);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     const int tpl = (p.n + TM - 1) / TM;
     const long long tiles = (long long)p.rows * tpl;
 
     if (tid == 0) {
         mbar_init(&B->x_full, 1);
-        mbar_init(&B->x_empty, 1);
+        mbar_init(&B->x_empty, 1 + EPI_WARPS);      // the MMAs and the epilogue warps' statistics pass both read the x tile
         for (int i = 0; i < 2; ++i) {
             mbar_init(&B->in_full[i], LOAD_WARPS); mbar_init(&B->in_empty[i], 1);
             mbar_init(&B->acc_full[i], 1); mbar_init(&B->acc_empty[i], EPI_WARPS);
@@ -154,26 +153,39 @@ trimul_epilogue_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
                         tma_load_4d(smem + OFF_XT + XT_BOX, &map_x, &B->x_full, pos0 + 64, r, 0, 0);
                     }
                 }
+                // the four rows of a pass stage by stage (sums, shuffles, variance, ...): instruction-level parallelism
+                // for a warp that has its scheduler almost to itself
+                float s4[4], ss4[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const int row = row0 + i * 4 + rq;
                     float s = 0.f;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) s += (v[i][j].x + v[i][j].y) + (v[i][j].z + v[i][j].w);
-                    s += __shfl_xor_sync(0xffffffffu, s, 1);
-                    s += __shfl_xor_sync(0xffffffffu, s, 2);
-                    s += __shfl_xor_sync(0xffffffffu, s, 4);
-                    const float mean = s * (1.f / KC);
+                    s4[i] = s;
+                }
+#pragma unroll
+                for (int step = 1; step < 8; step <<= 1)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) s4[i] += __shfl_xor_sync(0xffffffffu, s4[i], step);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float mean = s4[i] * (1.f / KC);
                     float ss = 0.f;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         v[i][j].x -= mean; v[i][j].y -= mean; v[i][j].z -= mean; v[i][j].w -= mean;
                         ss += (v[i][j].x * v[i][j].x + v[i][j].y * v[i][j].y) + (v[i][j].z * v[i][j].z + v[i][j].w * v[i][j].w);
                     }
-                    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
-                    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
-                    ss += __shfl_xor_sync(0xffffffffu, ss, 4);
-                    const float rstd = rsqrtf(ss * (1.f / KC) + LN_EPS);
+                    ss4[i] = ss;
+                }
+#pragma unroll
+                for (int step = 1; step < 8; step <<= 1)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) ss4[i] += __shfl_xor_sync(0xffffffffu, ss4[i], step);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int row = row0 + i * 4 + rq;
+                    const float rstd = rsqrtf(ss4[i] * (1.f / KC) + LN_EPS);
                     const float kz = valid[i] ? 1.f : 0.f;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
@@ -187,24 +199,6 @@ trimul_epilogue_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
             }
             if (warp == 0) ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;     // lane 0 waited for the x buffer
             if (!ok) break;
-            // statistics over d of the raw x tile: one position per thread
-            ok = mbar_wait(&B->x_full, it & 1, abort_flag);
-            if (!ok) break;
-            {
-                const int pos = warp * 32 + lane;
-                const uint8_t* col = smem + OFF_XT + (pos >> 6) * XT_BOX + (pos & 7) * 2;
-                const int pchunk = (pos & 63) >> 3;
-                float s = 0.f, ss = 0.f;
-#pragma unroll 8
-                for (int d = 0; d < 128; ++d) {
-                    float xv = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(col + d * 128 + ((pchunk ^ (d & 7)) << 4)));
-                    s += xv;
-                    ss = fmaf(xv, xv, ss);
-                }
-                const float mean = s * (1.f / KC);
-                const float var = fmaxf(ss * (1.f / KC) - mean * mean, 0.f);
-                stats_s[stage * 128 + pos] = make_float2(mean, rsqrtf(var + LN_EPS));
-            }
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(&B->in_full[stage]);
@@ -251,10 +245,31 @@ trimul_epilogue_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
         for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
             const int r = (int)(t / tpl), pos0 = (int)(t % tpl) * TM;
             const uint32_t stage = it & 1, ph = (it >> 1) & 1;
+            // LayerNorm statistics over the 128 channels of the raw x tile for this thread's position (both warps of a
+            // lane quarter compute them; it is cheaper here than on the four loader warps, which bound the kernel)
+            ok = mbar_wait(&B->x_full, it & 1, abort_flag);
+            if (!ok) break;
+            float2 st;
+            {
+                const uint8_t* col = smem + OFF_XT + (lrow >> 6) * XT_BOX + (lrow & 7) * 2;
+                const int pchunk = (lrow & 63) >> 3;
+                float s0 = 0.f, s1 = 0.f, q0 = 0.f, q1 = 0.f;
+#pragma unroll 8
+                for (int d = 0; d < 128; d += 2) {
+                    const float xa = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(col + d * 128 + ((pchunk ^ (d & 7)) << 4)));
+                    const float xb = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(col + (d + 1) * 128 + ((pchunk ^ ((d + 1) & 7)) << 4)));
+                    s0 += xa; q0 = fmaf(xa, xa, q0);
+                    s1 += xb; q1 = fmaf(xb, xb, q1);
+                }
+                const float mean = (s0 + s1) * (1.f / KC);
+                const float var = fmaxf((q0 + q1) * (1.f / KC) - mean * mean, 0.f);
+                st = make_float2(mean, rsqrtf(var + LN_EPS));
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&B->x_empty);
             ok = mbar_wait(&B->acc_full[stage], ph, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            const float2 st = stats_s[stage * 128 + lrow];
             const uint32_t tbase = tmem_base + lane_off + stage * 256;
 #pragma unroll 1
             for (int rd = 0; rd < 2; ++rd, ++round) {
