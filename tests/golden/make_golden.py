@@ -62,7 +62,7 @@ def build_masks(kind: str, n: int):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of moritztng/tt-boltz (the directory that holds tt_bio/)")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     sys.modules["ttnn"] = MagicMock(name="ttnn")
