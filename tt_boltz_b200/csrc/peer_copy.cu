@@ -15,16 +15,34 @@ struct PeerPtrs {
     unsigned long long recv[PEER_MAX_RANKS];     // receive buffer of rank t as mapped on this device
 };
 
+// Each thread moves UNROLL independent 16-byte pieces per step (all loads first, then all stores): NVLink stores
+// are posted, so what limits the rate is how many bytes a thread has in flight between its loads and stores.
+constexpr int PEER_UNROLL = 4;
+
 __global__ void __launch_bounds__(256)
 peer_scatter_kernel(const uint4* __restrict__ send, PeerPtrs peers, long long block_vec, int rank, int world) {
     const long long total = block_vec * world;
     const long long stride = (long long)gridDim.x * blockDim.x;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-        // start every rank on a different destination so that no receiver is hit by all senders at once
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i + (PEER_UNROLL - 1) * stride < total; i += PEER_UNROLL * stride) {
+        uint4 v[PEER_UNROLL];
+        uint4* dst[PEER_UNROLL];
+#pragma unroll
+        for (int u = 0; u < PEER_UNROLL; ++u) {
+            // start every rank on a different destination so that no receiver is hit by all senders at once
+            const long long e = i + u * stride, slot = e / block_vec, off = e - slot * block_vec;
+            const int t = (int)((slot + rank) % world);
+            dst[u] = reinterpret_cast<uint4*>(peers.recv[t]) + (long long)rank * block_vec + off;
+            v[u] = __ldg(send + (long long)t * block_vec + off);
+        }
+#pragma unroll
+        for (int u = 0; u < PEER_UNROLL; ++u) *dst[u] = v[u];
+    }
+    for (; i < total; i += stride) {
         const long long slot = i / block_vec, off = i - slot * block_vec;
         const int t = (int)((slot + rank) % world);
-        uint4* dst = reinterpret_cast<uint4*>(peers.recv[t]) + (long long)rank * block_vec + off;
-        *dst = __ldg(send + (long long)t * block_vec + off);
+        uint4* d = reinterpret_cast<uint4*>(peers.recv[t]) + (long long)rank * block_vec + off;
+        *d = __ldg(send + (long long)t * block_vec + off);
     }
 }
 
