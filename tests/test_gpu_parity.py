@@ -336,6 +336,21 @@ def test_stack_64_blocks_bf16(dev):
     assert rel_l2(so[0][:v], sr[:v]) < 2e-2
 
 
+@pytest.mark.parametrize("precision,tol", [("fp32", 1e-4), ("bf16", 2e-2), ("mxfp8", 5e-2)])
+@pytest.mark.parametrize("n", [1, 2, 3, 7, 33, 129])
+def test_tiny_and_ragged_token_counts(dev, n, precision, tol):
+    """Sizes below one tile, one past a tile boundary, and a single token, in every tier."""
+    sd = synthetic.make_weights(1, seed=1, std=0.05, affine_jitter=0.3)
+    s, z = synthetic.make_inputs(n, seed=n)
+    npad = 1 if n > 2 else 0
+    m, pm = synthetic.tail_padding_mask(n, npad)
+    so, zo = run_module(sd, 1, s, z, m, pm, dev, precision)
+    sr, zr = orc.pairformer_stack(s[0], z[0], m[0], pm[0], sd, 1)
+    v = n - npad
+    assert rel_l2(zo[0][:v, :v], zr[:v, :v]) < tol
+    assert rel_l2(so[0][:v], sr[:v]) < tol
+
+
 def test_layer_forward_signature(dev):
     """PairformerLayer.forward(s, z, mask, pair_mask, chunk_size_tri_attn, use_kernels) returns new tensors."""
     n = 32
