@@ -243,6 +243,35 @@ def test_padding_is_isolated_exactly(dev, precision):
     assert torch.isfinite(zb).all() and torch.isfinite(sb).all()
 
 
+def test_full_size_properties_n1024(dev):
+    """At the benchmark's token count the oracle takes minutes per block, so two size-independent properties stand in:
+    (1) what is stored at padded tokens never reaches the valid region (bit-exact), (2) the trunk commutes with a
+    permutation of the tokens (up to bf16 rounding: the permutation changes tile membership and summation order)."""
+    n, npad, nb = 1024, 24, 2
+    sd = synthetic.make_weights(nb, seed=3)
+    s, z = synthetic.make_inputs(n, seed=5)
+    m, pm = synthetic.tail_padding_mask(n, npad)
+    g = torch.Generator().manual_seed(13)
+    v = n - npad
+    sa, za = run_module(sd, nb, s, z, m, pm, dev, "bf16")
+    assert torch.isfinite(za).all() and torch.isfinite(sa).all()
+    # (1) garbage in the padding
+    z2, s2 = z.clone(), s.clone()
+    z2[0, v:] = 30 * torch.randn(npad, n, 128, generator=g)
+    z2[0, :, v:] = 30 * torch.randn(n, npad, 128, generator=g)
+    s2[0, v:] = 30 * torch.randn(npad, 384, generator=g)
+    sb, zb = run_module(sd, nb, s2, z2, m, pm, dev, "bf16")
+    assert torch.equal(za[0, :v, :v], zb[0, :v, :v])
+    assert torch.equal(sa[0, :v], sb[0, :v])
+    del z2, s2, sb, zb
+    # (2) permutation of the tokens
+    perm = torch.randperm(n, generator=g)
+    sp, zp = run_module(sd, nb, s[:, perm], z[:, perm][:, :, perm], m[:, perm], pm[:, perm][:, :, perm], dev, "bf16")
+    keep = pm[0].bool()
+    assert rel_l2(zp[0][keep[perm][:, perm]], za[0][perm][:, perm][keep[perm][:, perm]]) < 5e-3
+    assert rel_l2(sp[0][m[0, perm].bool()], sa[0][perm][m[0, perm].bool()]) < 5e-3
+
+
 def test_fully_masked_line_matches_reference(dev):
     """A line whose keys are all masked attends uniformly (finite), as the reference does."""
     n = 40
