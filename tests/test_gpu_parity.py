@@ -392,3 +392,32 @@ def test_layer_forward_signature(dev):
     so, zo = layer(s.to(dev), zd, m.to(dev), pm.to(dev), 128, False)
     assert zo.shape == z.shape and so.shape == s.shape and zo.data_ptr() != zd.data_ptr()
     assert torch.equal(zd.cpu(), z)            # the caller's tensor is untouched
+
+
+@pytest.mark.parametrize("nq,nk", [(1024, 1024), (128, 1024), (37, 300), (5, 132)])
+def test_staged_single_track_attention_equals_direct_kernel(dev, nq, nk):
+    """b200pf_f32_sattention picks a shared-memory staged kernel when its operands are 16-byte aligned and the
+    direct-load kernel otherwise; both use the same work split and arithmetic, so they must agree bit for bit."""
+    import math
+    from tt_boltz_b200._lib import call, ptr, stream
+    heads, hd = 16, 24
+    cs = heads * hd
+    g = torch.Generator().manual_seed(nq * 7 + nk)
+    pitch = (nk + 3) // 4 * 4
+    qg = torch.randn(nq, 2 * cs, generator=g).to(dev)
+    kvt = torch.randn(2 * cs, pitch, generator=g).to(dev)
+    mask = (torch.rand(nk, generator=g) > 0.1).to(torch.uint8).to(dev)
+    bias_qs = pitch                                            # padded rows keep the aligned path eligible for ragged nk
+    bias_al = torch.randn(heads * nq * bias_qs + 4, generator=g).to(dev)
+    bias_un = torch.empty_like(bias_al)
+    bias_un[1:].copy_(bias_al[:-1])                            # same values, 4 bytes off alignment: forces the direct kernel
+    outs = []
+    for b in (bias_al, bias_un[1:]):
+        o = torch.zeros(nq, cs, device=dev)
+        call("b200pf_f32_sattention", ptr(qg), 2 * cs, qg.data_ptr() + 4 * cs, 2 * cs, ptr(kvt), kvt.data_ptr() + 4 * cs * pitch, pitch,
+             ptr(o), cs, b.data_ptr(), nq * bias_qs, bias_qs, ptr(mask), nq, nk, heads, hd, 1.0 / math.sqrt(hd), 1e6, stream())
+        outs.append(o)
+    torch.cuda.synchronize()
+    assert bias_al.data_ptr() % 16 == 0 and bias_un[1:].data_ptr() % 16 == 4
+    assert torch.isfinite(outs[0]).all()
+    assert torch.equal(outs[0], outs[1])

@@ -307,6 +307,144 @@ __global__ void __launch_bounds__(256) f32_sattention_kernel(SAttnArgs p) {
 }
 
 // ------------------------------------------------------------------------------------------
+// The same attention with K^T, V^T and the bias rows staged through shared memory in tiles of 128 keys
+// (cp.async, two stages): the direct kernel above is bound by the latency of its global loads (one
+// dependent L2 round trip per key step), here the inner loop only reads shared memory.  Work split, key
+// order and arithmetic per (query, lane) are those of the direct kernel, so the results are bit-identical.
+// Needs 16-byte aligned kt / vt / bias and pitches that are multiples of 4 floats.
+// ------------------------------------------------------------------------------------------
+namespace sat {
+constexpr int KT = 128, QB = 4, QBLK = 32, STAGES = 2;
+template <int HD> __host__ __device__ constexpr int stage_floats() { return (2 * HD + QBLK) * KT; }
+template <int HD> __host__ __device__ constexpr int smem_bytes() { return (STAGES * stage_floats<HD>() + 8 * HD * QB) * 4; }
+
+__device__ __forceinline__ void cp_async16(float* dst, const float* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(src_bytes)
+                 : "memory");
+}
+}  // namespace sat
+
+template <int HD>
+__global__ void __launch_bounds__(256) f32_sattention_staged_kernel(SAttnArgs p) {
+    using namespace sat;
+    extern __shared__ __align__(16) float sat_smem[];
+    float* qs = sat_smem + STAGES * stage_floats<HD>();                 // [8 warps][HD][QB]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+    const int qblocks = (p.n_q + QBLK - 1) / QBLK;
+    const int h = blockIdx.x / qblocks, qblk0 = (blockIdx.x % qblocks) * QBLK, q0 = qblk0 + warp * QB;
+    const bool active = q0 < p.n_q;                                     // idle warps still help to load
+    for (int i = lane; i < HD * QB; i += 32) {
+        int e = i / QB, qb = i % QB;
+        int qi = min(q0 + qb, p.n_q - 1);
+        qs[(warp * HD + e) * QB + qb] = p.q[(long long)qi * p.q_pitch + h * HD + e] * p.scale;
+    }
+    __syncwarp();
+    const float* kt = p.kt + (long long)h * HD * p.kt_pitch;
+    const float* vt = p.vt + (long long)h * HD * p.kt_pitch;
+    const int ntiles = (p.n_k + KT - 1) / KT;
+
+    auto load_tile = [&](int t, bool with_v) {
+        float* st = sat_smem + (t & 1) * stage_floats<HD>();
+        const int k0 = t * KT;
+        constexpr int CH = KT / 4;                                      // 16-byte chunks per row
+        for (int i = tid; i < HD * CH; i += 256) {
+            const int e = i / CH, kk = k0 + (i % CH) * 4;
+            const int bytes = max(0, min(16, (p.n_k - kk) * 4));
+            const long long off = (long long)e * p.kt_pitch + (bytes ? kk : 0);
+            cp_async16(st + e * KT + (i % CH) * 4, kt + off, bytes);
+            if (with_v) cp_async16(st + (HD + e) * KT + (i % CH) * 4, vt + off, bytes);
+        }
+        for (int i = tid; i < QBLK * CH; i += 256) {
+            const int r = i / CH, kk = k0 + (i % CH) * 4;
+            const int qi = min(qblk0 + r, p.n_q - 1);
+            const int bytes = max(0, min(16, (p.n_k - kk) * 4));
+            cp_async16(st + (2 * HD + r) * KT + (i % CH) * 4, p.bias + h * p.bias_hs + qi * p.bias_qs + (bytes ? kk : 0), bytes);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    auto logits = [&](const float* st, int kl, int kk, float (&l)[QB]) {
+#pragma unroll
+        for (int qb = 0; qb < QB; ++qb) l[qb] = 0.f;
+#pragma unroll
+        for (int e = 0; e < HD; ++e) {
+            const float kv = st[e * KT + kl];
+            const float4 qv = *reinterpret_cast<const float4*>(&qs[(warp * HD + e) * QB]);
+            l[0] = fmaf(qv.x, kv, l[0]); l[1] = fmaf(qv.y, kv, l[1]); l[2] = fmaf(qv.z, kv, l[2]); l[3] = fmaf(qv.w, kv, l[3]);
+        }
+        const float mterm = p.mask ? -p.inf_value * (1.f - (float)p.mask[kk]) : 0.f;
+#pragma unroll
+        for (int qb = 0; qb < QB; ++qb) l[qb] = (l[qb] + st[(2 * HD + warp * QB + qb) * KT + kl]) + mterm;
+    };
+
+    float mx[QB], sum[QB], acc[QB][HD];
+#pragma unroll
+    for (int qb = 0; qb < QB; ++qb) {
+        mx[qb] = -INFINITY; sum[qb] = 0.f;
+#pragma unroll
+        for (int e = 0; e < HD; ++e) acc[qb][e] = 0.f;
+    }
+#pragma unroll 1
+    for (int pass = 0; pass < 2; ++pass) {
+        load_tile(0, pass == 1);
+#pragma unroll 1
+        for (int t = 0; t < ntiles; ++t) {
+            if (t + 1 < ntiles) {
+                load_tile(t + 1, pass == 1);
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
+            } else {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+            }
+            __syncthreads();
+            const float* st = sat_smem + (t & 1) * stage_floats<HD>();
+            if (active) {
+#pragma unroll 1
+                for (int j = 0; j < KT / 32; ++j) {
+                    const int kl = j * 32 + lane, kk = t * KT + kl;
+                    if (kk < p.n_k) {
+                        float l[QB];
+                        logits(st, kl, kk, l);
+                        if (pass == 0) {
+#pragma unroll
+                            for (int qb = 0; qb < QB; ++qb) mx[qb] = fmaxf(mx[qb], l[qb]);
+                        } else {
+#pragma unroll
+                            for (int qb = 0; qb < QB; ++qb) { l[qb] = expf(l[qb] - mx[qb]); sum[qb] += l[qb]; }
+#pragma unroll
+                            for (int e = 0; e < HD; ++e) {
+                                const float vv = st[(HD + e) * KT + kl];
+#pragma unroll
+                                for (int qb = 0; qb < QB; ++qb) acc[qb][e] = fmaf(l[qb], vv, acc[qb][e]);
+                            }
+                        }
+                    }
+                }
+            }
+            __syncthreads();                                            // the stage is refilled two tiles later
+        }
+        if (pass == 0) {
+#pragma unroll
+            for (int qb = 0; qb < QB; ++qb) mx[qb] = warp_max(mx[qb]);
+        }
+    }
+    if (!active) return;
+#pragma unroll
+    for (int qb = 0; qb < QB; ++qb) {
+        const float inv = 1.f / warp_sum(sum[qb]);
+        float mine = 0.f;
+#pragma unroll
+        for (int e = 0; e < HD; ++e) {
+            float tot = warp_sum(acc[qb][e]);
+            if (lane == e) mine = tot;
+        }
+        const int qi = q0 + qb;
+        if (qi < p.n_q && lane < HD) {
+            float gate = p.g ? sigmoid_precise(p.g[(long long)qi * p.g_pitch + h * HD + lane]) : 1.f;
+            p.o[(long long)qi * p.o_pitch + h * HD + lane] = mine * inv * gate;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
 // dst[j][i][:] (+)= src[i][j][:]
 // ------------------------------------------------------------------------------------------
 __global__ void f32_transpose01_kernel(const float* __restrict__ src, float* __restrict__ dst, int n, int c,
@@ -731,7 +869,13 @@ int b200pf_f32_sattention(const float* q, long long q_pitch, const float* g, lon
     B200PF_REQUIRE(kt_pitch >= n_k, B200PF_ERR_INVALID, "f32_sattention: kt_pitch must cover the keys");
     SAttnArgs p{q, g, kt, vt, bias, o, mask, q_pitch, g_pitch, o_pitch, kt_pitch, bias_hs, bias_qs, n_q, n_k, heads, scale, inf_value};
     unsigned blocks = (unsigned)(heads * ((n_q + 31) / 32));
-    f32_sattention_kernel<24><<<blocks, 256, 0, (cudaStream_t)stream>>>(p);
+    const bool staged = aligned16(kt) && aligned16(vt) && aligned16(bias) && kt_pitch % 4 == 0 && bias_hs % 4 == 0 && bias_qs % 4 == 0;
+    if (staged) {
+        B200PF_CUDA(cudaFuncSetAttribute(f32_sattention_staged_kernel<24>, cudaFuncAttributeMaxDynamicSharedMemorySize, sat::smem_bytes<24>()));
+        f32_sattention_staged_kernel<24><<<blocks, 256, sat::smem_bytes<24>(), (cudaStream_t)stream>>>(p);
+    } else {
+        f32_sattention_kernel<24><<<blocks, 256, 0, (cudaStream_t)stream>>>(p);
+    }
     B200PF_LAUNCH_CHECK();
     return B200PF_OK;
 }
