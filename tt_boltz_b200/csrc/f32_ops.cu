@@ -555,8 +555,9 @@ ln_proj_heads_kernel(const float* __restrict__ z, const float* __restrict__ gamm
 // The same for 16 heads on the tensor cores, still at fp32 accuracy: mma.sync m16n8k8 with the
 // 3xTF32 split (x = hi + lo in tf32; hi*hi + lo*hi + hi*lo, fp32 accumulation: error ~2^-19 per
 // product).  A warp takes 16 rows per step: lane (g, t) = (lane / 4, lane % 4) holds channels
-// [32 t, 32 t + 32) of rows g and g + 8.  K step ks uses channels 32 t + 2 ks (+1) of every lane,
-// which is the k <-> channel map the weights are laid out with in shared memory.
+// 16 j + 4 t .. + 3 (j = 0 .. 7) of rows g and g + 8, so the four lanes of a row read 64 contiguous bytes
+// per load instruction.  K step ks uses the lane's values 2 ks and 2 ks + 1, i.e. channels
+// 16 (ks / 2) + 4 t + 2 (ks % 2) (+1): the k <-> channel map the weights are laid out with in shared memory.
 __device__ __forceinline__ uint32_t to_tf32(float x) {
     uint32_t r;
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
@@ -575,7 +576,7 @@ ln_proj_heads16_mma_kernel(const float* __restrict__ z, const float* __restrict_
     __shared__ float cs[HEADS];
     for (int i = threadIdx.x; i < 16 * 2 * 32; i += blockDim.x) {
         const int ln = i & 31, nt = (i >> 5) & 1, ks = i >> 6;
-        const int g = ln >> 2, t = ln & 3, h = nt * 8 + g, c0 = 32 * t + 2 * ks;
+        const int g = ln >> 2, t = ln & 3, h = nt * 8 + g, c0 = 16 * (ks >> 1) + 4 * t + 2 * (ks & 1);
         const float v0 = w[h * C + c0] * gamma[c0], v1 = w[h * C + c0 + 1] * gamma[c0 + 1];
         const uint32_t h0 = to_tf32(v0), h1 = to_tf32(v1);
         w_hi[ks][nt][ln] = make_uint2(h0, h1);
@@ -595,10 +596,10 @@ ln_proj_heads16_mma_kernel(const float* __restrict__ z, const float* __restrict_
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             const long long row = base + g + 8 * r;
-            const float4* src = reinterpret_cast<const float4*>(z + (row < rows ? row : 0) * C + 32 * t);
+            const float4* src = reinterpret_cast<const float4*>(z + (row < rows ? row : 0) * C) + t;
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
-                const float4 v = row < rows ? __ldg(src + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+                const float4 v = row < rows ? __ldg(src + 4 * q) : make_float4(0.f, 0.f, 0.f, 0.f);
                 x[r][4 * q] = v.x; x[r][4 * q + 1] = v.y; x[r][4 * q + 2] = v.z; x[r][4 * q + 3] = v.w;
             }
         }
