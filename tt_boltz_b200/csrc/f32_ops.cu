@@ -582,10 +582,15 @@ ln_proj_heads16_mma_kernel(const float* __restrict__ z, const float* __restrict_
         w_hi[ks][nt][ln] = make_uint2(h0, h1);
         w_lo[ks][nt][ln] = make_uint2(to_tf32(v0 - __uint_as_float(h0)), to_tf32(v1 - __uint_as_float(h1)));
     }
-    if (threadIdx.x < HEADS) {
+    {   // LayerNorm offset carried through the weights, cs[h] = sum_c w[h][c] beta[c]: 16 threads per head (one
+        // thread per head walked 128 dependent steps while the rest of the CTA waited at the barrier)
+        const int h = threadIdx.x >> 4, sub = threadIdx.x & 15;
         float sacc = 0.f;
-        for (int c = 0; c < C; ++c) sacc += w[threadIdx.x * C + c] * beta[c];
-        cs[threadIdx.x] = sacc;
+#pragma unroll
+        for (int j = 0; j < C / 16; ++j) sacc += w[h * C + sub + 16 * j] * beta[sub + 16 * j];
+#pragma unroll
+        for (int st = 1; st < 16; st <<= 1) sacc += __shfl_xor_sync(0xffffffffu, sacc, st);
+        if (sub == 0) cs[h] = sacc;
     }
     __syncthreads();
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -855,7 +860,7 @@ int b200pf_ln_proj_heads(const float* z, const float* gamma, const float* beta, 
     if (heads == 4)
         ln_proj_heads_kernel<4><<<blocks, 256, 0, (cudaStream_t)stream>>>(z, gamma, beta, w, out, out_hs, rows);
     else
-        ln_proj_heads16_mma_kernel<<<(unsigned)min((long long)148 * 4, (rows + 127) / 128), 256, 0, (cudaStream_t)stream>>>(
+        ln_proj_heads16_mma_kernel<<<(unsigned)min((long long)148 * 2, (rows + 127) / 128), 256, 0, (cudaStream_t)stream>>>(
             z, gamma, beta, w, out, out_hs, rows);
     B200PF_LAUNCH_CHECK();
     return B200PF_OK;
