@@ -1,0 +1,87 @@
+"""The module classes must be constructible and loadable the way every call site of the reference does it.
+
+Two constructor conventions exist in the reference: the CPU modules' (tt_bio/reference.py:921-934, 1096-1108)
+and the device backend's (tt_bio/tenstorrent.py:2194-2204), which is what the template (boltz2.py:3751),
+confidence (:4503), affinity (:4689) and trunk (:5016) call sites build when the backend is selected.
+No GPU is needed: nothing here runs a kernel.
+"""
+import inspect
+
+import pytest
+import torch
+
+from tt_boltz_b200 import (B200PairformerLayer, B200PairformerModule, B200PairformerNoSeqLayer,
+                           B200PairformerNoSeqModule, synthetic)
+
+
+def _params(fn):
+    return list(inspect.signature(fn).parameters)
+
+
+def test_forward_signatures_match_the_reference():
+    # tt_bio/reference.py:958-965 and tt_bio/tenstorrent.py:2227-2234
+    assert _params(B200PairformerModule.forward) == ["self", "s", "z", "mask", "pair_mask", "use_kernels"]
+    # tt_bio/reference.py:865-875
+    assert _params(B200PairformerLayer.forward)[:7] == ["self", "s", "z", "mask", "pair_mask", "chunk_size_tri_attn", "use_kernels"]
+    # tt_bio/reference.py:1034-1042
+    assert _params(B200PairformerNoSeqLayer.forward) == ["self", "z", "pair_mask", "chunk_size_tri_attn", "use_kernels",
+                                                         "use_cuequiv_mul", "use_cuequiv_attn"]
+    # tt_bio/reference.py:1109-1114
+    assert _params(B200PairformerNoSeqModule.forward) == ["self", "z", "pair_mask", "use_kernels"]
+
+
+@pytest.mark.parametrize("args, with_s, blocks", [
+    ((64, 32, 4, 24, 16, True), True, 64),          # trunk, boltz2.py:5016
+    ((8, 32, 4, 24, 16, True), True, 8),            # confidence, boltz2.py:4503
+    ((2, 32, 4, None, None, False), False, 2),      # templates, boltz2.py:3751
+])
+def test_backend_style_constructor(args, with_s, blocks):
+    mod = B200PairformerModule(*args)
+    assert mod.transform_s is with_s and len(mod.layers) == blocks
+    keys = set(mod.state_dict().keys())
+    assert keys == set(synthetic.make_weights(blocks, with_s=with_s).keys())
+    assert ("layers.0.pre_norm_s.weight" in keys) is with_s
+
+
+def test_backend_style_keywords_and_affinity_flag():
+    mod = B200PairformerModule(n_blocks=4, tri_att_head_dim=32, tri_att_n_heads=4, att_head_dim=None,
+                               att_n_heads=None, transform_s=False, affinity=True)
+    assert mod.affinity and not mod.transform_s and len(mod.layers) == 4
+
+
+def test_cpu_module_style_constructor_still_works():
+    mod = B200PairformerModule(384, 128, 3, num_heads=16, dropout=0.25, pairwise_head_width=32,
+                               pairwise_num_heads=4, post_layer_norm=False, activation_checkpointing=False, v2=True)
+    assert mod.transform_s and len(mod.layers) == 3
+    mod.load_state_dict(synthetic.make_weights(3), strict=True)
+    with pytest.raises(TypeError):
+        B200PairformerModule(384, 128)
+
+
+@pytest.mark.parametrize("with_s", [True, False])
+def test_load_state_dict_with_the_backend_key_convention(with_s):
+    """The backend reads the triangle-attention projections with the ``mha.`` level stripped
+    (tt_bio/tenstorrent.py:973, 981); both spellings must load, strictly, to the same parameters."""
+    sd = synthetic.make_weights(2, with_s=with_s)
+    stripped = {k.replace(".mha.", "."): v for k, v in sd.items()}
+    assert any(k not in sd for k in stripped)
+    a = B200PairformerModule(2, 32, 4, 24 if with_s else None, 16 if with_s else None, with_s)
+    b = B200PairformerModule(2, 32, 4, 24 if with_s else None, 16 if with_s else None, with_s)
+    a.load_state_dict(sd, strict=True)
+    b.load_state_dict(stripped, strict=True)
+    for (ka, va), (kb, vb) in zip(a.state_dict().items(), b.state_dict().items()):
+        assert ka == kb and torch.equal(va, vb)
+    layer = B200PairformerNoSeqLayer(128)
+    one = {k[len("layers.0."):].replace("mha.", ""): v for k, v in synthetic.make_weights(1, with_s=False).items()}
+    layer.load_state_dict(one, strict=True)
+
+
+def test_no_cpu_path_on_any_surface():
+    z = torch.zeros(1, 8, 8, 128)
+    pm = torch.ones(1, 8, 8)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        B200PairformerModule(1, 32, 4, None, None, False)(None, z, None, pm)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        B200PairformerNoSeqLayer(128)(z, pm)
+    with pytest.raises(RuntimeError, match="single track"):
+        B200PairformerModule(1, 32, 4, 24, 16, True)(None, z.cuda() if torch.cuda.is_available() else z, None, pm)

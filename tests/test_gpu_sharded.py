@@ -53,9 +53,26 @@ def test_sharded_trunk_matches_oracle(world):
     procs = [ctx.Process(target=_worker, args=(r, world, port, n, blocks, q)) for r in range(world)]
     for p in procs:
         p.start()
-    res = sorted((q.get(timeout=150) for _ in procs), key=lambda t: t[0])
-    for p in procs:
-        p.join(timeout=60)
+    res = []
+    try:
+        for _ in procs:
+            try:
+                res.append(q.get(timeout=150))
+            except Exception:  # noqa: BLE001  (queue.Empty: a rank died or stalled)
+                break
+        for p in procs:
+            p.join(timeout=60)
+    finally:
+        # never leave a rank behind in a collective: it would hold its GPU on a shared box
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+        for p in procs:
+            p.join(timeout=10)
+            if p.is_alive():
+                p.kill()
+    assert len(res) == world, f"only {len(res)} of {world} ranks reported; errors: {[r[4] for r in res if r[4]]}"
+    res.sort(key=lambda t: t[0])
     for rank, so, zo, status, err in res:
         assert err is None, f"rank {rank}: {err}"
         assert status == 0

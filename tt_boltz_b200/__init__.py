@@ -1,5 +1,6 @@
 """B200-native (sm_100a) Boltz-2 Pairformer trunk: hand-written CUDA kernels behind the
 reference's PairformerModule / PairformerLayer call surface.  See include/b200pf.h for the C ABI."""
-from .pairformer import B200PairformerLayer, B200PairformerModule, B200PairformerNoSeqModule
+from .pairformer import (B200PairformerLayer, B200PairformerModule, B200PairformerNoSeqLayer,
+                         B200PairformerNoSeqModule)
 
-__all__ = ["B200PairformerLayer", "B200PairformerModule", "B200PairformerNoSeqModule"]
+__all__ = ["B200PairformerLayer", "B200PairformerModule", "B200PairformerNoSeqLayer", "B200PairformerNoSeqModule"]

@@ -75,11 +75,14 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    if not os.path.exists(LIB_PATH):
-        if not build_if_missing:
-            raise RuntimeError(f"{LIB_PATH} is missing; run `python -m tt_boltz_b200.build`")
+    if build_if_missing:
+        # build() is a no-op when the stamp over the sources matches, so a library left over from before a
+        # source edit is never loaded silently; without nvcc an existing library is used as it is
         from . import build as _build
-        _build.build()
+        if _build.have_nvcc() or not os.path.exists(LIB_PATH):
+            _build.build()
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(f"{LIB_PATH} is missing; run `python -m tt_boltz_b200.build`")
     lib = C.CDLL(LIB_PATH)
     for name, args in SIGNATURES.items():
         fn = getattr(lib, name)          # AttributeError here = the .so does not export the symbol

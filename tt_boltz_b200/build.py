@@ -36,6 +36,14 @@ def _nvcc() -> str:
     raise RuntimeError("nvcc not found: the b200pf kernels cannot be built")
 
 
+def have_nvcc() -> bool:
+    try:
+        _nvcc()
+        return True
+    except RuntimeError:
+        return False
+
+
 def sources() -> list[str]:
     return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cu"))
 

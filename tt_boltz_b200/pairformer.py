@@ -9,6 +9,13 @@ Call surface mirrors the reference:
     use_kernels=False) -> z``                 (tt_bio/reference.py:1096-1139)
   * ``B200PairformerLayer.forward(s, z, mask, pair_mask, chunk_size_tri_attn=None,
     use_kernels=False, ...)``                 (tt_bio/reference.py:865-914)
+  * ``B200PairformerNoSeqLayer(token_z, ...).forward(z, pair_mask, chunk_size_tri_attn=None,
+    use_kernels=False, ...) -> z``            (tt_bio/reference.py:1007-1095)
+  * the device backend's constructor, which is what the template / confidence / affinity / Protenix /
+    ESMFold2 call sites build: ``B200PairformerModule(n_blocks, tri_att_head_dim, tri_att_n_heads,
+    att_head_dim, att_n_heads, transform_s, affinity=False).forward(s or None, z, mask=None,
+    pair_mask=None, use_kernels=False) -> (s or None, z)``   (tt_bio/tenstorrent.py:2194-2234,
+    tt_bio/boltz2.py:3751, 4503, 4689, 5016)
 Parameters carry the reference's state-dict key names, so ``load_state_dict`` of a reference
 checkpoint slice works unchanged (tt_bio/tenstorrent.py:2179-2180 does the same for its backend).
 
@@ -21,6 +28,7 @@ or "fp32" (un-fused fp32 kernels, the validation tier).
 """
 from __future__ import annotations
 
+import re
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -70,6 +78,7 @@ class B200PairformerLayer(nn.Module):
             _register_tree(self, name, shape)
         self._packed: Optional[Dict[str, Dict[str, torch.Tensor]]] = None
         self.register_load_state_dict_post_hook(lambda module, incompatible: module.reset_static_cache())
+        self._register_load_state_dict_pre_hook(_accept_backend_keys)
 
     # same name as the reference backend's cache reset (tt_bio/tenstorrent.py:2185-2191)
     def reset_static_cache(self) -> None:
@@ -127,6 +136,36 @@ class B200PairformerLayer(nn.Module):
         return _run_layers([self], s, z, mask, pair_mask)
 
 
+class B200PairformerNoSeqLayer(B200PairformerLayer):
+    """Pair-only block with the reference's constructor and ``forward(z, pair_mask, ...) -> z``
+    (tt_bio/reference.py:1007-1095)."""
+
+    def __init__(self, token_z: int = 128, dropout: float = 0.25, pairwise_head_width: int = 32,
+                 pairwise_num_heads: int = 4, post_layer_norm: bool = False, precision: str = "bf16") -> None:
+        super().__init__(384, token_z, 16, dropout, pairwise_head_width, pairwise_num_heads, post_layer_norm,
+                         False, precision, with_s=False)
+
+    def forward(self, z: torch.Tensor, pair_mask: Optional[torch.Tensor] = None,      # type: ignore[override]
+                chunk_size_tri_attn: Optional[int] = None, use_kernels: bool = False,
+                use_cuequiv_mul: bool = False, use_cuequiv_attn: bool = False) -> torch.Tensor:
+        return _run_layers([self], None, z, None, pair_mask)[1]
+
+
+_TRI_ATT_KEY = re.compile(r"((?:^|\.)tri_att_(?:start|end)\.)linear_[qkvog]\.")
+
+
+def _accept_backend_keys(state_dict, prefix, *_unused) -> None:
+    """The reference's device backend reads the triangle-attention projections with or without the
+    ``mha.`` level in their key (tt_bio/tenstorrent.py:973, 981 strip it; the Protenix / ESMFold2 remaps
+    emit keys without it, tt_bio/protenix_weights.py:80-83).  Accept both: insert the level where it is missing."""
+    for key in list(state_dict.keys()):
+        if not key.startswith(prefix):
+            continue
+        m = _TRI_ATT_KEY.search(key)
+        if m is not None:
+            state_dict[key[:m.end(1)] + "mha." + key[m.end(1):]] = state_dict.pop(key)
+
+
 def _run_layers(layers, s, z, mask, pair_mask, ws_cache: Optional[dict] = None):
     if not z.is_cuda:
         raise RuntimeError("B200 Pairformer: inputs must be CUDA tensors (there is no CPU path)")
@@ -156,26 +195,85 @@ def _run_layers(layers, s, z, mask, pair_mask, ws_cache: Optional[dict] = None):
 
 
 class B200PairformerModule(nn.Module):
-    """Stack of Pairformer blocks with the reference's constructor and forward signature."""
+    """Stack of Pairformer blocks behind both of the reference's constructors.
 
-    def __init__(self, token_s: int, token_z: int, num_blocks: int, num_heads: int = 16, dropout: float = 0.25,
-                 pairwise_head_width: int = 32, pairwise_num_heads: int = 4, post_layer_norm: bool = False,
-                 activation_checkpointing: bool = False, v2: bool = False, precision: str = "bf16", **kwargs) -> None:
+    * CPU modules' style (tt_bio/reference.py:921-934): ``(token_s, token_z, num_blocks, num_heads=16,
+      dropout=0.25, pairwise_head_width=32, pairwise_num_heads=4, post_layer_norm=False,
+      activation_checkpointing=False, v2=False)``
+    * device backend's style (tt_bio/tenstorrent.py:2194-2204): ``(n_blocks, tri_att_head_dim, tri_att_n_heads,
+      att_head_dim, att_n_heads, transform_s, affinity=False)``; chosen when ``transform_s`` is given (sixth
+      positional argument or keyword).  ``transform_s=False`` builds pair-only blocks and ``forward`` then
+      takes ``s=None`` and returns ``(None, z)``.  The pair width is not part of that signature (the backend
+      reads it off the weights); it is 128 unless ``token_z=`` says otherwise.  ``affinity`` only selects how the
+      backend builds its masks; here every call honours the full 2-D ``pair_mask`` like the CPU modules.
+
+    ``forward(s, z, mask=None, pair_mask=None, use_kernels=False) -> (s, z)`` in both cases; a missing
+    ``pair_mask`` is the outer product of ``mask`` (all ones when that is missing too), which is what the
+    backend derives from the token mask (tt_bio/tenstorrent.py:2257-2267).
+    """
+
+    def __init__(self, *args, precision: str = "bf16", **kwargs) -> None:
         super().__init__()
-        self.token_z, self.num_blocks, self.num_heads = token_z, num_blocks, num_heads
+        if "transform_s" in kwargs or (len(args) >= 6 and isinstance(args[5], bool)):
+            names = ("n_blocks", "tri_att_head_dim", "tri_att_n_heads", "att_head_dim", "att_n_heads", "transform_s", "affinity")
+            if len(args) > len(names):
+                raise TypeError("too many positional arguments for the backend-style constructor")
+            cfg = dict(zip(names, args))
+            for k in names:
+                if k in kwargs:
+                    cfg[k] = kwargs.pop(k)
+            missing = [k for k in names[:6] if k not in cfg]
+            if missing:
+                raise TypeError(f"backend-style constructor: missing {missing}")
+            with_s = bool(cfg["transform_s"])
+            num_blocks = int(cfg["n_blocks"])
+            token_z = int(kwargs.pop("token_z", 128))
+            num_heads = int(cfg["att_n_heads"]) if with_s else 16
+            token_s = int(kwargs.pop("token_s", num_heads * int(cfg["att_head_dim"]) if with_s else 384))
+            head_width, tri_heads = int(cfg["tri_att_head_dim"]), int(cfg["tri_att_n_heads"])
+            self.affinity = bool(cfg.get("affinity", False))
+            dropout, post_layer_norm, v2 = 0.0, False, True
+        else:
+            names = ("token_s", "token_z", "num_blocks", "num_heads", "dropout", "pairwise_head_width",
+                     "pairwise_num_heads", "post_layer_norm", "activation_checkpointing", "v2")
+            if len(args) > len(names):
+                raise TypeError("too many positional arguments")
+            cfg = {"num_heads": 16, "dropout": 0.25, "pairwise_head_width": 32, "pairwise_num_heads": 4,
+                   "post_layer_norm": False, "activation_checkpointing": False, "v2": False}
+            cfg.update(zip(names, args))
+            for k in names:
+                if k in kwargs:
+                    cfg[k] = kwargs.pop(k)
+            missing = [k for k in names[:3] if k not in cfg]
+            if missing:
+                raise TypeError(f"missing constructor arguments {missing}")
+            with_s, num_blocks = True, int(cfg["num_blocks"])
+            token_s, token_z, num_heads = int(cfg["token_s"]), int(cfg["token_z"]), int(cfg["num_heads"])
+            head_width, tri_heads = int(cfg["pairwise_head_width"]), int(cfg["pairwise_num_heads"])
+            dropout, post_layer_norm, v2 = cfg["dropout"], cfg["post_layer_norm"], cfg["v2"]
+            self.affinity = False
+        self.token_z, self.num_blocks, self.num_heads, self.transform_s = token_z, num_blocks, num_heads, with_s
         self.layers = nn.ModuleList([
-            B200PairformerLayer(token_s, token_z, num_heads, dropout, pairwise_head_width, pairwise_num_heads,
-                                post_layer_norm, v2, precision, with_s=True) for _ in range(num_blocks)])
+            B200PairformerLayer(token_s, token_z, num_heads, dropout, head_width, tri_heads,
+                                post_layer_norm, v2, precision, with_s=with_s) for _ in range(num_blocks)])
         self._ws_cache: dict = {}
+        self._register_load_state_dict_pre_hook(_accept_backend_keys)
 
     def reset_static_cache(self) -> None:
         self._ws_cache.clear()
         for layer in self.layers:
             layer.reset_static_cache()
 
-    def forward(self, s: torch.Tensor, z: torch.Tensor, mask: Optional[torch.Tensor] = None,
+    def forward(self, s: Optional[torch.Tensor], z: torch.Tensor, mask: Optional[torch.Tensor] = None,
                 pair_mask: Optional[torch.Tensor] = None, use_kernels: bool = False
-                ) -> Tuple[torch.Tensor, torch.Tensor]:
+                ) -> Tuple[Optional[torch.Tensor], torch.Tensor]:
+        if pair_mask is None and mask is not None:
+            m = mask.reshape(1, -1).to(z.device)
+            pair_mask = m[:, :, None] * m[:, None, :]
+        if not self.transform_s:
+            return None, _run_layers(list(self.layers), None, z, None, pair_mask, self._ws_cache)[1]
+        if s is None:
+            raise RuntimeError("B200PairformerModule: this stack has a single track; s must be given")
         return _run_layers(list(self.layers), s, z, mask, pair_mask, self._ws_cache)
 
 
@@ -188,9 +286,10 @@ class B200PairformerNoSeqModule(nn.Module):
         super().__init__()
         self.token_z, self.num_blocks = token_z, num_blocks
         self.layers = nn.ModuleList([
-            B200PairformerLayer(384, token_z, 16, dropout, pairwise_head_width, pairwise_num_heads,
-                                post_layer_norm, False, precision, with_s=False) for _ in range(num_blocks)])
+            B200PairformerNoSeqLayer(token_z, dropout, pairwise_head_width, pairwise_num_heads, post_layer_norm, precision)
+            for _ in range(num_blocks)])
         self._ws_cache: dict = {}
+        self._register_load_state_dict_pre_hook(_accept_backend_keys)
 
     def reset_static_cache(self) -> None:
         self._ws_cache.clear()
