@@ -42,7 +42,8 @@ long long   b200pf_launch_count(void);
  * the environment variable B200PF_ATT_DEBUG is set (per-phase cycles of one softmax warp).  Synchronises. */
 int         b200pf_debug_counters(long long* host_out, int n);
 /* Reads (and clears) the device status word kernels set when a bounded wait runs out.
- * Synchronises `stream`.  0 = clean. */
+ * Synchronises `stream`.  0 = clean; bit 1 = an mbarrier wait inside a kernel ran out, bit 2 = an index
+ * check failed, bit 4 = a cross-rank barrier gave up waiting for a peer. */
 int         b200pf_device_status(void* stream);
 
 /* ------------------------------------------------------------------------------------------
@@ -313,8 +314,12 @@ int b200pf_transition_z_tc(float* z, const float* ln_gamma, const float* ln_beta
  *     tcgen05 stage entry points (ln_gamma / ln_beta [128], w_pg [512][128], and w_pout / w_gout / wsum / wb as
  *     for b200pf_trimul_epilogue_tc);
  *   - the call itself never calls cudaMalloc / cudaFree or any allocating routine;
- *   - the first call on a device looks up the device address of the array
- *     (cudaGetSymbolAddress); make that first call before starting any stream capture;
+ *   - the first call on a device looks up the device address of the array (cudaGetSymbolAddress), and
+ *     the three stages it runs raise their kernels' shared-memory limit and resolve the tensor-map
+ *     encoder on their first use per device; the driver may also load the kernels lazily at the first
+ *     launch.  So make one complete warm-up call per device before starting any stream capture and
+ *     before calling from a context that must not enter the driver's loader (cudaDeviceReset
+ *     invalidates the cached addresses: do not call again in that process after one);
  *   - all calls share the one array and it keeps the previous call's contents.  Nothing in it
  *     has to start at zero (each stage overwrites everything the next one reads), but two calls
  *     whose kernels overlap on the GPU (different streams) race on it: serialise them. */
@@ -334,6 +339,17 @@ int b200pf_peer_scatter(const void* send, const unsigned long long* recv_ptrs, l
 /* All-gather form of the same: `send` is ONE block, written to slot `rank` of every rank's receive buffer. */
 int b200pf_peer_broadcast(const void* send, const unsigned long long* recv_ptrs, long long block_bytes,
                           int rank, int world, void* stream);
+/* Cross-rank barrier of the peer-write exchanges (no counterpart in the reference: its cards never wait on
+ * each other; the nearest thing is the job lease that expires when a worker stops reporting,
+ * tt_bio/distributed.py:22, 214).  pad_ptrs is a HOST array of the world signal pads as mapped in this process
+ * (each at least world 32-bit words, zero before the first barrier).  One tiny launch per rank: it stores
+ * `generation` into slot `rank` of every rank's pad and waits until every slot of its own pad has reached
+ * `generation`.  Generations must grow by one per barrier on every rank.  Enqueued after an exchange on the
+ * same stream it means "my blocks have landed" to the peers and "all blocks for me have landed" to the kernels
+ * behind it.  The wait gives up after timeout_ns: the kernel then sets bit 4 of the device status word
+ * (b200pf_device_status) and returns; it never traps, and the context stays usable. */
+int b200pf_peer_barrier(const unsigned long long* pad_ptrs, unsigned int generation, int rank, int world,
+                        long long timeout_ns, void* stream);
 
 #ifdef __cplusplus
 }

@@ -57,3 +57,43 @@ def test_peer_scatter_rejects_bad_arguments(dev):
     bad = (C.c_ulonglong * 2)(recv.data_ptr(), 0)
     with pytest.raises(RuntimeError):
         call("b200pf_peer_scatter", ptr(send), bad, 48, 0, 2, stream())           # a null receive buffer
+
+
+def test_peer_barrier_passes_when_every_peer_has_signalled(dev):
+    """World of 3 on one device, seen from rank 1: the other ranks' signals are already in its pad (written here
+    with torch, generation 7 and the later 8 of a peer that is one barrier ahead), so the wait ends at once, and
+    rank 1's own signal lands in slot 1 of every pad."""
+    from tt_boltz_b200 import _lib
+    from tt_boltz_b200._lib import call, stream
+    world, rank, gen = 3, 1, 7
+    pads = [torch.zeros(16, dtype=torch.int32, device=dev) for _ in range(world)]
+    pads[rank][0], pads[rank][2] = gen, gen + 1
+    ptrs = (C.c_ulonglong * world)(*[p.data_ptr() for p in pads])
+    call("b200pf_peer_barrier", ptrs, gen, rank, world, 50_000_000, stream())
+    assert _lib.device_status() == 0
+    for t in range(world):
+        assert int(pads[t][rank]) == gen
+    assert int(pads[0][0]) == 0 and int(pads[2][2]) == 0
+
+
+def test_peer_barrier_gives_up_on_a_missing_rank_without_losing_the_context(dev):
+    """The second rank's launch is never issued, so its signal never comes: after the 1 ms limit the kernel
+    returns, the status word says why, and the device keeps working (no trap, no hang)."""
+    import time
+    from tt_boltz_b200 import _lib
+    from tt_boltz_b200._lib import call, stream
+    pads = [torch.zeros(16, dtype=torch.int32, device=dev) for _ in range(2)]
+    ptrs = (C.c_ulonglong * 2)(*[p.data_ptr() for p in pads])
+    assert _lib.device_status() == 0
+    t0 = time.perf_counter()
+    call("b200pf_peer_barrier", ptrs, 1, 0, 2, 1_000_000, stream())
+    status = _lib.device_status()               # synchronises
+    assert time.perf_counter() - t0 < 5.0
+    assert status == 4, status
+    assert "cross-rank barrier" in _lib.last_error()
+    assert int(pads[1][0]) == 1                 # its own signal was sent before it started to wait
+    assert _lib.device_status() == 0            # the word is cleared by the read
+    x = torch.arange(1024, device=dev, dtype=torch.float32)
+    assert float((x * 2).sum()) == 1023 * 1024  # the context is intact
+    with pytest.raises(RuntimeError):
+        call("b200pf_peer_barrier", ptrs, 2, 0, 2, 0, stream())          # a wait without a limit is refused

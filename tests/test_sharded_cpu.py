@@ -66,6 +66,69 @@ def test_sharded_block_matches_unsharded_oracle(world, n):
         assert rz < 2e-6 and rs < 2e-6, (rank, rz, rs)
 
 
+def _leaving_worker(rank, world, port, n, out_q):
+    """Two blocks; the last rank leaves after the first (between steps, nothing of its own in flight)."""
+    import datetime
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    torch.set_num_threads(1)
+    from tests.sharded_oracle import sharded_block_cpu
+    sd = synthetic.make_weights(1, seed=5, std=0.05)
+    s, z = synthetic.make_inputs(n, seed=4)
+    tm, pm = torch.ones(n), torch.ones(n, n)
+    r0, nr = shard_rows(n, rank, world)
+    z_loc = z[0, r0:r0 + nr].clone()
+    with torch.no_grad():
+        s1, z_loc = sharded_block_cpu(sd, "layers.0.", s[0], z_loc, tm, pm, rank, world)
+        if rank == world - 1:
+            out_q.put((rank, "left", 0.0))
+            out_q.close()
+            out_q.join_thread()                          # the report is out before the process dies
+            os._exit(0)                                  # gone without a goodbye, like a crashed worker
+        t0 = time.perf_counter()
+        try:
+            sharded_block_cpu(sd, "layers.0.", s1, z_loc, tm, pm, rank, world)
+            out_q.put((rank, "completed", time.perf_counter() - t0))
+        except Exception as e:  # noqa: BLE001
+            out_q.put((rank, "raised " + type(e).__name__, time.perf_counter() - t0))
+    out_q.close()
+    out_q.join_thread()
+    os._exit(0)                                          # the group cannot be torn down cleanly any more
+
+
+def test_a_rank_that_leaves_between_blocks_ends_the_others_with_an_error():
+    """Failure detection on the host side of the sharded trunk: the survivors' next exchange raises within the
+    process-group timeout instead of waiting forever (the reference's counterpart is the job lease that expires
+    when a worker stops reporting, tt_bio/distributed.py:22, 214)."""
+    world, n = 2, 16
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_leaving_worker, args=(r, world, _free_port_shared(), n, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    try:
+        res = dict((r, (what, dt)) for r, what, dt in (q.get(timeout=120) for _ in procs))
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
+    assert res[world - 1][0] == "left"
+    what, dt = res[0]
+    assert what.startswith("raised"), what
+    assert dt < 60.0, dt
+
+
+_SHARED_PORT = []
+
+
+def _free_port_shared():
+    if not _SHARED_PORT:
+        _SHARED_PORT.append(_free_port())
+    return _SHARED_PORT[0]
+
+
 def test_shard_rows_rejects_ragged():
     assert shard_rows(1024, 3, 8) == (384, 128)
     with pytest.raises(RuntimeError):

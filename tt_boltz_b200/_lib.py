@@ -63,6 +63,7 @@ SIGNATURES = {
     "b200pf_transition_z_tc": [_vp, _vp, _vp, _vp, _vp, _ll, _vp],
     "b200pf_peer_scatter": [_vp, C.POINTER(C.c_ulonglong), _ll, _i, _i, _vp],
     "b200pf_peer_broadcast": [_vp, C.POINTER(C.c_ulonglong), _ll, _i, _i, _vp],
+    "b200pf_peer_barrier": [C.POINTER(C.c_ulonglong), C.c_uint, _i, _i, _ll, _vp],
     "b200pf_tri_mul_noalloc": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
 }
 _RESTYPES = {"b200pf_last_error": C.c_char_p, "b200pf_launch_count": _ll, "b200pf_mx_scale_bytes": _ll}

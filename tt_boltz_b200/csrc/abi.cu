@@ -57,7 +57,7 @@ int b200pf_device_status(void* stream) {
     if (v != 0) {
         B200PF_CUDA(cudaMemsetAsync(p, 0, sizeof(v), st));
         B200PF_CUDA(cudaStreamSynchronize(st));
-        b200pf::set_error("device status word = 0x%x (1 = a bounded mbarrier wait ran out, 2 = index check)", v);
+        b200pf::set_error("device status word = 0x%x (1 = a bounded mbarrier wait ran out, 2 = index check, 4 = a cross-rank barrier gave up on a peer)", v);
     }
     return static_cast<int>(v);
 }

@@ -44,6 +44,19 @@ unsigned int* device_status_word();   // device address of the status word, cach
         }                                                                              \
     } while (0)
 
+// Raises a kernel's dynamic shared-memory limit the first time the call site runs on a device (the attribute
+// is per device and sticks), instead of on every launch.
+#define B200PF_SMEM_ATTR_ONCE(kernel, bytes)                                                         \
+    do {                                                                                             \
+        static bool done__[64] = {false};                                                            \
+        int d__ = 0;                                                                                 \
+        B200PF_CUDA(cudaGetDevice(&d__));                                                            \
+        if (d__ < 0 || d__ >= 64 || !done__[d__]) {                                                  \
+            B200PF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(bytes))); \
+            if (d__ >= 0 && d__ < 64) done__[d__] = true;                                            \
+        }                                                                                            \
+    } while (0)
+
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 // ---- device side -------------------------------------------------------------------------
@@ -76,5 +89,6 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 // Status codes kernels may OR into the device status word (never trap, never spin forever).
 constexpr unsigned int DEV_STATUS_MBAR_TIMEOUT = 1u;
 constexpr unsigned int DEV_STATUS_BAD_INDEX    = 2u;
+constexpr unsigned int DEV_STATUS_PEER_TIMEOUT = 4u;   // a cross-rank barrier gave up waiting for a peer
 
 }  // namespace b200pf

@@ -877,7 +877,7 @@ int b200pf_f32_sattention(const float* q, long long q_pitch, const float* g, lon
     unsigned blocks = (unsigned)(heads * ((n_q + 31) / 32));
     const bool staged = aligned16(kt) && aligned16(vt) && aligned16(bias) && kt_pitch % 4 == 0 && bias_hs % 4 == 0 && bias_qs % 4 == 0;
     if (staged) {
-        B200PF_CUDA(cudaFuncSetAttribute(f32_sattention_staged_kernel<24>, cudaFuncAttributeMaxDynamicSharedMemorySize, sat::smem_bytes<24>()));
+        B200PF_SMEM_ATTR_ONCE(f32_sattention_staged_kernel<24>, sat::smem_bytes<24>());
         f32_sattention_staged_kernel<24><<<blocks, 256, sat::smem_bytes<24>(), (cudaStream_t)stream>>>(p);
     } else {
         f32_sattention_kernel<24><<<blocks, 256, 0, (cudaStream_t)stream>>>(p);

@@ -4,8 +4,8 @@
 // (symmetric memory: plain peer mappings over NVLink, no multicast).  Block t of this rank's send
 // buffer goes to slot `rank` of rank t's receive buffer, so one launch on every rank is the whole
 // exchange: 16-byte loads from local memory, 16-byte stores to local or peer memory, all SMs.  The
-// caller orders it against the consumers with a cross-rank barrier afterwards; nothing here waits
-// on another GPU.
+// caller orders it against the consumers with the cross-rank barrier below (b200pf_peer_barrier);
+// the copy kernels themselves never wait on another GPU.
 #include "common.cuh"
 
 namespace b200pf {
@@ -59,9 +59,61 @@ peer_broadcast_kernel(const uint4* __restrict__ send, PeerPtrs peers, long long 
     }
 }
 
+// Cross-rank barrier on symmetric signal pads (one 32-bit slot per sender in every rank's pad), one warp.
+// Lane t tells rank t "rank `rank` has reached generation `gen`" with a system-scope release store into slot
+// `rank` of rank t's pad, then waits until slot t of its own pad shows that rank t has reached `gen` too.
+// Generations only grow, and a rank can be at most one barrier ahead of a peer that is still waiting, so the
+// test is "slot - gen >= 0" in wrap-around arithmetic.  Launched after an exchange kernel on the same stream,
+// it tells the receivers that this rank's blocks have landed (the exchange's stores are complete when it
+// starts) and holds this rank's consumers back until every sender's have.
+// The wait is bounded: after `limit_ns` without the peer's signal the lane ORs DEV_STATUS_PEER_TIMEOUT into the
+// device status word and returns.  Nothing traps; the context stays usable and the host reads the word.
+__global__ void __launch_bounds__(32)
+peer_barrier_kernel(PeerPtrs pads, unsigned int gen, int rank, int world, unsigned long long limit_ns, unsigned int* status) {
+    const int t = threadIdx.x;
+    if (t >= world) return;
+    __threadfence_system();
+    unsigned int* remote = reinterpret_cast<unsigned int*>(pads.recv[t]) + rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(gen) : "memory");
+    const unsigned int* mine = reinterpret_cast<const unsigned int*>(pads.recv[rank]) + t;
+    unsigned long long t0 = 0;
+    for (unsigned int spins = 0;; ++spins) {
+        unsigned int v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+        if ((int)(v - gen) >= 0) return;
+        if ((spins & 63u) == 63u) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (t0 == 0) t0 = now;
+            if (now - t0 > limit_ns) {
+                atomicOr(status, DEV_STATUS_PEER_TIMEOUT);
+                return;
+            }
+            __nanosleep(200);
+        }
+    }
+}
+
 }  // namespace b200pf
 
 using namespace b200pf;
+
+extern "C" int b200pf_peer_barrier(const unsigned long long* pad_ptrs, unsigned int generation, int rank, int world,
+                                   long long timeout_ns, void* stream) {
+    B200PF_REQUIRE(pad_ptrs && world > 0 && world <= PEER_MAX_RANKS && rank >= 0 && rank < world, B200PF_ERR_INVALID,
+                   "peer_barrier: bad argument (at most %d ranks)", PEER_MAX_RANKS);
+    B200PF_REQUIRE(timeout_ns > 0, B200PF_ERR_INVALID, "peer_barrier: the wait must have a positive limit");
+    PeerPtrs p{};
+    for (int t = 0; t < world; ++t) {
+        B200PF_REQUIRE(pad_ptrs[t] != 0 && pad_ptrs[t] % 4 == 0, B200PF_ERR_INVALID, "peer_barrier: bad signal pad of rank %d", t);
+        p.recv[t] = pad_ptrs[t];
+    }
+    unsigned int* status = device_status_word();
+    B200PF_REQUIRE(status, B200PF_ERR_CUDA, "peer_barrier: no device status word");
+    peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(p, generation, rank, world, (unsigned long long)timeout_ns, status);
+    B200PF_LAUNCH_CHECK();
+    return B200PF_OK;
+}
 
 static int peer_launch(bool broadcast, const void* send, const unsigned long long* recv_ptrs, long long block_bytes,
                        int rank, int world, void* stream) {

@@ -463,7 +463,7 @@ static int launch(const Args& a, cudaStream_t st) {
     B200PF_REQUIRE(status, B200PF_ERR_CUDA, "row512: no device status word");
     B200PF_REQUIRE(a.ln_gamma && a.ln_beta && aligned16(a.ln_gamma) && aligned16(a.ln_beta), B200PF_ERR_INVALID,
                    "row512: LayerNorm gain / offset must be given and 16-byte aligned");
-    B200PF_CUDA(cudaFuncSetAttribute(row512_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    B200PF_SMEM_ATTR_ONCE(row512_kernel<MODE>, SMEM_BYTES);
     int dev = 0, sms = 148;
     B200PF_CUDA(cudaGetDevice(&dev));
     B200PF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));

@@ -137,7 +137,7 @@ extern "C" int b200pf_transition_z(float* z, const b200pf_bf16* w12, const float
     B200PF_REQUIRE(aligned16(z) && aligned16(w12) && aligned16(w3), B200PF_ERR_INVALID,
                    "transition_z: pointers must be 16-byte aligned");
     TransitionArgs p{z, (const __nv_bfloat16*)w12, (const __nv_bfloat16*)w3, bias12, n_rows_flat};
-    B200PF_CUDA(cudaFuncSetAttribute(transition_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TRANSITION_SMEM));
+    B200PF_SMEM_ATTR_ONCE(transition_kernel, TRANSITION_SMEM);
     int dev = 0, sms = 148;
     B200PF_CUDA(cudaGetDevice(&dev));
     B200PF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));

@@ -369,7 +369,7 @@ extern "C" int b200pf_transition_z_tc(float* z, const float* ln_gamma, const flo
     }
     unsigned int* status = device_status_word();
     B200PF_REQUIRE(status, B200PF_ERR_CUDA, "transition_z_tc: no device status word");
-    B200PF_CUDA(cudaFuncSetAttribute(transition_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    B200PF_SMEM_ATTR_ONCE(transition_tc_kernel, SMEM_BYTES);
     int dev = 0, sms = 148;
     B200PF_CUDA(cudaGetDevice(&dev));
     B200PF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));

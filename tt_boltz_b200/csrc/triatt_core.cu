@@ -265,7 +265,7 @@ __global__ void __launch_bounds__(256) triatt_core_kernel(AttCoreArgs p) {
 template <int LINES>
 static int launch_core(const AttCoreArgs& p, cudaStream_t st) {
     using S = AttSmem<LINES>;
-    B200PF_CUDA(cudaFuncSetAttribute(triatt_core_kernel<LINES>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+    B200PF_SMEM_ATTR_ONCE(triatt_core_kernel<LINES>, S::TOTAL);
     int qtiles = (p.n + AQ - 1) / AQ;
     long long blocks = (long long)qtiles * 4 * ((p.lines + LINES - 1) / LINES);
     B200PF_REQUIRE(blocks < (1ll << 31), B200PF_ERR_UNSUPPORTED, "triatt_core: grid too large");

@@ -484,7 +484,7 @@ extern "C" int b200pf_triatt_core_tc4(const b200pf_bf16* q, const b200pf_bf16* k
     }
     unsigned int* status = device_status_word();
     B200PF_REQUIRE(status, B200PF_ERR_CUDA, "triatt_core_tc4: no device status word");
-    B200PF_CUDA(cudaFuncSetAttribute(triatt_core_tc4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    B200PF_SMEM_ATTR_ONCE(triatt_core_tc4_kernel, SMEM_BYTES);
     int dev = 0, sms = 148;
     B200PF_CUDA(cudaGetDevice(&dev));
     B200PF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));

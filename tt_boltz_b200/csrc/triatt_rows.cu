@@ -249,7 +249,7 @@ extern "C" int b200pf_triatt_producer(const float* z, const float* ln_gamma, con
         a.rows = rows; a.n = n; a.transposed = ending;
         return r512::launch_triatt(a, (cudaStream_t)stream);
     }
-    B200PF_CUDA(cudaFuncSetAttribute(triatt_producer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_PRODUCER_SMEM));
+    B200PF_SMEM_ATTR_ONCE(triatt_producer_kernel, ATT_PRODUCER_SMEM);
     int span = ending ? rows : n;
     long long units = (long long)(ending ? n : rows) * ((span + UNIT - 1) / UNIT);
     triatt_producer_kernel<<<grid_for_units(units, 1), WARPS * 32, ATT_PRODUCER_SMEM, (cudaStream_t)stream>>>(p);
@@ -263,7 +263,7 @@ extern "C" int b200pf_triatt_epilogue(float* z, const b200pf_bf16* o, const b200
     B200PF_REQUIRE(aligned16(z) && aligned16(o) && aligned16(g) && aligned16(w_o), B200PF_ERR_INVALID,
                    "triatt_epilogue: pointers must be 16-byte aligned");
     AttEpilogueArgs p{z, (const __nv_bfloat16*)o, (const __nv_bfloat16*)g, (const __nv_bfloat16*)w_o, n_rows_flat};
-    B200PF_CUDA(cudaFuncSetAttribute(triatt_epilogue_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_EPILOGUE_SMEM));
+    B200PF_SMEM_ATTR_ONCE(triatt_epilogue_kernel, ATT_EPILOGUE_SMEM);
     long long units = (n_rows_flat + UNIT - 1) / UNIT;
     triatt_epilogue_kernel<<<grid_for_units(units, 2), WARPS * 32, ATT_EPILOGUE_SMEM, (cudaStream_t)stream>>>(p);
     B200PF_LAUNCH_CHECK();

@@ -342,7 +342,7 @@ extern "C" int b200pf_trimul_epilogue_tc(float* z, const b200pf_bf16* x, long lo
     }
     unsigned int* status = device_status_word();
     B200PF_REQUIRE(status, B200PF_ERR_CUDA, "trimul_epilogue_tc: no device status word");
-    B200PF_CUDA(cudaFuncSetAttribute(trimul_epilogue_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    B200PF_SMEM_ATTR_ONCE(trimul_epilogue_tc_kernel, SMEM_BYTES);
     int dev = 0, sms = 148;
     B200PF_CUDA(cudaGetDevice(&dev));
     B200PF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));

@@ -238,7 +238,7 @@ int launch_contract(const b200pf_planes* a, const b200pf_planes* b, const void* 
         if ((rc = tmap_encode(&maps[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, const_cast<void*>(ops[i]->ptr), 4, dims, str, box,
                               CU_TENSOR_MAP_SWIZZLE_128B, i ? "mx B" : "mx A")) != B200PF_OK) return rc;
     }
-    B200PF_CUDA(cudaFuncSetAttribute(trimul_contract_mx_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    B200PF_SMEM_ATTR_ONCE(trimul_contract_mx_kernel, SMEM);
     int dev = 0, sms = 148;
     B200PF_CUDA(cudaGetDevice(&dev));
     B200PF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));

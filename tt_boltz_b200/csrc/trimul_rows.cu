@@ -268,7 +268,7 @@ extern "C" int b200pf_trimul_producer(const float* z, const uint8_t* mask, const
         a.pitch = pitch; a.rows = rows; a.n = n; a.transposed = incoming;
         return r512::launch_trimul(a, (cudaStream_t)stream);
     }
-    B200PF_CUDA(cudaFuncSetAttribute(trimul_producer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PRODUCER_SMEM));
+    B200PF_SMEM_ATTR_ONCE(trimul_producer_kernel, PRODUCER_SMEM);
     int span = incoming ? rows : n;
     long long units = (long long)(incoming ? n : rows) * ((span + UNIT - 1) / UNIT);
     trimul_producer_kernel<<<grid_for(units), WARPS * 32, PRODUCER_SMEM, (cudaStream_t)stream>>>(p);
@@ -310,7 +310,7 @@ extern "C" int b200pf_trimul_epilogue(float* z, const b200pf_bf16* x, long long 
                    "trimul_epilogue: pointers must be 16-byte aligned");
     EpilogueArgs p{z, (const __nv_bfloat16*)x, x_plane_stride, x_pitch, (const __nv_bfloat16*)w_pout,
                    (const __nv_bfloat16*)w_gout, bias_pout, bias_gout, rows, n};
-    B200PF_CUDA(cudaFuncSetAttribute(trimul_epilogue_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, EPILOGUE_SMEM));
+    B200PF_SMEM_ATTR_ONCE(trimul_epilogue_kernel, EPILOGUE_SMEM);
     long long units = (long long)rows * ((n + UNIT - 1) / UNIT);
     trimul_epilogue_kernel<<<grid_for(units), WARPS * 32, EPILOGUE_SMEM, (cudaStream_t)stream>>>(p);
     B200PF_LAUNCH_CHECK();

@@ -28,7 +28,7 @@ import torch.distributed as dist
 from torch import nn
 
 from . import ops, weights
-from ._lib import PlaneOut, Planes, call, ptr, stream
+from ._lib import PlaneOut, Planes, call, device_status, ptr, stream
 from .pairformer import B200PairformerLayer, _mask_u8
 
 C_Z = 128
@@ -47,7 +47,7 @@ def all_gather_cat(x: torch.Tensor, group=None, tag: Optional[str] = None) -> to
         if peer is not None:
             recv, hdl, ptrs = peer
             call("b200pf_peer_broadcast", ptr(x), ptrs, nbytes, dist.get_rank(group), world, stream())
-            hdl.barrier(channel=0, timeout_ms=_BARRIER_TIMEOUT_MS)
+            peer_barrier(x.device, group)
             return recv.view((world,) + tuple(x.shape))
     out = torch.empty((world,) + tuple(x.shape), dtype=x.dtype, device=x.device)
     if x.is_cuda:
@@ -65,7 +65,33 @@ os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 _SYMM: Dict[tuple, tuple] = {}
 _SYMM_TURN: Dict[tuple, int] = {}
 _PEER_COPY = {"enabled": os.environ.get("B200PF_PEER_COPY", "1") != "0"}       # "0": every exchange through NCCL
-_BARRIER_TIMEOUT_MS = 20000           # a rank that never arrives ends the wait with an error instead of a hang
+# A rank that never arrives ends the wait after this long: the barrier kernel sets bit 4 of the device status word
+# and returns (no trap, the context stays usable); ShardedPairformerModule.forward reads the word and raises.
+_BARRIER_TIMEOUT_MS = int(os.environ.get("B200PF_BARRIER_TIMEOUT_MS", "20000"))
+_BARRIERS: Dict[tuple, list] = {}
+
+
+def peer_barrier(device: torch.device, group=None) -> None:
+    """Enqueue the library's own cross-rank barrier (``b200pf_peer_barrier``) on the current stream.
+
+    The signal pads are one small symmetric allocation per (device, group), zeroed before the first use; the
+    generation counter lives on the host and grows by one per call, the same on every rank because every rank
+    enqueues the same sequence of exchanges."""
+    key = (device.index, id(group))
+    st = _BARRIERS.get(key)
+    if st is None:
+        import torch.distributed._symmetric_memory as symm
+        pg = group if group is not None else dist.group.WORLD
+        pad = symm.empty(64, dtype=torch.int32, device=device)
+        pad.zero_()
+        hdl = symm.rendezvous(pad, pg)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)                      # every pad is zero before any rank signals
+        ptrs = (C.c_ulonglong * hdl.world_size)(*[int(p) for p in hdl.buffer_ptrs])
+        st = _BARRIERS[key] = [pad, hdl, ptrs, 0]
+    st[3] = (st[3] + 1) & 0xFFFFFFFF
+    call("b200pf_peer_barrier", st[2], st[3], dist.get_rank(group), dist.get_world_size(group),
+         _BARRIER_TIMEOUT_MS * 1000000, stream())
 
 
 def _symm_buffer(tag: str, numel: int, dtype: torch.dtype, device: torch.device, group):
@@ -114,7 +140,7 @@ def all_to_all_blocks(send: torch.Tensor, group=None, tag: Optional[str] = None)
         if peer is not None:
             recv, hdl, ptrs = peer
             call("b200pf_peer_scatter", ptr(send), ptrs, send.numel() * send.element_size() // world, rank, world, stream())
-            hdl.barrier(channel=0, timeout_ms=_BARRIER_TIMEOUT_MS)
+            peer_barrier(send.device, group)
             return recv.view(send.shape)
     recv = torch.empty_like(send)
     dist.all_to_all_single(recv, send, group=group)
@@ -277,4 +303,8 @@ class ShardedPairformerModule(nn.Module):
         z_loc = z[0, r0:r0 + nr].to(torch.float32).clone(memory_format=torch.contiguous_format)
         sw, z_loc = self.forward_sharded(s[0], z_loc, mask, pair_mask)
         z_out = all_gather_cat(z_loc, self.group).view(1, n, n, z.shape[-1])
+        status = device_status()
+        if status:
+            raise RuntimeError(f"sharded Pairformer: device status 0x{status:x} on rank {rank} "
+                               "(4 = a peer did not reach an exchange barrier in time; 1 = a wait inside a kernel ran out)")
         return sw.unsqueeze(0).to(s.dtype), z_out.to(z.dtype)
