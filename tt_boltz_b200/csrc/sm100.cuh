@@ -37,6 +37,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
+// Non-blocking test of a phase.  try_wait may suspend the thread for a system-dependent time when the phase
+// is not complete, which is what a thread that waits for ONE barrier wants; a thread that polls SEVERAL
+// barriers and serves whichever is ready must use this form, or a barrier that is not ready delays the
+// others by that suspension.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ uint64_t global_timer_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -58,6 +71,22 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
             }
         }
     }
+}
+
+// Bounded wait run by a whole warp, with the same answer in every lane (a limit that runs out in one lane a
+// poll earlier than in another must not split the warp).
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag)) != 0;
+}
+// One lane of a converged warp.  tcgen05.mma / tcgen05.commit take their descriptors and barrier addresses
+// from uniform registers; issued under this predicate from code that the whole warp runs, the compiler keeps
+// them there.  Issued from a divergent `if (lane == 0)` branch instead, every such instruction cost the
+// thread about 100 clocks instead of about 40 (measured with clock64 around the issue blocks of the
+// attention core), which bounds any kernel whose MMAs are small.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred P1;\n\telect.sync _|P1, 0xffffffff;\n\tselp.u32 %0, 1, 0, P1;\n\t}" : "=r"(pred));
+    return pred != 0;
 }
 
 // ---- TMA -----------------------------------------------------------------------------------

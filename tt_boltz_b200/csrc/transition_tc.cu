@@ -206,60 +206,62 @@ transition_tc_kernel(const __grid_constant__ CUtensorMap map_w12, const __grid_c
             }
         }
     } else if (warp == MMA_WARP) {
-        if (lane == 0) {
-            // ---------------------------- MMA issuer ----------------------------
-            constexpr uint32_t idesc = make_idesc_bf16(TM, 128);
-            uint32_t it = 0, g = 0, h_cnt[2] = {0, 0};
-            bool ok = true;
-            // A tcgen05.mma of this size occupies the tensor pipe for ~64 cycles; building two descriptors from
-            // addresses costs the issuing thread more than that, so they are a precomputed base plus constants
-            // (the descriptor's address field counts 16-byte units).
-            const uint64_t d_a0 = make_desc_k_sw128(smem_u32(smem + OFF_A));
-            const uint64_t d_w0 = make_desc_k_sw128(smem_u32(smem + OFF_W));
-            const uint64_t d_w3_0 = make_desc_k_sw128(smem_u32(smem + OFF_W + W12_BYTES));
-            auto gemm1 = [&](uint32_t a_stage, uint32_t w_stage, uint32_t buf) {
+        // ---------------------------- MMA issuer ----------------------------
+        // The whole warp runs the loop and waits; one elected lane issues (see sm100::elect_one).
+        constexpr uint32_t idesc = make_idesc_bf16(TM, 128);
+        uint32_t it = 0, g = 0, h_cnt[2] = {0, 0};
+        bool ok = true;
+        // descriptors are a precomputed base plus constants (the address field counts 16-byte units)
+        const uint64_t d_a0 = make_desc_k_sw128(smem_u32(smem + OFF_A));
+        const uint64_t d_w0 = make_desc_k_sw128(smem_u32(smem + OFF_W));
+        const uint64_t d_w3_0 = make_desc_k_sw128(smem_u32(smem + OFF_W + W12_BYTES));
+        auto gemm1 = [&](uint32_t a_stage, uint32_t w_stage, uint32_t buf, bool release_a) {
+            if (elect_one()) {
                 const uint64_t da = d_a0 + a_stage * (uint64_t)(A_TILE_BYTES >> 4), dw = d_w0 + w_stage * (uint64_t)(WSTAGE >> 4);
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)
                     umma_bf16(tmem_base + COL_D1 + buf * 128, da + (ks >> 2) * (A_KB_BYTES >> 4) + (ks & 3) * 2,
                               dw + (ks >> 2) * ((128 * 128) >> 4) + (ks & 3) * 2, idesc, ks ? 1u : 0u);
                 umma_commit(&B->d1_full[buf]);
-            };
-            for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
-                const uint32_t stage = it & 1, ph = (it >> 1) & 1;
-                ok = mbar_wait(&B->a_full[stage], ph, abort_flag) && mbar_wait(&B->w_full[g % WSTAGES], (g / WSTAGES) & 1, abort_flag);
-                if (!ok) break;
-                tc_fence_after();
-                gemm1(stage, g % WSTAGES, 0);
-                for (int c = 0; c < CHUNKS && ok; ++c, ++g) {
-                    const uint32_t buf = c & 1, ws = g % WSTAGES;
-                    if (c + 1 < CHUNKS) {
-                        const uint32_t g1 = g + 1;
-                        ok = mbar_wait(&B->w_full[g1 % WSTAGES], (g1 / WSTAGES) & 1, abort_flag);
-                        if (!ok) break;
-                        tc_fence_after();
-                        gemm1(stage, g1 % WSTAGES, buf ^ 1);
-                    } else {
-                        umma_commit(&B->a_empty[stage]);         // all GEMM1 of this tile issued: the A tile is free once they finish
-                    }
-                    ok = mbar_wait(&B->h_full[buf], h_cnt[buf] & 1, abort_flag);
+                if (release_a) umma_commit(&B->a_empty[a_stage]);    // all GEMM1 of this tile issued: the A tile is free once they finish
+            }
+            __syncwarp();
+        };
+        for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
+            const uint32_t stage = it & 1, ph = (it >> 1) & 1;
+            ok = mbar_wait_warp(&B->a_full[stage], ph, abort_flag) && mbar_wait_warp(&B->w_full[g % WSTAGES], (g / WSTAGES) & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            gemm1(stage, g % WSTAGES, 0, CHUNKS == 1);
+            for (int c = 0; c < CHUNKS && ok; ++c, ++g) {
+                const uint32_t buf = c & 1, ws = g % WSTAGES;
+                if (c + 1 < CHUNKS) {
+                    const uint32_t g1 = g + 1;
+                    ok = mbar_wait_warp(&B->w_full[g1 % WSTAGES], (g1 / WSTAGES) & 1, abort_flag);
                     if (!ok) break;
-                    ++h_cnt[buf];
-                    if (c == 0) {                                // D2 of the previous tile has been read out
-                        ok = mbar_wait(&B->d2_empty, (it & 1) ^ 1, abort_flag);
-                        if (!ok) break;
-                    }
                     tc_fence_after();
+                    gemm1(stage, g1 % WSTAGES, buf ^ 1, c + 2 == CHUNKS);
+                }
+                ok = mbar_wait_warp(&B->h_full[buf], h_cnt[buf] & 1, abort_flag);
+                if (!ok) break;
+                ++h_cnt[buf];
+                if (c == 0) {                                // D2 of the previous tile has been read out
+                    ok = mbar_wait_warp(&B->d2_empty, (it & 1) ^ 1, abort_flag);
+                    if (!ok) break;
+                }
+                tc_fence_after();
+                if (elect_one()) {
                     const uint64_t dw3 = d_w3_0 + ws * (uint64_t)(WSTAGE >> 4);
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)               // 64 hidden = 4 k-steps; h: 8 TMEM columns per step
                         umma_bf16_ts(tmem_base + COL_D2, tmem_base + COL_H + buf * 32 + kk * 8, dw3 + kk * 2, idesc, (c | kk) ? 1u : 0u);
                     umma_commit(&B->w_empty[ws]);
+                    if (c + 1 == CHUNKS) umma_commit(&B->d2_full);
                 }
-                if (ok) umma_commit(&B->d2_full);
+                __syncwarp();
             }
-            if (!ok) atomicOr(status, DEV_STATUS_MBAR_TIMEOUT);
         }
+        if (!ok && lane == 0) atomicOr(status, DEV_STATUS_MBAR_TIMEOUT);
     } else {
         // ---------------------------- epilogue ----------------------------
         const int quarter = warp & 3, eh = (warp - EPI_WARP0) >> 2;

@@ -1,25 +1,23 @@
 // Fused triangle attention on tcgen05 / TMEM, four lines per CTA.
 //
-// The two-line kernel (triatt_core_tc.cu) is bound by the length of each softmax group's serial
-// chain (wait S -> tcgen05.ld -> max -> exp2 -> tcgen05.st -> signal), not by any pipe: with two
-// groups there are only two warps per scheduler to hide it.  This kernel keeps FOUR softmax
-// groups (16 warps, four per scheduler) in flight on four consecutive lines that share the bias
-// tile, so one group's exponentials run in the latency gaps of the others, and the bias tile is
-// fetched and multiplied once per PAIR of lines.
-//
-// One CTA works on (head, 128-query tile, four lines).  Roles (608 threads):
-//   warps 0-15  softmax group g = warp / 4 -> line l + g   (thread = query row = TMEM lane)
+// One CTA works on (head, 128-query tile, four consecutive lines that share the bias tile).  Roles (608 threads):
+//   warps 0-15  softmax group g = warp / 4 -> line l + g   (thread = query row = TMEM lane); four groups, i.e.
+//               four warps per scheduler, so that one group's exponentials run in the latency gaps of the others
 //   warp  16    TMA producer   (bias tile shared by the four lines; K and V^T tiles per line)
-//   warps 17,18 MMA issuers    (one per pair of groups; a polling state machine, so a group that
-//                               is not ready never holds up the other)
-// Per key tile of 64 and pair of groups: S_pair (128 x 128 fp32, TMEM) = bias_tile x [I | I]
-// (the bf16 bias lands in both lines' score columns exactly), then S_g += Q_g K_g^T per group.
-// The softmax thread takes the row maximum, p = exp2(s - m) (fp32 ex2.approx, packed to bf16)
-// goes back to TENSOR memory as the A operand of O_g += P_g V_g^T.  The running output stays
-// in tensor memory; it is rescaled only when a row maximum has grown by more than 2^8 since the
-// last rescale (probabilities stay <= 256).  Row sums are kept in fp32 registers.
-// TMEM columns: S 4 x 64 | P 4 x 32 | O 4 x 32 = 512.  S and P are single-buffered: the waits
-// this exposes in one group are covered by the other three.
+//   warps 17,18 MMA issuers    (one per pair of groups; a polling state machine, so a group that is not ready
+//                               never holds up the other.  The whole warp runs it and one elected lane issues.)
+// Per key tile of 64 and pair of groups: S_pair (128 x 128 fp32, TMEM) = bias_tile x [I | I]^T (the bf16 bias
+// lands in both lines' score columns exactly), then S_g += Q_g K_g^T per group.  The softmax thread reads its row
+// in two halves, applies the key mask and computes p = exp2(s - m) in ONE pass with the reference m of the tiles
+// before (scaling by a stale reference is exact in floating point; a check keeps it far from overflow and hands the
+// rare tile that fails it, like the first tile of a line, to a two-pass path).  p goes back to TENSOR memory as
+// packed bf16, the A operand of O_g += P_g V_g^T.  The running output stays in tensor memory and is rescaled only
+// when a row maximum has grown by more than 2^8; row sums are kept in fp32 registers.
+// TMEM columns: S 4 x 64 | P 4 x 32 | O 4 x 32 = 512.  S and P are single-buffered; S is released as soon as its
+// second half is in registers, so the next tile's products run under this tile's exponentials.
+// What bounds it (measured by leaving parts out): with no softmax arithmetic at all the MMA / barrier skeleton takes
+// 1.08 ms at N = 1024 (every tcgen05.mma costs its issuing thread ~40 clocks and every tcgen05.commit ~75, and the
+// bias product alone 0.22 ms); with the softmax arithmetic and only the Q K^T products 1.36 ms; together 1.45 ms.
 // Scores are in the log2 domain (host folds log2(e)/sqrt(32) into W_q and log2(e) into the bias).
 // Every wait is bounded; a wait that runs out raises the status word and the CTA unwinds.
 #include "sm100.cuh"
@@ -44,6 +42,7 @@ constexpr int TMA_WARP = 16, MMA_WARP0 = 17;
 constexpr uint32_t COL_S = 0, COL_P = 256, COL_O = 384;
 constexpr float MASKED_SCORE = -1.0e9f * 1.4426950408889634f;
 constexpr float RESCALE_STEP = 8.f;
+constexpr float ONE_PASS_HEADROOM = 64.f;        // a one-pass tile may exceed its reference by 2^64 at most
 
 struct Args {
     const uint8_t* mask;        // [lines][mask_pitch], 1 = attend
@@ -92,6 +91,69 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     float m;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(m) : "f"(a), "f"(b), "f"(c));
     return m;
+}
+// Two fp32 values in one 64-bit register for the packed add (one instruction, two results).
+__device__ __forceinline__ uint64_t f2_pack(float a, float b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& a, float& b) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+// Masked keys of a full tile get the score the reference's fp32 sum rounds to.  `even` / `odd` hold one bit per
+// key pair (bit l: key 2l / 2l+1 attends); they are uniform over the warp, so every test is a uniform branch and a
+// tile (or a group of 8 keys) without masked keys costs one compare.
+template <int HF>
+__device__ __forceinline__ void mask_half(uint32_t (&sr)[32], uint32_t even, uint32_t odd) {
+    const uint32_t e16 = (even >> (HF * 16)) & 0xffffu, o16 = (odd >> (HF * 16)) & 0xffffu, b16 = e16 & o16;
+    if (b16 == 0xffffu) return;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        if (((b16 >> (4 * q)) & 0xfu) == 0xfu) continue;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const int pe = 4 * q + t;
+            if (!((e16 >> pe) & 1u)) sr[2 * pe] = __float_as_uint(MASKED_SCORE);
+            if (!((o16 >> pe) & 1u)) sr[2 * pe + 1] = __float_as_uint(MASKED_SCORE);
+        }
+    }
+}
+// The same for any tile: keys at or beyond n (tile padding) are excluded altogether.
+__device__ __forceinline__ void mask_half_general(uint32_t (&sr)[32], uint32_t even, uint32_t odd, int hf, int key0, int n) {
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+        const int pe = hf * 16 + (e >> 1);
+        const uint32_t bit = (((e & 1) ? odd : even) >> pe) & 1u;
+        const int key = key0 + hf * 32 + e;
+        sr[e] = (key >= n) ? __float_as_uint(-INFINITY) : (bit ? sr[e] : __float_as_uint(MASKED_SCORE));
+    }
+}
+__device__ __forceinline__ void max_half(const uint32_t (&sr)[32], float (&m4)[4]) {
+#pragma unroll
+    for (int e = 0; e < 32; e += 8) {
+        m4[0] = max3(m4[0], __uint_as_float(sr[e]), __uint_as_float(sr[e + 1]));
+        m4[1] = max3(m4[1], __uint_as_float(sr[e + 2]), __uint_as_float(sr[e + 3]));
+        m4[2] = max3(m4[2], __uint_as_float(sr[e + 4]), __uint_as_float(sr[e + 5]));
+        m4[3] = max3(m4[3], __uint_as_float(sr[e + 6]), __uint_as_float(sr[e + 7]));
+    }
+}
+// p = exp2(s - m) for 32 scores -> 16 packed bf16 pairs; the subtraction and the row sums use the packed fp32 add.
+__device__ __forceinline__ void exp_half(const uint32_t (&sr)[32], uint32_t (&pw)[16], uint64_t negm2, uint64_t& l2a, uint64_t& l2b) {
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+        float x0, x1;
+        f2_unpack(f2_add(f2_pack(__uint_as_float(sr[2 * e]), __uint_as_float(sr[2 * e + 1])), negm2), x0, x1);
+        const float p0 = ex2_f32(x0), p1 = ex2_f32(x1);
+        if (e & 1) l2b = f2_add(l2b, f2_pack(p0, p1));
+        else l2a = f2_add(l2a, f2_pack(p0, p1));
+        pw[e] = pack_bf16x2(p0, p1);
+    }
 }
 // Gives up (false) after ~2 s without progress or when another thread of the CTA has aborted.
 struct IdleGuard {
@@ -195,40 +257,42 @@ triatt_core_tc4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
         }
     } else if (warp >= MMA_WARP0) {
-        if (lane == 0) {
-            // ------------------------------ MMA issuer of the group pair pr ------------------------------
-            // Polls what is ready instead of blocking on one barrier: the next S of the pair, and the
-            // P V product of either group.  Tiles are counted over all items of this CTA (index G).
-            const int pr = warp - MMA_WARP0, g0 = 2 * pr;
-            constexpr uint32_t idesc_bias = make_idesc_bf16(AQ, 2 * AK);
-            constexpr uint32_t idesc_s = make_idesc_bf16(AQ, AK);
-            constexpr uint32_t idesc_pv = make_idesc_bf16(AQ, HD);
-            // A tcgen05.mma of this size occupies the tensor pipe for ~50 cycles, so the issuing thread must
-            // not spend longer than that per instruction: every descriptor is a precomputed base plus a
-            // small constant (the address field counts 16-byte units; a K step of 16 bf16 is 32 bytes = 2).
-            constexpr uint64_t STAGE_STEP = STAGE_BYTES >> 4, Q_STEP = (NG * Q_BYTES) >> 4;
-            const uint64_t d_ident = make_desc_k_sw128(smem_u32(smem + OFF_IDENT));
-            const uint64_t d_bias0 = make_desc_k_sw128(smem_u32(smem));
-            const uint64_t d_k0[2] = {desc_sw64(smem_u32(smem + BIAS_BYTES + g0 * K_BYTES)),
-                                      desc_sw64(smem_u32(smem + BIAS_BYTES + (g0 + 1) * K_BYTES))};
-            const uint64_t d_vt0[2] = {make_desc_k_sw128(smem_u32(smem + BIAS_BYTES + NG * K_BYTES + g0 * VT_BYTES)),
-                                       make_desc_k_sw128(smem_u32(smem + BIAS_BYTES + NG * K_BYTES + (g0 + 1) * VT_BYTES))};
-            const uint64_t d_q0[2] = {desc_sw64(smem_u32(smem + OFF_Q + g0 * Q_BYTES)), desc_sw64(smem_u32(smem + OFF_Q + (g0 + 1) * Q_BYTES))};
-            const uint32_t t_s = tmem_base + COL_S + (uint32_t)(g0 * AK);
-            const uint32_t t_p = tmem_base + COL_P + (uint32_t)(g0 * (AK / 2));
-            const uint32_t t_o = tmem_base + COL_O + (uint32_t)(g0 * HD);
-            uint32_t Gs = 0, Gp[2] = {0u, 0u};
-            uint32_t js = 0, ks = 0, stage_s = 0, phase_s = 0;          // tile-in-item, item, stage and its phase of the next S
-            uint32_t jp[2] = {0u, 0u}, stage_p[2] = {0u, 0u};
-            IdleGuard guard;
-            bool ok = true;
-            while (ok && (Gp[0] < total_tiles || Gp[1] < total_tiles)) {
-                bool progress = false;
-                if (Gs < total_tiles) {
-                    const uint32_t qb = ks & 1;
-                    if (mbar_try_wait(&B->kv_full[stage_s], phase_s) && mbar_try_wait(&B->s_empty[g0], (Gs & 1) ^ 1) &&
-                        mbar_try_wait(&B->s_empty[g0 + 1], (Gs & 1) ^ 1) && (js != 0 || mbar_try_wait(&B->q_full[qb], (ks >> 1) & 1))) {
-                        tc_fence_after();
+        // ------------------------------ MMA issuer of the group pair pr ------------------------------
+        // Run by the WHOLE warp with warp-uniform state; one elected lane issues, so that descriptors and
+        // barrier addresses stay in uniform registers (issued from a divergent `lane == 0` branch, every
+        // tcgen05 instruction cost the thread ~100 clocks instead of ~40, measured with clock64).  Polls with
+        // the non-blocking test_wait what is ready instead of blocking on one barrier: the next S of the
+        // pair, and the P V product of either group.  Tiles are counted over all items of this CTA.
+        const int pr = __shfl_sync(0xffffffffu, warp - MMA_WARP0, 0), g0 = 2 * pr;
+        constexpr uint32_t idesc_bias = make_idesc_bf16(AQ, 2 * AK);
+        constexpr uint32_t idesc_s = make_idesc_bf16(AQ, AK);
+        constexpr uint32_t idesc_pv = make_idesc_bf16(AQ, HD);
+        // every descriptor is a precomputed base plus a small constant (the address field counts 16-byte
+        // units; a K step of 16 bf16 is 32 bytes = 2)
+        constexpr uint64_t STAGE_STEP = STAGE_BYTES >> 4, Q_STEP = (NG * Q_BYTES) >> 4;
+        const uint64_t d_ident = make_desc_k_sw128(smem_u32(smem + OFF_IDENT));
+        const uint64_t d_bias0 = make_desc_k_sw128(smem_u32(smem));
+        const uint64_t d_k0[2] = {desc_sw64(smem_u32(smem + BIAS_BYTES + g0 * K_BYTES)),
+                                  desc_sw64(smem_u32(smem + BIAS_BYTES + (g0 + 1) * K_BYTES))};
+        const uint64_t d_vt0[2] = {make_desc_k_sw128(smem_u32(smem + BIAS_BYTES + NG * K_BYTES + g0 * VT_BYTES)),
+                                   make_desc_k_sw128(smem_u32(smem + BIAS_BYTES + NG * K_BYTES + (g0 + 1) * VT_BYTES))};
+        const uint64_t d_q0[2] = {desc_sw64(smem_u32(smem + OFF_Q + g0 * Q_BYTES)), desc_sw64(smem_u32(smem + OFF_Q + (g0 + 1) * Q_BYTES))};
+        const uint32_t t_s = tmem_base + COL_S + (uint32_t)(g0 * AK);
+        const uint32_t t_p = tmem_base + COL_P + (uint32_t)(g0 * (AK / 2));
+        const uint32_t t_o = tmem_base + COL_O + (uint32_t)(g0 * HD);
+        uint32_t Gs = 0, Gp[2] = {0u, 0u};
+        uint32_t js = 0, ks = 0, stage_s = 0, phase_s = 0;          // tile-in-item, item, stage and its phase of the next S
+        uint32_t jp[2] = {0u, 0u}, stage_p[2] = {0u, 0u};
+        IdleGuard guard;
+        bool ok = true;
+        while (ok && (Gp[0] < total_tiles || Gp[1] < total_tiles)) {
+            bool progress = false;
+            if (Gs < total_tiles) {
+                const uint32_t qb = ks & 1;
+                if (mbar_test_wait(&B->kv_full[stage_s], phase_s) && mbar_test_wait(&B->s_empty[g0], (Gs & 1) ^ 1) &&
+                    mbar_test_wait(&B->s_empty[g0 + 1], (Gs & 1) ^ 1) && (js != 0 || mbar_test_wait(&B->q_full[qb], (ks >> 1) & 1))) {
+                    tc_fence_after();
+                    if (elect_one()) {
                         const uint64_t so = stage_s * STAGE_STEP;
 #pragma unroll
                         for (int kk = 0; kk < AK / 16; ++kk)
@@ -241,17 +305,20 @@ triatt_core_tc4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                             umma_commit(&B->s_full[g0 + i]);
                         }
                         if (js == (uint32_t)T - 1) umma_commit(&B->q_empty[qb]);
-                        ++Gs;
-                        if (++js == (uint32_t)T) { js = 0; ++ks; }
-                        if (++stage_s == ST) { stage_s = 0; phase_s ^= 1; }
-                        progress = true;
                     }
+                    __syncwarp();
+                    ++Gs;
+                    if (++js == (uint32_t)T) { js = 0; ++ks; }
+                    if (++stage_s == ST) { stage_s = 0; phase_s ^= 1; }
+                    progress = true;
                 }
+            }
 #pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    const uint32_t G = Gp[i];
-                    if (G < Gs && mbar_try_wait(&B->p_full[g0 + i], G & 1)) {
-                        tc_fence_after();
+            for (int i = 0; i < 2; ++i) {
+                const uint32_t G = Gp[i];
+                if (G < Gs && mbar_test_wait(&B->p_full[g0 + i], G & 1)) {
+                    tc_fence_after();
+                    if (elect_one()) {
                         const uint64_t dv = d_vt0[i] + stage_p[i] * STAGE_STEP;
                         const uint32_t d = t_o + (uint32_t)(i * HD), a = t_p + (uint32_t)(i * (AK / 2));
                         if (jp[i] == 0) umma_bf16_ts(d, a, dv, idesc_pv, 0u);
@@ -259,18 +326,19 @@ triatt_core_tc4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
                         for (int kk = 1; kk < AK / 16; ++kk) umma_bf16_ts(d, a + (uint32_t)(kk * 8), dv + 2 * kk, idesc_pv, 1u);
                         umma_commit(&B->pv_done[g0 + i]);
-                        Gp[i] = G + 1;
                         if (Gp[1 - i] > G) umma_commit(&B->kv_empty[stage_p[i]]);     // both groups of the pair are through this stage
-                        if (++jp[i] == (uint32_t)T) jp[i] = 0;
-                        if (++stage_p[i] == ST) stage_p[i] = 0;
-                        progress = true;
                     }
+                    __syncwarp();
+                    Gp[i] = G + 1;
+                    if (++jp[i] == (uint32_t)T) jp[i] = 0;
+                    if (++stage_p[i] == ST) stage_p[i] = 0;
+                    progress = true;
                 }
-                if (progress) guard.reset();
-                else ok = guard.keep_waiting(abort_flag);
             }
-            if (!ok) atomicOr(status, DEV_STATUS_MBAR_TIMEOUT);
+            if (progress) guard.reset();
+            else ok = __all_sync(0xffffffffu, guard.keep_waiting(abort_flag));
         }
+        if (!ok && lane == 0) atomicOr(status, DEV_STATUS_MBAR_TIMEOUT);
     } else {
         // ------------------------------ softmax groups ------------------------------
         const int g = warp >> 2, quarter = warp & 3;
@@ -281,97 +349,115 @@ triatt_core_tc4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const uint32_t o_addr = tmem_base + lane_off + COL_O + (uint32_t)(g * HD);
         uint32_t G = 0;
         bool ok = true;
-        
-        
-        auto mask_fetch = [&](const uint8_t* mrow, int j) -> uint4 {      // lanes 0-3: 16 mask bytes each, a tile ahead of use
-            uint4 v = make_uint4(0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u);
-            if (lane < 4) v = __ldg(reinterpret_cast<const uint4*>(mrow + j * AK) + lane);
-            return v;
+        // The key mask of a line is the same for every query row, i.e. uniform over the warp: lane l fetches the
+        // mask bytes of keys 2l and 2l+1 of the NEXT tile, and two ballots turn them into one bit per key.
+        auto mask_fetch = [&](const uint8_t* mrow, int j) -> uint32_t {
+            return (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(mrow + j * AK) + lane);
         };
         for (long long it = blockIdx.x; it < items && ok; it += gridDim.x) {
             int qt, h, line0;
             decode(it, qt, h, line0);
             const int line = line0 + g;
             const uint8_t* mrow = p.mask + (long long)clamp_line(line) * p.mask_pitch;
-            float m_used = 0.f, l_run = 0.f;
-            uint4 mnext = mask_fetch(mrow, 0);
+            // m_used: the reference the stored probabilities and the running output are scaled by; m_seen: the
+            // largest score met so far.  They differ by at most RESCALE_STEP after a rescale, and by whatever one
+            // tile of the one-pass path has added since (bounded by ONE_PASS_HEADROOM).
+            float m_used = 0.f, m_seen = 0.f, l_run = 0.f;
+            bool pending = false;                       // warp-uniform: some row is due for a rescale
+            uint32_t vnext = mask_fetch(mrow, 0);
             for (int j = 0; j < T && ok; ++j, ++G) {
-                const bool fast = __all_sync(0xffffffffu, (mnext.x & mnext.y & mnext.z & mnext.w) == 0x01010101u) && (j * AK + AK <= n);
-                if (j + 1 < T) mnext = mask_fetch(mrow, j + 1);
+                const uint32_t even = __ballot_sync(0xffffffffu, (vnext & 0x00ffu) != 0);    // bit l: key 2l attends
+                const uint32_t odd = __ballot_sync(0xffffffffu, (vnext & 0xff00u) != 0);     // bit l: key 2l+1 attends
+                const bool full_tile = (j * AK + AK <= n);
+                if (j + 1 < T) vnext = mask_fetch(mrow, j + 1);
                 ok = mbar_wait(&B->s_full[g], G & 1, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-                // pass 1: row maximum of the tile (the scores are read again in pass 2: holding all 64 in
-                // registers does not fit the 96 registers that 19 warps leave each thread)
-                float mx;
-                uint32_t mw[16];
-                if (fast) {
+                bool done = false;
+                if (j > 0 && full_tile && !pending) {
+                    // ---- one pass: p = exp2(s - m_used) with the reference of the tiles before, no maximum first.
+                    // Scaling by a stale reference is exact in floating point; it only has to stay far from
+                    // overflow, which the check before the scores are released guarantees (otherwise the tile is
+                    // redone by the two-pass path below, the scores being still in tensor memory).
+                    const uint64_t negm2 = f2_pack(-m_used, -m_used);
+                    uint64_t l2a = f2_pack(0.f, 0.f), l2b = l2a;
                     float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-                    for (int hf = 0; hf < 2; ++hf) {
-                        uint32_t sr[32];
-                        tmem_ld_32x32(s_addr + hf * 32, sr);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int e = 0; e < 32; e += 8) {
-                            m4[0] = max3(m4[0], __uint_as_float(sr[e]), __uint_as_float(sr[e + 1]));
-                            m4[1] = max3(m4[1], __uint_as_float(sr[e + 2]), __uint_as_float(sr[e + 3]));
-                            m4[2] = max3(m4[2], __uint_as_float(sr[e + 4]), __uint_as_float(sr[e + 5]));
-                            m4[3] = max3(m4[3], __uint_as_float(sr[e + 6]), __uint_as_float(sr[e + 7]));
-                        }
-                    }
-                    mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const uint4 v = __ldg(reinterpret_cast<const uint4*>(mrow + j * AK) + c);
-                        mw[c * 4] = v.x; mw[c * 4 + 1] = v.y; mw[c * 4 + 2] = v.z; mw[c * 4 + 3] = v.w;
-                    }
-                    mx = -INFINITY;
-#pragma unroll
-                    for (int hf = 0; hf < 2; ++hf) {
-                        uint32_t sr[32];
-                        tmem_ld_32x32(s_addr + hf * 32, sr);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int e = 0; e < 32; ++e) {
-                            const int key = hf * 32 + e;
-                            const uint32_t mbyte = (mw[key >> 2] >> ((key & 3) * 8)) & 0xffu;
-                            const float v = (j * AK + key >= n) ? -INFINITY : (mbyte ? __uint_as_float(sr[e]) : MASKED_SCORE);
-                            mx = fmaxf(mx, v);
-                        }
+                    uint32_t sr[32], pw[16];
+                    tmem_ld_32x32(s_addr, sr);
+                    tmem_ld_wait();
+                    mask_half<0>(sr, even, odd);
+                    max_half(sr, m4);
+                    exp_half(sr, pw, negm2, l2a, l2b);
+                    // the previous P V product of this group must have read its P operand before it is overwritten
+                    ok = mbar_wait(&B->pv_done[g], (G & 1) ^ 1, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    tmem_st_32x16(p_addr, pw);
+                    tmem_ld_32x32(s_addr + 32, sr);
+                    tmem_ld_wait();
+                    mask_half<1>(sr, even, odd);
+                    max_half(sr, m4);
+                    const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+                    if (!__any_sync(0xffffffffu, mx > m_used + ONE_PASS_HEADROOM)) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&B->s_empty[g]);          // S may be overwritten by the next tile
+                        exp_half(sr, pw, negm2, l2a, l2b);
+                        tmem_st_32x16(p_addr + 16, pw);
+                        float a0, a1, b0, b1;
+                        f2_unpack(l2a, a0, a1);
+                        f2_unpack(l2b, b0, b1);
+                        l_run += (a0 + a1) + (b0 + b1);
+                        m_seen = fmaxf(m_seen, mx);
+                        pending = __any_sync(0xffffffffu, m_seen > m_used + RESCALE_STEP);
+                        done = true;
                     }
                 }
-                // The previous P V product of this group has to be complete before its P operand is overwritten
-                // (checked after the exponentials, when it normally is) and before the running output is rescaled.
-                bool pv_waited = false;
-                if (j == 0) {
-                    m_used = mx;
-                } else {
-                    const bool grow = mx > m_used + RESCALE_STEP;
-                    if (__any_sync(0xffffffffu, grow)) {
-                        ok = mbar_wait(&B->pv_done[g], (G & 1) ^ 1, abort_flag);
-                        if (!ok) break;
-                        tc_fence_after();
-                        pv_waited = true;
-                        const float f = grow ? ex2_f32(m_used - mx) : 1.f;
-                        if (grow) m_used = mx;
-                        uint32_t ov[32];
-                        tmem_ld_32x32(o_addr, ov);
-                        tmem_ld_wait();
+                if (!done) {
+                    // ---- two passes (first tile of a line, ragged last tile, a rescale that is due, or a tile the
+                    // one-pass path gave back): row maximum first, then the exponentials
+                    const bool plain = full_tile && (even & odd) == 0xffffffffu;
+                    float mx;
+                    {
+                        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                        for (int e = 0; e < HD; ++e) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * f);
-                        tmem_st_32x32(o_addr, ov);
-                        l_run *= f;
+                        for (int hf = 0; hf < 2; ++hf) {
+                            uint32_t sr[32];
+                            tmem_ld_32x32(s_addr + hf * 32, sr);
+                            tmem_ld_wait();
+                            if (!plain) mask_half_general(sr, even, odd, hf, j * AK, n);
+                            max_half(sr, m4);
+                        }
+                        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
                     }
-                }
-                // pass 2: p = exp2(s - m) -> packed bf16 pairs, both halves, then into tensor memory
-                {
-                    float l0 = 0.f, l1 = 0.f;
-                    uint32_t pw[2][16];
+                    // The previous P V product of this group has to be complete before its P operand is overwritten
+                    // and before the running output is rescaled.
+                    ok = mbar_wait(&B->pv_done[g], (G & 1) ^ 1, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (j == 0) {
+                        m_used = m_seen = mx;
+                    } else {
+                        m_seen = fmaxf(m_seen, mx);
+                        const bool grow = m_seen > m_used + RESCALE_STEP;
+                        if (__any_sync(0xffffffffu, grow)) {
+                            const float f = grow ? ex2_f32(m_used - m_seen) : 1.f;
+                            if (grow) m_used = m_seen;
+                            uint32_t ov[32];
+                            tmem_ld_32x32(o_addr, ov);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int e = 0; e < HD; ++e) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * f);
+                            tmem_st_32x32(o_addr, ov);
+                            l_run *= f;
+                        }
+                    }
+                    pending = false;
+                    const uint64_t negm2 = f2_pack(-m_used, -m_used);
+                    uint64_t l2a = f2_pack(0.f, 0.f), l2b = l2a;
 #pragma unroll
                     for (int hf = 0; hf < 2; ++hf) {
-                        uint32_t sr[32];
+                        uint32_t sr[32], pw[16];
                         tmem_ld_32x32(s_addr + hf * 32, sr);
                         tmem_ld_wait();
                         if (hf == 1) {               // every score is in registers or consumed: S may be overwritten
@@ -379,31 +465,14 @@ triatt_core_tc4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                             __syncwarp();
                             if (lane == 0) mbar_arrive(&B->s_empty[g]);
                         }
-                        if (!fast) {
-#pragma unroll
-                            for (int e = 0; e < 32; ++e) {
-                                const int key = hf * 32 + e;
-                                const uint32_t mbyte = (mw[key >> 2] >> ((key & 3) * 8)) & 0xffu;
-                                sr[e] = __float_as_uint((j * AK + key >= n) ? -INFINITY : (mbyte ? __uint_as_float(sr[e]) : MASKED_SCORE));
-                            }
-                        }
-#pragma unroll
-                        for (int e = 0; e < 16; ++e) {
-                            const float p0 = ex2_f32(__uint_as_float(sr[2 * e]) - m_used);
-                            const float p1 = ex2_f32(__uint_as_float(sr[2 * e + 1]) - m_used);
-                            l0 += p0;
-                            l1 += p1;
-                            pw[hf][e] = pack_bf16x2(p0, p1);
-                        }
+                        if (!plain) mask_half_general(sr, even, odd, hf, j * AK, n);
+                        exp_half(sr, pw, negm2, l2a, l2b);
+                        tmem_st_32x16(p_addr + hf * 16, pw);
                     }
-                    l_run += l0 + l1;
-                    if (!pv_waited) {
-                        ok = mbar_wait(&B->pv_done[g], (G & 1) ^ 1, abort_flag);
-                        if (!ok) break;
-                        tc_fence_after();
-                    }
-                    tmem_st_32x16(p_addr, pw[0]);
-                    tmem_st_32x16(p_addr + 16, pw[1]);
+                    float a0, a1, b0, b1;
+                    f2_unpack(l2a, a0, a1);
+                    f2_unpack(l2b, b0, b1);
+                    l_run += (a0 + a1) + (b0 + b1);
                 }
                 tmem_st_wait();
                 tc_fence_before();
