@@ -213,25 +213,26 @@ row512_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ 
         }
         if (!ok && lane == 0) atomicOr(status, DEV_STATUS_MBAR_TIMEOUT);
     } else if (warp == MMA_WARP) {
-        if (lane == 0) {
-            // ---------------------------- MMA issuer ----------------------------
-            constexpr uint32_t idesc128 = make_idesc_bf16(TM, 128), idesc256 = make_idesc_bf16(TM, 256);
-            const uint64_t d_w = make_desc_k_sw128(smem_u32(smem));            // weight row r starts 8 r units further
-            const uint64_t d_x0 = make_desc_k_sw128(smem_u32(smem + OFF_A));
-            constexpr uint32_t W_KB16 = W_KB >> 4, A_KB16 = A_KB_BYTES >> 4;
-            uint32_t it = 0, acc_cnt[2] = {0, 0};
-            bool ok = true;
-            for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
-                const uint32_t stage = it & 1, ph = (it >> 1) & 1;
-                ok = mbar_wait(&B->a_full[stage], ph, abort_flag);
+        // ---------------------------- MMA issuer ----------------------------
+        // The whole warp runs the loop and waits; one elected lane issues (see sm100::elect_one).
+        constexpr uint32_t idesc128 = make_idesc_bf16(TM, 128), idesc256 = make_idesc_bf16(TM, 256);
+        const uint64_t d_w = make_desc_k_sw128(smem_u32(smem));            // weight row r starts 8 r units further
+        const uint64_t d_x0 = make_desc_k_sw128(smem_u32(smem + OFF_A));
+        constexpr uint32_t W_KB16 = W_KB >> 4, A_KB16 = A_KB_BYTES >> 4;
+        uint32_t it = 0, acc_cnt[2] = {0, 0};
+        bool ok = true;
+        for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
+            const uint32_t stage = it & 1, ph = (it >> 1) & 1;
+            ok = mbar_wait_warp(&B->a_full[stage], ph, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const uint64_t d_x = d_x0 + stage * (uint64_t)(A_TILE_BYTES >> 4);
+            for (int half = 0; half < 2 && ok; ++half) {
+                ok = mbar_wait_warp(&B->acc_empty[half], (acc_cnt[half] & 1) ^ 1, abort_flag);
                 if (!ok) break;
+                ++acc_cnt[half];
                 tc_fence_after();
-                const uint64_t d_x = d_x0 + stage * (uint64_t)(A_TILE_BYTES >> 4);
-                for (int half = 0; half < 2 && ok; ++half) {
-                    ok = mbar_wait(&B->acc_empty[half], (acc_cnt[half] & 1) ^ 1, abort_flag);
-                    if (!ok) break;
-                    ++acc_cnt[half];
-                    tc_fence_after();
+                if (elect_one()) {
                     const uint32_t d = tmem_base + half * 256;
                     if (MODE != MODE_TRIATT) {
                         // channels on the lanes: A = 128 weight rows, B = the x tile (positions)
@@ -244,11 +245,12 @@ row512_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ 
                         gemm_k128(d + 128, d_w + 384 * 8, W_KB16, d_x, A_KB16, idesc128);          // v^T
                     }
                     umma_commit(&B->acc_full[half]);
+                    if (half == 1) umma_commit(&B->a_empty[stage]);
                 }
-                if (ok) umma_commit(&B->a_empty[stage]);
+                __syncwarp();
             }
-            if (!ok) atomicOr(status, DEV_STATUS_MBAR_TIMEOUT);
         }
+        if (!ok && lane == 0) atomicOr(status, DEV_STATUS_MBAR_TIMEOUT);
     } else {
         // ---------------------------- epilogue ----------------------------
         // Each round moves one [128 x 128] bf16 block out: TMEM -> registers -> swizzled staging tile

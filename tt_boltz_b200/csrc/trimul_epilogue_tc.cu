@@ -205,19 +205,20 @@ trimul_epilogue_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
         }
         if (!ok && lane == 0) atomicOr(status, DEV_STATUS_MBAR_TIMEOUT);
     } else if (warp == MMA_WARP) {
-        if (lane == 0) {
-            // ---------------------------- MMA issuer ----------------------------
-            constexpr uint32_t idesc_g = make_idesc_bf16(TM, 128);
-            constexpr uint32_t idesc_p = make_idesc_bf16(TM, 128) | (1u << 15);      // A operand MN-major
-            const uint32_t wp_addr = smem_u32(smem + OFF_WP), wg_addr = smem_u32(smem + OFF_WG), xt_addr = smem_u32(smem + OFF_XT);
-            uint32_t it = 0;
-            bool ok = true;
-            for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
-                const uint32_t stage = it & 1, ph = (it >> 1) & 1;
-                ok = mbar_wait(&B->in_full[stage], ph, abort_flag) && mbar_wait(&B->x_full, it & 1, abort_flag) &&
-                     mbar_wait(&B->acc_empty[stage], ph ^ 1, abort_flag);
-                if (!ok) break;
-                tc_fence_after();
+        // ---------------------------- MMA issuer ----------------------------
+        // The whole warp runs the loop and waits; one elected lane issues (see sm100::elect_one).
+        constexpr uint32_t idesc_g = make_idesc_bf16(TM, 128);
+        constexpr uint32_t idesc_p = make_idesc_bf16(TM, 128) | (1u << 15);      // A operand MN-major
+        const uint32_t wp_addr = smem_u32(smem + OFF_WP), wg_addr = smem_u32(smem + OFF_WG), xt_addr = smem_u32(smem + OFF_XT);
+        uint32_t it = 0;
+        bool ok = true;
+        for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
+            const uint32_t stage = it & 1, ph = (it >> 1) & 1;
+            ok = mbar_wait_warp(&B->in_full[stage], ph, abort_flag) && mbar_wait_warp(&B->x_full, it & 1, abort_flag) &&
+                 mbar_wait_warp(&B->acc_empty[stage], ph ^ 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            if (elect_one()) {
                 const uint32_t az_addr = smem_u32(smem + OFF_AZ + stage * A_TILE_BYTES);
                 const uint32_t d = tmem_base + stage * 256;
 #pragma unroll
@@ -232,8 +233,9 @@ trimul_epilogue_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
                 umma_commit(&B->x_empty);
                 umma_commit(&B->acc_full[stage]);
             }
-            if (!ok) atomicOr(status, DEV_STATUS_MBAR_TIMEOUT);
+            __syncwarp();
         }
+        if (!ok && lane == 0) atomicOr(status, DEV_STATUS_MBAR_TIMEOUT);
     } else {
         // ---------------------------- epilogue ----------------------------
         const int quarter = warp & 3, chalf = (warp - EPI_WARP0) >> 2;

@@ -100,8 +100,9 @@ trimul_contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             uint64_t t0 = global_timer_ns();
             while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
         }
-    } else if (warp == 1 && lane == 0) {
+    } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
+        // The whole warp runs the loop and waits; one elected lane issues (see sm100::elect_one).
         constexpr uint32_t idesc = make_idesc_bf16(BM, BN);
         const uint64_t d_a0 = make_desc_k_sw128(smem_u32(smem)), d_b0 = make_desc_k_sw128(smem_u32(smem + A_BYTES));
         uint32_t stage = 0, phase = 0;
@@ -109,23 +110,26 @@ trimul_contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         long long it = 0;
         for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
             uint32_t ab = (uint32_t)(it & 1), aphase = (uint32_t)((it >> 1) & 1);
-            ok = mbar_wait(&acc_empty[ab], aphase ^ 1, abort_flag);
+            ok = mbar_wait_warp(&acc_empty[ab], aphase ^ 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
             uint32_t tmem_d = tmem_base + ab * BN;
             for (int kb = 0; kb < kb_total; ++kb) {
-                ok = mbar_wait(&full[stage], phase, abort_flag);
+                ok = mbar_wait_warp(&full[stage], phase, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-                const uint64_t so = stage * (uint64_t)(STAGE_BYTES >> 4);      // descriptors: precomputed base + 16-byte units
+                if (elect_one()) {
+                    const uint64_t so = stage * (uint64_t)(STAGE_BYTES >> 4);      // descriptors: precomputed base + 16-byte units
 #pragma unroll
-                for (int kk = 0; kk < BK / 16; ++kk) umma_bf16(tmem_d, d_a0 + so + kk * 2, d_b0 + so + kk * 2, idesc, (kb | kk) ? 1u : 0u);
-                umma_commit(&empty[stage]);
+                    for (int kk = 0; kk < BK / 16; ++kk) umma_bf16(tmem_d, d_a0 + so + kk * 2, d_b0 + so + kk * 2, idesc, (kb | kk) ? 1u : 0u);
+                    umma_commit(&empty[stage]);
+                    if (kb + 1 == kb_total) umma_commit(&acc_full[ab]);
+                }
+                __syncwarp();
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
-            if (ok) umma_commit(&acc_full[ab]);
         }
-        if (!ok) atomicOr(status, DEV_STATUS_MBAR_TIMEOUT);
+        if (!ok && lane == 0) atomicOr(status, DEV_STATUS_MBAR_TIMEOUT);
     } else if (warp >= 2) {
         // ---------------- epilogue ----------------
         const int quarter = warp & 3;                 // TMEM lanes this warp may touch: 32*quarter ..

@@ -100,36 +100,40 @@ trimul_contract_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             uint64_t t0 = global_timer_ns();
             while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
         }
-    } else if (warp == 1 && lane == 0) {
+    } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
+        // The whole warp runs the loop and waits; one elected lane issues (see sm100::elect_one).
         uint32_t stage = 0, phase = 0;
         bool ok = true;
         long long it = 0;
         for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
-            ok = mbar_wait(acc_empty, (uint32_t)(it & 1) ^ 1, abort_flag);
+            ok = mbar_wait_warp(acc_empty, (uint32_t)(it & 1) ^ 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
             for (int kb = 0; kb < kb_total; ++kb) {
-                ok = mbar_wait(&full[stage], phase, abort_flag);
+                ok = mbar_wait_warp(&full[stage], phase, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t sa = smem_u32(smem + stage * DATA_BYTES), sb = sa + A_BYTES;
-                const uint32_t sf = smem_u32(smem + OFF_SF + stage * SF_BYTES);
-                tmem_cp_scale_block(tmem_base + COL_SFA, make_desc_scale_block(sf));
-                tmem_cp_scale_block(tmem_base + COL_SFB, make_desc_scale_block(sf + mx::SF_BLOCK_BYTES));
-                tmem_cp_scale_block(tmem_base + COL_SFB + 4, make_desc_scale_block(sf + 2 * mx::SF_BLOCK_BYTES));
+                if (elect_one()) {
+                    const uint32_t sa = smem_u32(smem + stage * DATA_BYTES), sb = sa + A_BYTES;
+                    const uint32_t sf = smem_u32(smem + OFF_SF + stage * SF_BYTES);
+                    tmem_cp_scale_block(tmem_base + COL_SFA, make_desc_scale_block(sf));
+                    tmem_cp_scale_block(tmem_base + COL_SFB, make_desc_scale_block(sf + mx::SF_BLOCK_BYTES));
+                    tmem_cp_scale_block(tmem_base + COL_SFB + 4, make_desc_scale_block(sf + 2 * mx::SF_BLOCK_BYTES));
 #pragma unroll
-                for (uint32_t kk = 0; kk < 4; ++kk) {
-                    umma_mxf8(tmem_base, make_desc_k_sw128(sa + kk * 32), make_desc_k_sw128(sb + kk * 32),
-                              make_idesc_mxf8(BM, BN, kk, kk), (tmem_base + COL_SFA) | (kk << 30),
-                              (tmem_base + COL_SFB) | (kk << 30), (kb | (int)kk) ? 1u : 0u);
+                    for (uint32_t kk = 0; kk < 4; ++kk) {
+                        umma_mxf8(tmem_base, make_desc_k_sw128(sa + kk * 32), make_desc_k_sw128(sb + kk * 32),
+                                  make_idesc_mxf8(BM, BN, kk, kk), (tmem_base + COL_SFA) | (kk << 30),
+                                  (tmem_base + COL_SFB) | (kk << 30), (kb | (int)kk) ? 1u : 0u);
+                    }
+                    umma_commit(&empty[stage]);
+                    if (kb + 1 == kb_total) umma_commit(acc_full);
                 }
-                umma_commit(&empty[stage]);
+                __syncwarp();
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
-            if (ok) umma_commit(acc_full);
         }
-        if (!ok) atomicOr(status, DEV_STATUS_MBAR_TIMEOUT);
+        if (!ok && lane == 0) atomicOr(status, DEV_STATUS_MBAR_TIMEOUT);
     } else if (warp >= 2) {
         // ---------------- epilogue ----------------
         const int quarter = warp & 3;                 // TMEM lanes this warp may touch: 32*quarter ..
