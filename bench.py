@@ -55,18 +55,31 @@ def kernel_work(n: int):
         "b200pf_transition_z": (6 * n * n * C * 4 * C, 8 * e),
         "b200pf_transition_z_tc": (6 * n * n * C * 4 * C, 8 * e),
         "b200pf_ln_proj_heads": (2 * n * n * C * 16, 4 * e + 4 * 16 * n * n),
+        "b200pf_f32_sattention": (4 * n * n * 384, 4 * 16 * n * n),
     }
 
 
-# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per launch divided by the algorithmic bytes, from
-# `ncu --set full` captures at N = 768 (profiles/tcgen05_kernels_n768_ncu_full.md, triatt_core_tc4_n768_ncu_full.md,
-# trimul_mxfp8_n768_ncu_full.md); traffic grows with N^2 * 128, so the full-size figure is this ratio times the
-# algorithmic bytes at the benchmark's N.
-NCU_TRAFFIC_RATIO = {
-    "b200pf_trimul_contract": 0.92, "b200pf_trimul_producer": 0.92, "b200pf_trimul_epilogue_tc": 0.92,
-    "b200pf_triatt_producer": 0.94, "b200pf_triatt_core_tc": 0.98, "b200pf_triatt_core_tc4": 0.98,
-    "b200pf_triatt_epilogue": 0.95, "b200pf_trimul_producer_mx": 0.93,
-}
+TRAFFIC_FILE = os.path.join("profiles", "trunk_kernels_n768_ncu.md")
+
+
+def ncu_traffic_ratios():
+    """{entry point: DRAM traffic / algorithmic bytes} read from the newest committed ncu capture summary.
+
+    The capture is made at N = 768 (operands larger than L2, a few GB on the device: a full-size capture is not
+    taken under ncu); traffic of every kernel here grows with N^2 * 128 like its algorithmic bytes, so the ratio is
+    what carries over.  The table rows look like ``| b200pf_entry | kernel | ... | 0.97 |`` (last cell = ratio)."""
+    out = {}
+    path = os.path.join(ROOT, TRAFFIC_FILE)
+    if not os.path.exists(path):
+        return out
+    for ln in open(path):
+        cells = [c.strip() for c in ln.strip().strip("|").split("|")]
+        if len(cells) >= 3 and cells[0].startswith("b200pf_"):
+            try:
+                out[cells[0]] = float(cells[-1])
+            except ValueError:
+                pass
+    return out
 
 
 def measured_peaks():
@@ -121,47 +134,93 @@ class ClockSampler:
 
 
 def cpu_block_seconds(n: int, threads: int, budget_s: float, max_steps: int, warmup: int):
-    """Seconds per block of the fp32 oracle (port of tt_bio/reference.py) on the host cores:
-    each step is one full block at n tokens, i.e. 1/64 of the trunk; stops early once budget_s is spent."""
-    from oracle import pairformer_oracle as orc
+    """Seconds per block of the reference's fp32 CPU Pairformer on the host cores: each step is one full block at
+    n tokens (1/64 of the trunk); stops early once budget_s is spent.  Uses the reference's own modules
+    (tt_bio/reference.py, installed unmodified under oracle/_ref by oracle/build_ref.py) when they are present,
+    else the oracle port of the same arithmetic.  Returns (seconds, timed steps, kind)."""
     from tt_boltz_b200 import synthetic
     torch.set_num_threads(threads)
     torch.set_float32_matmul_precision("highest")
     sd = synthetic.make_weights(1, seed=1)
     s, z = synthetic.make_inputs(n, seed=0)
     m, pm = synthetic.tail_padding_mask(n, 0)
+    from oracle import ref_modules
+    if ref_modules.available():
+        kind = "reference"
+        mod = ref_modules.load()[0](384, 128, 1, v2=True).eval()
+        mod.load_state_dict(sd, strict=True)
+        step = lambda: mod(s, z, m, pm, use_kernels=False)
+    else:
+        kind = "port"
+        from oracle import pairformer_oracle as orc
+        step = lambda: orc.pairformer_layer(s[0], z[0], m[0], pm[0], sd, "layers.0.")
     times, t_start = [], time.perf_counter()
     with torch.no_grad():
         for it in range(warmup + max_steps):
             t0 = time.perf_counter()
-            orc.pairformer_layer(s[0], z[0], m[0], pm[0], sd, "layers.0.")
+            step()
             dt = time.perf_counter() - t0
             if it >= warmup or (it == warmup - 1 and time.perf_counter() - t_start > budget_s):
                 times.append(dt)
             if times and time.perf_counter() - t_start > budget_s:
                 break
-    return sum(times) / len(times), len(times)
+    return sum(times) / len(times), len(times), kind
+
+
+def cpu_sample_text(kind: str, done: int, n: int, blocks: int, threads: int, tail: str) -> str:
+    what = ("tt_bio.reference.PairformerModule (the reference's own module, unmodified install under oracle/_ref)"
+            if kind == "reference" else "the oracle port of tt_bio/reference.py")
+    return f"{done} timed step(s), each one full fp32 block (1 of {blocks}) at N={n} through {what}, {threads} threads; {tail}"
+
+
+def workload_config(args) -> dict:
+    """The ``config`` object of the JSON line: the workload, identical for both arms (the reference arm is timed
+    on the configuration of the arm it is the baseline of)."""
+    n, nb, world = args.n, args.blocks, args.gpus
+    return {"workload": f"Pairformer trunk, {nb} blocks, N={n}, c_z=128, c_s=384", "tokens": n, "blocks": nb,
+            "arithmetic": ("bf16 operands, fp32 accumulation and residual stream" if args.precision == "bf16" else
+                           "MXFP8 triangle-multiplication operands, bf16 elsewhere, fp32 accumulation and residual stream")
+                          + "; the CPU reference arm computes in fp32",
+            "masks": "all-ones masks" if args.pad_frac == 0 else f"{args.pad_frac:.0%} of the tokens masked at random",
+            "parallelism": "single GPU" if world == 1 else f"row-sharded x{world}",
+            "l2": "inputs larger than L2 (z fp32 = %d MiB)" % (n * n * C * 4 >> 20)}
 
 
 def run_reference(args, rank: int) -> None:
-    """Reference arm: the reference's CPU algorithm (oracle restatement) on all host cores."""
+    """Reference arm: the reference's CPU implementation of the path on all host cores."""
     if rank != 0:
         return
     threads = os.cpu_count() or 1
     n = args.n
-    sec, done = cpu_block_seconds(n, threads, args.cpu_budget, args.steps, min(args.warmup, 1))
+    sec, done, kind = cpu_block_seconds(n, threads, args.cpu_budget, args.steps, min(args.warmup, 1))
     ms = sec * 1e3
-    sample = (f"{done} timed step(s), each one full fp32 block (1 of {args.blocks}) at N={n} through the oracle port of "
-              f"tt_bio/reference.py, {threads} threads; stops after {args.cpu_budget:.0f} s")
+    sample = cpu_sample_text(kind, done, n, args.blocks, threads, f"stops after {args.cpu_budget:.0f} s")
     line = {"impl": "reference", "metric": "pairformer_ms_per_block", "value": ms, "unit": "ms", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms * args.blocks, "higher_is_better": False,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "tflops": block_flops(n) / (ms * 1e-3) / 1e12,
-            "config": {"workload": f"Pairformer trunk, {args.blocks} blocks, N={n}, c_z=128, c_s=384", "tokens": n,
-                       "blocks": args.blocks},
-            "cpu_baseline": {"value": ms, "unit": "ms", "cores": threads, "kind": "port", "sample": sample},
+            "config": workload_config(args),
+            "cpu_baseline": {"value": ms, "unit": "ms", "cores": threads, "kind": kind, "sample": sample},
             "e2e": {"value": ms, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
+
+
+def parity_against_fixture(n: int, blocks: int, pad_frac: float, s_out, z_out, tol: float):
+    """rel-L2 of the timed trunk's own output against the committed sampled fixture of the reference's CPU modules
+    (tests/golden/sampled/, made by tests/golden/make_sampled_trunk.py), when one exists for this workload."""
+    import numpy as np
+    from tt_boltz_b200 import synthetic
+    name = f"trunk_n{n}_b64.npz" if pad_frac == 0 else f"trunk_n{n}_b1_pad.npz"
+    path = os.path.join(ROOT, "tests", "golden", "sampled", name)
+    if not os.path.exists(path):
+        return {"checked": False, "why": f"no sampled fixture {name} for this workload"}
+    fx = np.load(path)
+    if f"z_samples_{blocks}" not in fx.files:
+        return {"checked": False, "why": f"fixture {name} has no snapshot after {blocks} blocks (has {fx['snapshots'].tolist()})"}
+    rz, rs = synthetic.sampled_fixture_errors(fx, blocks, s_out[0], z_out[0])
+    return {"checked": True, "reference": "tt_bio.reference.PairformerModule, fp32 CPU, fixture tests/golden/sampled/" + name,
+            "blocks": blocks, "rel_l2_z": rz, "rel_l2_s": rs, "z_positions_sampled": int(fx["index"].shape[0]),
+            "tolerance": tol, "ok": bool(rz < tol and rs < tol)}
 
 
 def main() -> None:
@@ -175,8 +234,9 @@ def main() -> None:
     ap.add_argument("--cpu-budget", type=float, default=150.0, help="seconds the CPU legs may spend")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--pad-frac", type=float, default=0.0, help="fraction of tokens masked at random (seed 3); 0 = all-ones masks")
     ap.add_argument("--precision", default="bf16", choices=["bf16", "mxfp8"],
-                    help="bf16 = the headline tier; mxfp8 = triangle-multiplication operands in MXFP8 (1 GPU only)")
+                    help="bf16 = the headline tier; mxfp8 = triangle-multiplication operands in MXFP8")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -198,31 +258,31 @@ def main() -> None:
     n, nb = args.n, args.blocks
     sd = synthetic.make_weights(nb, seed=1)
     s_cpu, z_cpu = synthetic.make_inputs(n, seed=0)
-    m_cpu, pm_cpu = synthetic.tail_padding_mask(n, 0)
+    m_cpu, pm_cpu = (synthetic.random_padding_mask(n, args.pad_frac, seed=3) if args.pad_frac > 0
+                     else synthetic.tail_padding_mask(n, 0))
     if world > 1:
-        from tt_boltz_b200.sharded import ShardedPairformerModule
-        if args.precision != "bf16":
-            raise SystemExit("--precision mxfp8 is built for one GPU only")
-        mod = ShardedPairformerModule(384, 128, nb, v2=True, precision="bf16")
+        from tt_boltz_b200.sharded import ShardedPairformerModule, shard_rows
+        mod = ShardedPairformerModule(384, 128, nb, v2=True, precision=args.precision)
     else:
         mod = B200PairformerModule(384, 128, nb, v2=True, precision=args.precision)
     mod.load_state_dict(sd, strict=True)
     del sd
-    s_pin, z_pin = s_cpu.pin_memory(), z_cpu.pin_memory()
-    m_pin, pm_pin = m_cpu.pin_memory(), pm_cpu.pin_memory()
-    s_d, z_d, m_d, pm_d = (t.to(dev) for t in (s_pin, z_pin, m_pin, pm_pin))
+    s_pin, m_pin, pm_pin = s_cpu.pin_memory(), m_cpu.pin_memory(), pm_cpu.pin_memory()
+    s_d, z_d, m_d, pm_d = (t.to(dev) for t in (s_pin, z_cpu, m_pin, pm_pin))
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    last = {}
+
     def timed(fn, steps):
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(steps):
-            fn()
+            last["out"] = fn()
         e1.record()
         barrier()
         ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
@@ -243,92 +303,118 @@ def main() -> None:
     ms_step = total_ms / args.steps
     ms_block = ms_step / nb
 
+    # ---- what was timed is what is checked: the last timed step's own output against the reference fixture ----
+    tol = 2e-2 if args.precision == "bf16" else 5e-2
+    parity = None
+    if rank == 0:
+        s_last, z_last = last["out"]
+        parity = parity_against_fixture(n, nb, args.pad_frac, s_last, z_last, tol)
+        parity["device_status"] = _lib.device_status()
+    last.clear()
+
     # ---- end to end through the module API with host buffers ----
     e2e = None
     if not args.no_e2e:
-        s_out = torch.empty_like(s_pin).pin_memory()
-        z_out = torch.empty_like(z_pin).pin_memory()
+        if world == 1:
+            z_pin = z_cpu.pin_memory()
+            s_out, z_out = torch.empty_like(s_pin).pin_memory(), torch.empty_like(z_pin).pin_memory()
 
-        def step_e2e():
-            so, zo = mod(s_pin.to(dev, non_blocking=True), z_pin.to(dev, non_blocking=True),
-                         m_pin.to(dev, non_blocking=True), pm_pin.to(dev, non_blocking=True))
-            s_out.copy_(so, non_blocking=True)
-            z_out.copy_(zo, non_blocking=True)
+            def step_e2e():
+                so, zo = mod(s_pin.to(dev, non_blocking=True), z_pin.to(dev, non_blocking=True),
+                             m_pin.to(dev, non_blocking=True), pm_pin.to(dev, non_blocking=True))
+                s_out.copy_(so, non_blocking=True)
+                z_out.copy_(zo, non_blocking=True)
+            api = "B200PairformerModule.forward"
+        else:
+            # one large complex over the GPUs of the box: every rank uploads and reads back ITS rows of z
+            # (ShardedPairformerModule.forward_rows), the single representation whole
+            r0, nr = shard_rows(n, rank, world)
+            z_pin = z_cpu[:, r0:r0 + nr].contiguous().pin_memory()
+            s_out, z_out = torch.empty_like(s_pin).pin_memory(), torch.empty_like(z_pin).pin_memory()
+
+            def step_e2e():
+                so, zo = mod.forward_rows(s_pin.to(dev, non_blocking=True), z_pin.to(dev, non_blocking=True),
+                                          m_pin.to(dev, non_blocking=True), pm_pin.to(dev, non_blocking=True))
+                s_out.copy_(so, non_blocking=True)
+                z_out.copy_(zo, non_blocking=True)
+            api = "ShardedPairformerModule.forward_rows (per rank: its N/P rows of z in and out, s whole)"
 
         step_e2e()
         e2e_ms = timed(step_e2e, args.steps) / args.steps
+        last.clear()
         h2d = sum(t.numel() * t.element_size() for t in (s_pin, z_pin, m_pin, pm_pin))
         d2h = sum(t.numel() * t.element_size() for t in (s_out, z_out))
-        e2e = {"value": e2e_ms / nb, "unit": "ms", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
-               "d2h_bytes_per_step": d2h}
+        e2e = {"value": e2e_ms / nb, "unit": "ms", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d * world,
+               "d2h_bytes_per_step": d2h * world, "api": api}
+        del z_pin, z_out
 
-    # ---- per-kernel pass (one extra, untimed-for-the-metric step with CUDA events per launch) ----
+    # ---- per-kernel pass (one extra, untimed-for-the-metric step with CUDA events per launch, on rank 0) ----
     peaks = measured_peaks()
+    fp8_peak = 2.0 * peaks["tflops_sustained"]      # no fp8 GEMM was measured on this pool: twice the measured bf16 rate (nominal 4.5 vs 2.25 PFLOP/s)
     kernels, roofline = {}, None
-    if world > 1 and rank == 0:
+    if rank == 0:
         _lib.timer = _lib.KernelTimer()
-    if world > 1:
-        step_dev()
-        if rank == 0:
-            summ = _lib.timer.summary()
-            _lib.timer = None
-            for name, (ms, cnt) in sorted(summ.items(), key=lambda kv: -kv[1][0]):
-                kernels[name] = {"launches": cnt, "ms_per_launch": ms / cnt, "ms_per_block": ms / nb}
-            kernels["_sum_ms_per_block"] = sum(v[0] for v in summ.values()) / nb
-    if world == 1:
-        _lib.timer = _lib.KernelTimer()
-        step_dev()
+    step_dev()
+    if rank == 0:
         summ = _lib.timer.summary()
         _lib.timer = None
+        rows = n // world                                     # rows of z a rank's row kernels process
         work = kernel_work(n)
+        ratios = ncu_traffic_ratios()
         tot = sum(v[0] for v in summ.values())
         for name, (ms, cnt) in sorted(summ.items(), key=lambda kv: -kv[1][0]):
-            ent = {"launches": cnt, "ms_per_launch": ms / cnt, "share": ms / tot}
+            ent = {"launches": cnt, "ms_per_launch": ms / cnt, "ms_per_block": ms / nb, "share": ms / tot}
             if name in work:
-                fl, by = work[name]
+                fl, by = (x / world for x in work[name])     # every sharded stage does 1/P of the single-GPU work
                 sec = ms / cnt * 1e-3
-                if name in NCU_TRAFFIC_RATIO:
-                    ent["traffic"] = NCU_TRAFFIC_RATIO[name] * by
+                is_fp8 = args.precision == "mxfp8" and name == "b200pf_trimul_contract"
+                tpeak = fp8_peak if is_fp8 else peaks["tflops_sustained"]
+                if name in ratios:
+                    ent["traffic"] = ratios[name] * by
                 ent.update({"tflops": fl / sec / 1e12, "gbs": by / sec / 1e9,
-                            "frac_tensor": fl / sec / 1e12 / peaks["tflops_sustained"],
-                            "frac_hbm": by / sec / 1e9 / peaks["hbm_gbs"]})
+                            "frac_tensor": fl / sec / 1e12 / tpeak, "frac_hbm": by / sec / 1e9 / peaks["hbm_gbs"]})
+                if is_fp8:
+                    ent["tensor_peak"] = "fp8: 2 x the measured sustained bf16 GEMM rate"
             kernels[name] = ent
+        kernels["_sum_ms_per_block"] = tot / nb
         top = next(iter(kernels))
         if top in work:
-            fl, by = work[top]
+            fl, by = (x / world for x in work[top])
             sec = kernels[top]["ms_per_launch"] * 1e-3
             t_tensor, t_hbm = fl / (peaks["tflops_sustained"] * 1e12), by / (peaks["hbm_gbs"] * 1e9)
             if t_tensor >= t_hbm:
                 roofline = {"kernel": top, "bound": "tensor", "achieved": fl / sec / 1e12, "peak": peaks["tflops_sustained"],
-                            "unit": "TFLOP/s", "frac": fl / sec / 1e12 / peaks["tflops_sustained"],
-                            "traffic": kernels[top].get("traffic")}
+                            "unit": "TFLOP/s", "frac": fl / sec / 1e12 / peaks["tflops_sustained"]}
             else:
                 roofline = {"kernel": top, "bound": "hbm", "achieved": by / sec / 1e9, "peak": peaks["hbm_gbs"],
-                            "unit": "GB/s", "frac": by / sec / 1e9 / peaks["hbm_gbs"], "traffic": kernels[top].get("traffic")}
+                            "unit": "GB/s", "frac": by / sec / 1e9 / peaks["hbm_gbs"]}
+            roofline["traffic"] = kernels[top].get("traffic")
+            roofline["traffic_source"] = (f"ratio to algorithmic bytes from {TRAFFIC_FILE} (ncu capture at N = 768), times this launch's algorithmic bytes"
+                                          if kernels[top].get("traffic") is not None else None)
             roofline["peak_source"] = peaks["source"] + " (sustained bf16 GEMM / copy bandwidth)"
             roofline["algorithmic_per_launch"] = {"flop": fl, "bytes": by}
+            roofline["launch_ms"] = kernels[top]["ms_per_launch"]
 
-    cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu:
-        threads = os.cpu_count() or 1
-        sec, done = cpu_block_seconds(n, threads, 30.0, 1, 0)
-        cpu = {"value": sec * 1e3, "unit": "ms", "cores": threads, "kind": "port",
-               "sample": f"one full fp32 block (1 of {nb}) at N={n} through the oracle port of tt_bio/reference.py, "
-                         f"{threads} threads, no warm-up"}
-    if rank == 0:
-        line = {"metric": "pairformer_ms_per_block", "value": ms_block, "unit": "ms", "n_gpus": world, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong",
-                "vs_baseline": None, "dtype": "bf16" if args.precision == "bf16" else "mxfp8 (tri-mul operands) + bf16",
-                "data": "synthetic",
-                "tflops": block_flops(n) / (ms_block * 1e-3) / 1e12,
-                "config": {"workload": f"Pairformer trunk, {nb} blocks, N={n}, c_z=128, c_s=384, bf16 operands / fp32 residual",
-                           "tokens": n, "blocks": nb, "parallelism": "single GPU" if world == 1 else f"row-sharded x{world}",
-                           "l2": "inputs larger than L2 (z fp32 = %d MiB)" % (n * n * C * 4 >> 20)},
-                "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "kernels": kernels,
-                "cpu_baseline": cpu}
-        print(json.dumps(line), flush=True)
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
+    if rank != 0:
+        return
+    cpu = None
+    if not args.no_cpu:
+        threads = os.cpu_count() or 1
+        sec, done, kind = cpu_block_seconds(n, threads, 30.0, 1, 0)
+        cpu = {"value": sec * 1e3, "unit": "ms", "cores": threads, "kind": kind,
+               "sample": cpu_sample_text(kind, done, n, nb, threads, "no warm-up")}
+    line = {"metric": "pairformer_ms_per_block", "value": ms_block, "unit": "ms", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16" if args.precision == "bf16" else "mxfp8 (tri-mul operands) + bf16",
+            "data": "synthetic",
+            "tflops": block_flops(n) / (ms_block * 1e-3) / 1e12,
+            "config": workload_config(args),
+            "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "parity": parity, "roofline": roofline, "kernels": kernels,
+            "cpu_baseline": cpu}
+    print(json.dumps(line), flush=True)
 
 
 if __name__ == "__main__":

@@ -292,6 +292,22 @@ class ShardedPairformerModule(nn.Module):
                 z_loc = sharded_block(layer, sw, z_loc, tm, pm, rank, world, self.group)
         return sw, z_loc
 
+    def forward_rows(self, s: torch.Tensor, z_rows: torch.Tensor, mask: Optional[torch.Tensor] = None,
+                     pair_mask: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+        """The trunk for a caller that keeps z sharded: ``z_rows`` [1, N/P, N, C] are THIS rank's rows (rank r owns
+        rows [r N/P, (r+1) N/P)), s [1, N, c_s] and the masks are whole and equal on every rank.  Returns
+        (s [1, N, c_s], this rank's rows of z) in the input dtypes; nothing of z is gathered."""
+        if not z_rows.is_cuda:
+            raise RuntimeError("ShardedPairformerModule: inputs must be CUDA tensors (there is no CPU path)")
+        rank = dist.get_rank(self.group)
+        z_loc = z_rows[0].to(torch.float32).clone(memory_format=torch.contiguous_format)
+        sw, z_loc = self.forward_sharded(s[0], z_loc, mask, pair_mask)
+        status = device_status()
+        if status:
+            raise RuntimeError(f"sharded Pairformer: device status 0x{status:x} on rank {rank} "
+                               "(4 = a peer did not reach an exchange barrier in time; 1 = a wait inside a kernel ran out)")
+        return sw.unsqueeze(0).to(s.dtype), z_loc.unsqueeze(0).to(z_rows.dtype)
+
     def forward(self, s: torch.Tensor, z: torch.Tensor, mask: Optional[torch.Tensor] = None,
                 pair_mask: Optional[torch.Tensor] = None, use_kernels: bool = False
                 ) -> Tuple[torch.Tensor, torch.Tensor]:
