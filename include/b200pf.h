@@ -177,8 +177,11 @@ typedef struct b200pf_planes {
  * along rows or along the contraction index (segments of 128-row multiples / 64-column multiples).
  * variant 0 = tcgen05 bf16, 1 = SIMT bf16
  * (debug cross-check of variant 0), 2 = tcgen05 block-scaled MXFP8: a / b are byte planes of e4m3
- * values (pitch, plane_stride in bytes, multiples of 16; nseg 1) and a_scales / b_scales their e8m0
- * scale blocks as written by b200pf_trimul_producer_mx.  The scales are ignored by variants 0, 1. */
+ * values (pitch, plane_stride, seg_stride in bytes, multiples of 16; k segments multiples of 128 columns)
+ * and a_scales / b_scales their e8m0 scale blocks as written by b200pf_trimul_producer_mx; for a segmented
+ * operand the scale buffers of the segments, each b200pf_mx_scale_bytes(rows, cols, channels) long for the
+ * rows / cols of ONE segment, lie one behind the other in segment order (which is what an all-to-all of the
+ * producer's channel-major scale blocks delivers).  The scales are ignored by variants 0, 1. */
 int b200pf_trimul_contract(const b200pf_planes* a, const b200pf_planes* b,
                            const void* a_scales, const void* b_scales,
                            b200pf_bf16* x, long long x_plane_stride, int x_pitch,
@@ -336,6 +339,15 @@ int b200pf_tri_mul_noalloc(float* z, const uint8_t* mask, const float* ln_gamma,
  * rank; the caller puts a cross-rank barrier between this and the consumers of the receive buffer. */
 int b200pf_peer_scatter(const void* send, const unsigned long long* recv_ptrs, long long block_bytes,
                         int rank, int world, void* stream);
+/* The same all-to-all for blocks that are strided on one or both sides (no counterpart in the reference either):
+ * block t is `chunks` pieces of chunk_bytes; piece q is read at send + t * src_block_stride + q * src_chunk_stride
+ * and written to rank t at recv_ptrs[t] + rank * dst_slot_stride + q * dst_chunk_stride (bytes, multiples of 16).
+ * It is how the row-sharded pair tensor is turned into a column shard for the ending-node attention, and back,
+ * without packing copies: rows -> columns reads nr pieces of nr * 128 elements out of every local row,
+ * columns -> rows writes them straight into the receiver's row shard. */
+int b200pf_peer_scatter_strided(const void* send, const unsigned long long* recv_ptrs, long long chunk_bytes, int chunks,
+                                long long src_block_stride, long long src_chunk_stride,
+                                long long dst_slot_stride, long long dst_chunk_stride, int rank, int world, void* stream);
 /* All-gather form of the same: `send` is ONE block, written to slot `rank` of every rank's receive buffer. */
 int b200pf_peer_broadcast(const void* send, const unsigned long long* recv_ptrs, long long block_bytes,
                           int rank, int world, void* stream);

@@ -147,6 +147,57 @@ def test_block_scaled_contraction(dev, n):
     assert rel_l2(x2[:, :, :n].float().cpu(), x0[:, :, :n].float().cpu()) < 1e-3
 
 
+def _encode_scales(e: torch.Tensor, rows: int, cols: int, channels: int, nbytes: int) -> torch.Tensor:
+    """e [channels][rows][ceil(cols/32)] scale bytes -> the 512-byte block layout."""
+    nkb = (cols + 31) // 32
+    kgroups, row_blocks = (cols + 127) // 128, 2 * ((rows + 255) // 256)
+    d = torch.arange(channels).view(-1, 1, 1)
+    r = torch.arange(rows).view(1, -1, 1)
+    kb = torch.arange(nkb).view(1, 1, -1)
+    off = ((d * kgroups + kb // 4) * row_blocks + r // 128) * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + kb % 4
+    flat = torch.zeros(nbytes, dtype=torch.uint8)
+    flat[off.reshape(-1)] = e.to(torch.uint8).reshape(-1)
+    return flat
+
+
+@pytest.mark.parametrize("seg_is_k", [0, 1])
+@pytest.mark.parametrize("world,nr", [(2, 128), (3, 128), (2, 256)])
+def test_block_scaled_contraction_segmented_operands_and_grouped_output(dev, seg_is_k, world, nr):
+    """The layouts of the sharded MXFP8 triangle multiplication: operands in `world` segments (blocks of rows or of
+    the contraction index), each with its own scale buffer packed behind the previous one, the result written in
+    groups of nr output rows.  Against an fp32 einsum of the decoded operands.  (world 3 x 128 rows: an odd number
+    of 128-row blocks, so the last 256-row B tile has no upper half.)"""
+    from tt_boltz_b200 import _lib
+    from tt_boltz_b200._lib import Planes, call, ptr, stream
+    lib = _lib.load()
+    cl, n = 8, world * nr
+    g = torch.Generator().manual_seed(5 * world + seg_is_k)
+    rows, cols = (n, nr) if seg_is_k else (nr, n)
+    sf_seg = lib.b200pf_mx_scale_bytes(rows, cols, cl)
+    full, vals, scales = [], [], []
+    for _ in range(2):
+        q = (torch.randn(cl, n, n, generator=g) * 100).clamp(-448, 448).to(torch.float8_e4m3fn)
+        e = torch.randint(118, 132, (cl, n, n // 32), generator=g, dtype=torch.int32)
+        full.append(q.float() * torch.pow(2.0, (e - 127).float()).repeat_interleave(32, dim=2))
+        qb = q.view(torch.uint8)
+        if seg_is_k:     # segment s: k in [s*nr, (s+1)*nr), all rows
+            v = qb.view(cl, n, world, nr).permute(2, 0, 1, 3).contiguous()
+            sc = torch.cat([_encode_scales(e[:, :, s * (nr // 32):(s + 1) * (nr // 32)], n, nr, cl, sf_seg) for s in range(world)])
+        else:            # segment s: rows [s*nr, (s+1)*nr), all k
+            v = qb.view(cl, world, nr, n).permute(1, 0, 2, 3).contiguous()
+            sc = torch.cat([_encode_scales(e[:, s * nr:(s + 1) * nr], nr, n, cl, sf_seg) for s in range(world)])
+        vals.append(v.to(dev))
+        scales.append(sc.to(dev))
+    ref = torch.einsum("cik,cjk->cij", full[0].to(dev), full[1].to(dev)).cpu()
+    x = torch.zeros(world, cl, nr, n, dtype=torch.bfloat16, device=dev)            # [group = i / nr][c][i local][j]
+    pa = Planes(ptr(vals[0]), rows * cols, cl * rows * cols, cols, rows, cols, world, seg_is_k)
+    pb = Planes(ptr(vals[1]), rows * cols, cl * rows * cols, cols, rows, cols, world, seg_is_k)
+    call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), ptr(scales[0]), ptr(scales[1]), ptr(x), nr * n, n, nr, cl * nr * n, cl, 2, stream())
+    assert _lib.device_status() == 0
+    got = x.permute(1, 0, 2, 3).reshape(cl, n, n).float().cpu()
+    assert rel_l2(got, ref) < 4e-3
+
+
 def _run(sd, blocks, s, z, m, pm, dev, precision, **attrs):
     mod = B200PairformerModule(384, 128, blocks, v2=True, precision=precision)
     mod.load_state_dict(sd, strict=True)

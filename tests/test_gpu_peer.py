@@ -97,3 +97,30 @@ def test_peer_barrier_gives_up_on_a_missing_rank_without_losing_the_context(dev)
     assert float((x * 2).sum()) == 1023 * 1024  # the context is intact
     with pytest.raises(RuntimeError):
         call("b200pf_peer_barrier", ptrs, 2, 0, 2, 0, stream())          # a wait without a limit is refused
+
+
+@pytest.mark.parametrize("world,nr,c", [(2, 8, 8), (4, 16, 12), (8, 24, 4)])
+def test_strided_scatter_is_the_row_column_transposition(dev, world, nr, c):
+    """Row shards -> column shards -> row shards of a [N][N][c] tensor with the strided exchange, bit-exact against
+    torch indexing (strides exactly as tt_boltz_b200.sharded.rows_to_cols / cols_to_rows pass them)."""
+    from tt_boltz_b200._lib import call, ptr, stream
+    n = world * nr
+    g = torch.Generator().manual_seed(7 * world)
+    z = torch.randn(n, n, c, generator=g).to(dev)
+    rows = [z[r * nr:(r + 1) * nr].contiguous() for r in range(world)]
+    cols = [torch.full((n, nr, c), float("nan"), device=dev) for _ in range(world)]
+    ptrs = (C.c_ulonglong * world)(*[t.data_ptr() for t in cols])
+    for rank in range(world):
+        call("b200pf_peer_scatter_strided", ptr(rows[rank]), ptrs, nr * c * 4, nr, nr * c * 4, n * c * 4, nr * nr * c * 4, nr * c * 4,
+             rank, world, stream())
+    torch.cuda.synchronize()
+    for t in range(world):
+        assert torch.equal(cols[t], z[:, t * nr:(t + 1) * nr]), t
+    back = [torch.full((nr, n, c), float("nan"), device=dev) for _ in range(world)]
+    ptrs = (C.c_ulonglong * world)(*[t.data_ptr() for t in back])
+    for rank in range(world):
+        call("b200pf_peer_scatter_strided", ptr(cols[rank]), ptrs, nr * c * 4, nr, nr * nr * c * 4, nr * c * 4, nr * c * 4, n * c * 4,
+             rank, world, stream())
+    torch.cuda.synchronize()
+    for t in range(world):
+        assert torch.equal(back[t], rows[t]), t

@@ -63,6 +63,7 @@ SIGNATURES = {
     "b200pf_transition_z_tc": [_vp, _vp, _vp, _vp, _vp, _ll, _vp],
     "b200pf_peer_scatter": [_vp, C.POINTER(C.c_ulonglong), _ll, _i, _i, _vp],
     "b200pf_peer_broadcast": [_vp, C.POINTER(C.c_ulonglong), _ll, _i, _i, _vp],
+    "b200pf_peer_scatter_strided": [_vp, C.POINTER(C.c_ulonglong), _ll, _i, _ll, _ll, _ll, _ll, _i, _i, _vp],
     "b200pf_peer_barrier": [C.POINTER(C.c_ulonglong), C.c_uint, _i, _i, _ll, _vp],
     "b200pf_tri_mul_noalloc": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
 }

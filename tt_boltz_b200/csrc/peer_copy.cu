@@ -46,6 +46,41 @@ peer_scatter_kernel(const uint4* __restrict__ send, PeerPtrs peers, long long bl
     }
 }
 
+// All-to-all of blocks that are not contiguous on one or both sides: block t consists of `chunks` pieces of
+// chunk_vec 16-byte vectors; piece q is read at send + t * src_block + q * src_chunk and written to rank t at
+// recv[t] + rank * dst_slot + q * dst_chunk (all in vectors).  This is the row-shard <-> column-shard transposition
+// of the pair tensor without a packing copy on either side.
+struct StridedCopy {
+    unsigned int chunks, chunk_vec;
+    long long src_block, src_chunk, dst_slot, dst_chunk;
+};
+__global__ void __launch_bounds__(256)
+peer_scatter_strided_kernel(const uint4* __restrict__ send, PeerPtrs peers, StridedCopy c, int rank, int world) {
+    const unsigned int block_vec = c.chunks * c.chunk_vec;
+    const unsigned long long total = (unsigned long long)block_vec * world;
+    const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+    unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i < total; i += PEER_UNROLL * stride) {
+        uint4 v[PEER_UNROLL];
+        uint4* dst[PEER_UNROLL];
+#pragma unroll
+        for (int u = 0; u < PEER_UNROLL; ++u) {
+            const unsigned long long e = i + u * stride;
+            dst[u] = nullptr;
+            if (e < total) {
+                const unsigned int slot = (unsigned int)(e / block_vec), rem = (unsigned int)(e - (unsigned long long)slot * block_vec);
+                const unsigned int q = rem / c.chunk_vec, off = rem - q * c.chunk_vec;
+                const int t = (int)((slot + rank) % world);
+                dst[u] = reinterpret_cast<uint4*>(peers.recv[t]) + rank * c.dst_slot + q * c.dst_chunk + off;
+                v[u] = __ldg(send + t * c.src_block + q * c.src_chunk + off);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < PEER_UNROLL; ++u)
+            if (dst[u]) *dst[u] = v[u];
+    }
+}
+
 // All-gather form: the one block of this rank goes to slot `rank` of every rank's receive buffer.
 __global__ void __launch_bounds__(256)
 peer_broadcast_kernel(const uint4* __restrict__ send, PeerPtrs peers, long long block_vec, int rank, int world) {
@@ -136,6 +171,35 @@ static int peer_launch(bool broadcast, const void* send, const unsigned long lon
         peer_broadcast_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(static_cast<const uint4*>(send), p, vec, rank, world);
     else
         peer_scatter_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(static_cast<const uint4*>(send), p, vec, rank, world);
+    B200PF_LAUNCH_CHECK();
+    return B200PF_OK;
+}
+
+extern "C" int b200pf_peer_scatter_strided(const void* send, const unsigned long long* recv_ptrs, long long chunk_bytes, int chunks,
+                                           long long src_block_stride, long long src_chunk_stride,
+                                           long long dst_slot_stride, long long dst_chunk_stride, int rank, int world, void* stream) {
+    B200PF_REQUIRE(send && recv_ptrs && world > 0 && world <= PEER_MAX_RANKS && rank >= 0 && rank < world, B200PF_ERR_INVALID,
+                   "peer_scatter_strided: bad argument (at most %d ranks)", PEER_MAX_RANKS);
+    B200PF_REQUIRE(chunks > 0 && chunk_bytes > 0 && chunk_bytes % 16 == 0 && aligned16(send) && src_block_stride % 16 == 0 &&
+                       src_chunk_stride % 16 == 0 && dst_slot_stride % 16 == 0 && dst_chunk_stride % 16 == 0 &&
+                       src_block_stride >= 0 && src_chunk_stride >= chunk_bytes && dst_slot_stride >= 0 && dst_chunk_stride >= chunk_bytes,
+                   B200PF_ERR_INVALID, "peer_scatter_strided: sizes and strides must be non-negative 16-byte multiples, chunk strides >= the chunk");
+    B200PF_REQUIRE(chunk_bytes / 16 < (1ll << 31) && (long long)chunks * (chunk_bytes / 16) < (1ll << 32), B200PF_ERR_UNSUPPORTED,
+                   "peer_scatter_strided: block too large");
+    PeerPtrs p{};
+    for (int t = 0; t < world; ++t) {
+        B200PF_REQUIRE(recv_ptrs[t] != 0 && recv_ptrs[t] % 16 == 0, B200PF_ERR_INVALID, "peer_scatter_strided: bad receive pointer of rank %d", t);
+        p.recv[t] = recv_ptrs[t];
+    }
+    int dev = 0, sms = 148;
+    B200PF_CUDA(cudaGetDevice(&dev));
+    B200PF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    StridedCopy c{(unsigned int)chunks, (unsigned int)(chunk_bytes / 16), src_block_stride / 16, src_chunk_stride / 16,
+                  dst_slot_stride / 16, dst_chunk_stride / 16};
+    const long long vec = (long long)chunks * (chunk_bytes / 16) * world;
+    long long blocks = (vec + 256 * PEER_UNROLL - 1) / (256 * PEER_UNROLL);
+    if (blocks > (long long)sms * 8) blocks = (long long)sms * 8;
+    peer_scatter_strided_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(static_cast<const uint4*>(send), p, c, rank, world);
     B200PF_LAUNCH_CHECK();
     return B200PF_OK;
 }

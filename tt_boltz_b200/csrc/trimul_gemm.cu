@@ -274,7 +274,8 @@ static int check_planes(const b200pf_planes* p, const char* what) {
 
 namespace gemm_mx {   // block-scaled fp8 kernel, trimul_gemm_mx.cu
 int launch_contract(const b200pf_planes* a, const b200pf_planes* b, const void* a_scales, const void* b_scales,
-                    b200pf_bf16* x, long long x_plane_stride, int x_pitch, int channels, cudaStream_t st);
+                    b200pf_bf16* x, long long x_plane_stride, int x_pitch, int x_row_group, long long x_group_stride,
+                    int channels, cudaStream_t st);
 }
 
 }  // namespace b200pf
@@ -287,8 +288,7 @@ extern "C" int b200pf_trimul_contract(const b200pf_planes* a, const b200pf_plane
                                       int x_row_group, long long x_group_stride,
                                       int channels, int variant, void* stream) {
     if (variant == 2) {
-        B200PF_REQUIRE(x_row_group <= 0, B200PF_ERR_UNSUPPORTED, "trimul_contract: variant 2 writes plain planes only");
-        return gemm_mx::launch_contract(a, b, a_scales, b_scales, x, x_plane_stride, x_pitch, channels,
+        return gemm_mx::launch_contract(a, b, a_scales, b_scales, x, x_plane_stride, x_pitch, x_row_group, x_group_stride, channels,
                                         static_cast<cudaStream_t>(stream));
     }
     int rc;

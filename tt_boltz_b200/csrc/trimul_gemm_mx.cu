@@ -28,11 +28,26 @@ constexpr int THREADS = 192;
 constexpr int SMEM = OFF_BAR + 256 + 1024 /*alignment slack*/;
 constexpr uint32_t COL_SFA = 256, COL_SFB = 264;
 
+// Operands may arrive in segments (the sharded trunk: one per source rank), either blocks of ROWS or blocks of the
+// contraction index; a segment holds [channels][rows][pitch] values and, packed right behind each other in the
+// same order, [channels][kgroups][row_blocks] scale blocks.  Unsegmented operands set the segment extents beyond
+// the tensor, so the quotients below are 0.
 struct Shape {
     int m_rows, n_rows, k_total, channels, x_pitch;
     long long x_plane_stride;
-    int a_kgroups, a_row_blocks, b_kgroups, b_row_blocks;
+    int a_kgroups, a_row_blocks, b_kgroups, b_row_blocks;      // per segment
+    int a_kseg_cols, a_rowseg_rows, b_kseg_cols, b_rowseg_rows;
+    long long a_sf_seg, b_sf_seg;                              // bytes between the scale buffers of two segments
+    int x_row_group;                                           // output rows per group (> m_rows: plain planes)
+    long long x_group_stride;
 };
+__device__ __forceinline__ long long sf_block_offset(int d, int k0, int row0, int kseg_cols, int rowseg_rows, int kgroups_, int row_blocks_,
+                                                     long long seg_stride) {
+    const int kseg = k0 / kseg_cols, kin = k0 - kseg * kseg_cols;
+    const int rseg = row0 / rowseg_rows, rin = row0 - rseg * rowseg_rows;
+    return (long long)(kseg + rseg) * seg_stride +
+           (((long long)d * kgroups_ + (kin >> 7)) * row_blocks_ + (rin >> 7)) * mx::SF_BLOCK_BYTES;
+}
 
 __global__ void __launch_bounds__(THREADS, 1)
 trimul_contract_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -84,14 +99,20 @@ trimul_contract_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                 uint8_t* sb = sa + A_BYTES;
                 uint8_t* sf = smem + OFF_SF + stage * SF_BYTES;
                 mbar_arrive_expect_tx(&full[stage], DATA_BYTES + SF_BYTES);
-                tma_load_4d(sa, &map_a, &full[stage], kb * BK, m0, d, 0);
-                tma_load_4d(sb, &map_b, &full[stage], kb * BK, n0, d, 0);
-                tma_load_4d(sb + 128 * BK, &map_b, &full[stage], kb * BK, n0 + 128, d, 0);
-                bulk_load_1d(sf, sfa + (((long long)d * s.a_kgroups + kb) * s.a_row_blocks + (m0 >> 7)) * mx::SF_BLOCK_BYTES,
+                const int k0 = kb * BK;
+                tma_load_4d(sa, &map_a, &full[stage], k0 % s.a_kseg_cols, m0 % s.a_rowseg_rows, d, m0 / s.a_rowseg_rows + k0 / s.a_kseg_cols);
+                bulk_load_1d(sf, sfa + sf_block_offset(d, k0, m0, s.a_kseg_cols, s.a_rowseg_rows, s.a_kgroups, s.a_row_blocks, s.a_sf_seg),
                              mx::SF_BLOCK_BYTES, &full[stage]);
-                bulk_load_1d(sf + mx::SF_BLOCK_BYTES,
-                             sfb + (((long long)d * s.b_kgroups + kb) * s.b_row_blocks + (n0 >> 7)) * mx::SF_BLOCK_BYTES,
-                             2 * mx::SF_BLOCK_BYTES, &full[stage]);
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const int j = n0 + half * 128;
+                    tma_load_4d(sb + half * (128 * BK), &map_b, &full[stage], k0 % s.b_kseg_cols, j % s.b_rowseg_rows, d,
+                                j / s.b_rowseg_rows + k0 / s.b_kseg_cols);          // rows past the end: zero fill
+                    const int js = j < s.n_rows ? j : n0;                           // their scales: any block that exists
+                    bulk_load_1d(sf + (1 + half) * mx::SF_BLOCK_BYTES,
+                                 sfb + sf_block_offset(d, k0, js, s.b_kseg_cols, s.b_rowseg_rows, s.b_kgroups, s.b_row_blocks, s.b_sf_seg),
+                                 mx::SF_BLOCK_BYTES, &full[stage]);
+                }
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
         }
@@ -146,7 +167,9 @@ trimul_contract_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             if (!ok) break;
             tc_fence_after();
             const int row = m0 + quarter * 32 + lane;
-            __nv_bfloat16* xrow = x + (long long)d * s.x_plane_stride + (long long)row * s.x_pitch;
+            const int rsafe = row < s.m_rows ? row : 0, grp = rsafe / s.x_row_group;
+            __nv_bfloat16* xrow = x + (long long)grp * s.x_group_stride + (long long)d * s.x_plane_stride +
+                                  (long long)(rsafe - grp * s.x_row_group) * s.x_pitch;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 const int col = n0 + c * 32;
@@ -209,35 +232,58 @@ mx_dequant_kernel(const uint8_t* __restrict__ planes, const uint8_t* __restrict_
 static int check_mx_planes(const b200pf_planes* p, const void* scales, const char* what) {
     B200PF_REQUIRE(p && p->ptr && scales, B200PF_ERR_INVALID, "mx: %s planes / scales are null", what);
     B200PF_REQUIRE(aligned16(p->ptr) && aligned16(scales), B200PF_ERR_INVALID, "mx: %s not 16-byte aligned", what);
-    B200PF_REQUIRE(p->nseg == 1, B200PF_ERR_UNSUPPORTED, "mx: segmented %s operands are not built", what);
-    B200PF_REQUIRE(p->rows > 0 && p->cols > 0 && p->pitch >= p->cols && p->pitch % 16 == 0, B200PF_ERR_INVALID,
+    B200PF_REQUIRE(p->rows > 0 && p->cols > 0 && p->nseg >= 1 && p->pitch >= p->cols && p->pitch % 16 == 0, B200PF_ERR_INVALID,
                    "mx: %s pitch %d must be >= cols %d and a multiple of 16 bytes", what, p->pitch, p->cols);
     B200PF_REQUIRE(p->plane_stride % 16 == 0 && p->plane_stride >= (long long)p->pitch * p->rows, B200PF_ERR_INVALID,
                    "mx: %s plane stride too small or not a multiple of 16", what);
+    if (p->nseg > 1) {
+        B200PF_REQUIRE(p->seg_stride % 16 == 0 && p->seg_stride > 0, B200PF_ERR_INVALID, "mx: %s bad segment stride", what);
+        if (p->seg_is_k)
+            B200PF_REQUIRE(p->cols % BK == 0, B200PF_ERR_UNSUPPORTED, "mx: %s k segments must be multiples of %d columns", what, BK);
+        else
+            B200PF_REQUIRE(p->rows % 128 == 0, B200PF_ERR_UNSUPPORTED, "mx: %s row segments must be multiples of 128 rows", what);
+    }
     return B200PF_OK;
 }
 
 int launch_contract(const b200pf_planes* a, const b200pf_planes* b, const void* a_scales, const void* b_scales,
-                    b200pf_bf16* x, long long x_plane_stride, int x_pitch, int channels, cudaStream_t st) {
+                    b200pf_bf16* x, long long x_plane_stride, int x_pitch, int x_row_group, long long x_group_stride,
+                    int channels, cudaStream_t st) {
     int rc;
     if ((rc = check_mx_planes(a, a_scales, "A")) != B200PF_OK) return rc;
     if ((rc = check_mx_planes(b, b_scales, "B")) != B200PF_OK) return rc;
-    B200PF_REQUIRE(a->cols == b->cols, B200PF_ERR_INVALID, "mx contract: contraction lengths differ (%d vs %d)", a->cols, b->cols);
-    B200PF_REQUIRE(x && aligned16(x) && channels > 0 && x_pitch % 8 == 0 && x_pitch >= b->rows &&
-                       x_plane_stride >= (long long)x_pitch * a->rows,
-                   B200PF_ERR_INVALID, "mx contract: bad output");
     Shape s;
-    s.m_rows = a->rows; s.n_rows = b->rows; s.k_total = a->cols; s.channels = channels;
+    s.m_rows = (a->nseg > 1 && !a->seg_is_k) ? a->rows * a->nseg : a->rows;
+    s.n_rows = (b->nseg > 1 && !b->seg_is_k) ? b->rows * b->nseg : b->rows;
+    const int ka = (a->nseg > 1 && a->seg_is_k) ? a->cols * a->nseg : a->cols;
+    const int kb = (b->nseg > 1 && b->seg_is_k) ? b->cols * b->nseg : b->cols;
+    B200PF_REQUIRE(ka == kb, B200PF_ERR_INVALID, "mx contract: contraction lengths differ (%d vs %d)", ka, kb);
+    s.k_total = ka; s.channels = channels;
+    s.a_kseg_cols = (a->nseg > 1 && a->seg_is_k) ? a->cols : (ka + BK);           // never reached by k0 when unsegmented
+    s.a_rowseg_rows = (a->nseg > 1 && !a->seg_is_k) ? a->rows : (s.m_rows + BM);
+    s.b_kseg_cols = (b->nseg > 1 && b->seg_is_k) ? b->cols : (kb + BK);
+    s.b_rowseg_rows = (b->nseg > 1 && !b->seg_is_k) ? b->rows : (s.n_rows + BN);
+    const bool grouped = x_row_group > 0 && x_row_group < s.m_rows;
+    s.x_row_group = grouped ? x_row_group : s.m_rows + BM;
+    s.x_group_stride = grouped ? x_group_stride : 0;
+    B200PF_REQUIRE(x && aligned16(x) && channels > 0 && x_pitch % 8 == 0 && x_pitch >= s.n_rows && x_plane_stride % 8 == 0 &&
+                       x_plane_stride >= (long long)x_pitch * (grouped ? x_row_group : s.m_rows),
+                   B200PF_ERR_INVALID, "mx contract: bad output");
+    B200PF_REQUIRE(!grouped || (x_group_stride % 8 == 0 && x_group_stride >= x_plane_stride * channels), B200PF_ERR_INVALID,
+                   "mx contract: bad x group stride");
     s.x_pitch = x_pitch; s.x_plane_stride = x_plane_stride;
     s.a_kgroups = mx::kgroups(a->cols); s.a_row_blocks = mx::row_blocks(a->rows);
     s.b_kgroups = mx::kgroups(b->cols); s.b_row_blocks = mx::row_blocks(b->rows);
+    s.a_sf_seg = mx::scale_bytes(a->rows, a->cols, channels);
+    s.b_sf_seg = mx::scale_bytes(b->rows, b->cols, channels);
     unsigned int* status = device_status_word();
     B200PF_REQUIRE(status, B200PF_ERR_CUDA, "mx contract: no device status word");
     CUtensorMap maps[2];
     const b200pf_planes* ops[2] = {a, b};
     for (int i = 0; i < 2; ++i) {
-        cuuint64_t dims[4] = {(cuuint64_t)ops[i]->cols, (cuuint64_t)ops[i]->rows, (cuuint64_t)channels, 1};
-        cuuint64_t str[3] = {(cuuint64_t)ops[i]->pitch, (cuuint64_t)ops[i]->plane_stride, (cuuint64_t)ops[i]->plane_stride * channels};
+        const long long seg_stride = ops[i]->nseg > 1 ? ops[i]->seg_stride : ops[i]->plane_stride * channels;
+        cuuint64_t dims[4] = {(cuuint64_t)ops[i]->cols, (cuuint64_t)ops[i]->rows, (cuuint64_t)channels, (cuuint64_t)ops[i]->nseg};
+        cuuint64_t str[3] = {(cuuint64_t)ops[i]->pitch, (cuuint64_t)ops[i]->plane_stride, (cuuint64_t)seg_stride};
         cuuint32_t box[4] = {(cuuint32_t)BK, 128u, 1u, 1u};
         if ((rc = tmap_encode(&maps[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, const_cast<void*>(ops[i]->ptr), 4, dims, str, box,
                               CU_TENSOR_MAP_SWIZZLE_128B, i ? "mx B" : "mx A")) != B200PF_OK) return rc;

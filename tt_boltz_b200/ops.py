@@ -279,8 +279,10 @@ def pack_single_track(w_att: Dict[str, torch.Tensor], w_trans: Dict[str, torch.T
 
 def single_track_local(s: torch.Tensor, z_rows: torch.Tensor, tok_mask_u8: torch.Tensor, w_norm: Dict[str, torch.Tensor],
                        w_att: Dict[str, torch.Tensor], fused: Dict[str, torch.Tensor], num_heads: int,
-                       r0: int = 0) -> torch.Tensor:
-    """Gated attention output sigmoid(g) * softmax(...) v for the query rows [r0, r0 + z_rows.shape[0]) (fp32)."""
+                       r0: int = 0, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Gated attention output sigmoid(g) * softmax(...) v for the query rows [r0, r0 + z_rows.shape[0]) (fp32).
+    ``bias`` = pair_bias_heads(z_rows, w_att) when the caller has computed it already (then z_rows is only read
+    for its shape)."""
     n, cs = s.shape
     nq = z_rows.shape[0]
     hd = cs // num_heads
@@ -290,7 +292,8 @@ def single_track_local(s: torch.Tensor, z_rows: torch.Tensor, tok_mask_u8: torch
     pitch = _round_up(n, 4)
     kvt = torch.empty(2 * cs, pitch, dtype=torch.float32, device=s.device)              # [k rows | v rows][key]
     call("b200pf_f32_linear_t", ptr(sn), ptr(fused["w_kv"]), None, ptr(kvt), pitch, n, cs, 2 * cs, st)
-    bias = pair_bias_heads(z_rows, w_att)                                                # [heads][nq * n]
+    if bias is None:
+        bias = pair_bias_heads(z_rows, w_att)                                            # [heads][nq * n]
     o = torch.empty(nq, cs, dtype=torch.float32, device=s.device)
     call("b200pf_f32_sattention", ptr(qg), 2 * cs, qg.data_ptr() + 4 * cs, 2 * cs, ptr(kvt), kvt.data_ptr() + 4 * cs * pitch, pitch,
          ptr(o), cs, ptr(bias), nq * n, n, ptr(tok_mask_u8), nq, n, num_heads, hd, 1.0 / math.sqrt(hd), 1e6, st)

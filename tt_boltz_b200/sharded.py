@@ -37,8 +37,9 @@ C_Z = 128
 # ------------------------------------------------------------------------------------------------
 # plumbing (backend-agnostic)
 # ------------------------------------------------------------------------------------------------
-def all_gather_cat(x: torch.Tensor, group=None, tag: Optional[str] = None) -> torch.Tensor:
-    """[P, *x.shape]: slot s holds rank s's tensor.  With a ``tag`` on CUDA: peer writes (see all_to_all_blocks)."""
+def all_gather_cat(x: torch.Tensor, group=None, tag: Optional[str] = None, channel: int = 0) -> torch.Tensor:
+    """[P, *x.shape]: slot s holds rank s's tensor.  With a ``tag`` on CUDA: peer writes (see all_to_all_blocks);
+    ``channel`` names the barrier state of the stream the call is enqueued on (see peer_barrier)."""
     world = dist.get_world_size(group)
     x = x.contiguous()
     nbytes = x.numel() * x.element_size()
@@ -47,7 +48,7 @@ def all_gather_cat(x: torch.Tensor, group=None, tag: Optional[str] = None) -> to
         if peer is not None:
             recv, hdl, ptrs = peer
             call("b200pf_peer_broadcast", ptr(x), ptrs, nbytes, dist.get_rank(group), world, stream())
-            peer_barrier(x.device, group)
+            peer_barrier(x.device, group, channel)
             return recv.view((world,) + tuple(x.shape))
     out = torch.empty((world,) + tuple(x.shape), dtype=x.dtype, device=x.device)
     if x.is_cuda:
@@ -71,13 +72,15 @@ _BARRIER_TIMEOUT_MS = int(os.environ.get("B200PF_BARRIER_TIMEOUT_MS", "20000"))
 _BARRIERS: Dict[tuple, list] = {}
 
 
-def peer_barrier(device: torch.device, group=None) -> None:
+def peer_barrier(device: torch.device, group=None, channel: int = 0) -> None:
     """Enqueue the library's own cross-rank barrier (``b200pf_peer_barrier``) on the current stream.
 
-    The signal pads are one small symmetric allocation per (device, group), zeroed before the first use; the
-    generation counter lives on the host and grows by one per call, the same on every rank because every rank
-    enqueues the same sequence of exchanges."""
-    key = (device.index, id(group))
+    The signal pads are one small symmetric allocation per (device, group, channel), zeroed before the first use;
+    the generation counter lives on the host and grows by one per call, the same on every rank because every rank
+    enqueues the same sequence of exchanges ON ONE STREAM.  Exchanges enqueued on another stream (the single
+    track's side stream) may interleave differently with them on different ranks, so they use a channel, i.e.
+    pads and a counter, of their own."""
+    key = (device.index, id(group), channel)
     st = _BARRIERS.get(key)
     if st is None:
         import torch.distributed._symmetric_memory as symm
@@ -147,18 +150,47 @@ def all_to_all_blocks(send: torch.Tensor, group=None, tag: Optional[str] = None)
     return recv
 
 
+def _strided_exchange(tag: str, src: torch.Tensor, out_numel: int, chunk_elems: int, chunks: int, src_block: int, src_chunk: int,
+                      dst_slot: int, dst_chunk: int, group):
+    """One launch of b200pf_peer_scatter_strided (strides in ELEMENTS of src) into the symmetric receive buffer of
+    ``tag``, then the barrier; None when peer copies are off or unavailable."""
+    if not (src.is_cuda and _PEER_COPY["enabled"]):
+        return None
+    peer = _peer_buffers(tag, out_numel, src.dtype, src.device, group)
+    if peer is None:
+        return None
+    recv, _, ptrs = peer
+    e = src.element_size()
+    call("b200pf_peer_scatter_strided", ptr(src), ptrs, chunk_elems * e, chunks, src_block * e, src_chunk * e, dst_slot * e, dst_chunk * e,
+         dist.get_rank(group), dist.get_world_size(group), stream())
+    peer_barrier(src.device, group)
+    return recv
+
+
 def rows_to_cols(z_loc: torch.Tensor, group=None) -> torch.Tensor:
-    """Row shard [nr, N, C] -> column shard stored [N, nr, C] (element [i][j_local])."""
+    """Row shard [nr, N, C] -> column shard stored [N, nr, C] (element [i][j_local]).  On CUDA the pieces are read
+    out of the row shard and written into the receivers' column shards directly (no packing copy); the result is
+    then the receive buffer (valid until the second-next call)."""
     world = dist.get_world_size(group)
     nr, n, c = z_loc.shape
+    # block for rank t = my rows x its columns: nr pieces (one per local row) of nr*c contiguous elements
+    recv = _strided_exchange("z_rows_to_cols", z_loc.contiguous(), n * nr * c, nr * c, nr, nr * c, n * c, nr * nr * c, nr * c, group)
+    if recv is not None:
+        return recv.view(n, nr, c)
     send = z_loc.view(nr, world, nr, c).permute(1, 0, 2, 3)      # [dest t][i_local][j_local][c]
     return all_to_all_blocks(send, group, "z_rows_to_cols").view(n, nr, c)   # [src s * nr + i_local][j_local][c]
 
 
 def cols_to_rows(zc: torch.Tensor, group=None) -> torch.Tensor:
-    """Inverse of rows_to_cols: column shard [N, nr, C] -> row shard [nr, N, C]."""
+    """Inverse of rows_to_cols: column shard [N, nr, C] -> row shard [nr, N, C].  On CUDA every piece lands at its
+    place in the receiver's row shard (no unpacking copy); the result is then the receive buffer (valid until the
+    second-next call)."""
     world = dist.get_world_size(group)
     n, nr, c = zc.shape
+    # block for rank t = its rows x my columns: piece i_local goes to row i_local, columns [rank*nr, (rank+1)*nr)
+    recv = _strided_exchange("z_cols_to_rows", zc.contiguous(), nr * n * c, nr * c, nr, nr * nr * c, nr * c, nr * c, n * c, group)
+    if recv is not None:
+        return recv.view(nr, n, c)
     recv = all_to_all_blocks(zc.view(world, nr, nr, c), group, "z_cols_to_rows")   # recv[s] = rows R_r, cols R_s
     return recv.permute(1, 0, 2, 3).reshape(nr, n, c).contiguous()
 
@@ -173,6 +205,11 @@ def shard_rows(n: int, rank: int, world: int) -> Tuple[int, int]:
 # ------------------------------------------------------------------------------------------------
 # one sharded block on the GPU
 # ------------------------------------------------------------------------------------------------
+def _lib_handle():
+    from . import _lib
+    return _lib.load()
+
+
 def _ru8(x: int) -> int:
     return (x + 7) // 8 * 8
 
@@ -181,10 +218,33 @@ def _bf16(n_elems: int, dev) -> torch.Tensor:
     return torch.empty(n_elems, dtype=torch.bfloat16, device=dev)
 
 
+class SideTrack:
+    """The stream the single track runs on, beside the pair track.
+
+    The single track of block b needs z after block b's pair transition and s after block b-1, and nothing in the
+    pair track ever reads s: so it runs on a stream of its own, under the next block's pair kernels and exchanges
+    (which at 8 GPUs leave most SMs idle).  Its one read of z, the pair-bias projection, has to be over before the
+    next block first writes z: ``bias_read`` is the event the pair stream waits for at that point."""
+
+    def __init__(self, device: torch.device) -> None:
+        self.stream = torch.cuda.Stream(device)
+        self.bias_read: Optional[torch.cuda.Event] = None
+
+    def before_z_write(self) -> None:
+        if self.bias_read is not None:
+            torch.cuda.current_stream().wait_event(self.bias_read)
+            self.bias_read = None
+
+    def join(self) -> None:
+        torch.cuda.current_stream().wait_stream(self.stream)
+        self.bias_read = None
+
+
 def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: torch.Tensor,
                   tok_mask_u8: Optional[torch.Tensor], masks: ops.PairMasks, rank: int, world: int,
-                  group=None) -> torch.Tensor:
-    """Update the local row shard z_loc [nr, N, 128] (returned; may be a new tensor) and s in place."""
+                  group=None, side: Optional[SideTrack] = None) -> torch.Tensor:
+    """Update the local row shard z_loc [nr, N, 128] (returned; may be a new tensor) and s in place.  With a
+    ``side`` track the update of s is only enqueued on its stream: the caller joins it before reading s."""
     pk = layer._pack(z_loc.device)
     dev = z_loc.device
     nr, n, _ = z_loc.shape
@@ -204,24 +264,44 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
     if C_Z % world:
         raise RuntimeError("the sharded triangle multiplication needs the rank count to divide 128 channels")
     cl = C_Z // world                                                                # channels contracted here
+    mx = layer.precision == "mxfp8"
     x_send, x_loc = _bf16(world * cl * nr * pn, dev), None
     for incoming in (0, 1):
         w = pk["tri_mul_in" if incoming else "tri_mul_out"]
         # outgoing: planes [D][local row i or j][k], k = all N columns; incoming: [D][column i or j][local row k]
         prow, pcol, pitch = (n, nr, pr) if incoming else (nr, n, pn)
-        a_loc, b_loc = _bf16(C_Z * prow * pitch, dev), _bf16(C_Z * prow * pitch, dev)
-        oa, ob = PlaneOut(ptr(a_loc), prow * pitch, 0, 0), PlaneOut(ptr(b_loc), prow * pitch, 0, 0)
-        call("b200pf_trimul_producer", ptr(z_loc), ptr(mask_loc), *ops.trimul_producer_weights(w, layer.row_impl),
-             C.byref(oa), C.byref(ob), pitch, nr, n, incoming, 0, layer.row_impl, st)
-        a_ch = all_to_all_blocks(a_loc.view(world, -1), group, "trimul_a")           # [src][cl][prow][pitch]
-        b_ch = all_to_all_blocks(b_loc.view(world, -1), group, "trimul_b")
+        if mx:
+            # MXFP8 on the wire: e4m3 byte planes (half the bytes of bf16) plus their e8m0 scale blocks, both
+            # channel-major, so the channel block of every destination rank is contiguous in each
+            pitch = (pcol + 15) // 16 * 16
+            lib = _lib_handle()
+            sf_all, sf_blk = lib.b200pf_mx_scale_bytes(prow, pcol, C_Z), lib.b200pf_mx_scale_bytes(prow, pcol, cl)
+            a_loc, b_loc = (torch.empty(C_Z * prow * pitch, dtype=torch.uint8, device=dev) for _ in range(2))
+            sa_loc, sb_loc = (torch.zeros(sf_all, dtype=torch.uint8, device=dev) for _ in range(2))
+            call("b200pf_trimul_producer_mx", ptr(z_loc), ptr(mask_loc), ptr(w["ln_in_gamma"]), ptr(w["ln_in_beta"]), ptr(w["w_pg_tc"]),
+                 ptr(a_loc), ptr(b_loc), ptr(sa_loc), ptr(sb_loc), prow * pitch, pitch, nr, n, incoming, st)
+            a_ch = all_to_all_blocks(a_loc.view(world, -1), group, "trimul_a8")
+            b_ch = all_to_all_blocks(b_loc.view(world, -1), group, "trimul_b8")
+            sa_ch = all_to_all_blocks(sa_loc.view(world, sf_blk), group, "trimul_sa")   # [src][cl][kgroups][row blocks][512]
+            sb_ch = all_to_all_blocks(sb_loc.view(world, sf_blk), group, "trimul_sb")
+            scales, variant = (ptr(sa_ch), ptr(sb_ch)), 2
+        else:
+            a_loc, b_loc = _bf16(C_Z * prow * pitch, dev), _bf16(C_Z * prow * pitch, dev)
+            oa, ob = PlaneOut(ptr(a_loc), prow * pitch, 0, 0), PlaneOut(ptr(b_loc), prow * pitch, 0, 0)
+            call("b200pf_trimul_producer", ptr(z_loc), ptr(mask_loc), *ops.trimul_producer_weights(w, layer.row_impl),
+                 C.byref(oa), C.byref(ob), pitch, nr, n, incoming, 0, layer.row_impl, st)
+            a_ch = all_to_all_blocks(a_loc.view(world, -1), group, "trimul_a")           # [src][cl][prow][pitch]
+            b_ch = all_to_all_blocks(b_loc.view(world, -1), group, "trimul_b")
+            scales, variant = (None, None), layer.contract_variant
         seg = cl * prow * pitch
         # outgoing: the source rank owns a block of ROWS of the operand; incoming: a block of the contraction index
         pa = Planes(ptr(a_ch), prow * pitch, seg, pitch, prow, pcol, world, incoming)
         pb = Planes(ptr(b_ch), prow * pitch, seg, pitch, prow, pcol, world, incoming)
-        call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), None, None, ptr(x_send), nr * pn, pn,
-             nr, cl * nr * pn, cl, layer.contract_variant, st)                      # x[dest][cl][nr][pn]
+        call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), *scales, ptr(x_send), nr * pn, pn,
+             nr, cl * nr * pn, cl, variant, st)                                     # x[dest][cl][nr][pn]
         x_loc = all_to_all_blocks(x_send.view(world, -1), group, "trimul_x")         # [src = channel block][cl][nr][pn] = [D][nr][pn]
+        if side is not None:
+            side.before_z_write()          # the previous block's pair-bias projection has read z
         ops.trimul_epilogue(z_loc, x_loc, nr * pn, pn, w, nr, n, layer.row_impl)
         del a_loc, b_loc, a_ch, b_ch
     del x_send, x_loc
@@ -254,12 +334,26 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
 
     # ---- single track: attention for the local query rows, the rest replicated --------------------
     if layer.with_s and s is not None:
-        og_loc = ops.single_track_local(s, z_loc, tok_mask_u8, pk["pre_norm_s"], pk["attention"], pk["s_fused"],
-                                        layer.num_heads, r0)
-        # output projection and transition are per row: run them on the local rows, then gather s
-        s_loc = s[r0:r0 + nr]
-        ops.single_track_finish(s_loc, og_loc, pk["attention"], pk["transition_s"], pk["s_fused"])
-        s.copy_(all_gather_cat(s_loc, group, "s_rows").view(n, s.shape[1]))
+        def single_track(channel: int) -> None:
+            bias = ops.pair_bias_heads(z_loc, pk["attention"])
+            if side is not None:
+                side.bias_read = torch.cuda.Event()
+                side.bias_read.record()
+            og_loc = ops.single_track_local(s, z_loc, tok_mask_u8, pk["pre_norm_s"], pk["attention"], pk["s_fused"],
+                                            layer.num_heads, r0, bias)
+            # output projection and transition are per row: run them on the local rows, then gather s
+            s_loc = s[r0:r0 + nr]
+            ops.single_track_finish(s_loc, og_loc, pk["attention"], pk["transition_s"], pk["s_fused"])
+            s.copy_(all_gather_cat(s_loc, group, "s_rows", channel).view(n, s.shape[1]))
+
+        if side is None:
+            single_track(0)
+        else:
+            z_ready = torch.cuda.Event()
+            z_ready.record()
+            with torch.cuda.stream(side.stream):
+                side.stream.wait_event(z_ready)
+                single_track(1)
     return z_loc
 
 
@@ -272,9 +366,10 @@ class ShardedPairformerModule(nn.Module):
                  activation_checkpointing: bool = False, v2: bool = False, precision: str = "bf16", group=None,
                  **kwargs) -> None:
         super().__init__()
-        if precision != "bf16":
-            raise NotImplementedError("the sharded trunk is built for the bf16 tier")
+        if precision not in ("bf16", "mxfp8"):
+            raise NotImplementedError("the sharded trunk is built for the bf16 and mxfp8 tiers")
         self.group = group
+        self._side: Optional[SideTrack] = None
         self.layers = nn.ModuleList([
             B200PairformerLayer(token_s, token_z, num_heads, dropout, pairwise_head_width, pairwise_num_heads,
                                 post_layer_norm, v2, precision, with_s=True) for _ in range(num_blocks)])
@@ -288,8 +383,16 @@ class ShardedPairformerModule(nn.Module):
             pm = ops.PairMasks(_mask_u8(pair_mask, (n, n), z_loc.device))
             tm = _mask_u8(mask, (n,), z_loc.device)
             sw = s.to(torch.float32).clone()
+            side = None
+            if z_loc.is_cuda and os.environ.get("B200PF_SIDE_TRACK", "1") != "0":
+                if self._side is None or self._side.stream.device != z_loc.device:
+                    self._side = SideTrack(z_loc.device)
+                side = self._side
             for layer in self.layers:
-                z_loc = sharded_block(layer, sw, z_loc, tm, pm, rank, world, self.group)
+                z_loc = sharded_block(layer, sw, z_loc, tm, pm, rank, world, self.group, side)
+            if side is not None:
+                side.join()
+            z_loc = z_loc.clone()          # the blocks hand back an exchange's receive buffer, which the next call reuses
         return sw, z_loc
 
     def forward_rows(self, s: torch.Tensor, z_rows: torch.Tensor, mask: Optional[torch.Tensor] = None,
