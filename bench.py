@@ -229,7 +229,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--n", type=int, default=1024, help="tokens")
+    ap.add_argument("--n", "--tokens", dest="n", type=int, default=1024,
+                    help="tokens (under torch.distributed.run spell it --tokens: its own parser claims --n)")
     ap.add_argument("--blocks", type=int, default=64)
     ap.add_argument("--cpu-budget", type=float, default=150.0, help="seconds the CPU legs may spend")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
