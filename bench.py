@@ -310,8 +310,26 @@ def main() -> None:
     if rank == 0:
         s_last, z_last = last["out"]
         parity = parity_against_fixture(n, nb, args.pad_frac, s_last, z_last, tol)
-        parity["device_status"] = _lib.device_status()
     last.clear()
+    if nb > 1:
+        # where the reference fixture only reaches one block (N = 2048: a reference block is minutes of CPU), one
+        # extra untimed pass of the FIRST block on the same inputs is what gets compared (every rank takes part)
+        need_first = torch.tensor([1 if (rank == 0 and not parity["checked"]) else 0], device=dev)
+        if world > 1:
+            dist.broadcast(need_first, 0)
+        if int(need_first.item()):
+            all_layers = mod.layers
+            mod.layers = torch.nn.ModuleList(list(all_layers)[:1])
+            s1, z1 = mod(s_d, z_d, m_d, pm_d)
+            mod.layers = all_layers
+            if rank == 0:
+                first = parity_against_fixture(n, 1, args.pad_frac, s1, z1, tol / 4)
+                if first["checked"]:
+                    first["note"] = f"the fixture holds one block only: first block of the {nb}-block trunk, untimed extra pass"
+                    parity = first
+            del s1, z1
+    if rank == 0:
+        parity["device_status"] = _lib.device_status()
 
     # ---- end to end through the module API with host buffers ----
     e2e = None

@@ -351,6 +351,24 @@ int b200pf_peer_scatter_strided(const void* send, const unsigned long long* recv
 /* All-gather form of the same: `send` is ONE block, written to slot `rank` of every rank's receive buffer. */
 int b200pf_peer_broadcast(const void* send, const unsigned long long* recv_ptrs, long long block_bytes,
                           int rank, int world, void* stream);
+/* The exchanges with the barrier that normally follows them built in: the CTA that finishes last signals the
+ * peers and waits for theirs, so one launch does what b200pf_peer_scatter + b200pf_peer_barrier do in two.
+ * `channel` (0..7) picks the device-side CTA counter: exchanges that may run at the same time on one device
+ * (different streams) must use different channels, and their signal pads and generations are per channel too. */
+typedef struct b200pf_peer_sync {
+    const unsigned long long* pad_ptrs;   /* HOST array: the world signal pads as mapped in this process */
+    unsigned int generation;              /* grows by one per barrier of this channel, on every rank */
+    long long    timeout_ns;              /* the wait gives up after this long: status bit 4, no trap */
+    int          channel;
+} b200pf_peer_sync;
+int b200pf_peer_scatter_sync(const void* send, const unsigned long long* recv_ptrs, long long block_bytes,
+                             int rank, int world, const b200pf_peer_sync* sync, void* stream);
+int b200pf_peer_broadcast_sync(const void* send, const unsigned long long* recv_ptrs, long long block_bytes,
+                               int rank, int world, const b200pf_peer_sync* sync, void* stream);
+int b200pf_peer_scatter_strided_sync(const void* send, const unsigned long long* recv_ptrs, long long chunk_bytes, int chunks,
+                                     long long src_block_stride, long long src_chunk_stride,
+                                     long long dst_slot_stride, long long dst_chunk_stride, int rank, int world,
+                                     const b200pf_peer_sync* sync, void* stream);
 /* Cross-rank barrier of the peer-write exchanges (no counterpart in the reference: its cards never wait on
  * each other; the nearest thing is the job lease that expires when a worker stops reporting,
  * tt_bio/distributed.py:22, 214).  pad_ptrs is a HOST array of the world signal pads as mapped in this process

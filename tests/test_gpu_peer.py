@@ -124,3 +124,45 @@ def test_strided_scatter_is_the_row_column_transposition(dev, world, nr, c):
     torch.cuda.synchronize()
     for t in range(world):
         assert torch.equal(back[t], rows[t]), t
+
+
+def test_exchanges_with_built_in_barrier(dev):
+    """The `_sync` forms on one device: every rank's launch is issued in turn, with the peers' signals already in
+    its pad (a kernel that waited for a later launch of the same stream would only run into its limit), so each
+    kernel's tail finds them at once.  Checked: the data (bit-exact), the signals each launch leaves in the peers'
+    pads, a clean status word, and that the CTA counter is ready for the next launch (two rounds)."""
+    from tt_boltz_b200 import _lib
+    from tt_boltz_b200._lib import PeerSync, call, ptr, stream
+    world, block_elems = 4, 8 * 1500
+    g = torch.Generator().manual_seed(3)
+    pads = [torch.zeros(16, dtype=torch.int32, device=dev) for _ in range(world)]
+    pad_ptrs = (C.c_ulonglong * world)(*[p.data_ptr() for p in pads])
+    for gen in (1, 2):
+        send = [torch.randint(-30000, 30000, (world, block_elems), generator=g, dtype=torch.int16).to(dev) for _ in range(world)]
+        recv = [torch.full((world, block_elems), -1, dtype=torch.int16, device=dev) for _ in range(world)]
+        ptrs = (C.c_ulonglong * world)(*[r.data_ptr() for r in recv])
+        for rank in range(world):
+            pads[rank].fill_(gen)                      # "every peer has arrived"
+            sync = PeerSync(pad_ptrs, gen, 50_000_000, 2)
+            if rank % 2 == 0:
+                call("b200pf_peer_scatter_sync", ptr(send[rank]), ptrs, block_elems * 2, rank, world, C.byref(sync), stream())
+            else:       # the strided form with contiguous blocks is the same exchange
+                call("b200pf_peer_scatter_strided_sync", ptr(send[rank]), ptrs, block_elems * 2, 1, block_elems * 2, block_elems * 2,
+                     block_elems * 2, block_elems * 2, rank, world, C.byref(sync), stream())
+        assert _lib.device_status() == 0
+        for t in range(world):
+            for src in range(world):
+                assert torch.equal(recv[t][src], send[src][t]), (gen, t, src)
+            assert all(int(pads[t][r]) == gen for r in range(world))
+    # all-gather form, and a missing peer: the tail gives up after its limit, status bit 4, context intact
+    x = torch.arange(8 * 64, dtype=torch.int16, device=dev)
+    out = [torch.zeros(2, 8 * 64, dtype=torch.int16, device=dev) for _ in range(2)]
+    ptrs = (C.c_ulonglong * 2)(*[o.data_ptr() for o in out])
+    pads2 = [torch.zeros(16, dtype=torch.int32, device=dev) for _ in range(2)]
+    pad_ptrs2 = (C.c_ulonglong * 2)(*[p.data_ptr() for p in pads2])
+    call("b200pf_peer_broadcast_sync", ptr(x), ptrs, 8 * 64 * 2, 0, 2, C.byref(PeerSync(pad_ptrs2, 1, 1_000_000, 3)), stream())
+    assert _lib.device_status() == 4
+    assert torch.equal(out[0][0], x) and torch.equal(out[1][0], x)
+    assert float(torch.ones(4, device=dev).sum()) == 4.0
+    with pytest.raises(RuntimeError):
+        call("b200pf_peer_scatter_sync", ptr(x), ptrs, 64, 0, 2, C.byref(PeerSync(pad_ptrs2, 2, 1_000_000, 9)), stream())   # channel out of range

@@ -24,6 +24,11 @@ class Planes(C.Structure):
                 ("cols", _i), ("nseg", _i), ("seg_is_k", _i)]
 
 
+class PeerSync(C.Structure):
+    """Mirror of ``b200pf_peer_sync``."""
+    _fields_ = [("pad_ptrs", C.POINTER(C.c_ulonglong)), ("generation", C.c_uint), ("timeout_ns", _ll), ("channel", _i)]
+
+
 class PlaneOut(C.Structure):
     """Mirror of ``b200pf_plane_out``."""
     _fields_ = [("ptr", _vp), ("plane_stride", _ll), ("group_stride", _ll), ("row_group", _i)]
@@ -65,6 +70,9 @@ SIGNATURES = {
     "b200pf_peer_broadcast": [_vp, C.POINTER(C.c_ulonglong), _ll, _i, _i, _vp],
     "b200pf_peer_scatter_strided": [_vp, C.POINTER(C.c_ulonglong), _ll, _i, _ll, _ll, _ll, _ll, _i, _i, _vp],
     "b200pf_peer_barrier": [C.POINTER(C.c_ulonglong), C.c_uint, _i, _i, _ll, _vp],
+    "b200pf_peer_scatter_sync": [_vp, C.POINTER(C.c_ulonglong), _ll, _i, _i, C.POINTER(PeerSync), _vp],
+    "b200pf_peer_broadcast_sync": [_vp, C.POINTER(C.c_ulonglong), _ll, _i, _i, C.POINTER(PeerSync), _vp],
+    "b200pf_peer_scatter_strided_sync": [_vp, C.POINTER(C.c_ulonglong), _ll, _i, _ll, _ll, _ll, _ll, _i, _i, C.POINTER(PeerSync), _vp],
     "b200pf_tri_mul_noalloc": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
 }
 _RESTYPES = {"b200pf_last_error": C.c_char_p, "b200pf_launch_count": _ll, "b200pf_mx_scale_bytes": _ll}

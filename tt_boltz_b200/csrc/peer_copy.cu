@@ -15,12 +15,72 @@ struct PeerPtrs {
     unsigned long long recv[PEER_MAX_RANKS];     // receive buffer of rank t as mapped on this device
 };
 
+// Cross-rank barrier on symmetric signal pads (one 32-bit slot per sender in every rank's pad), run by one warp.
+// Lane t tells rank t "rank `rank` has reached generation `gen`" with a system-scope release store into slot
+// `rank` of rank t's pad, then waits until slot t of its own pad shows that rank t has reached `gen` too.
+// Generations only grow, and a rank can be at most one barrier ahead of a peer that is still waiting, so the
+// test is "slot - gen >= 0" in wrap-around arithmetic.  After an exchange on the same stream it tells the
+// receivers that this rank's blocks have landed and holds this rank's consumers back until every sender's have.
+// The wait is bounded: after `limit_ns` without the peer's signal the lane ORs DEV_STATUS_PEER_TIMEOUT into the
+// device status word and returns.  Nothing traps; the context stays usable and the host reads the word.
+struct BarrierArgs {
+    PeerPtrs pads;
+    unsigned int gen;
+    int rank, world;         // world 0: no barrier
+    int channel;
+    unsigned long long limit_ns;
+    unsigned int* status;
+};
+__device__ __forceinline__ void peer_barrier_lane(const BarrierArgs& b, int t) {
+    if (t >= b.world) return;
+    __threadfence_system();
+    unsigned int* remote = reinterpret_cast<unsigned int*>(b.pads.recv[t]) + b.rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(b.gen) : "memory");
+    const unsigned int* mine = reinterpret_cast<const unsigned int*>(b.pads.recv[b.rank]) + t;
+    unsigned long long t0 = 0;
+    for (unsigned int spins = 0;; ++spins) {
+        unsigned int v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+        if ((int)(v - b.gen) >= 0) return;
+        if ((spins & 63u) == 63u) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (t0 == 0) t0 = now;
+            if (now - t0 > b.limit_ns) {
+                atomicOr(b.status, DEV_STATUS_PEER_TIMEOUT);
+                return;
+            }
+            __nanosleep(200);
+        }
+    }
+}
+__global__ void __launch_bounds__(32) peer_barrier_kernel(BarrierArgs b) { peer_barrier_lane(b, threadIdx.x); }
+
+// Tail of an exchange kernel that carries its own barrier (b.world > 0): every CTA makes its stores visible
+// system-wide and counts itself in; the CTA that completes the count resets it for the next launch and runs
+// the barrier, so the kernel ends when every peer's blocks have landed here.  One launch instead of two.
+constexpr int PEER_CHANNELS = 8;      // exchanges that may run at the same time on one device use different channels
+__device__ unsigned int g_exchange_ctas_done[PEER_CHANNELS];
+__device__ __forceinline__ void exchange_tail(const BarrierArgs& b) {
+    if (b.world <= 0) return;
+    __shared__ unsigned int is_last;
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int done = atomicAdd(&g_exchange_ctas_done[b.channel], 1u);
+        is_last = (done == gridDim.x - 1);
+        if (is_last) g_exchange_ctas_done[b.channel] = 0;   // the next launch on this channel starts after this one has ended
+    }
+    __syncthreads();
+    if (is_last && threadIdx.x < 32) peer_barrier_lane(b, threadIdx.x);
+}
+
 // Each thread moves UNROLL independent 16-byte pieces per step (all loads first, then all stores): NVLink stores
 // are posted, so what limits the rate is how many bytes a thread has in flight between its loads and stores.
 constexpr int PEER_UNROLL = 4;
 
 __global__ void __launch_bounds__(256)
-peer_scatter_kernel(const uint4* __restrict__ send, PeerPtrs peers, long long block_vec, int rank, int world) {
+peer_scatter_kernel(const uint4* __restrict__ send, PeerPtrs peers, long long block_vec, int rank, int world, BarrierArgs bar) {
     const long long total = block_vec * world;
     const long long stride = (long long)gridDim.x * blockDim.x;
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -44,6 +104,7 @@ peer_scatter_kernel(const uint4* __restrict__ send, PeerPtrs peers, long long bl
         uint4* d = reinterpret_cast<uint4*>(peers.recv[t]) + (long long)rank * block_vec + off;
         *d = __ldg(send + (long long)t * block_vec + off);
     }
+    exchange_tail(bar);
 }
 
 // All-to-all of blocks that are not contiguous on one or both sides: block t consists of `chunks` pieces of
@@ -55,7 +116,7 @@ struct StridedCopy {
     long long src_block, src_chunk, dst_slot, dst_chunk;
 };
 __global__ void __launch_bounds__(256)
-peer_scatter_strided_kernel(const uint4* __restrict__ send, PeerPtrs peers, StridedCopy c, int rank, int world) {
+peer_scatter_strided_kernel(const uint4* __restrict__ send, PeerPtrs peers, StridedCopy c, int rank, int world, BarrierArgs bar) {
     const unsigned int block_vec = c.chunks * c.chunk_vec;
     const unsigned long long total = (unsigned long long)block_vec * world;
     const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
@@ -79,11 +140,12 @@ peer_scatter_strided_kernel(const uint4* __restrict__ send, PeerPtrs peers, Stri
         for (int u = 0; u < PEER_UNROLL; ++u)
             if (dst[u]) *dst[u] = v[u];
     }
+    exchange_tail(bar);
 }
 
 // All-gather form: the one block of this rank goes to slot `rank` of every rank's receive buffer.
 __global__ void __launch_bounds__(256)
-peer_broadcast_kernel(const uint4* __restrict__ send, PeerPtrs peers, long long block_vec, int rank, int world) {
+peer_broadcast_kernel(const uint4* __restrict__ send, PeerPtrs peers, long long block_vec, int rank, int world, BarrierArgs bar) {
     const long long total = block_vec * world;
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
@@ -92,66 +154,45 @@ peer_broadcast_kernel(const uint4* __restrict__ send, PeerPtrs peers, long long 
         uint4* dst = reinterpret_cast<uint4*>(peers.recv[t]) + (long long)rank * block_vec + off;
         *dst = __ldg(send + off);
     }
-}
-
-// Cross-rank barrier on symmetric signal pads (one 32-bit slot per sender in every rank's pad), one warp.
-// Lane t tells rank t "rank `rank` has reached generation `gen`" with a system-scope release store into slot
-// `rank` of rank t's pad, then waits until slot t of its own pad shows that rank t has reached `gen` too.
-// Generations only grow, and a rank can be at most one barrier ahead of a peer that is still waiting, so the
-// test is "slot - gen >= 0" in wrap-around arithmetic.  Launched after an exchange kernel on the same stream,
-// it tells the receivers that this rank's blocks have landed (the exchange's stores are complete when it
-// starts) and holds this rank's consumers back until every sender's have.
-// The wait is bounded: after `limit_ns` without the peer's signal the lane ORs DEV_STATUS_PEER_TIMEOUT into the
-// device status word and returns.  Nothing traps; the context stays usable and the host reads the word.
-__global__ void __launch_bounds__(32)
-peer_barrier_kernel(PeerPtrs pads, unsigned int gen, int rank, int world, unsigned long long limit_ns, unsigned int* status) {
-    const int t = threadIdx.x;
-    if (t >= world) return;
-    __threadfence_system();
-    unsigned int* remote = reinterpret_cast<unsigned int*>(pads.recv[t]) + rank;
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(gen) : "memory");
-    const unsigned int* mine = reinterpret_cast<const unsigned int*>(pads.recv[rank]) + t;
-    unsigned long long t0 = 0;
-    for (unsigned int spins = 0;; ++spins) {
-        unsigned int v;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
-        if ((int)(v - gen) >= 0) return;
-        if ((spins & 63u) == 63u) {
-            unsigned long long now;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-            if (t0 == 0) t0 = now;
-            if (now - t0 > limit_ns) {
-                atomicOr(status, DEV_STATUS_PEER_TIMEOUT);
-                return;
-            }
-            __nanosleep(200);
-        }
-    }
+    exchange_tail(bar);
 }
 
 }  // namespace b200pf
 
 using namespace b200pf;
 
+static int fill_barrier(BarrierArgs* b, const b200pf_peer_sync* sync, int rank, int world, const char* who) {
+    *b = BarrierArgs{};
+    if (!sync) return B200PF_OK;
+    B200PF_REQUIRE(sync->pad_ptrs && sync->timeout_ns > 0 && sync->channel >= 0 && sync->channel < PEER_CHANNELS, B200PF_ERR_INVALID,
+                   "%s: the barrier needs signal pads, a positive limit and a channel below %d", who, PEER_CHANNELS);
+    for (int t = 0; t < world; ++t) {
+        B200PF_REQUIRE(sync->pad_ptrs[t] != 0 && sync->pad_ptrs[t] % 4 == 0, B200PF_ERR_INVALID, "%s: bad signal pad of rank %d", who, t);
+        b->pads.recv[t] = sync->pad_ptrs[t];
+    }
+    b->gen = sync->generation; b->rank = rank; b->world = world; b->channel = sync->channel;
+    b->limit_ns = (unsigned long long)sync->timeout_ns;
+    b->status = device_status_word();
+    B200PF_REQUIRE(b->status, B200PF_ERR_CUDA, "%s: no device status word", who);
+    return B200PF_OK;
+}
+
 extern "C" int b200pf_peer_barrier(const unsigned long long* pad_ptrs, unsigned int generation, int rank, int world,
                                    long long timeout_ns, void* stream) {
     B200PF_REQUIRE(pad_ptrs && world > 0 && world <= PEER_MAX_RANKS && rank >= 0 && rank < world, B200PF_ERR_INVALID,
                    "peer_barrier: bad argument (at most %d ranks)", PEER_MAX_RANKS);
     B200PF_REQUIRE(timeout_ns > 0, B200PF_ERR_INVALID, "peer_barrier: the wait must have a positive limit");
-    PeerPtrs p{};
-    for (int t = 0; t < world; ++t) {
-        B200PF_REQUIRE(pad_ptrs[t] != 0 && pad_ptrs[t] % 4 == 0, B200PF_ERR_INVALID, "peer_barrier: bad signal pad of rank %d", t);
-        p.recv[t] = pad_ptrs[t];
-    }
-    unsigned int* status = device_status_word();
-    B200PF_REQUIRE(status, B200PF_ERR_CUDA, "peer_barrier: no device status word");
-    peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(p, generation, rank, world, (unsigned long long)timeout_ns, status);
+    b200pf_peer_sync sync{pad_ptrs, generation, timeout_ns, 0};
+    BarrierArgs b;
+    int rc = fill_barrier(&b, &sync, rank, world, "peer_barrier");
+    if (rc != B200PF_OK) return rc;
+    peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(b);
     B200PF_LAUNCH_CHECK();
     return B200PF_OK;
 }
 
 static int peer_launch(bool broadcast, const void* send, const unsigned long long* recv_ptrs, long long block_bytes,
-                       int rank, int world, void* stream) {
+                       int rank, int world, const b200pf_peer_sync* sync, void* stream) {
     B200PF_REQUIRE(send && recv_ptrs && world > 0 && world <= PEER_MAX_RANKS && rank >= 0 && rank < world, B200PF_ERR_INVALID,
                    "peer_scatter: bad argument (at most %d ranks)", PEER_MAX_RANKS);
     B200PF_REQUIRE(block_bytes > 0 && block_bytes % 16 == 0 && aligned16(send), B200PF_ERR_INVALID,
@@ -161,6 +202,9 @@ static int peer_launch(bool broadcast, const void* send, const unsigned long lon
         B200PF_REQUIRE(recv_ptrs[t] != 0 && recv_ptrs[t] % 16 == 0, B200PF_ERR_INVALID, "peer_scatter: bad receive pointer of rank %d", t);
         p.recv[t] = recv_ptrs[t];
     }
+    BarrierArgs bar;
+    int rc = fill_barrier(&bar, sync, rank, world, "peer_scatter");
+    if (rc != B200PF_OK) return rc;
     int dev = 0, sms = 148;
     B200PF_CUDA(cudaGetDevice(&dev));
     B200PF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
@@ -168,16 +212,16 @@ static int peer_launch(bool broadcast, const void* send, const unsigned long lon
     long long blocks = (vec * world + 255) / 256;
     if (blocks > (long long)sms * 8) blocks = (long long)sms * 8;
     if (broadcast)
-        peer_broadcast_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(static_cast<const uint4*>(send), p, vec, rank, world);
+        peer_broadcast_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(static_cast<const uint4*>(send), p, vec, rank, world, bar);
     else
-        peer_scatter_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(static_cast<const uint4*>(send), p, vec, rank, world);
+        peer_scatter_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(static_cast<const uint4*>(send), p, vec, rank, world, bar);
     B200PF_LAUNCH_CHECK();
     return B200PF_OK;
 }
 
-extern "C" int b200pf_peer_scatter_strided(const void* send, const unsigned long long* recv_ptrs, long long chunk_bytes, int chunks,
-                                           long long src_block_stride, long long src_chunk_stride,
-                                           long long dst_slot_stride, long long dst_chunk_stride, int rank, int world, void* stream) {
+static int strided_launch(const void* send, const unsigned long long* recv_ptrs, long long chunk_bytes, int chunks,
+                          long long src_block_stride, long long src_chunk_stride, long long dst_slot_stride, long long dst_chunk_stride,
+                          int rank, int world, const b200pf_peer_sync* sync, void* stream) {
     B200PF_REQUIRE(send && recv_ptrs && world > 0 && world <= PEER_MAX_RANKS && rank >= 0 && rank < world, B200PF_ERR_INVALID,
                    "peer_scatter_strided: bad argument (at most %d ranks)", PEER_MAX_RANKS);
     B200PF_REQUIRE(chunks > 0 && chunk_bytes > 0 && chunk_bytes % 16 == 0 && aligned16(send) && src_block_stride % 16 == 0 &&
@@ -191,6 +235,9 @@ extern "C" int b200pf_peer_scatter_strided(const void* send, const unsigned long
         B200PF_REQUIRE(recv_ptrs[t] != 0 && recv_ptrs[t] % 16 == 0, B200PF_ERR_INVALID, "peer_scatter_strided: bad receive pointer of rank %d", t);
         p.recv[t] = recv_ptrs[t];
     }
+    BarrierArgs bar;
+    int rc = fill_barrier(&bar, sync, rank, world, "peer_scatter_strided");
+    if (rc != B200PF_OK) return rc;
     int dev = 0, sms = 148;
     B200PF_CUDA(cudaGetDevice(&dev));
     B200PF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
@@ -199,17 +246,45 @@ extern "C" int b200pf_peer_scatter_strided(const void* send, const unsigned long
     const long long vec = (long long)chunks * (chunk_bytes / 16) * world;
     long long blocks = (vec + 256 * PEER_UNROLL - 1) / (256 * PEER_UNROLL);
     if (blocks > (long long)sms * 8) blocks = (long long)sms * 8;
-    peer_scatter_strided_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(static_cast<const uint4*>(send), p, c, rank, world);
+    peer_scatter_strided_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(static_cast<const uint4*>(send), p, c, rank, world, bar);
     B200PF_LAUNCH_CHECK();
     return B200PF_OK;
 }
 
+extern "C" int b200pf_peer_scatter_strided(const void* send, const unsigned long long* recv_ptrs, long long chunk_bytes, int chunks,
+                                           long long src_block_stride, long long src_chunk_stride,
+                                           long long dst_slot_stride, long long dst_chunk_stride, int rank, int world, void* stream) {
+    return strided_launch(send, recv_ptrs, chunk_bytes, chunks, src_block_stride, src_chunk_stride, dst_slot_stride, dst_chunk_stride,
+                          rank, world, nullptr, stream);
+}
+
 extern "C" int b200pf_peer_scatter(const void* send, const unsigned long long* recv_ptrs, long long block_bytes,
                                    int rank, int world, void* stream) {
-    return peer_launch(false, send, recv_ptrs, block_bytes, rank, world, stream);
+    return peer_launch(false, send, recv_ptrs, block_bytes, rank, world, nullptr, stream);
 }
 
 extern "C" int b200pf_peer_broadcast(const void* send, const unsigned long long* recv_ptrs, long long block_bytes,
                                      int rank, int world, void* stream) {
-    return peer_launch(true, send, recv_ptrs, block_bytes, rank, world, stream);
+    return peer_launch(true, send, recv_ptrs, block_bytes, rank, world, nullptr, stream);
+}
+
+extern "C" int b200pf_peer_scatter_sync(const void* send, const unsigned long long* recv_ptrs, long long block_bytes,
+                                        int rank, int world, const b200pf_peer_sync* sync, void* stream) {
+    B200PF_REQUIRE(sync, B200PF_ERR_INVALID, "peer_scatter_sync: the barrier description is missing");
+    return peer_launch(false, send, recv_ptrs, block_bytes, rank, world, sync, stream);
+}
+
+extern "C" int b200pf_peer_broadcast_sync(const void* send, const unsigned long long* recv_ptrs, long long block_bytes,
+                                          int rank, int world, const b200pf_peer_sync* sync, void* stream) {
+    B200PF_REQUIRE(sync, B200PF_ERR_INVALID, "peer_broadcast_sync: the barrier description is missing");
+    return peer_launch(true, send, recv_ptrs, block_bytes, rank, world, sync, stream);
+}
+
+extern "C" int b200pf_peer_scatter_strided_sync(const void* send, const unsigned long long* recv_ptrs, long long chunk_bytes, int chunks,
+                                                long long src_block_stride, long long src_chunk_stride,
+                                                long long dst_slot_stride, long long dst_chunk_stride, int rank, int world,
+                                                const b200pf_peer_sync* sync, void* stream) {
+    B200PF_REQUIRE(sync, B200PF_ERR_INVALID, "peer_scatter_strided_sync: the barrier description is missing");
+    return strided_launch(send, recv_ptrs, chunk_bytes, chunks, src_block_stride, src_chunk_stride, dst_slot_stride, dst_chunk_stride,
+                          rank, world, sync, stream);
 }

@@ -28,7 +28,7 @@ import torch.distributed as dist
 from torch import nn
 
 from . import ops, weights
-from ._lib import PlaneOut, Planes, call, device_status, ptr, stream
+from ._lib import PeerSync, PlaneOut, Planes, call, device_status, ptr, stream
 from .pairformer import B200PairformerLayer, _mask_u8
 
 C_Z = 128
@@ -47,8 +47,8 @@ def all_gather_cat(x: torch.Tensor, group=None, tag: Optional[str] = None, chann
         peer = _peer_buffers(tag, world * x.numel(), x.dtype, x.device, group)
         if peer is not None:
             recv, hdl, ptrs = peer
-            call("b200pf_peer_broadcast", ptr(x), ptrs, nbytes, dist.get_rank(group), world, stream())
-            peer_barrier(x.device, group, channel)
+            call("b200pf_peer_broadcast_sync", ptr(x), ptrs, nbytes, dist.get_rank(group), world,
+                 C.byref(_next_sync(x.device, group, channel)), stream())
             return recv.view((world,) + tuple(x.shape))
     out = torch.empty((world,) + tuple(x.shape), dtype=x.dtype, device=x.device)
     if x.is_cuda:
@@ -72,14 +72,12 @@ _BARRIER_TIMEOUT_MS = int(os.environ.get("B200PF_BARRIER_TIMEOUT_MS", "20000"))
 _BARRIERS: Dict[tuple, list] = {}
 
 
-def peer_barrier(device: torch.device, group=None, channel: int = 0) -> None:
-    """Enqueue the library's own cross-rank barrier (``b200pf_peer_barrier``) on the current stream.
-
-    The signal pads are one small symmetric allocation per (device, group, channel), zeroed before the first use;
-    the generation counter lives on the host and grows by one per call, the same on every rank because every rank
-    enqueues the same sequence of exchanges ON ONE STREAM.  Exchanges enqueued on another stream (the single
-    track's side stream) may interleave differently with them on different ranks, so they use a channel, i.e.
-    pads and a counter, of their own."""
+def _barrier_state(device: torch.device, group, channel: int) -> list:
+    """[pad, handle, pad pointers, generation] of one barrier channel: a small symmetric allocation per (device,
+    group, channel), zeroed before the first use.  The generation counter lives on the host and grows by one per
+    barrier, the same on every rank because every rank enqueues the same sequence of exchanges ON ONE STREAM.
+    Exchanges enqueued on another stream (the single track's side stream) may interleave differently with them on
+    different ranks, so they use a channel, i.e. pads and a counter, of their own."""
     key = (device.index, id(group), channel)
     st = _BARRIERS.get(key)
     if st is None:
@@ -92,6 +90,19 @@ def peer_barrier(device: torch.device, group=None, channel: int = 0) -> None:
         dist.barrier(group=group)                      # every pad is zero before any rank signals
         ptrs = (C.c_ulonglong * hdl.world_size)(*[int(p) for p in hdl.buffer_ptrs])
         st = _BARRIERS[key] = [pad, hdl, ptrs, 0]
+    return st
+
+
+def _next_sync(device: torch.device, group, channel: int) -> PeerSync:
+    """The barrier description for the next exchange of this channel (``b200pf_peer_*_sync``)."""
+    st = _barrier_state(device, group, channel)
+    st[3] = (st[3] + 1) & 0xFFFFFFFF
+    return PeerSync(st[2], st[3], _BARRIER_TIMEOUT_MS * 1000000, channel)
+
+
+def peer_barrier(device: torch.device, group=None, channel: int = 0) -> None:
+    """Enqueue the library's own cross-rank barrier alone (``b200pf_peer_barrier``) on the current stream."""
+    st = _barrier_state(device, group, channel)
     st[3] = (st[3] + 1) & 0xFFFFFFFF
     call("b200pf_peer_barrier", st[2], st[3], dist.get_rank(group), dist.get_world_size(group),
          _BARRIER_TIMEOUT_MS * 1000000, stream())
@@ -125,12 +136,13 @@ def _peer_buffers(tag: str, numel: int, dtype: torch.dtype, device: torch.device
         return None
 
 
-def all_to_all_blocks(send: torch.Tensor, group=None, tag: Optional[str] = None) -> torch.Tensor:
+def all_to_all_blocks(send: torch.Tensor, group=None, tag: Optional[str] = None, barrier: bool = True) -> torch.Tensor:
     """send[t] goes to rank t; recv[s] is what rank s sent to this rank.
 
     On CUDA with a ``tag`` (one per call site) every rank writes its blocks straight into the destination
     ranks' symmetric receive buffers over NVLink with one kernel (``b200pf_peer_scatter``), followed by one
-    device-side barrier that says every block has landed.  Each call site alternates between two receive
+    device-side barrier at the end of the same kernel that says every block has landed (``barrier=False`` leaves it
+    to a following exchange of the same group of calls).  Each call site alternates between two receive
     buffers: a rank can only pass the barrier of exchange k+1 after every rank has enqueued it, i.e. after
     their consumers of exchange k in stream order, so exchange k+2 may overwrite buffer k without another
     barrier.  The returned tensor is the receive buffer: valid until the second-next exchange of the same
@@ -142,8 +154,11 @@ def all_to_all_blocks(send: torch.Tensor, group=None, tag: Optional[str] = None)
         peer = _peer_buffers(tag, send.numel(), send.dtype, send.device, group)
         if peer is not None:
             recv, hdl, ptrs = peer
-            call("b200pf_peer_scatter", ptr(send), ptrs, send.numel() * send.element_size() // world, rank, world, stream())
-            peer_barrier(send.device, group)
+            nbytes = send.numel() * send.element_size() // world
+            if barrier:
+                call("b200pf_peer_scatter_sync", ptr(send), ptrs, nbytes, rank, world, C.byref(_next_sync(send.device, group, 0)), stream())
+            else:       # the caller follows up with another exchange that carries the barrier for both
+                call("b200pf_peer_scatter", ptr(send), ptrs, nbytes, rank, world, stream())
             return recv.view(send.shape)
     recv = torch.empty_like(send)
     dist.all_to_all_single(recv, send, group=group)
@@ -152,8 +167,8 @@ def all_to_all_blocks(send: torch.Tensor, group=None, tag: Optional[str] = None)
 
 def _strided_exchange(tag: str, src: torch.Tensor, out_numel: int, chunk_elems: int, chunks: int, src_block: int, src_chunk: int,
                       dst_slot: int, dst_chunk: int, group):
-    """One launch of b200pf_peer_scatter_strided (strides in ELEMENTS of src) into the symmetric receive buffer of
-    ``tag``, then the barrier; None when peer copies are off or unavailable."""
+    """One launch of b200pf_peer_scatter_strided_sync (strides in ELEMENTS of src; the barrier is the kernel's tail)
+    into the symmetric receive buffer of ``tag``; None when peer copies are off or unavailable."""
     if not (src.is_cuda and _PEER_COPY["enabled"]):
         return None
     peer = _peer_buffers(tag, out_numel, src.dtype, src.device, group)
@@ -161,9 +176,8 @@ def _strided_exchange(tag: str, src: torch.Tensor, out_numel: int, chunk_elems: 
         return None
     recv, _, ptrs = peer
     e = src.element_size()
-    call("b200pf_peer_scatter_strided", ptr(src), ptrs, chunk_elems * e, chunks, src_block * e, src_chunk * e, dst_slot * e, dst_chunk * e,
-         dist.get_rank(group), dist.get_world_size(group), stream())
-    peer_barrier(src.device, group)
+    call("b200pf_peer_scatter_strided_sync", ptr(src), ptrs, chunk_elems * e, chunks, src_block * e, src_chunk * e, dst_slot * e, dst_chunk * e,
+         dist.get_rank(group), dist.get_world_size(group), C.byref(_next_sync(src.device, group, 0)), stream())
     return recv
 
 
@@ -276,24 +290,31 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
             pitch = (pcol + 15) // 16 * 16
             lib = _lib_handle()
             sf_all, sf_blk = lib.b200pf_mx_scale_bytes(prow, pcol, C_Z), lib.b200pf_mx_scale_bytes(prow, pcol, cl)
-            a_loc, b_loc = (torch.empty(C_Z * prow * pitch, dtype=torch.uint8, device=dev) for _ in range(2))
+            ab_loc = torch.empty(2 * C_Z * prow * pitch, dtype=torch.uint8, device=dev)
+            a_loc, b_loc = ab_loc[:C_Z * prow * pitch], ab_loc[C_Z * prow * pitch:]
             sa_loc, sb_loc = (torch.zeros(sf_all, dtype=torch.uint8, device=dev) for _ in range(2))
             call("b200pf_trimul_producer_mx", ptr(z_loc), ptr(mask_loc), ptr(w["ln_in_gamma"]), ptr(w["ln_in_beta"]), ptr(w["w_pg_tc"]),
                  ptr(a_loc), ptr(b_loc), ptr(sa_loc), ptr(sb_loc), prow * pitch, pitch, nr, n, incoming, st)
-            a_ch = all_to_all_blocks(a_loc.view(world, -1), group, "trimul_a8")
-            b_ch = all_to_all_blocks(b_loc.view(world, -1), group, "trimul_b8")
-            sa_ch = all_to_all_blocks(sa_loc.view(world, sf_blk), group, "trimul_sa")   # [src][cl][kgroups][row blocks][512]
-            sb_ch = all_to_all_blocks(sb_loc.view(world, sf_blk), group, "trimul_sb")
+            sa_ch = all_to_all_blocks(sa_loc.view(world, sf_blk), group, "trimul_sa", barrier=False)   # [src][cl][kgroups][row blocks][512]
+            sb_ch = all_to_all_blocks(sb_loc.view(world, sf_blk), group, "trimul_sb", barrier=False)
             scales, variant = (ptr(sa_ch), ptr(sb_ch)), 2
         else:
-            a_loc, b_loc = _bf16(C_Z * prow * pitch, dev), _bf16(C_Z * prow * pitch, dev)
+            ab_loc = _bf16(2 * C_Z * prow * pitch, dev)
+            a_loc, b_loc = ab_loc[:C_Z * prow * pitch], ab_loc[C_Z * prow * pitch:]
             oa, ob = PlaneOut(ptr(a_loc), prow * pitch, 0, 0), PlaneOut(ptr(b_loc), prow * pitch, 0, 0)
             call("b200pf_trimul_producer", ptr(z_loc), ptr(mask_loc), *ops.trimul_producer_weights(w, layer.row_impl),
                  C.byref(oa), C.byref(ob), pitch, nr, n, incoming, 0, layer.row_impl, st)
+            scales, variant = (None, None), layer.contract_variant
+        # ONE exchange for both operands: block t = (a planes of rank t's channels | b planes of rank t's channels),
+        # received as [src][a | b][cl][prow][pitch]; its barrier also covers the scale blocks sent just before
+        blk = cl * prow * pitch
+        ab_ch = _strided_exchange("trimul_ab", ab_loc, 2 * world * blk, blk, 2, blk, C_Z * prow * pitch, 2 * blk, blk, group)
+        if ab_ch is not None:
+            a_ch, b_ch, seg = ab_ch, ab_ch[blk:], 2 * blk
+        else:
             a_ch = all_to_all_blocks(a_loc.view(world, -1), group, "trimul_a")           # [src][cl][prow][pitch]
             b_ch = all_to_all_blocks(b_loc.view(world, -1), group, "trimul_b")
-            scales, variant = (None, None), layer.contract_variant
-        seg = cl * prow * pitch
+            seg = blk
         # outgoing: the source rank owns a block of ROWS of the operand; incoming: a block of the contraction index
         pa = Planes(ptr(a_ch), prow * pitch, seg, pitch, prow, pcol, world, incoming)
         pb = Planes(ptr(b_ch), prow * pitch, seg, pitch, prow, pcol, world, incoming)
@@ -303,7 +324,7 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
         if side is not None:
             side.before_z_write()          # the previous block's pair-bias projection has read z
         ops.trimul_epilogue(z_loc, x_loc, nr * pn, pn, w, nr, n, layer.row_impl)
-        del a_loc, b_loc, a_ch, b_ch
+        del ab_loc, a_loc, b_loc, ab_ch, a_ch, b_ch
     del x_send, x_loc
 
     # ---- triangle attention, starting node (lines = local rows) ---------------------------------

@@ -122,11 +122,20 @@ def chain_block_mask(n: int, n_chains: int = 3, n_pad: int = 0, seed: int = 2,
 def sampled_fixture_errors(fixture, blocks: int, s_out: torch.Tensor, z_out: torch.Tensor) -> Tuple[float, float]:
     """rel-L2 of (s_out [N, c_s], z_out [N, N, c_z]) against a sampled full-size fixture (an ``np.load`` of a file
     written by tests/golden/make_sampled_trunk.py) after ``blocks`` blocks: z over the fixture's sampled positions,
-    s over the whole tensor.  Works on any device; returns (rel_l2_z, rel_l2_s)."""
+    s over the whole tensor; positions of masked tokens (the fixture's ``mask``) are left out, the reference does
+    not define them.  Works on any device; returns (rel_l2_z, rel_l2_s)."""
+    n, c = z_out.shape[0], z_out.shape[-1]
     idx = torch.from_numpy(fixture["index"]).to(z_out.device)
     z_ref = torch.from_numpy(fixture[f"z_samples_{blocks}"]).to(z_out.device).double()
     s_ref = torch.from_numpy(fixture[f"s_{blocks}"]).to(s_out.device).double()
     z_got = z_out.reshape(-1)[idx].double()
+    s_got = s_out.double()
+    if "mask" in getattr(fixture, "files", fixture):
+        m = torch.from_numpy(fixture["mask"]).to(z_out.device) != 0
+        if not bool(m.all()):
+            ok = m[idx // (n * c)] & m[(idx // c) % n]
+            z_got, z_ref = z_got[ok], z_ref[ok]
+            s_got, s_ref = s_got[m.to(s_out.device)], s_ref[m.to(s_out.device)]
     rz = float((z_got - z_ref).norm() / z_ref.norm())
-    rs = float((s_out.double() - s_ref).norm() / s_ref.norm())
+    rs = float((s_got - s_ref).norm() / s_ref.norm())
     return rz, rs
