@@ -86,7 +86,8 @@ def trimul_epilogue(z, x, plane_stride, pitch, w, rows, n, impl: int) -> None:
 
 
 def tri_mul_bf16(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Tensor], ws: Workspace,
-                 incoming: bool, contract_variant: int = 0, row_impl: int = 0) -> None:
+                 incoming: bool, contract_variant: int = 0, row_impl: int = 0, before_z_write=None) -> None:
+    """``before_z_write`` is called (if given) right before the first kernel that writes z, the epilogue."""
     n = z.shape[0]
     a, b, x = ws.buf[0], ws.buf[1], ws.buf[2]
     st = stream()
@@ -98,11 +99,13 @@ def tri_mul_bf16(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Tens
     pb = Planes(ptr(b), ws.plane_stride, 0, ws.pitch, n, n, 1, 0)
     call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), None, None, ptr(x), ws.plane_stride, ws.pitch,
          0, 0, C_Z, contract_variant, st)
+    if before_z_write is not None:
+        before_z_write()
     trimul_epilogue(z, x, ws.plane_stride, ws.pitch, w, n, n, row_impl)
 
 
 def tri_mul_mxfp8(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Tensor], ws: Workspace,
-                  incoming: bool, contract_variant: int = 2) -> None:
+                  incoming: bool, contract_variant: int = 2, before_z_write=None) -> None:
     """Triangle multiplication with MXFP8 operands (e4m3 values, e8m0 scale per 32 along k).
 
     contract_variant 2 = block-scaled tcgen05 contraction; 0 / 1 = expand the operands to bf16
@@ -129,6 +132,8 @@ def tri_mul_mxfp8(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Ten
         pb = Planes(ptr(b), ws.plane_stride, 0, ws.pitch, n, n, 1, 0)
         call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), None, None, ptr(x), ws.plane_stride, ws.pitch,
              0, 0, C_Z, contract_variant, st)
+    if before_z_write is not None:
+        before_z_write()
     trimul_epilogue(z, x, ws.plane_stride, ws.pitch, w, n, n, 0)
 
 
@@ -316,9 +321,13 @@ def single_track_finish(s: torch.Tensor, og_all: torch.Tensor, w_att: Dict[str, 
 
 def single_track(s: torch.Tensor, z: torch.Tensor, tok_mask_u8: torch.Tensor, w_norm: Dict[str, torch.Tensor],
                  w_att: Dict[str, torch.Tensor], w_trans: Dict[str, torch.Tensor], num_heads: int,
-                 fused: Optional[Dict[str, torch.Tensor]] = None) -> None:
-    """s += AttentionPairBias(LN(s), z); s += Transition(s) in fp32 (tt_bio/reference.py:906-912)."""
+                 fused: Optional[Dict[str, torch.Tensor]] = None, after_z_read=None) -> None:
+    """s += AttentionPairBias(LN(s), z); s += Transition(s) in fp32 (tt_bio/reference.py:906-912).
+    The pair-bias projection, the single track's only read of z, comes first; ``after_z_read`` is called behind it."""
     if fused is None:
         fused = pack_single_track(w_att, w_trans)
-    og = single_track_local(s, z, tok_mask_u8, w_norm, w_att, fused, num_heads)
+    bias = pair_bias_heads(z, w_att)
+    if after_z_read is not None:
+        after_z_read()
+    og = single_track_local(s, z, tok_mask_u8, w_norm, w_att, fused, num_heads, 0, bias)
     single_track_finish(s, og, w_att, w_trans, fused)

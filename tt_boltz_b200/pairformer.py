@@ -28,6 +28,7 @@ or "fp32" (un-fused fp32 kernels, the validation tier).
 """
 from __future__ import annotations
 
+import os
 import re
 from typing import Dict, Optional, Tuple
 
@@ -52,6 +53,33 @@ def _mask_u8(m: Optional[torch.Tensor], shape, device) -> torch.Tensor:
     if m is None:
         return torch.ones(shape, dtype=torch.uint8, device=device)
     return (m.reshape(shape) != 0).to(device=device, dtype=torch.uint8).contiguous()
+
+
+class SideTrack:
+    """The stream the single track runs on, beside the pair track.
+
+    The single track of block b needs z after block b's pair transition and s after block b-1, and nothing in the
+    pair track ever reads s: so it can run on a stream of its own, under the next block's pair kernels (and, in the
+    sharded trunk, under its exchanges, which leave most SMs idle).  Its one read of z, the pair-bias projection,
+    has to be over before the next block first writes z: ``bias_read`` is the event the pair stream waits for
+    at that point."""
+
+    def __init__(self, device: torch.device) -> None:
+        self.stream = torch.cuda.Stream(device)
+        self.bias_read: Optional[torch.cuda.Event] = None
+
+    def mark_z_read(self) -> None:
+        self.bias_read = torch.cuda.Event()
+        self.bias_read.record()
+
+    def before_z_write(self) -> None:
+        if self.bias_read is not None:
+            torch.cuda.current_stream().wait_event(self.bias_read)
+            self.bias_read = None
+
+    def join(self) -> None:
+        torch.cuda.current_stream().wait_stream(self.stream)
+        self.bias_read = None
 
 
 class B200PairformerLayer(nn.Module):
@@ -106,28 +134,40 @@ class B200PairformerLayer(nn.Module):
         return pk
 
     def forward_inplace(self, s: Optional[torch.Tensor], z: torch.Tensor, tok_mask_u8: Optional[torch.Tensor],
-                        masks: ops.PairMasks, ws: Optional[ops.Workspace]) -> None:
-        """Update fp32 working copies z [N,N,128] and s [N,c_s] in place."""
+                        masks: ops.PairMasks, ws: Optional[ops.Workspace], side: Optional["SideTrack"] = None) -> None:
+        """Update fp32 working copies z [N,N,128] and s [N,c_s] in place.  With a ``side`` track the update of s is
+        only enqueued on its stream (the caller joins it before reading s)."""
         pk = self._pack(z.device)
+        wait_bias = side.before_z_write if side is not None else None
         if self.fused:
             if self.precision == "mxfp8":
-                ops.tri_mul_mxfp8(z, masks.pm, pk["tri_mul_out"], ws, False, self.mx_contract_variant)
+                ops.tri_mul_mxfp8(z, masks.pm, pk["tri_mul_out"], ws, False, self.mx_contract_variant, wait_bias)
                 ops.tri_mul_mxfp8(z, masks.pm, pk["tri_mul_in"], ws, True, self.mx_contract_variant)
             else:
-                ops.tri_mul_bf16(z, masks.pm, pk["tri_mul_out"], ws, False, self.contract_variant, self.row_impl)
+                ops.tri_mul_bf16(z, masks.pm, pk["tri_mul_out"], ws, False, self.contract_variant, self.row_impl, wait_bias)
                 ops.tri_mul_bf16(z, masks.pm, pk["tri_mul_in"], ws, True, self.contract_variant, self.row_impl)
             ops.tri_att_bf16(z, masks, pk["tri_att_start"], ws, False, self.attention_core, self.lines_per_cta, self.row_impl)
             ops.tri_att_bf16(z, masks, pk["tri_att_end"], ws, True, self.attention_core, self.lines_per_cta, self.row_impl)
             ops.transition_z_bf16(z, pk["transition_z"], self.row_impl)
         else:
+            if side is not None:
+                side.before_z_write()
             ops.tri_mul_f32(z, masks.pm, pk["tri_mul_out"], False)
             ops.tri_mul_f32(z, masks.pm, pk["tri_mul_in"], True)
             ops.tri_att_f32(z, masks.pm, pk["tri_att_start"], False)
             ops.tri_att_f32(z, masks.pm, pk["tri_att_end"], True)
             ops.transition_f32(z, pk["transition_z"])
         if self.with_s and s is not None:
-            ops.single_track(s, z, tok_mask_u8, pk["pre_norm_s"], pk["attention"], pk["transition_s"], self.num_heads,
-                             pk["s_fused"])
+            if side is None:
+                ops.single_track(s, z, tok_mask_u8, pk["pre_norm_s"], pk["attention"], pk["transition_s"], self.num_heads,
+                                 pk["s_fused"])
+            else:
+                z_ready = torch.cuda.Event()
+                z_ready.record()
+                with torch.cuda.stream(side.stream):
+                    side.stream.wait_event(z_ready)
+                    ops.single_track(s, z, tok_mask_u8, pk["pre_norm_s"], pk["attention"], pk["transition_s"], self.num_heads,
+                                     pk["s_fused"], side.mark_z_read)
 
     def forward(self, s: Optional[torch.Tensor], z: torch.Tensor, mask: Optional[torch.Tensor] = None,
                 pair_mask: Optional[torch.Tensor] = None, chunk_size_tri_attn: Optional[int] = None,
@@ -187,8 +227,13 @@ def _run_layers(layers, s, z, mask, pair_mask, ws_cache: Optional[dict] = None):
                 if ws_cache is not None:
                     ws_cache.clear()
                     ws_cache[key] = ws
+        side = None
+        if sw is not None and len(layers) > 1 and os.environ.get("B200PF_SIDE_TRACK", "0") == "1":
+            side = SideTrack(z.device)
         for layer in layers:
-            layer.forward_inplace(sw, zw, tm, pm, ws)
+            layer.forward_inplace(sw, zw, tm, pm, ws, side)
+        if side is not None:
+            side.join()
     z_out = zw.unsqueeze(0).to(z.dtype)
     s_out = None if sw is None else sw.unsqueeze(0).to(s.dtype)
     return s_out, z_out

@@ -29,7 +29,7 @@ from torch import nn
 
 from . import ops, weights
 from ._lib import PeerSync, PlaneOut, Planes, call, device_status, ptr, stream
-from .pairformer import B200PairformerLayer, _mask_u8
+from .pairformer import B200PairformerLayer, SideTrack, _mask_u8
 
 C_Z = 128
 
@@ -232,28 +232,6 @@ def _bf16(n_elems: int, dev) -> torch.Tensor:
     return torch.empty(n_elems, dtype=torch.bfloat16, device=dev)
 
 
-class SideTrack:
-    """The stream the single track runs on, beside the pair track.
-
-    The single track of block b needs z after block b's pair transition and s after block b-1, and nothing in the
-    pair track ever reads s: so it runs on a stream of its own, under the next block's pair kernels and exchanges
-    (which at 8 GPUs leave most SMs idle).  Its one read of z, the pair-bias projection, has to be over before the
-    next block first writes z: ``bias_read`` is the event the pair stream waits for at that point."""
-
-    def __init__(self, device: torch.device) -> None:
-        self.stream = torch.cuda.Stream(device)
-        self.bias_read: Optional[torch.cuda.Event] = None
-
-    def before_z_write(self) -> None:
-        if self.bias_read is not None:
-            torch.cuda.current_stream().wait_event(self.bias_read)
-            self.bias_read = None
-
-    def join(self) -> None:
-        torch.cuda.current_stream().wait_stream(self.stream)
-        self.bias_read = None
-
-
 def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: torch.Tensor,
                   tok_mask_u8: Optional[torch.Tensor], masks: ops.PairMasks, rank: int, world: int,
                   group=None, side: Optional[SideTrack] = None) -> torch.Tensor:
@@ -358,8 +336,7 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
         def single_track(channel: int) -> None:
             bias = ops.pair_bias_heads(z_loc, pk["attention"])
             if side is not None:
-                side.bias_read = torch.cuda.Event()
-                side.bias_read.record()
+                side.mark_z_read()
             og_loc = ops.single_track_local(s, z_loc, tok_mask_u8, pk["pre_norm_s"], pk["attention"], pk["s_fused"],
                                             layer.num_heads, r0, bias)
             # output projection and transition are per row: run them on the local rows, then gather s
