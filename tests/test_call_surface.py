@@ -11,7 +11,7 @@ import pytest
 import torch
 
 from tt_boltz_b200 import (B200PairformerLayer, B200PairformerModule, B200PairformerNoSeqLayer,
-                           B200PairformerNoSeqModule, synthetic)
+                           B200PairformerNoSeqModule, B200RecyclingTrunk, synthetic)
 
 
 def _params(fn):
@@ -85,3 +85,15 @@ def test_no_cpu_path_on_any_surface():
         B200PairformerNoSeqLayer(128)(z, pm)
     with pytest.raises(RuntimeError, match="single track"):
         B200PairformerModule(1, 32, 4, 24, 16, True)(None, z.cuda() if torch.cuda.is_available() else z, None, pm)
+
+
+def test_recycling_trunk_carries_the_reference_key_names():
+    """tt_bio/boltz2.py:4961-4966 names the recycle parameters; `pairformer_module.` prefixes the stack (:5015)."""
+    trunk = B200RecyclingTrunk(B200PairformerModule(64, 32, 4, 24, 16, True))
+    keys = set(trunk.state_dict().keys())
+    for k in ("s_norm.weight", "s_norm.bias", "z_norm.weight", "z_norm.bias", "s_recycle.weight", "z_recycle.weight",
+              "pairformer_module.layers.63.transition_z.fc3.weight"):
+        assert k in keys, k
+    assert _params(B200RecyclingTrunk.forward) == ["self", "s_init", "z_init", "mask", "pair_mask", "recycling_steps", "pair_update"]
+    with pytest.raises(RuntimeError, match="CUDA"):
+        trunk(torch.zeros(1, 8, 384), torch.zeros(1, 8, 8, 128))

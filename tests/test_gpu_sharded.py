@@ -23,6 +23,13 @@ def _masks(n, kind):
     return synthetic.random_padding_mask(n, 0.05, seed=3) if kind == "random" else synthetic.tail_padding_mask(n, 13)
 
 
+def _recycle_weights():
+    g = torch.Generator().manual_seed(23)
+    return {"s_norm.weight": 1 + 0.1 * torch.randn(384, generator=g), "s_norm.bias": 0.1 * torch.randn(384, generator=g),
+            "z_norm.weight": 1 + 0.1 * torch.randn(128, generator=g), "z_norm.bias": 0.1 * torch.randn(128, generator=g),
+            "s_recycle.weight": 0.05 * torch.randn(384, 384, generator=g), "z_recycle.weight": 0.08 * torch.randn(128, 128, generator=g)}
+
+
 def _worker(rank, world, port, n, blocks, precision, mask_kind, out_q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
@@ -44,9 +51,17 @@ def _worker(rank, world, port, n, blocks, precision, mask_kind, out_q):
         torch.cuda.synchronize()
         status = _lib.device_status()
         same = bool(torch.equal(zr2[0], zo[0, rank * nr:(rank + 1) * nr]) and torch.equal(so2, so))
-        out_q.put((rank, so.cpu(), zo.cpu() if rank == 0 else None, status, None if same else "forward_rows differs from forward"))
+        # the resident recycling loop on the row shard (one recycle; identity-like recycle weights from a seed)
+        from tt_boltz_b200 import B200RecyclingTrunk
+        trunk = B200RecyclingTrunk(mod)
+        trunk.load_state_dict(_recycle_weights(), strict=False)
+        s_rec, z_rec = trunk(s.to(dev), z[:, rank * nr:(rank + 1) * nr].to(dev), m.to(dev), pm.to(dev), recycling_steps=1)
+        torch.cuda.synchronize()
+        status |= _lib.device_status()
+        out_q.put((rank, so.cpu(), zo.cpu() if rank == 0 else None, status, None if same else "forward_rows differs from forward",
+                   s_rec.cpu() if rank == 0 else None, z_rec.cpu() if rank == 0 else None))
     except Exception as e:  # noqa: BLE001
-        out_q.put((rank, None, None, -1, repr(e)))
+        out_q.put((rank, None, None, -1, repr(e), None, None))
     finally:
         dist.destroy_process_group()
 
@@ -85,7 +100,7 @@ def test_sharded_trunk_matches_oracle(world, precision, mask_kind, tol):
                 p.kill()
     assert len(res) == world, f"only {len(res)} of {world} ranks reported; errors: {[r[4] for r in res if r[4]]}"
     res.sort(key=lambda t: t[0])
-    for rank, so, zo, status, err in res:
+    for rank, so, zo, status, err, _, _ in res:
         assert err is None, f"rank {rank}: {err}"
         assert status == 0
     sd = synthetic.make_weights(blocks, seed=1, std=0.05, affine_jitter=0.2)
@@ -97,5 +112,18 @@ def test_sharded_trunk_matches_oracle(world, precision, mask_kind, tol):
     zo, so = res[0][2][0], res[0][1][0]
     assert float((zo[keep][:, keep] - zr[keep][:, keep]).norm() / zr[keep][:, keep].norm()) < tol
     assert float((so[keep] - sr[keep]).norm() / sr[keep].norm()) < tol
-    for rank, so_r, _, _, _ in res[1:]:
+    for rank, so_r, *_ in res[1:]:
         assert torch.equal(so_r[0], so), "s must stay replicated bit for bit"
+    # the recycling loop, rank 0's rows, against the same loop on the CPU
+    import torch.nn.functional as F
+    w = _recycle_weights()
+    with torch.no_grad():
+        s_c, z_c = torch.zeros_like(s[0]), torch.zeros_like(z[0])
+        for _ in range(2):
+            s_c = s[0] + F.layer_norm(s_c, (384,), w["s_norm.weight"], w["s_norm.bias"]) @ w["s_recycle.weight"].T
+            z_c = z[0] + F.layer_norm(z_c, (128,), w["z_norm.weight"], w["z_norm.bias"]) @ w["z_recycle.weight"].T
+            s_c, z_c = orc.pairformer_stack(s_c, z_c, m[0], pm[0], sd, blocks)
+    nr = n // world
+    s_rec, z_rec = res[0][5][0], res[0][6][0]
+    assert float((z_rec[keep[:nr]][:, keep] - z_c[:nr][keep[:nr]][:, keep]).norm() / z_c[:nr][keep[:nr]][:, keep].norm()) < tol
+    assert float((s_rec[keep] - s_c[keep]).norm() / s_c[keep].norm()) < tol

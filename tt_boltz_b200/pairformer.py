@@ -206,15 +206,25 @@ def _accept_backend_keys(state_dict, prefix, *_unused) -> None:
             state_dict[key[:m.end(1)] + "mha." + key[m.end(1):]] = state_dict.pop(key)
 
 
-def _run_layers(layers, s, z, mask, pair_mask, ws_cache: Optional[dict] = None):
+def _run_layers(layers, s, z, mask, pair_mask, ws_cache: Optional[dict] = None, inplace: bool = False):
+    """``inplace``: s [N, c_s] and z [N, N, C] are the caller's fp32 contiguous working tensors and are updated
+    where they are (nothing is returned); otherwise [1, ...] inputs are copied and new tensors returned."""
     if not z.is_cuda:
         raise RuntimeError("B200 Pairformer: inputs must be CUDA tensors (there is no CPU path)")
-    if z.dim() != 4 or z.shape[0] != 1 or z.shape[1] != z.shape[2]:
+    if inplace:
+        if z.dim() != 3 or z.shape[0] != z.shape[1] or z.dtype != torch.float32 or not z.is_contiguous():
+            raise RuntimeError("B200 Pairformer: the in-place form takes a contiguous fp32 z [N, N, C]")
+        if s is not None and (s.dtype != torch.float32 or not s.is_contiguous() or s.dim() != 2):
+            raise RuntimeError("B200 Pairformer: the in-place form takes a contiguous fp32 s [N, c_s]")
+    elif z.dim() != 4 or z.shape[0] != 1 or z.shape[1] != z.shape[2]:
         raise RuntimeError(f"B200 Pairformer: z must be [1, N, N, C], got {tuple(z.shape)}")
-    n = z.shape[1]
+    n = z.shape[-2]
     with torch.cuda.device(z.device), torch.no_grad():
-        zw = z[0].to(torch.float32).clone(memory_format=torch.contiguous_format)
-        sw = None if s is None else s[0].to(torch.float32).clone(memory_format=torch.contiguous_format)
+        if inplace:
+            zw, sw = z, s
+        else:
+            zw = z[0].to(torch.float32).clone(memory_format=torch.contiguous_format)
+            sw = None if s is None else s[0].to(torch.float32).clone(memory_format=torch.contiguous_format)
         pm = ops.PairMasks(_mask_u8(pair_mask, (n, n), z.device))
         tm = _mask_u8(mask, (n,), z.device) if s is not None else None
         ws = None
@@ -234,6 +244,8 @@ def _run_layers(layers, s, z, mask, pair_mask, ws_cache: Optional[dict] = None):
             layer.forward_inplace(sw, zw, tm, pm, ws, side)
         if side is not None:
             side.join()
+    if inplace:
+        return None
     z_out = zw.unsqueeze(0).to(z.dtype)
     s_out = None if sw is None else sw.unsqueeze(0).to(s.dtype)
     return s_out, z_out
@@ -308,6 +320,16 @@ class B200PairformerModule(nn.Module):
         self._ws_cache.clear()
         for layer in self.layers:
             layer.reset_static_cache()
+
+    def run_inplace(self, s: Optional[torch.Tensor], z: torch.Tensor, mask: Optional[torch.Tensor] = None,
+                    pair_mask: Optional[torch.Tensor] = None) -> None:
+        """The stack on the caller's resident fp32 tensors s [N, c_s] and z [N, N, C], updated in place: the form a
+        recycling loop uses to keep z on the device between passes (see ``B200RecyclingTrunk``)."""
+        if pair_mask is None and mask is not None:
+            m = mask.reshape(1, -1).to(z.device)
+            pair_mask = m[:, :, None] * m[:, None, :]
+        _run_layers(list(self.layers), s if self.transform_s else None, z, mask if self.transform_s else None, pair_mask,
+                    self._ws_cache, inplace=True)
 
     def forward(self, s: Optional[torch.Tensor], z: torch.Tensor, mask: Optional[torch.Tensor] = None,
                 pair_mask: Optional[torch.Tensor] = None, use_kernels: bool = False
