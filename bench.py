@@ -45,14 +45,10 @@ def kernel_work(n: int):
         "b200pf_trimul_producer": (2 * n * n * C * 512, 8 * e),
         "b200pf_trimul_producer_mx": (2 * n * n * C * 512, 6 * e + e // 16),
         "b200pf_trimul_contract": (2 * n ** 3 * C, 6 * e),
-        "b200pf_trimul_epilogue": (2 * n * n * C * 256, 10 * e),
         "b200pf_trimul_epilogue_tc": (2 * n * n * C * 256, 10 * e),
         "b200pf_triatt_producer": (2 * n * n * C * 516, 12 * e),
-        "b200pf_triatt_core": (4 * n ** 3 * C, 8 * e + 2 * 4 * n * n),
-        "b200pf_triatt_core_tc": (4 * n ** 3 * C, 8 * e + 2 * 4 * n * n),
         "b200pf_triatt_core_tc4": (4 * n ** 3 * C, 8 * e + 2 * 4 * n * n),
         "b200pf_triatt_epilogue": (2 * n * n * C * C, 12 * e),
-        "b200pf_transition_z": (6 * n * n * C * 4 * C, 8 * e),
         "b200pf_transition_z_tc": (6 * n * n * C * 4 * C, 8 * e),
         "b200pf_ln_proj_heads": (2 * n * n * C * 16, 4 * e + 4 * 16 * n * n),
         "b200pf_f32_sattention": (4 * n * n * 384, 4 * 16 * n * n),

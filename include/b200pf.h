@@ -38,9 +38,6 @@ int         b200pf_version(void);
 const char* b200pf_last_error(void);
 /* Number of kernels this library has launched in the calling process (for benchmarks). */
 long long   b200pf_launch_count(void);
-/* Profiling aid: copies and clears the cycle counters the tcgen05 attention core accumulates when
- * the environment variable B200PF_ATT_DEBUG is set (per-phase cycles of one softmax warp).  Synchronises. */
-int         b200pf_debug_counters(long long* host_out, int n);
 /* Reads (and clears) the device status word kernels set when a bounded wait runs out.
  * Synchronises `stream`.  0 = clean; bit 1 = an mbarrier wait inside a kernel ran out, bit 2 = an index
  * check failed, bit 4 = a cross-rank barrier gave up waiting for a peer. */
@@ -131,15 +128,11 @@ int b200pf_ln_proj_heads(const float* z, const float* gamma, const float* beta, 
 /* Triangle-multiplication producer: LN_in -> [p_in | g_in] projection -> p*sigmoid(g) -> mask
  * -> a/b written channel-major.  Replaces tt_bio/tenstorrent.py:410-452 (reference.py:456-464).
  *   z: fp32 [rows][n][128];  mask: [rows][n];
- *   impl 0 (tcgen05 kernel): the LayerNorm affine (ln_gamma, ln_beta: fp32 [128]) is applied in the
- *         kernel; w_pg bf16 [512][128] = 0.5 * (p_in rows of a, g_in rows of a, p_in rows of b, g_in
- *         rows of b), 128 each (the halves turn p*sigmoid(g) into p' + p'*tanh(g')); bias_pg unused.
- *   impl 1 (mma.sync cross-check): LN gain folded into w_pg, 8 chunks of 64 rows, chunk q = channels
- *         32*(q%4)..+31 of operand a (q < 4) or b (q >= 4): 32 p_in rows then 32 g_in rows;
- *         bias_pg: fp32 [512] LN-offset term in the same order; ln_gamma / ln_beta unused.
+ *   the LayerNorm affine (ln_gamma, ln_beta: fp32 [128]) is applied in the kernel;
+ *   w_pg bf16 [512][128] = 0.5 * (p_in rows of a, g_in rows of a, p_in rows of b, g_in rows of b),
+ *   128 each (the halves turn p*sigmoid(g) into p' + p'*tanh(g'));
  *   incoming == 0: a[d][r][k] = u_a[r][k][d]  (plane rows = local z rows, cols = k)
- *   incoming != 0: a[d][c][r] = u_a[r][c][d]  (plane rows = z columns, cols = local z rows)
- *   value_mode 0 = bf16 planes (the only mode built so far). */
+ *   incoming != 0: a[d][c][r] = u_a[r][c][d]  (plane rows = z columns, cols = local z rows) */
 typedef struct b200pf_plane_out {
     void*     ptr;            /* bf16 planes to write                                              */
     long long plane_stride;   /* elements between channels                                         */
@@ -150,9 +143,8 @@ typedef struct b200pf_plane_out {
  *   ptr[(row / row_group) * group_stride + d * plane_stride + (row % row_group) * pitch + col];
  * row groups let a rank lay its planes out as one contiguous block per destination rank. */
 int b200pf_trimul_producer(const float* z, const uint8_t* mask, const float* ln_gamma, const float* ln_beta,
-                           const float* bias_pg, const b200pf_bf16* w_pg, const b200pf_plane_out* a_out,
-                           const b200pf_plane_out* b_out, int pitch, int rows, int n, int incoming,
-                           int value_mode, int impl, void* stream);
+                           const b200pf_bf16* w_pg, const b200pf_plane_out* a_out, const b200pf_plane_out* b_out,
+                           int pitch, int rows, int n, int incoming, void* stream);
 
 /* Operand description for the contraction: element (seg, d, row, col) of an operand lives at
  * ptr[seg*seg_stride + d*plane_stride + row*pitch + col]. */
@@ -175,13 +167,12 @@ typedef struct b200pf_planes {
  * (i % x_row_group) * x_pitch + j, so that a rank that contracts a slice of the channels for every
  * row can send each owner of output rows one contiguous block.  Both operands may be segmented
  * along rows or along the contraction index (segments of 128-row multiples / 64-column multiples).
- * variant 0 = tcgen05 bf16, 1 = SIMT bf16
- * (debug cross-check of variant 0), 2 = tcgen05 block-scaled MXFP8: a / b are byte planes of e4m3
+ * variant 0 = tcgen05 bf16, 2 = tcgen05 block-scaled MXFP8: a / b are byte planes of e4m3
  * values (pitch, plane_stride, seg_stride in bytes, multiples of 16; k segments multiples of 128 columns)
  * and a_scales / b_scales their e8m0 scale blocks as written by b200pf_trimul_producer_mx; for a segmented
  * operand the scale buffers of the segments, each b200pf_mx_scale_bytes(rows, cols, channels) long for the
  * rows / cols of ONE segment, lie one behind the other in segment order (which is what an all-to-all of the
- * producer's channel-major scale blocks delivers).  The scales are ignored by variants 0, 1. */
+ * producer's channel-major scale blocks delivers).  The scales are ignored by variant 0. */
 int b200pf_trimul_contract(const b200pf_planes* a, const b200pf_planes* b,
                            const void* a_scales, const void* b_scales,
                            b200pf_bf16* x, long long x_plane_stride, int x_pitch,
@@ -189,7 +180,7 @@ int b200pf_trimul_contract(const b200pf_planes* a, const b200pf_planes* b,
                            int channels, int variant, void* stream);
 
 /* MXFP8 form of the producer (the counterpart of the reference's block-fp8 "fast" mode,
- * tt_bio/tenstorrent.py:178-181, 432-452): same computation as b200pf_trimul_producer impl 0, but
+ * tt_bio/tenstorrent.py:178-181, 432-452): same computation as b200pf_trimul_producer, but
  * a / b are quantised straight from fp32 to e4m3 with one e8m0 scale per 32 elements along the
  * contraction index (scale = smallest power of two with amax / scale <= 448).
  *   a_out / b_out: byte planes [128][plane rows][pitch] (pitch, plane_stride in bytes, multiples of 16);
@@ -201,22 +192,15 @@ int b200pf_trimul_producer_mx(const float* z, const uint8_t* mask, const float* 
                               const b200pf_bf16* w_pg, uint8_t* a_out, uint8_t* b_out, uint8_t* a_scales,
                               uint8_t* b_scales, long long plane_stride, int pitch, int rows, int n, int incoming,
                               void* stream);
-/* Expand MXFP8 planes to bf16 planes (exact).  Cross-check of variant 2 and a way to feed MXFP8
+/* Expand MXFP8 planes to bf16 planes (exact).  Cross-check of the block-scaled contraction and a way to feed MXFP8
  * operands to consumers that want bf16. */
 int b200pf_mx_dequant(const uint8_t* planes, const uint8_t* scales, b200pf_bf16* out, long long plane_stride,
                       int pitch, long long out_plane_stride, int out_pitch, int rows, int cols, int channels,
                       void* stream);
 
-/* Triangle-multiplication epilogue: z += (LN_out(x) W_pout^T) * sigmoid(LN_in(z) W_gout^T).
+/* Triangle-multiplication epilogue: z += (LN_out(x) W_pout^T) * sigmoid(LN_in(z) W_gout^T), on tcgen05.
  * Replaces tt_bio/tenstorrent.py:463-502 plus the residual add :1007-1011.
- * Reads z (pre-update) and writes z in place; x planes as written by the contraction.
- *   w_pout / w_gout: bf16 [128][128] with the LN_out / LN_in gain folded in;  bias_*: fp32 [128]. */
-int b200pf_trimul_epilogue(float* z, const b200pf_bf16* x, long long x_plane_stride, int x_pitch,
-                           const b200pf_bf16* w_pout, const b200pf_bf16* w_gout,
-                           const float* bias_pout, const float* bias_gout,
-                           int rows, int n, void* stream);
-
-/* The same epilogue on tcgen05 (production path).  x is multiplied RAW as an MN-major operand
+ * x planes as written by the contraction; x is multiplied RAW as an MN-major operand
  * straight from its planes; the LayerNorm over the channels of x is applied after the GEMM per
  * position (mean / rstd from the tile), the update leaves through TMA reduce-add into z.
  *   w_pout: bf16 [128][128] = 0.5 * W_pout * gamma_out;  wsum: fp32 [128] row sums of that bf16 matrix;
@@ -230,54 +214,33 @@ int b200pf_trimul_epilogue_tc(float* z, const b200pf_bf16* x, long long x_plane_
 /* Triangle-attention producer: LN -> [q|k|v|g] projection and the 4-head triangle bias.
  * Replaces tt_bio/tenstorrent.py:545-567, 603-614 (reference.py:331-341, 99-120).
  *   z is viewed as [rows][n][128] (a row shard, or a column shard stored [i][j_local][128]);
- *   impl 1 (mma.sync): w_qkvg bf16 [528][128] = q rows (scaled by log2(e)/sqrt(32)), k, v, g rows,
- *           the 4 bias rows (scaled by log2(e)), 12 zero rows, LN gain folded; bias_qkvg: fp32 [528];
- *   impl 0 (tcgen05): LN affine from ln_gamma / ln_beta; w_qkvg bf16 [512][128] = q (scaled), k,
- *           0.5 * g, v rows; w_bias_f32: fp32 [4][128] bias rows times log2(e); v is written
- *           transposed (vt_pitch > 0 required); bias_qkvg unused.
+ *   LN affine from ln_gamma / ln_beta (fp32 [128]); w_qkgv bf16 [512][128] = q rows (scaled by
+ *   log2(e)/sqrt(32)), k, 0.5 * g, v rows; w_bias_f32: fp32 [4][128] bias rows times log2(e);
  * A "line" is a row of the view (ending == 0, positions = its n columns) or a column of the view
  * (ending != 0, positions = its `rows` rows).  Outputs (bf16):
- *   q,k: impl 0 [line][pos][head][32], impl 1 [line][head][pos][32];  v: like q when vt_pitch == 0, else transposed
- *          [line][head][32][vt_pitch] (positions contiguous) as the tcgen05 attention core reads it;
+ *   q,k: [line][pos][head][32];  v: transposed, [line][head][32][vt_pitch] (positions contiguous), as the
+ *          attention core reads it;
  *   g:     sigmoid(gate) in the layout of the view, [rows][n][128];
  *   tri_bias: element (head, line, pos) at tri_bias[head*bias_hs + line*bias_qs + pos]: the bias
- *          of query `line` and key `pos` (for the ending node that is beta[row pos][col line]);
- *   impl: 0 = tcgen05 kernel, 1 = mma.sync cross-check (same weights for both). */
+ *          of query `line` and key `pos` (for the ending node that is beta[row pos][col line]). */
 int b200pf_triatt_producer(const float* z, const float* ln_gamma, const float* ln_beta, const float* w_bias_f32,
-                           const b200pf_bf16* w_qkvg, const float* bias_qkvg,
+                           const b200pf_bf16* w_qkgv,
                            b200pf_bf16* q, b200pf_bf16* k, b200pf_bf16* v, b200pf_bf16* g,
                            b200pf_bf16* tri_bias, long long bias_hs, long long bias_qs,
-                           int vt_pitch, int rows, int n, int ending, int impl, void* stream);
+                           int vt_pitch, int rows, int n, int ending, void* stream);
 
-/* Fused flash-style triangle attention: for each line and head, softmax(q k^T + mask + bias) v
+/* Fused flash-style triangle attention on tcgen05 / TMEM: for each line and head, softmax(q k^T + mask + bias) v
  * with online softmax in the log2 domain; logits never leave the SM.  Replaces the SDPA call at
  * tt_bio/tenstorrent.py:569-572 (reference.py:343-360, boltz2.py:790-810).
- *   n = queries = keys per line; q,k,v as written by the producer ([line][head][n][32]);
- *   bias element (head, query, key) at bias[head*bias_hs + query*bias_qs + key], key < bias_cols;
- *   mask byte for (line, key) = mask[line*mask_ls + key*mask_ks]; masked keys get -1e9;
- *   o element (line, pos, c) at o[line*o_line_stride + pos*o_pos_stride + c];
- *   lines_per_cta: 1, 2 or 4 lines share one fetch of each bias tile (0 = default). */
-int b200pf_triatt_core(const b200pf_bf16* q, const b200pf_bf16* k, const b200pf_bf16* v,
-                       const b200pf_bf16* bias, long long bias_hs, long long bias_qs, int bias_cols,
-                       const uint8_t* mask, long long mask_ls, long long mask_ks,
-                       b200pf_bf16* o, long long o_line_stride, long long o_pos_stride,
-                       int lines, int n, int lines_per_cta, void* stream);
-
-/* The same attention on tcgen05 / TMEM (the production core; b200pf_triatt_core is the mma.sync
- * cross-check).  S = Q K^T and O = P V run as tcgen05.mma with accumulators in TMEM, operands come
- * in by TMA, the bias tile is fetched once for two lines, softmax runs one thread per query row.
- *   q, k: [line][pos][head][32] (as written by the impl-0 producer); vt: v transposed
- *   [line][head][32][vt_pitch];  bias as above with bias_cols == n;
+ * S = Q K^T and O = P V run as tcgen05.mma with accumulators in TMEM, operands come in by TMA; four lines per
+ * CTA (four softmax groups in flight, one thread per query row), the bias tile fetched once for the four and
+ * multiplied in once per pair of lines; masked keys get -1e9 (times log2 e); the running output stays in TMEM and
+ * is rescaled only when a row maximum has grown by more than 2^8.
+ *   n = queries = keys per line;  q, k: [line][pos][head][32] (as written by the producer); vt: v transposed
+ *   [line][head][32][vt_pitch];  bias element (head, query, key) at bias[head*bias_hs + query*bias_qs + key];
  *   mask_lines: uint8 [lines][mask_pitch] (1 = attend), one contiguous row per line, mask_pitch a
- *   multiple of 16 covering n rounded up to 64 (the host transposes the mask for the ending node). */
-int b200pf_triatt_core_tc(const b200pf_bf16* q, const b200pf_bf16* k, const b200pf_bf16* vt, int vt_pitch,
-                          const b200pf_bf16* bias, long long bias_hs, long long bias_qs,
-                          const uint8_t* mask_lines, int mask_pitch,
-                          b200pf_bf16* o, long long o_line_stride, long long o_pos_stride,
-                          int lines, int n, void* stream);
-/* Same arguments and result; four lines per CTA (four softmax groups in flight, the bias tile
- * fetched and multiplied once per pair of lines, running output kept in TMEM with a rescale only
- * when a row maximum has grown by more than 2^8). */
+ *   multiple of 16 covering n rounded up to 64 (the host transposes the mask for the ending node);
+ *   o element (line, pos, c) at o[line*o_line_stride + pos*o_pos_stride + c]. */
 int b200pf_triatt_core_tc4(const b200pf_bf16* q, const b200pf_bf16* k, const b200pf_bf16* vt, int vt_pitch,
                            const b200pf_bf16* bias, long long bias_hs, long long bias_qs,
                            const uint8_t* mask_lines, int mask_pitch,
@@ -289,14 +252,9 @@ int b200pf_triatt_core_tc4(const b200pf_bf16* q, const b200pf_bf16* k, const b20
 int b200pf_triatt_epilogue(float* z, const b200pf_bf16* o, const b200pf_bf16* g,
                            const b200pf_bf16* w_o, long long n_rows_flat, void* stream);
 
-/* Pair transition: z += W3( silu(W1 LN(z)) * (W2 LN(z)) ), hidden 512 kept on chip.
+/* Pair transition: z += W3( silu(W1 LN(z)) * (W2 LN(z)) ), hidden 512 kept on chip, on tcgen05.
  * Replaces tt_bio/tenstorrent.py:869-946 and the residual :1023-1025 (boltz2.py:1241-1246).
- *   w12: bf16 [1024][128], 32 groups of 32 rows = 16 fc1 rows then the 16 fc2 rows of the same
- *        hidden channels;  bias12: fp32 [1024];  w3: bf16 [8][128][64] (fc3 columns per step). */
-int b200pf_transition_z(float* z, const b200pf_bf16* w12, const float* bias12,
-                        const b200pf_bf16* w3, long long n_rows_flat, void* stream);
-
-/* The same transition on tcgen05 (production path): GEMM1 per 64-channel chunk of the hidden layer into
+ * GEMM1 per 64-channel chunk of the hidden layer into
  * TMEM, SwiGLU in registers, hidden activations written back to TMEM as the A operand of GEMM2,
  * update through TMA reduce-add into z; weights streamed from L2 by TMA.
  *   ln_gamma / ln_beta: fp32 [128], applied in the kernel;

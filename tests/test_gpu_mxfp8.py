@@ -74,8 +74,8 @@ def test_producer_writes_the_documented_format(dev, n, incoming):
     # the same operands from the bf16 producer
     a16, b16 = ws.buf[0], ws.buf[1]
     oa, ob = PlaneOut(ptr(a16), ws.plane_stride, 0, 0), PlaneOut(ptr(b16), ws.plane_stride, 0, 0)
-    call("b200pf_trimul_producer", ptr(zd), ptr(pmd), ptr(w["ln_in_gamma"]), ptr(w["ln_in_beta"]), None, ptr(w["w_pg_tc"]),
-         C.byref(oa), C.byref(ob), ws.pitch, n, n, int(incoming), 0, 0, stream())
+    call("b200pf_trimul_producer", ptr(zd), ptr(pmd), ptr(w["ln_in_gamma"]), ptr(w["ln_in_beta"]), ptr(w["w_pg_tc"]),
+         C.byref(oa), C.byref(ob), ws.pitch, n, n, int(incoming), stream())
     torch.cuda.synchronize()
     assert _lib.device_status() == 0
     for v8, sc, v16 in ((a8, sa, a16), (b8, sb, b16)):

@@ -123,7 +123,7 @@ def test_sub_operations_bf16(dev, n):
         assert rel_l2(upd[v][:, v], want[v][:, v]) < 2e-2, name
 
 
-def test_contraction_tcgen05_matches_simt_and_einsum(dev):
+def test_contraction_tcgen05_matches_einsum(dev):
     from tt_boltz_b200._lib import Planes, call, ptr, stream
     from tt_boltz_b200 import _lib
     for n in (24, 100, 128, 264, 512):
@@ -133,18 +133,13 @@ def test_contraction_tcgen05_matches_simt_and_einsum(dev):
         a = torch.randn(128, n, pitch, generator=g).bfloat16()
         b = torch.randn(128, n, pitch, generator=g).bfloat16()
         ad, bd = a.to(dev), b.to(dev)
-        outs = []
-        for variant in (0, 1):
-            x = torch.zeros(128, n, pitch, dtype=torch.bfloat16, device=dev)
-            pa = Planes(ptr(ad), ps, 0, pitch, n, n, 1, 0)
-            pb = Planes(ptr(bd), ps, 0, pitch, n, n, 1, 0)
-            call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), None, None, ptr(x), ps, pitch, 0, 0, 128, variant, stream())
-            assert _lib.device_status() == 0
-            outs.append(x[:, :, :n].float().cpu())
+        x = torch.zeros(128, n, pitch, dtype=torch.bfloat16, device=dev)
+        pa = Planes(ptr(ad), ps, 0, pitch, n, n, 1, 0)
+        pb = Planes(ptr(bd), ps, 0, pitch, n, n, 1, 0)
+        call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), None, None, ptr(x), ps, pitch, 0, 0, 128, 0, stream())
+        assert _lib.device_status() == 0
         ref = torch.einsum("dik,djk->dij", a[:, :, :n].float(), b[:, :, :n].float())
-        assert rel_l2(outs[0], ref) < 4e-3, n       # bf16 rounding of the stored result
-        assert rel_l2(outs[1], ref) < 4e-3, n
-        assert rel_l2(outs[0], outs[1]) < 1e-3, n
+        assert rel_l2(x[:, :, :n].float().cpu(), ref) < 4e-3, n       # bf16 rounding of the stored result
 
 
 @pytest.mark.parametrize("seg_is_k", [0, 1])
@@ -168,35 +163,31 @@ def test_contraction_segmented_operands_and_grouped_output(dev, seg_is_k):
         rows, cols = nr, n
     ad, bd = a_seg.to(dev), b_seg.to(dev)
     ref = torch.einsum("cik,cjk->cij", a.float(), b.float())
-    outs = []
-    for variant in (0, 1):
-        x = torch.zeros(world, cl, nr, n, dtype=torch.bfloat16, device=dev)        # [group = i / nr][c][i local][j]
-        pa = Planes(ptr(ad), rows * cols, cl * rows * cols, cols, rows, cols, world, seg_is_k)
-        pb = Planes(ptr(bd), rows * cols, cl * rows * cols, cols, rows, cols, world, seg_is_k)
-        call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), None, None, ptr(x), nr * n, n, nr, cl * nr * n, cl, variant, stream())
-        assert _lib.device_status() == 0
-        outs.append(x.permute(1, 0, 2, 3).reshape(cl, n, n).float().cpu())
-    assert rel_l2(outs[0], ref) < 4e-3
-    assert rel_l2(outs[1], ref) < 4e-3
-    assert rel_l2(outs[0], outs[1]) < 1e-3
+    x = torch.zeros(world, cl, nr, n, dtype=torch.bfloat16, device=dev)        # [group = i / nr][c][i local][j]
+    pa = Planes(ptr(ad), rows * cols, cl * rows * cols, cols, rows, cols, world, seg_is_k)
+    pb = Planes(ptr(bd), rows * cols, cl * rows * cols, cols, rows, cols, world, seg_is_k)
+    call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), None, None, ptr(x), nr * n, n, nr, cl * nr * n, cl, 0, stream())
+    assert _lib.device_status() == 0
+    assert rel_l2(x.permute(1, 0, 2, 3).reshape(cl, n, n).float().cpu(), ref) < 4e-3
 
 
-def test_tcgen05_kernels_match_mma_sync_cross_checks(dev):
-    """One layer with every tcgen05 kernel against the same layer on the mma.sync / SIMT cross-check kernels."""
+def test_fused_tier_matches_the_fp32_tier(dev):
+    """One layer on the fused tcgen05 kernels against the same layer on the un-fused fp32 SIMT kernels: two
+    independent implementations inside the library (besides the comparisons with the CPU oracle)."""
     n = 136
     sd = synthetic.make_weights(1, seed=1, std=0.05, affine_jitter=0.3)
     s, z = synthetic.make_inputs(n, seed=0)
     m, pm = synthetic.tail_padding_mask(n, 11)
     _, z_tc = run_module(sd, 1, s, z, m, pm, dev, "bf16")
-    _, z_x = run_module(sd, 1, s, z, m, pm, dev, "bf16", row_impl=1, attention_core=1, contract_variant=1)
+    _, z_x = run_module(sd, 1, s, z, m, pm, dev, "fp32")
     v = n - 11
     assert rel_l2((z_tc - z)[0, :v, :v], (z_x - z)[0, :v, :v]) < 8e-3
 
 
 @pytest.mark.parametrize("n", [50, 128, 200, 330])
-def test_attention_tcgen05_core_matches_mma_sync_core(dev, n):
-    """The attention cores (tcgen05 / TMEM with two and with four lines per CTA, and the mma.sync cross-check)
-    see the same q, k, v, bias."""
+def test_attention_core_against_fp32_tier_with_general_masks(dev, n):
+    """Triangle attention (starting and ending node) on the tcgen05 path against the fp32 tier's un-fused kernels,
+    with a random 2-D mask (most key tiles hold masked keys: the per-tile mask path) and one fully masked line."""
     from tt_boltz_b200 import _lib, ops, weights
     sd = strip(synthetic.make_weights(1, seed=5, std=0.05, affine_jitter=0.3))
     _, z = synthetic.make_inputs(n, seed=4, with_s=False)
@@ -206,19 +197,15 @@ def test_attention_tcgen05_core_matches_mma_sync_core(dev, n):
     masks = ops.PairMasks(pm.to(dev))
     ws = ops.Workspace(n, dev)
     for ending in (False, True):
-        w = weights.pack_triatt(sd, "tri_att_end." if ending else "tri_att_start.", dev)
-        outs = []
-        for core in (0, 1, 2):
-            zd = z[0].to(dev).clone()
-            ops.tri_att_bf16(zd, masks, w, ws, ending, core)
-            assert _lib.device_status() == 0
-            outs.append((zd.cpu() - z[0]))
-        assert torch.isfinite(outs[0]).all() and torch.isfinite(outs[2]).all()
-        # the tcgen05 producer takes the four bias heads from the bf16-rounded normalised rows, the mma.sync
-        # producer from fp32 rows: a little more spread between the two than between the cores alone
-        assert rel_l2(outs[0], outs[1]) < 7e-3, (n, ending)
-        assert rel_l2(outs[2], outs[1]) < 7e-3, (n, ending)
-        assert rel_l2(outs[0], outs[2]) < 3e-3, (n, ending)          # same producer, different cores
+        pre = "tri_att_end." if ending else "tri_att_start."
+        zd = z[0].to(dev).clone()
+        ops.tri_att_bf16(zd, masks, weights.pack_triatt(sd, pre, dev), ws, ending)
+        assert _lib.device_status() == 0
+        zf = z[0].to(dev).clone()
+        ops.tri_att_f32(zf, masks.pm, weights.to_device_f32(sd, pre, dev), ending)
+        upd, ref = zd.cpu() - z[0], zf.cpu() - z[0]
+        assert torch.isfinite(upd).all()
+        assert rel_l2(upd, ref) < 7e-3, (n, ending)
 
 
 # ---------------------------------------------------------------------------------------------

@@ -1,8 +1,8 @@
 """Host logic: weight packing and the module's state-dict surface, checked on the CPU.
 
 The kernels cannot run here, so each packing layout is validated by a small torch model of what
-the kernel does with the packed buffers (normalise without affine, multiply by the packed bf16
-rows, add the folded bias, combine the values the layout puts side by side) against the oracle.
+the kernel does with the packed buffers (LayerNorm with the affine, multiply by the packed bf16
+rows, combine the values the layout puts side by side) against the oracle.
 """
 import math
 
@@ -32,20 +32,30 @@ def setup():
     return sd, z[0], pm
 
 
+def ln_affine(z, gamma, beta):
+    return xhat(z) * gamma + beta
+
+
 @pytest.mark.parametrize("incoming", [False, True])
 def test_trimul_packing_model(setup, incoming):
+    """What the producer and the epilogue kernels do with their packed weights: halved p / g rows so that
+    p * sigmoid(g) = p' + p' * tanh(g'), and the epilogue's LayerNorm over channels applied AFTER the GEMM
+    (p = rstd * (acc - mean * wsum) + wb)."""
     sd, z, pm = setup
     pre = "tri_mul_in" if incoming else "tri_mul_out"
     pk = weights.pack_trimul(sd, pre + ".", "cpu")
-    y = xhat(z) @ pk["w_pg"].float().T + pk["bias_pg"]            # [N,N,512]
-    a = torch.empty(N, N, 128)
-    b = torch.empty(N, N, 128)
-    for q in range(8):
-        ch = (q % 4) * 32
-        u = y[..., q * 64:q * 64 + 32] * torch.sigmoid(y[..., q * 64 + 32:q * 64 + 64]) * pm[..., None]
-        (a if q < 4 else b)[..., ch:ch + 32] = u
+    assert pk["w_pg_tc"].shape == (512, 128)
+    x = ln_affine(z, pk["ln_in_gamma"], pk["ln_in_beta"])
+    y = x @ pk["w_pg_tc"].float().T                                  # [N,N,512] = 0.5 * [p_a | g_a | p_b | g_b]
+    gated = lambda pp, gg: (pp + pp * torch.tanh(gg)) * pm[..., None]
+    a, b = gated(y[..., 0:128], y[..., 128:256]), gated(y[..., 256:384], y[..., 384:512])
     t = torch.einsum("kic,kjc->ijc", a, b) if incoming else torch.einsum("ikc,jkc->ijc", a, b)
-    upd = (xhat(t) @ pk["w_pout"].float().T + pk["bias_pout"]) * torch.sigmoid(xhat(z) @ pk["w_gout"].float().T + pk["bias_gout"])
+    acc = t @ pk["w_pout_tc"].float().T                              # raw x against 0.5 * W_pout * gamma_out
+    mean = t.mean(-1, keepdim=True)
+    rstd = torch.rsqrt(((t - mean) ** 2).mean(-1, keepdim=True) + 1e-5)
+    pp = rstd * (acc - mean * pk["wsum_tc"]) + pk["wb_tc"]
+    gg = x @ pk["w_gout_tc"].float().T
+    upd = pp + pp * torch.tanh(gg)
     ref = orc.tri_mul(z, sd, pre, pm, incoming)
     assert rel_l2(upd, ref) < 1e-2
 
@@ -55,16 +65,18 @@ def test_triatt_packing_model(setup, ending):
     sd, z, pm = setup
     pre = "tri_att_end" if ending else "tri_att_start"
     pk = weights.pack_triatt(sd, pre + ".", "cpu")
-    assert pk["w_qkvg"].shape == (528, 128) and pk["bias_qkvg"].shape == (528,)
-    y = xhat(z) @ pk["w_qkvg"].float().T + pk["bias_qkvg"]        # [N,N,528] in z layout (r, c)
+    assert pk["w_qkgv_tc"].shape == (512, 128) and pk["w_bias_f32"].shape == (4, 128)
+    x = ln_affine(z, pk["ln_gamma"], pk["ln_beta"])
+    y = x @ pk["w_qkgv_tc"].float().T                                # [N,N,512] in z layout (r, c): q | k | 0.5 g | v
+    bias = x @ pk["w_bias_f32"].T                                    # [r, c, h], log2 domain
     if ending:          # line = column: (line, pos) = (c, r)
-        y = y.transpose(0, 1)
+        y, bias = y.transpose(0, 1), bias.transpose(0, 1)
         mask = pm.T
     else:
         mask = pm
-    q, k, v = (y[..., i * 128:(i + 1) * 128].reshape(N, N, 4, 32) for i in range(3))
-    gate = torch.sigmoid(y[..., 384:512])
-    bias = y[..., 512:516]                                          # [line(q), pos(k), h], log2 domain
+    q, k = (y[..., i * 128:(i + 1) * 128].reshape(N, N, 4, 32) for i in range(2))
+    v = y[..., 384:512].reshape(N, N, 4, 32)
+    gate = 0.5 + 0.5 * torch.tanh(y[..., 256:384])
     s = torch.einsum("lqhd,lkhd->lhqk", q, k) + bias.permute(2, 0, 1)[None]
     s = torch.where(mask[:, None, None, :] > 0, s, torch.full_like(s, -1e9 * weights.LOG2E))
     p = torch.exp2(s - s.amax(-1, keepdim=True))
@@ -80,15 +92,14 @@ def test_triatt_packing_model(setup, ending):
 def test_transition_packing_model(setup):
     sd, z, _ = setup
     pk = weights.pack_transition_z(sd, "transition_z.", "cpu")
-    assert pk["w12"].shape == (1024, 128) and pk["w3"].shape == (8, 128, 64)
-    y = xhat(z) @ pk["w12"].float().T + pk["bias12"]               # [N,N,1024]
+    assert pk["w12_tc"].shape == (8, 128, 128) and pk["w3"].shape == (8, 128, 64)
+    x = ln_affine(z, pk["ln_gamma"], pk["ln_beta"])
     out = torch.zeros(N, N, 128)
-    for step in range(8):
-        for sub in range(4):
-            base = step * 128 + sub * 32
-            f1, f2 = y[..., base:base + 16], y[..., base + 16:base + 32]
-            h = torch.nn.functional.silu(f1) * f2
-            out += h @ pk["w3"][step].float()[:, sub * 16:(sub + 1) * 16].T
+    for c in range(8):
+        y = x @ pk["w12_tc"][c].float().T                           # [N,N,128] = 0.5 * fc1 chunk | fc2 chunk
+        a, f2 = y[..., :64], y[..., 64:]
+        h = (a + a * torch.tanh(a)) * f2                             # silu(f1) * f2 with a = f1 / 2
+        out += h @ pk["w3"][c].float().T
     ref = orc.transition(z, sd, "transition_z")
     assert rel_l2(out, ref) < 1e-2
 

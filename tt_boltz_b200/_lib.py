@@ -40,7 +40,6 @@ SIGNATURES = {
     "b200pf_last_error": [],
     "b200pf_launch_count": [],
     "b200pf_device_status": [_vp],
-    "b200pf_debug_counters": [C.POINTER(_ll), _i],
     "b200pf_f32_layernorm": [_vp, _vp, _vp, _vp, _ll, _i, _vp],
     "b200pf_f32_linear": [_vp, _vp, _vp, _vp, _ll, _i, _i, _i, _vp],
     "b200pf_f32_gate": [_vp, _vp, _vp, _vp, _ll, _i, _i, _vp],
@@ -52,19 +51,15 @@ SIGNATURES = {
     "b200pf_f32_gate_strided": [_vp, _ll, _vp, _ll, _vp, _ll, _ll, _i, _i, _vp],
     "b200pf_f32_sattention": [_vp, _ll, _vp, _ll, _vp, _vp, _ll, _vp, _ll, _vp, _ll, _ll, _vp, _i, _i, _i, _i, _f, _f, _vp],
     "b200pf_ln_proj_heads": [_vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _vp],
-    "b200pf_trimul_producer": [_vp, _vp, _vp, _vp, _vp, _vp, C.POINTER(PlaneOut), C.POINTER(PlaneOut), _i, _i, _i, _i, _i, _i, _vp],
+    "b200pf_trimul_producer": [_vp, _vp, _vp, _vp, _vp, C.POINTER(PlaneOut), C.POINTER(PlaneOut), _i, _i, _i, _i, _vp],
     "b200pf_trimul_contract": [C.POINTER(Planes), C.POINTER(Planes), _vp, _vp, _vp, _ll, _i, _i, _ll, _i, _i, _vp],
     "b200pf_mx_scale_bytes": [_i, _i, _i],
     "b200pf_trimul_producer_mx": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _vp],
     "b200pf_mx_dequant": [_vp, _vp, _vp, _ll, _i, _ll, _i, _i, _i, _i, _vp],
-    "b200pf_trimul_epilogue": [_vp, _vp, _ll, _i, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "b200pf_trimul_epilogue_tc": [_vp, _vp, _ll, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
-    "b200pf_triatt_producer": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _vp],
-    "b200pf_triatt_core_tc": [_vp, _vp, _vp, _i, _vp, _ll, _ll, _vp, _i, _vp, _ll, _ll, _i, _i, _vp],
+    "b200pf_triatt_producer": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _vp],
     "b200pf_triatt_core_tc4": [_vp, _vp, _vp, _i, _vp, _ll, _ll, _vp, _i, _vp, _ll, _ll, _i, _i, _vp],
-    "b200pf_triatt_core": [_vp, _vp, _vp, _vp, _ll, _ll, _i, _vp, _ll, _ll, _vp, _ll, _ll, _i, _i, _i, _vp],
     "b200pf_triatt_epilogue": [_vp, _vp, _vp, _vp, _ll, _vp],
-    "b200pf_transition_z": [_vp, _vp, _vp, _vp, _ll, _vp],
     "b200pf_transition_z_tc": [_vp, _vp, _vp, _vp, _vp, _ll, _vp],
     "b200pf_peer_scatter": [_vp, C.POINTER(C.c_ulonglong), _ll, _i, _i, _vp],
     "b200pf_peer_broadcast": [_vp, C.POINTER(C.c_ulonglong), _ll, _i, _i, _vp],

@@ -177,49 +177,6 @@ trimul_contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
-// ---- legacy SIMT cross-check (same operand description, no tensor cores) ---------------------
-struct PlaneView {
-    const __nv_bfloat16* ptr;
-    long long plane_stride, seg_stride;
-    int pitch, rows, cols, nseg, seg_is_k;
-};
-__device__ __forceinline__ float plane_at(const PlaneView& p, int d, int row, int k) {
-    int seg = 0;
-    if (p.nseg > 1) {
-        if (p.seg_is_k) { seg = k / p.cols; k -= seg * p.cols; }
-        else { seg = row / p.rows; row -= seg * p.rows; }
-    }
-    return __bfloat162float(p.ptr[seg * p.seg_stride + d * p.plane_stride + (long long)row * p.pitch + k]);
-}
-__global__ void __launch_bounds__(256)
-trimul_contract_simt_kernel(PlaneView a, PlaneView b, __nv_bfloat16* __restrict__ x, GemmShape s) {
-    __shared__ float as[16][64 + 1], bs[16][64 + 1];
-    int d = blockIdx.z, i0 = blockIdx.y * 64, j0 = blockIdx.x * 64;
-    int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
-    float acc[4][4] = {};
-    for (int k0 = 0; k0 < s.k_total; k0 += 16) {
-        for (int e = threadIdx.x; e < 64 * 16; e += 256) {
-            int r = e >> 4, kk = e & 15;
-            as[kk][r] = (i0 + r < s.m_rows && k0 + kk < s.k_total) ? plane_at(a, d, i0 + r, k0 + kk) : 0.f;
-            bs[kk][r] = (j0 + r < s.n_rows && k0 + kk < s.k_total) ? plane_at(b, d, j0 + r, k0 + kk) : 0.f;
-        }
-        __syncthreads();
-#pragma unroll
-        for (int kk = 0; kk < 16; ++kk)
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-#pragma unroll
-                for (int v = 0; v < 4; ++v) acc[u][v] = fmaf(as[kk][ty * 4 + u], bs[kk][tx * 4 + v], acc[u][v]);
-        __syncthreads();
-    }
-    for (int u = 0; u < 4; ++u)
-        for (int v = 0; v < 4; ++v) {
-            int i = i0 + ty * 4 + u, j = j0 + tx * 4 + v;
-            if (i < s.m_rows && j < s.n_rows)
-                x[x_row_offset(s, d, i) + j] = __float2bfloat16(acc[u][v]);
-        }
-}
-
 // ---- host: tensor maps -----------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -318,14 +275,6 @@ extern "C" int b200pf_trimul_contract(const b200pf_planes* a, const b200pf_plane
     B200PF_REQUIRE(!grouped || (x_group_stride % 8 == 0 && x_group_stride >= x_plane_stride * channels), B200PF_ERR_INVALID,
                    "trimul_contract: bad x group stride");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (variant == 1) {
-        PlaneView va{(const __nv_bfloat16*)a->ptr, a->plane_stride, a->seg_stride, a->pitch, a->rows, a->cols, a->nseg, a->seg_is_k};
-        PlaneView vb{(const __nv_bfloat16*)b->ptr, b->plane_stride, b->seg_stride, b->pitch, b->rows, b->cols, b->nseg, b->seg_is_k};
-        dim3 grid((s.n_rows + 63) / 64, (s.m_rows + 63) / 64, channels);
-        trimul_contract_simt_kernel<<<grid, 256, 0, st>>>(va, vb, (__nv_bfloat16*)x, s);
-        B200PF_LAUNCH_CHECK();
-        return B200PF_OK;
-    }
     B200PF_REQUIRE(variant == 0, B200PF_ERR_UNSUPPORTED, "trimul_contract: variant %d is not built", variant);
     unsigned int* status = device_status_word();
     B200PF_REQUIRE(status, B200PF_ERR_CUDA, "trimul_contract: no device status word");

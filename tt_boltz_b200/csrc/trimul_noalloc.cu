@@ -65,7 +65,7 @@ extern "C" int b200pf_tri_mul_noalloc(float* z, const uint8_t* mask, const float
     // The producer writes every element the contraction reads and the contraction every element
     // the epilogue reads (padding columns included), so nothing has to be cleared between calls.
     b200pf_plane_out oa{a, plane_stride, 0, 0}, ob{b, plane_stride, 0, 0};
-    rc = b200pf_trimul_producer(z, mask, ln_gamma, ln_beta, nullptr, w_pg, &oa, &ob, pitch, n, n, incoming, 0, 0, stream);
+    rc = b200pf_trimul_producer(z, mask, ln_gamma, ln_beta, w_pg, &oa, &ob, pitch, n, n, incoming, stream);
     if (rc != B200PF_OK) return rc;
     b200pf_planes pa{a, plane_stride, 0, pitch, n, n, 1, 0}, pb{b, plane_stride, 0, pitch, n, n, 1, 0};
     rc = b200pf_trimul_contract(&pa, &pb, nullptr, nullptr, reinterpret_cast<b200pf_bf16*>(x), plane_stride, pitch,

@@ -62,53 +62,45 @@ class Workspace:
 # ------------------------------------------------------------------------------------------------
 # bf16 tier (fused kernels)
 # ------------------------------------------------------------------------------------------------
-def trimul_producer_weights(w: Dict[str, torch.Tensor], impl: int):
-    """(ln_gamma, ln_beta, bias_pg, w_pg) pointers for the chosen producer implementation."""
-    if impl == 0:
-        return ptr(w["ln_in_gamma"]), ptr(w["ln_in_beta"]), None, ptr(w["w_pg_tc"])
-    return None, None, ptr(w["bias_pg"]), ptr(w["w_pg"])
+def trimul_producer_weights(w: Dict[str, torch.Tensor]):
+    """(ln_gamma, ln_beta, w_pg) pointers of the triangle-multiplication producer."""
+    return ptr(w["ln_in_gamma"]), ptr(w["ln_in_beta"]), ptr(w["w_pg_tc"])
 
 
-def triatt_producer_weights(w: Dict[str, torch.Tensor], impl: int):
-    """(ln_gamma, ln_beta, w_bias_f32, w, bias) pointers for the chosen producer implementation."""
-    if impl == 0:
-        return ptr(w["ln_gamma"]), ptr(w["ln_beta"]), ptr(w["w_bias_f32"]), ptr(w["w_qkgv_tc"]), None
-    return None, None, None, ptr(w["w_qkvg"]), ptr(w["bias_qkvg"])
+def triatt_producer_weights(w: Dict[str, torch.Tensor]):
+    """(ln_gamma, ln_beta, w_bias_f32, w_qkgv) pointers of the triangle-attention producer."""
+    return ptr(w["ln_gamma"]), ptr(w["ln_beta"]), ptr(w["w_bias_f32"]), ptr(w["w_qkgv_tc"])
 
 
-def trimul_epilogue(z, x, plane_stride, pitch, w, rows, n, impl: int) -> None:
-    if impl == 0:
-        call("b200pf_trimul_epilogue_tc", ptr(z), ptr(x), plane_stride, pitch, ptr(w["ln_in_gamma"]), ptr(w["ln_in_beta"]),
-             ptr(w["w_pout_tc"]), ptr(w["w_gout_tc"]), ptr(w["wsum_tc"]), ptr(w["wb_tc"]), rows, n, stream())
-    else:
-        call("b200pf_trimul_epilogue", ptr(z), ptr(x), plane_stride, pitch, ptr(w["w_pout"]), ptr(w["w_gout"]),
-             ptr(w["bias_pout"]), ptr(w["bias_gout"]), rows, n, stream())
+def trimul_epilogue(z, x, plane_stride, pitch, w, rows, n) -> None:
+    call("b200pf_trimul_epilogue_tc", ptr(z), ptr(x), plane_stride, pitch, ptr(w["ln_in_gamma"]), ptr(w["ln_in_beta"]),
+         ptr(w["w_pout_tc"]), ptr(w["w_gout_tc"]), ptr(w["wsum_tc"]), ptr(w["wb_tc"]), rows, n, stream())
 
 
 def tri_mul_bf16(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Tensor], ws: Workspace,
-                 incoming: bool, contract_variant: int = 0, row_impl: int = 0, before_z_write=None) -> None:
+                 incoming: bool, before_z_write=None) -> None:
     """``before_z_write`` is called (if given) right before the first kernel that writes z, the epilogue."""
     n = z.shape[0]
     a, b, x = ws.buf[0], ws.buf[1], ws.buf[2]
     st = stream()
     oa = PlaneOut(ptr(a), ws.plane_stride, 0, 0)
     ob = PlaneOut(ptr(b), ws.plane_stride, 0, 0)
-    call("b200pf_trimul_producer", ptr(z), ptr(mask_u8), *trimul_producer_weights(w, row_impl), C.byref(oa), C.byref(ob),
-         ws.pitch, n, n, int(incoming), 0, row_impl, st)
+    call("b200pf_trimul_producer", ptr(z), ptr(mask_u8), *trimul_producer_weights(w), C.byref(oa), C.byref(ob),
+         ws.pitch, n, n, int(incoming), st)
     pa = Planes(ptr(a), ws.plane_stride, 0, ws.pitch, n, n, 1, 0)
     pb = Planes(ptr(b), ws.plane_stride, 0, ws.pitch, n, n, 1, 0)
     call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), None, None, ptr(x), ws.plane_stride, ws.pitch,
-         0, 0, C_Z, contract_variant, st)
+         0, 0, C_Z, 0, st)
     if before_z_write is not None:
         before_z_write()
-    trimul_epilogue(z, x, ws.plane_stride, ws.pitch, w, n, n, row_impl)
+    trimul_epilogue(z, x, ws.plane_stride, ws.pitch, w, n, n)
 
 
 def tri_mul_mxfp8(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Tensor], ws: Workspace,
                   incoming: bool, contract_variant: int = 2, before_z_write=None) -> None:
     """Triangle multiplication with MXFP8 operands (e4m3 values, e8m0 scale per 32 along k).
 
-    contract_variant 2 = block-scaled tcgen05 contraction; 0 / 1 = expand the operands to bf16
+    contract_variant 2 = block-scaled tcgen05 contraction; 0 = expand the operands to bf16
     (exactly) and run the bf16 contraction: the cross-check of variant 2.
     """
     n = z.shape[0]
@@ -131,45 +123,32 @@ def tri_mul_mxfp8(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Ten
         pa = Planes(ptr(a), ws.plane_stride, 0, ws.pitch, n, n, 1, 0)
         pb = Planes(ptr(b), ws.plane_stride, 0, ws.pitch, n, n, 1, 0)
         call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), None, None, ptr(x), ws.plane_stride, ws.pitch,
-             0, 0, C_Z, contract_variant, st)
+             0, 0, C_Z, 0, st)
     if before_z_write is not None:
         before_z_write()
-    trimul_epilogue(z, x, ws.plane_stride, ws.pitch, w, n, n, 0)
+    trimul_epilogue(z, x, ws.plane_stride, ws.pitch, w, n, n)
 
 
-def tri_att_bf16(z: torch.Tensor, masks: PairMasks, w: Dict[str, torch.Tensor], ws: Workspace,
-                 ending: bool, core: int = 0, lines_per_cta: int = 0, row_impl: int = 0) -> None:
-    """core 0 = tcgen05 attention core (four lines per CTA, the production kernel), 2 = the earlier tcgen05
-    core with two lines per CTA, 1 = mma.sync core (the last two are cross-checks)."""
+def tri_att_bf16(z: torch.Tensor, masks: PairMasks, w: Dict[str, torch.Tensor], ws: Workspace, ending: bool) -> None:
     n = z.shape[0]
     q, k, v, g, o = ws.buf
     st = stream()
     bias_hs, bias_qs = ws.pitch, 4 * ws.pitch          # layout [query][head][key]: a row shard is contiguous
-    if core == 1:
-        row_impl = 1          # the mma.sync core reads v untransposed, which only the mma.sync producer writes
-    call("b200pf_triatt_producer", ptr(z), *triatt_producer_weights(w, row_impl), ptr(q), ptr(k), ptr(v), ptr(g),
-         ptr(ws.tri_bias), bias_hs, bias_qs, ws.pitch if core != 1 else 0, n, n, int(ending), row_impl, st)
+    call("b200pf_triatt_producer", ptr(z), *triatt_producer_weights(w), ptr(q), ptr(k), ptr(v), ptr(g),
+         ptr(ws.tri_bias), bias_hs, bias_qs, ws.pitch, n, n, int(ending), st)
     if ending:      # line = column j: o element (line, pos) -> z position [pos][line]
         o_ls, o_ps = C_Z, n * C_Z
     else:
         o_ls, o_ps = n * C_Z, C_Z
-    if core != 1:
-        lines_mask = masks.cols if ending else masks.rows
-        call("b200pf_triatt_core_tc4" if core == 0 else "b200pf_triatt_core_tc", ptr(q), ptr(k), ptr(v), ws.pitch, ptr(ws.tri_bias), bias_hs, bias_qs,
-             ptr(lines_mask), masks.pitch, ptr(o), o_ls, o_ps, n, n, st)
-    else:
-        mask_ls, mask_ks = (1, n) if ending else (n, 1)
-        call("b200pf_triatt_core", ptr(q), ptr(k), ptr(v), ptr(ws.tri_bias), bias_hs, bias_qs, ws.pitch, ptr(masks.pm),
-             mask_ls, mask_ks, ptr(o), o_ls, o_ps, n, n, lines_per_cta, st)
+    lines_mask = masks.cols if ending else masks.rows
+    call("b200pf_triatt_core_tc4", ptr(q), ptr(k), ptr(v), ws.pitch, ptr(ws.tri_bias), bias_hs, bias_qs,
+         ptr(lines_mask), masks.pitch, ptr(o), o_ls, o_ps, n, n, st)
     call("b200pf_triatt_epilogue", ptr(z), ptr(o), ptr(g), ptr(w["w_o"]), n * n, st)
 
 
-def transition_z_bf16(z: torch.Tensor, w: Dict[str, torch.Tensor], impl: int = 0) -> None:
+def transition_z_bf16(z: torch.Tensor, w: Dict[str, torch.Tensor]) -> None:
     rows = z.shape[0] * z.shape[1]
-    if impl == 0:
-        call("b200pf_transition_z_tc", ptr(z), ptr(w["ln_gamma"]), ptr(w["ln_beta"]), ptr(w["w12_tc"]), ptr(w["w3"]), rows, stream())
-    else:
-        call("b200pf_transition_z", ptr(z), ptr(w["w12"]), ptr(w["bias12"]), ptr(w["w3"]), rows, stream())
+    call("b200pf_transition_z_tc", ptr(z), ptr(w["ln_gamma"]), ptr(w["ln_beta"]), ptr(w["w12_tc"]), ptr(w["w3"]), rows, stream())
 
 
 # ------------------------------------------------------------------------------------------------

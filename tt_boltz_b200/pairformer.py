@@ -96,11 +96,7 @@ class B200PairformerLayer(nn.Module):
         self.token_s, self.token_z, self.num_heads = token_s, token_z, num_heads
         self.dropout, self.with_s, self.precision = dropout, with_s, precision
         self.fused = precision != "fp32"
-        self.contract_variant = 0      # 0 = tcgen05, 1 = SIMT cross-check
         self.mx_contract_variant = 2   # 2 = block-scaled tcgen05, 0 = expand to bf16 + bf16 contraction (cross-check)
-        self.attention_core = 0        # 0 = tcgen05 (four lines per CTA); cross-checks: 2 = tcgen05 two lines per CTA, 1 = mma.sync
-        self.row_impl = 0              # 0 = tcgen05 row-tile kernels, 1 = mma.sync cross-check
-        self.lines_per_cta = 0
         for name, shape in layer_param_shapes(token_s, token_z, num_heads, pairwise_num_heads,
                                               pairwise_head_width, with_s):
             _register_tree(self, name, shape)
@@ -144,11 +140,11 @@ class B200PairformerLayer(nn.Module):
                 ops.tri_mul_mxfp8(z, masks.pm, pk["tri_mul_out"], ws, False, self.mx_contract_variant, wait_bias)
                 ops.tri_mul_mxfp8(z, masks.pm, pk["tri_mul_in"], ws, True, self.mx_contract_variant)
             else:
-                ops.tri_mul_bf16(z, masks.pm, pk["tri_mul_out"], ws, False, self.contract_variant, self.row_impl, wait_bias)
-                ops.tri_mul_bf16(z, masks.pm, pk["tri_mul_in"], ws, True, self.contract_variant, self.row_impl)
-            ops.tri_att_bf16(z, masks, pk["tri_att_start"], ws, False, self.attention_core, self.lines_per_cta, self.row_impl)
-            ops.tri_att_bf16(z, masks, pk["tri_att_end"], ws, True, self.attention_core, self.lines_per_cta, self.row_impl)
-            ops.transition_z_bf16(z, pk["transition_z"], self.row_impl)
+                ops.tri_mul_bf16(z, masks.pm, pk["tri_mul_out"], ws, False, wait_bias)
+                ops.tri_mul_bf16(z, masks.pm, pk["tri_mul_in"], ws, True)
+            ops.tri_att_bf16(z, masks, pk["tri_att_start"], ws, False)
+            ops.tri_att_bf16(z, masks, pk["tri_att_end"], ws, True)
+            ops.transition_z_bf16(z, pk["transition_z"])
         else:
             if side is not None:
                 side.before_z_write()

@@ -280,9 +280,9 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
             ab_loc = _bf16(2 * C_Z * prow * pitch, dev)
             a_loc, b_loc = ab_loc[:C_Z * prow * pitch], ab_loc[C_Z * prow * pitch:]
             oa, ob = PlaneOut(ptr(a_loc), prow * pitch, 0, 0), PlaneOut(ptr(b_loc), prow * pitch, 0, 0)
-            call("b200pf_trimul_producer", ptr(z_loc), ptr(mask_loc), *ops.trimul_producer_weights(w, layer.row_impl),
-                 C.byref(oa), C.byref(ob), pitch, nr, n, incoming, 0, layer.row_impl, st)
-            scales, variant = (None, None), layer.contract_variant
+            call("b200pf_trimul_producer", ptr(z_loc), ptr(mask_loc), *ops.trimul_producer_weights(w),
+                 C.byref(oa), C.byref(ob), pitch, nr, n, incoming, st)
+            scales, variant = (None, None), 0
         # ONE exchange for both operands: block t = (a planes of rank t's channels | b planes of rank t's channels),
         # received as [src][a | b][cl][prow][pitch]; its barrier also covers the scale blocks sent just before
         blk = cl * prow * pitch
@@ -301,7 +301,7 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
         x_loc = all_to_all_blocks(x_send.view(world, -1), group, "trimul_x")         # [src = channel block][cl][nr][pn] = [D][nr][pn]
         if side is not None:
             side.before_z_write()          # the previous block's pair-bias projection has read z
-        ops.trimul_epilogue(z_loc, x_loc, nr * pn, pn, w, nr, n, layer.row_impl)
+        ops.trimul_epilogue(z_loc, x_loc, nr * pn, pn, w, nr, n)
         del ab_loc, a_loc, b_loc, ab_ch, a_ch, b_ch
     del x_send, x_loc
 
@@ -309,8 +309,8 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
     w = pk["tri_att_start"]
     q, k, v, g, o = (_bf16(nr * n * C_Z, dev) for _ in range(5))
     bias_loc = _bf16(nr * 4 * pn, dev)
-    call("b200pf_triatt_producer", ptr(z_loc), *ops.triatt_producer_weights(w, layer.row_impl), ptr(q), ptr(k), ptr(v), ptr(g),
-         ptr(bias_loc), pn, 4 * pn, pn, nr, n, 0, layer.row_impl, st)
+    call("b200pf_triatt_producer", ptr(z_loc), *ops.triatt_producer_weights(w), ptr(q), ptr(k), ptr(v), ptr(g),
+         ptr(bias_loc), pn, 4 * pn, pn, nr, n, 0, st)
     bias_all = all_gather_cat(bias_loc, group, "tri_bias")                           # [query][head][key]
     call("b200pf_triatt_core_tc4", ptr(q), ptr(k), ptr(v), pn, ptr(bias_all), pn, 4 * pn, ptr(masks.rows[r0:r0 + nr]),
          masks.pitch, ptr(o), n * C_Z, C_Z, nr, n, st)
@@ -319,8 +319,8 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
     # ---- triangle attention, ending node (lines = local columns of the column shard) ------------
     w = pk["tri_att_end"]
     zc = rows_to_cols(z_loc, group)                                                  # [N][nr][128] fp32
-    call("b200pf_triatt_producer", ptr(zc), *ops.triatt_producer_weights(w, layer.row_impl), ptr(q), ptr(k), ptr(v), ptr(g),
-         ptr(bias_loc), pn, 4 * pn, pn, n, nr, 1, layer.row_impl, st)
+    call("b200pf_triatt_producer", ptr(zc), *ops.triatt_producer_weights(w), ptr(q), ptr(k), ptr(v), ptr(g),
+         ptr(bias_loc), pn, 4 * pn, pn, n, nr, 1, st)
     bias_all = all_gather_cat(bias_loc, group, "tri_bias")
     call("b200pf_triatt_core_tc4", ptr(q), ptr(k), ptr(v), pn, ptr(bias_all), pn, 4 * pn, ptr(masks.cols[r0:r0 + nr]),
          masks.pitch, ptr(o), C_Z, nr * C_Z, nr, n, st)
@@ -329,7 +329,7 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
     del q, k, v, g, o, zc, bias_loc, bias_all
 
     # ---- pair transition ---------------------------------------------------------------------------
-    ops.transition_z_bf16(z_loc, pk["transition_z"], layer.row_impl)
+    ops.transition_z_bf16(z_loc, pk["transition_z"])
 
     # ---- single track: attention for the local query rows, the rest replicated --------------------
     if layer.with_s and s is not None:

@@ -1,9 +1,9 @@
 """Host-side weight packing for the b200pf kernels.
 
 Input: the reference's flat state dict for one layer (keys as in tt_bio/reference.py:825-863).
-Output: device tensors in the layouts include/b200pf.h documents.  LayerNorm gains are folded
-into the weight rows and LayerNorm offsets into fp32 bias vectors, so that the kernels only
-compute (x - mean) * rstd; rows are re-ordered so that values one thread combines sit together.
+Output: device tensors in the layouts include/b200pf.h documents: bf16 rows grouped the way one
+GEMM of a kernel wants them, the 0.5 of sigmoid(x) = 0.5 + 0.5 tanh(x / 2) folded into gate rows,
+LayerNorm gains / offsets as fp32 vectors the kernels apply themselves.
 """
 from __future__ import annotations
 
@@ -17,11 +17,6 @@ C_Z = 128
 TRI_HEADS, TRI_HEAD_DIM = 4, 32
 
 
-def _fold(w: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor):
-    """(W * gamma) as the new weight and W @ beta as the bias: LN(x) W^T = xhat (W*gamma)^T + W beta."""
-    return w * gamma[None, :], w @ beta
-
-
 def pack_trimul(sd: Dict[str, torch.Tensor], pre: str, device) -> Dict[str, torch.Tensor]:
     f = {k: sd[pre + k].detach().float().cpu() for k in
          ("norm_in.weight", "norm_in.bias", "p_in.weight", "g_in.weight", "norm_out.weight", "norm_out.bias",
@@ -29,26 +24,17 @@ def pack_trimul(sd: Dict[str, torch.Tensor], pre: str, device) -> Dict[str, torc
     d = f["p_in.weight"].shape[0] // 2
     if d != C_Z or f["p_in.weight"].shape[1] != C_Z:
         raise RuntimeError("the fused triangle-multiplication kernels are built for c_z = hidden = 128")
-    rows = []
-    for q in range(8):
-        ch0 = (q // 4) * d + (q % 4) * 32
-        rows += [f["p_in.weight"][ch0:ch0 + 32], f["g_in.weight"][ch0:ch0 + 32]]
-    w_pg, bias_pg = _fold(torch.cat(rows, 0), f["norm_in.weight"], f["norm_in.bias"])
-    # tcgen05 producer: 0.5 * [p_a | g_a | p_b | g_b], 128 rows each, LayerNorm affine applied in the kernel
+    # producer: 0.5 * [p_a | g_a | p_b | g_b], 128 rows each, LayerNorm affine applied in the kernel
     w_pg_tc = 0.5 * torch.cat([f["p_in.weight"][:d], f["g_in.weight"][:d], f["p_in.weight"][d:], f["g_in.weight"][d:]], 0)
-    w_pout, bias_pout = _fold(f["p_out.weight"], f["norm_out.weight"], f["norm_out.bias"])
-    w_gout, bias_gout = _fold(f["g_out.weight"], f["norm_in.weight"], f["norm_in.bias"])
-    # tcgen05 epilogue: raw-x GEMM with 0.5 * W_pout * gamma_out, LayerNorm over channels applied after the GEMM
+    # epilogue: raw-x GEMM with 0.5 * W_pout * gamma_out, LayerNorm over channels applied after the GEMM
     w_pout_tc = (0.5 * f["p_out.weight"] * f["norm_out.weight"][None, :]).to(torch.bfloat16)
     wsum_tc = w_pout_tc.float().sum(1)
     wb_tc = 0.5 * (f["p_out.weight"] @ f["norm_out.bias"])
     w_gout_tc = 0.5 * f["g_out.weight"]
     bf = lambda t: t.to(device=device, dtype=torch.bfloat16).contiguous()
     fp = lambda t: t.to(device=device, dtype=torch.float32).contiguous()
-    return {"w_pg": bf(w_pg), "bias_pg": fp(bias_pg), "w_pg_tc": bf(w_pg_tc), "w_pout_tc": bf(w_pout_tc), "wsum_tc": fp(wsum_tc), "wb_tc": fp(wb_tc),
-            "w_gout_tc": bf(w_gout_tc),
-            "ln_in_gamma": fp(f["norm_in.weight"]), "ln_in_beta": fp(f["norm_in.bias"]), "w_pout": bf(w_pout), "bias_pout": fp(bias_pout),
-            "w_gout": bf(w_gout), "bias_gout": fp(bias_gout)}
+    return {"w_pg_tc": bf(w_pg_tc), "w_pout_tc": bf(w_pout_tc), "wsum_tc": fp(wsum_tc), "wb_tc": fp(wb_tc),
+            "w_gout_tc": bf(w_gout_tc), "ln_in_gamma": fp(f["norm_in.weight"]), "ln_in_beta": fp(f["norm_in.bias"])}
 
 
 def pack_triatt(sd: Dict[str, torch.Tensor], pre: str, device) -> Dict[str, torch.Tensor]:
@@ -57,19 +43,13 @@ def pack_triatt(sd: Dict[str, torch.Tensor], pre: str, device) -> Dict[str, torc
           "mha.linear_v.weight", "mha.linear_g.weight", "mha.linear_o.weight")}
     if f["linear.weight"].shape != (TRI_HEADS, C_Z) or f["mha.linear_q.weight"].shape != (TRI_HEADS * TRI_HEAD_DIM, C_Z):
         raise RuntimeError("the fused triangle-attention kernels are built for c_z = 128 and 4 heads x 32")
-    rows = torch.cat([f["mha.linear_q.weight"] * (LOG2E / math.sqrt(TRI_HEAD_DIM)), f["mha.linear_k.weight"],
-                      f["mha.linear_v.weight"], f["mha.linear_g.weight"], f["linear.weight"] * LOG2E,
-                      torch.zeros(12, C_Z)], 0)
-    w, b = _fold(rows, f["layer_norm.weight"], f["layer_norm.bias"])
-    # tcgen05 producer: [q (scaled) | k | 0.5 g | v], LayerNorm affine and the bias heads applied in fp32 in the kernel
+    # producer: [q (scaled) | k | 0.5 g | v], LayerNorm affine and the bias heads applied in fp32 in the kernel
     w_tc = torch.cat([f["mha.linear_q.weight"] * (LOG2E / math.sqrt(TRI_HEAD_DIM)), f["mha.linear_k.weight"],
                       0.5 * f["mha.linear_g.weight"], f["mha.linear_v.weight"]], 0)
     return {"w_qkgv_tc": w_tc.to(device=device, dtype=torch.bfloat16).contiguous(),
             "w_bias_f32": (f["linear.weight"] * LOG2E).to(device=device, dtype=torch.float32).contiguous(),
             "ln_gamma": f["layer_norm.weight"].to(device=device, dtype=torch.float32).contiguous(),
             "ln_beta": f["layer_norm.bias"].to(device=device, dtype=torch.float32).contiguous(),
-            "w_qkvg": w.to(device=device, dtype=torch.bfloat16).contiguous(),
-            "bias_qkvg": b.to(device=device, dtype=torch.float32).contiguous(),
             "w_o": f["mha.linear_o.weight"].to(device=device, dtype=torch.bfloat16).contiguous()}
 
 
@@ -78,17 +58,11 @@ def pack_transition_z(sd: Dict[str, torch.Tensor], pre: str, device) -> Dict[str
     hidden = f["fc1.weight"].shape[0]
     if hidden != 4 * C_Z or f["fc1.weight"].shape[1] != C_Z:
         raise RuntimeError("the fused transition kernel is built for 128 -> 512 -> 128")
-    rows = []
-    for grp in range(hidden // 16):
-        rows += [f["fc1.weight"][grp * 16:(grp + 1) * 16], f["fc2.weight"][grp * 16:(grp + 1) * 16]]
-    w12, bias12 = _fold(torch.cat(rows, 0), f["norm.weight"], f["norm.bias"])
     w3 = torch.stack([f["fc3.weight"][:, st * 64:(st + 1) * 64] for st in range(hidden // 64)], 0)   # [8][128][64]
-    # tcgen05 kernel: per 64-channel chunk [0.5 * fc1 rows | fc2 rows], LayerNorm affine applied in the kernel
+    # per 64-channel chunk [0.5 * fc1 rows | fc2 rows], LayerNorm affine applied in the kernel
     w12_tc = torch.stack([torch.cat([0.5 * f["fc1.weight"][c * 64:(c + 1) * 64], f["fc2.weight"][c * 64:(c + 1) * 64]], 0)
                           for c in range(hidden // 64)], 0)
-    return {"w12": w12.to(device=device, dtype=torch.bfloat16).contiguous(),
-            "bias12": bias12.to(device=device, dtype=torch.float32).contiguous(),
-            "w3": w3.to(device=device, dtype=torch.bfloat16).contiguous(),
+    return {"w3": w3.to(device=device, dtype=torch.bfloat16).contiguous(),
             "w12_tc": w12_tc.to(device=device, dtype=torch.bfloat16).contiguous(),
             "ln_gamma": f["norm.weight"].to(device=device, dtype=torch.float32).contiguous(),
             "ln_beta": f["norm.bias"].to(device=device, dtype=torch.float32).contiguous()}
