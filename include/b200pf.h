@@ -228,6 +228,12 @@ int b200pf_triatt_producer(const float* z, const float* ln_gamma, const float* l
                            b200pf_bf16* q, b200pf_bf16* k, b200pf_bf16* v, b200pf_bf16* g,
                            b200pf_bf16* tri_bias, long long bias_hs, long long bias_qs,
                            int vt_pitch, int rows, int n, int ending, void* stream);
+/* The same producer reading the pair tensor in bf16 (same view), as it arrives from the sharded exchange. */
+int b200pf_triatt_producer_bf16z(const b200pf_bf16* z, const float* ln_gamma, const float* ln_beta, const float* w_bias_f32,
+                           const b200pf_bf16* w_qkgv,
+                           b200pf_bf16* q, b200pf_bf16* k, b200pf_bf16* v, b200pf_bf16* g,
+                           b200pf_bf16* tri_bias, long long bias_hs, long long bias_qs,
+                           int vt_pitch, int rows, int n, int ending, void* stream);
 
 /* Fused flash-style triangle attention on tcgen05 / TMEM: for each line and head, softmax(q k^T + mask + bias) v
  * with online softmax in the log2 domain; logits never leave the SM.  Replaces the SDPA call at
@@ -251,6 +257,10 @@ int b200pf_triatt_core_tc4(const b200pf_bf16* q, const b200pf_bf16* k, const b20
  * Replaces tt_bio/tenstorrent.py:580-591 and the residual :1013-1021 (reference.py:122-136). */
 int b200pf_triatt_epilogue(float* z, const b200pf_bf16* o, const b200pf_bf16* g,
                            const b200pf_bf16* w_o, long long n_rows_flat, void* stream);
+/* The same product stored instead of added: upd = (o * g) W_o^T in bf16, [n_rows_flat][128].  The sharded ending node
+ * uses it to send the update, not the whole fp32 tensor, back to the row owners. */
+int b200pf_triatt_epilogue_update(b200pf_bf16* upd, const b200pf_bf16* o, const b200pf_bf16* g,
+                                  const b200pf_bf16* w_o, long long n_rows_flat, void* stream);
 
 /* Pair transition: z += W3( silu(W1 LN(z)) * (W2 LN(z)) ), hidden 512 kept on chip, on tcgen05.
  * Replaces tt_bio/tenstorrent.py:869-946 and the residual :1023-1025 (boltz2.py:1241-1246).
@@ -327,6 +337,16 @@ int b200pf_peer_scatter_strided_sync(const void* send, const unsigned long long*
                                      long long src_block_stride, long long src_chunk_stride,
                                      long long dst_slot_stride, long long dst_chunk_stride, int rank, int world,
                                      const b200pf_peer_sync* sync, void* stream);
+/* The strided exchange with fp32 -> bf16 narrowing on the way (the sharded ending-node attention sends z to the
+ * column owners in bf16: the producer rounds its LayerNorm output to bf16 anyway).  Sizes and strides count ELEMENTS
+ * (multiples of 8); `send` is fp32, the receive buffers hold bf16. */
+int b200pf_peer_scatter_strided_f32_bf16_sync(const float* send, const unsigned long long* recv_ptrs, long long chunk_elems, int chunks,
+                                              long long src_block_stride, long long src_chunk_stride,
+                                              long long dst_slot_stride, long long dst_chunk_stride, int rank, int world,
+                                              const b200pf_peer_sync* sync, void* stream);
+/* z[i] += upd[i] for n_elems elements (bf16 update into the fp32 residual stream): the receiving end of an update
+ * that crossed the wire in bf16. */
+int b200pf_add_bf16(float* z, const b200pf_bf16* upd, long long n_elems, void* stream);
 /* Cross-rank barrier of the peer-write exchanges (no counterpart in the reference: its cards never wait on
  * each other; the nearest thing is the job lease that expires when a worker stops reporting,
  * tt_bio/distributed.py:22, 214).  pad_ptrs is a HOST array of the world signal pads as mapped in this process

@@ -208,6 +208,39 @@ def test_attention_core_against_fp32_tier_with_general_masks(dev, n):
         assert rel_l2(upd, ref) < 7e-3, (n, ending)
 
 
+@pytest.mark.parametrize("n", [72, 200])
+def test_attention_with_bf16_input_and_stored_update(dev, n):
+    """The forms the sharded ending node uses: the producer reading the pair tensor in bf16, the epilogue storing
+    the update in bf16 instead of adding it.  Against the fp32-input / in-place forms on the same data."""
+    from tt_boltz_b200 import _lib, ops, weights
+    from tt_boltz_b200._lib import call, ptr, stream
+    sd = strip(synthetic.make_weights(1, seed=5, std=0.05, affine_jitter=0.3))
+    _, z = synthetic.make_inputs(n, seed=4, with_s=False)
+    g = torch.Generator().manual_seed(9)
+    pm = (torch.rand(n, n, generator=g) > 0.1).to(torch.uint8)
+    masks = ops.PairMasks(pm.to(dev))
+    ws = ops.Workspace(n, dev)
+    for ending in (False, True):
+        w = weights.pack_triatt(sd, "tri_att_end." if ending else "tri_att_start.", dev)
+        z_ref = z[0].to(dev).clone()
+        ops.tri_att_bf16(z_ref, masks, w, ws, ending)
+        ref = z_ref.cpu() - z[0]
+        # bf16 input, stored update
+        z16 = z[0].to(dev).to(torch.bfloat16).contiguous()
+        q, k, v, gg, o = ws.buf
+        call("b200pf_triatt_producer_bf16z", ptr(z16), *ops.triatt_producer_weights(w), ptr(q), ptr(k), ptr(v), ptr(gg),
+             ptr(ws.tri_bias), ws.pitch, 4 * ws.pitch, ws.pitch, n, n, int(ending), stream())
+        o_ls, o_ps = (128, n * 128) if ending else (n * 128, 128)
+        call("b200pf_triatt_core_tc4", ptr(q), ptr(k), ptr(v), ws.pitch, ptr(ws.tri_bias), ws.pitch, 4 * ws.pitch,
+             ptr(masks.cols if ending else masks.rows), masks.pitch, ptr(o), o_ls, o_ps, n, n, stream())
+        upd = torch.full((n * n * 128,), float("nan"), dtype=torch.bfloat16, device=dev)
+        call("b200pf_triatt_epilogue_update", ptr(upd), ptr(o), ptr(gg), ptr(w["w_o"]), n * n, stream())
+        assert _lib.device_status() == 0
+        got = upd.float().cpu().view(n, n, 128)
+        assert torch.isfinite(got).all()
+        assert rel_l2(got, ref) < 8e-3, (n, ending)      # z rounded to bf16 before the LayerNorm, update rounded to bf16
+
+
 # ---------------------------------------------------------------------------------------------
 # masks: what is stored at masked-out tokens must not reach the valid region (bit-exact)
 # ---------------------------------------------------------------------------------------------

@@ -166,3 +166,29 @@ def test_exchanges_with_built_in_barrier(dev):
     assert float(torch.ones(4, device=dev).sum()) == 4.0
     with pytest.raises(RuntimeError):
         call("b200pf_peer_scatter_sync", ptr(x), ptrs, 64, 0, 2, C.byref(PeerSync(pad_ptrs2, 2, 1_000_000, 9)), stream())   # channel out of range
+
+
+def test_narrowing_exchange_and_bf16_add(dev):
+    """fp32 row shards -> bf16 column shards with the narrowing exchange (every rank's launch issued in turn, the
+    peers' barrier signals preset), bit-exact against torch's round-to-nearest-even; and z += bf16 update."""
+    from tt_boltz_b200 import _lib
+    from tt_boltz_b200._lib import PeerSync, call, ptr, stream
+    world, nr, c = 4, 8, 16
+    n = world * nr
+    g = torch.Generator().manual_seed(77)
+    z = (torch.randn(n, n, c, generator=g) * 3).to(dev)
+    rows = [z[r * nr:(r + 1) * nr].contiguous() for r in range(world)]
+    cols = [torch.zeros(n, nr, c, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+    ptrs = (C.c_ulonglong * world)(*[t.data_ptr() for t in cols])
+    pads = [torch.ones(16, dtype=torch.int32, device=dev) for _ in range(world)]
+    pad_ptrs = (C.c_ulonglong * world)(*[p.data_ptr() for p in pads])
+    for rank in range(world):
+        call("b200pf_peer_scatter_strided_f32_bf16_sync", ptr(rows[rank]), ptrs, nr * c, nr, nr * c, n * c, nr * nr * c, nr * c,
+             rank, world, C.byref(PeerSync(pad_ptrs, 1, 50_000_000, 4)), stream())
+    assert _lib.device_status() == 0
+    for t in range(world):
+        assert torch.equal(cols[t], z[:, t * nr:(t + 1) * nr].to(torch.bfloat16)), t
+    upd = torch.randn(n * n * c, generator=g).to(torch.bfloat16).to(dev)
+    acc = z.clone().view(-1)
+    call("b200pf_add_bf16", ptr(acc), ptr(upd), n * n * c, stream())
+    assert torch.equal(acc, z.view(-1) + upd.float())

@@ -58,8 +58,12 @@ SIGNATURES = {
     "b200pf_mx_dequant": [_vp, _vp, _vp, _ll, _i, _ll, _i, _i, _i, _i, _vp],
     "b200pf_trimul_epilogue_tc": [_vp, _vp, _ll, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "b200pf_triatt_producer": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _vp],
+    "b200pf_triatt_producer_bf16z": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _vp],
     "b200pf_triatt_core_tc4": [_vp, _vp, _vp, _i, _vp, _ll, _ll, _vp, _i, _vp, _ll, _ll, _i, _i, _vp],
     "b200pf_triatt_epilogue": [_vp, _vp, _vp, _vp, _ll, _vp],
+    "b200pf_triatt_epilogue_update": [_vp, _vp, _vp, _vp, _ll, _vp],
+    "b200pf_add_bf16": [_vp, _vp, _ll, _vp],
+    "b200pf_peer_scatter_strided_f32_bf16_sync": [_vp, C.POINTER(C.c_ulonglong), _ll, _i, _ll, _ll, _ll, _ll, _i, _i, C.POINTER(PeerSync), _vp],
     "b200pf_transition_z_tc": [_vp, _vp, _vp, _vp, _vp, _ll, _vp],
     "b200pf_peer_scatter": [_vp, C.POINTER(C.c_ulonglong), _ll, _i, _i, _vp],
     "b200pf_peer_broadcast": [_vp, C.POINTER(C.c_ulonglong), _ll, _i, _i, _vp],

@@ -57,16 +57,17 @@ __device__ __forceinline__ void peer_barrier_lane(const BarrierArgs& b, int t) {
 __global__ void __launch_bounds__(32) peer_barrier_kernel(BarrierArgs b) { peer_barrier_lane(b, threadIdx.x); }
 
 // Tail of an exchange kernel that carries its own barrier (b.world > 0): every CTA makes its stores visible
-// system-wide and counts itself in; the CTA that completes the count resets it for the next launch and runs
+// system-wide (one fence by thread 0 behind a CTA barrier: a fence per thread cost more than the copy gained from
+// short CTAs) and counts itself in; the CTA that completes the count resets it for the next launch and runs
 // the barrier, so the kernel ends when every peer's blocks have landed here.  One launch instead of two.
 constexpr int PEER_CHANNELS = 8;      // exchanges that may run at the same time on one device use different channels
 __device__ unsigned int g_exchange_ctas_done[PEER_CHANNELS];
 __device__ __forceinline__ void exchange_tail(const BarrierArgs& b) {
     if (b.world <= 0) return;
     __shared__ unsigned int is_last;
-    __threadfence_system();
-    __syncthreads();
+    __syncthreads();                          // the CTA's stores are ordered before thread 0's fence ...
     if (threadIdx.x == 0) {
+        __threadfence_system();               // ... which makes them visible system-wide before the count goes up
         const unsigned int done = atomicAdd(&g_exchange_ctas_done[b.channel], 1u);
         is_last = (done == gridDim.x - 1);
         if (is_last) g_exchange_ctas_done[b.channel] = 0;   // the next launch on this channel starts after this one has ended
@@ -78,10 +79,11 @@ __device__ __forceinline__ void exchange_tail(const BarrierArgs& b) {
 // Each thread moves UNROLL independent 16-byte pieces per step (all loads first, then all stores): NVLink stores
 // are posted, so what limits the rate is how many bytes a thread has in flight between its loads and stores.
 constexpr int PEER_UNROLL = 4;
-// Grid cap in CTAs per SM.  Far more CTAs than fit at once (8 x 256 threads per SM): short CTAs keep every SM
-// evenly loaded to the end of the copy.  Measured between two GPUs (64 MB each way plus 64 MB local per rank):
-// 8 per SM 571 GB/s per direction, 16: 616, 32: 631, 64: 646.
-constexpr int PEER_CTAS_PER_SM = 64;
+// Grid cap in CTAs per SM (8 x 256 threads are resident at once).  Alone between two GPUs more and shorter CTAs copy
+// faster (64 MB each way plus 64 MB local: 8 per SM 571 GB/s per direction, 16: 616, 64: 646), but inside the trunk,
+// with the barrier tail and the single track's kernels on the side stream, 64 per SM made a block 5 % slower than
+// 8 or 16 (4.85 vs 4.60 ms at 2 GPUs), which measured the same.
+constexpr int PEER_CTAS_PER_SM = 16;
 
 __global__ void __launch_bounds__(256)
 peer_scatter_kernel(const uint4* __restrict__ send, PeerPtrs peers, long long block_vec, int rank, int world, BarrierArgs bar) {
@@ -145,6 +147,51 @@ peer_scatter_strided_kernel(const uint4* __restrict__ send, PeerPtrs peers, Stri
             if (dst[u]) *dst[u] = v[u];
     }
     exchange_tail(bar);
+}
+
+// The same strided all-to-all with the elements narrowed on the way: fp32 in this rank's memory, bf16 on the wire
+// and in the receivers' buffers.  All StridedCopy fields count DESTINATION vectors (8 bf16 = 16 bytes); a source
+// vector is the matching 8 floats (two 16-byte loads).
+__global__ void __launch_bounds__(256)
+peer_scatter_strided_f32_bf16_kernel(const float4* __restrict__ send, PeerPtrs peers, StridedCopy c, int rank, int world, BarrierArgs bar) {
+    const unsigned int block_vec = c.chunks * c.chunk_vec;
+    const unsigned long long total = (unsigned long long)block_vec * world;
+    const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+    unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i < total; i += PEER_UNROLL * stride) {
+        float4 v[PEER_UNROLL][2];
+        uint4* dst[PEER_UNROLL];
+#pragma unroll
+        for (int u = 0; u < PEER_UNROLL; ++u) {
+            const unsigned long long e = i + u * stride;
+            dst[u] = nullptr;
+            if (e < total) {
+                const unsigned int slot = (unsigned int)(e / block_vec), rem = (unsigned int)(e - (unsigned long long)slot * block_vec);
+                const unsigned int q = rem / c.chunk_vec, off = rem - q * c.chunk_vec;
+                const int t = (int)((slot + rank) % world);
+                dst[u] = reinterpret_cast<uint4*>(peers.recv[t]) + rank * c.dst_slot + q * c.dst_chunk + off;
+                const float4* src = send + 2 * (t * c.src_block + q * c.src_chunk + off);
+                v[u][0] = __ldg(src);
+                v[u][1] = __ldg(src + 1);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < PEER_UNROLL; ++u)
+            if (dst[u]) *dst[u] = make_uint4(pack_bf16x2(v[u][0].x, v[u][0].y), pack_bf16x2(v[u][0].z, v[u][0].w),
+                                             pack_bf16x2(v[u][1].x, v[u][1].y), pack_bf16x2(v[u][1].z, v[u][1].w));
+    }
+    exchange_tail(bar);
+}
+
+// z += update (bf16 -> fp32), element-wise: how an update that crossed the wire in bf16 reaches the fp32 residual stream.
+__global__ void __launch_bounds__(256) add_bf16_kernel(float4* __restrict__ z, const uint2* __restrict__ upd, long long vec4) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < vec4; i += stride) {
+        const uint2 u = __ldg(upd + i);
+        float4 v = z[i];
+        v.x += bf16_lo(u.x); v.y += bf16_hi(u.x); v.z += bf16_lo(u.y); v.w += bf16_hi(u.y);
+        z[i] = v;
+    }
 }
 
 // All-gather form: the one block of this rank goes to slot `rank` of every rank's receive buffer.
@@ -251,6 +298,54 @@ static int strided_launch(const void* send, const unsigned long long* recv_ptrs,
     long long blocks = (vec + 256 * PEER_UNROLL - 1) / (256 * PEER_UNROLL);
     if (blocks > (long long)sms * PEER_CTAS_PER_SM) blocks = (long long)sms * PEER_CTAS_PER_SM;
     peer_scatter_strided_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(static_cast<const uint4*>(send), p, c, rank, world, bar);
+    B200PF_LAUNCH_CHECK();
+    return B200PF_OK;
+}
+
+extern "C" int b200pf_peer_scatter_strided_f32_bf16_sync(const float* send, const unsigned long long* recv_ptrs, long long chunk_elems, int chunks,
+                                                         long long src_block_stride, long long src_chunk_stride,
+                                                         long long dst_slot_stride, long long dst_chunk_stride, int rank, int world,
+                                                         const b200pf_peer_sync* sync, void* stream) {
+    B200PF_REQUIRE(send && recv_ptrs && sync && world > 0 && world <= PEER_MAX_RANKS && rank >= 0 && rank < world, B200PF_ERR_INVALID,
+                   "peer_scatter_strided_f32_bf16: bad argument (at most %d ranks)", PEER_MAX_RANKS);
+    B200PF_REQUIRE(chunks > 0 && chunk_elems > 0 && chunk_elems % 8 == 0 && (reinterpret_cast<uintptr_t>(send) & 31) == 0 &&
+                       src_block_stride % 8 == 0 && src_chunk_stride % 8 == 0 && dst_slot_stride % 8 == 0 && dst_chunk_stride % 8 == 0 &&
+                       src_block_stride >= 0 && src_chunk_stride >= chunk_elems && dst_slot_stride >= 0 && dst_chunk_stride >= chunk_elems,
+                   B200PF_ERR_INVALID, "peer_scatter_strided_f32_bf16: sizes and strides count elements, multiples of 8, chunk strides >= the chunk; "
+                                       "the source must be 32-byte aligned");
+    B200PF_REQUIRE(chunk_elems / 8 < (1ll << 31) && (long long)chunks * (chunk_elems / 8) < (1ll << 32), B200PF_ERR_UNSUPPORTED,
+                   "peer_scatter_strided_f32_bf16: block too large");
+    PeerPtrs p{};
+    for (int t = 0; t < world; ++t) {
+        B200PF_REQUIRE(recv_ptrs[t] != 0 && recv_ptrs[t] % 16 == 0, B200PF_ERR_INVALID, "peer_scatter_strided_f32_bf16: bad receive pointer of rank %d", t);
+        p.recv[t] = recv_ptrs[t];
+    }
+    BarrierArgs bar;
+    int rc = fill_barrier(&bar, sync, rank, world, "peer_scatter_strided_f32_bf16");
+    if (rc != B200PF_OK) return rc;
+    int dev = 0, sms = 148;
+    B200PF_CUDA(cudaGetDevice(&dev));
+    B200PF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    StridedCopy c{(unsigned int)chunks, (unsigned int)(chunk_elems / 8), src_block_stride / 8, src_chunk_stride / 8,
+                  dst_slot_stride / 8, dst_chunk_stride / 8};
+    const long long vec = (long long)chunks * (chunk_elems / 8) * world;
+    long long blocks = (vec + 256 * PEER_UNROLL - 1) / (256 * PEER_UNROLL);
+    if (blocks > (long long)sms * PEER_CTAS_PER_SM) blocks = (long long)sms * PEER_CTAS_PER_SM;
+    peer_scatter_strided_f32_bf16_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<const float4*>(send), p, c, rank, world, bar);
+    B200PF_LAUNCH_CHECK();
+    return B200PF_OK;
+}
+
+extern "C" int b200pf_add_bf16(float* z, const b200pf_bf16* upd, long long n_elems, void* stream) {
+    B200PF_REQUIRE(z && upd && n_elems > 0 && n_elems % 4 == 0 && aligned16(z) && (reinterpret_cast<uintptr_t>(upd) & 7) == 0,
+                   B200PF_ERR_INVALID, "add_bf16: element count must be a multiple of 4, z 16-byte and the update 8-byte aligned");
+    int dev = 0, sms = 148;
+    B200PF_CUDA(cudaGetDevice(&dev));
+    B200PF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const long long vec4 = n_elems / 4;
+    long long blocks = (vec4 + 255) / 256;
+    if (blocks > (long long)sms * 16) blocks = (long long)sms * 16;
+    add_bf16_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<float4*>(z), reinterpret_cast<const uint2*>(upd), vec4);
     B200PF_LAUNCH_CHECK();
     return B200PF_OK;
 }

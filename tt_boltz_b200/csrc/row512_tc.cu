@@ -134,9 +134,15 @@ row512_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ 
                 if (tn < tiles) {
                     const long long f = flat_of((int)(tn / tpl), (int)(tn % tpl) * TM + warp * 32 + lane);
                     if (f >= 0) {
-                        const char* rowp = reinterpret_cast<const char*>(p.z + f * KC);
+                        if (p.z_bf16) {
+                            const char* rowp = reinterpret_cast<const char*>(p.z_bf16 + f * KC);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) asm volatile("prefetch.global.L2 [%0];" ::"l"(rowp + j * 128));
+                            for (int j = 0; j < 2; ++j) asm volatile("prefetch.global.L2 [%0];" ::"l"(rowp + j * 128));
+                        } else {
+                            const char* rowp = reinterpret_cast<const char*>(p.z + f * KC);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) asm volatile("prefetch.global.L2 [%0];" ::"l"(rowp + j * 128));
+                        }
                     }
                 }
             }
@@ -148,9 +154,18 @@ row512_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ 
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     fl[i] = flat_of(line, pos0 + row0 + i * 4 + rq);
-                    const float4* src = reinterpret_cast<const float4*>(p.z + (fl[i] < 0 ? 0 : fl[i]) * KC);
+                    if (p.z_bf16) {          // warp-uniform: four bf16 channels per lane and j, widened on the fly
+                        const uint2* src = reinterpret_cast<const uint2*>(p.z_bf16 + (fl[i] < 0 ? 0 : fl[i]) * KC);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) v[i][j] = fl[i] < 0 ? make_float4(0.f, 0.f, 0.f, 0.f) : __ldg(src + j * 8 + sub);
+                        for (int j = 0; j < 4; ++j) {
+                            const uint2 w = fl[i] < 0 ? make_uint2(0u, 0u) : __ldg(src + j * 8 + sub);
+                            v[i][j] = make_float4(bf16_lo(w.x), bf16_hi(w.x), bf16_lo(w.y), bf16_hi(w.y));
+                        }
+                    } else {
+                        const float4* src = reinterpret_cast<const float4*>(p.z + (fl[i] < 0 ? 0 : fl[i]) * KC);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) v[i][j] = fl[i] < 0 ? make_float4(0.f, 0.f, 0.f, 0.f) : __ldg(src + j * 8 + sub);
+                    }
                 }
                 // The four rows of a pass are worked on stage by stage (all sums, then all shuffles, ...), not row by
                 // row: one loader warp per scheduler has nothing else to hide a dependent chain behind.

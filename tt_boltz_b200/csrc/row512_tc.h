@@ -9,6 +9,7 @@ namespace r512 {
 
 struct Args {
     const float* z;
+    const __nv_bfloat16* z_bf16;       // when set, the pair tensor is read from here (bf16, same [rows][n][128] view) instead of z
     const float* ln_gamma;             // [128] LayerNorm gain, applied by the loader warps
     const float* ln_beta;              // [128] LayerNorm offset
     const uint8_t* mask;               // triangle multiplication: [rows][n]

@@ -9,7 +9,8 @@
 namespace b200pf {
 
 struct AttEpilogueArgs {
-    float* z;
+    float* z;                       // residual stream to add into, or
+    __nv_bfloat16* upd;             // (z == nullptr) where to store the update itself, bf16, same layout
     const __nv_bfloat16 *o, *g, *w_o;
     long long rows_flat;
 };
@@ -65,11 +66,17 @@ __global__ void __launch_bounds__(WARPS * 32, 1) triatt_epilogue_kernel(AttEpilo
                 for (int hh = 0; hh < 2; ++hh) {
                     long long f = base + mi * 16 + g + hh * 8;
                     if (f >= p.rows_flat) continue;
-                    float* zr = p.z + f * KC + c * 64 + 2 * t;
+                    if (p.z) {
+                        float* zr = p.z + f * KC + c * 64 + 2 * t;
 #pragma unroll
-                    for (int nt = 0; nt < 8; ++nt)      // residual add done by L2 (no load to wait for)
-                        asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(zr + nt * 8), "f"(acc[mi][nt][hh * 2]),
-                                     "f"(acc[mi][nt][hh * 2 + 1]) : "memory");
+                        for (int nt = 0; nt < 8; ++nt)      // residual add done by L2 (no load to wait for)
+                            asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(zr + nt * 8), "f"(acc[mi][nt][hh * 2]),
+                                         "f"(acc[mi][nt][hh * 2 + 1]) : "memory");
+                    } else {
+                        uint32_t* ur = reinterpret_cast<uint32_t*>(p.upd + f * KC + c * 64 + 2 * t);
+#pragma unroll
+                        for (int nt = 0; nt < 8; ++nt) ur[nt * 4] = pack_bf16x2(acc[mi][nt][hh * 2], acc[mi][nt][hh * 2 + 1]);
+                    }
                 }
         }
         __syncwarp();
@@ -91,21 +98,22 @@ static int grid_for_units(long long units, int ctas_per_sm) {
 
 using namespace b200pf;
 
-extern "C" int b200pf_triatt_producer(const float* z, const float* ln_gamma, const float* ln_beta, const float* w_bias_f32,
-                                      const b200pf_bf16* w_qkgv,
-                                      b200pf_bf16* q, b200pf_bf16* k, b200pf_bf16* v, b200pf_bf16* g,
-                                      b200pf_bf16* tri_bias, long long bias_hs, long long bias_qs,
-                                      int vt_pitch, int rows, int n, int ending, void* stream) {
-    B200PF_REQUIRE(z && ln_gamma && ln_beta && w_bias_f32 && w_qkgv && q && k && v && g && tri_bias, B200PF_ERR_INVALID,
+static int triatt_producer(const float* z, const b200pf_bf16* z_bf16, const float* ln_gamma, const float* ln_beta,
+                           const float* w_bias_f32, const b200pf_bf16* w_qkgv,
+                           b200pf_bf16* q, b200pf_bf16* k, b200pf_bf16* v, b200pf_bf16* g,
+                           b200pf_bf16* tri_bias, long long bias_hs, long long bias_qs,
+                           int vt_pitch, int rows, int n, int ending, void* stream) {
+    B200PF_REQUIRE((z || z_bf16) && ln_gamma && ln_beta && w_bias_f32 && w_qkgv && q && k && v && g && tri_bias, B200PF_ERR_INVALID,
                    "triatt_producer: null pointer");
     B200PF_REQUIRE(rows > 0 && n > 0, B200PF_ERR_INVALID, "triatt_producer: bad rows/n");
     B200PF_REQUIRE(bias_hs > 0 && bias_qs > 0, B200PF_ERR_INVALID, "triatt_producer: bad bias strides");
     B200PF_REQUIRE(vt_pitch > 0 && vt_pitch % 8 == 0 && vt_pitch >= (ending ? rows : n), B200PF_ERR_INVALID,
                    "triatt_producer: vt_pitch must be a multiple of 8 covering the positions of a line");
-    B200PF_REQUIRE(aligned16(z) && aligned16(w_qkgv) && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(g),
+    B200PF_REQUIRE(aligned16(z) && aligned16(z_bf16) && aligned16(w_qkgv) && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(g),
                    B200PF_ERR_INVALID, "triatt_producer: pointers must be 16-byte aligned");
     r512::Args a{};
-    a.z = z; a.w = (const __nv_bfloat16*)w_qkgv; a.ln_gamma = ln_gamma; a.ln_beta = ln_beta; a.w_bias_f32 = w_bias_f32;
+    a.z = z; a.z_bf16 = (const __nv_bfloat16*)z_bf16;
+    a.w = (const __nv_bfloat16*)w_qkgv; a.ln_gamma = ln_gamma; a.ln_beta = ln_beta; a.w_bias_f32 = w_bias_f32;
     a.q = (__nv_bfloat16*)q; a.k = (__nv_bfloat16*)k; a.v = (__nv_bfloat16*)v; a.g = (__nv_bfloat16*)g;
     a.tri_bias = (__nv_bfloat16*)tri_bias;
     a.bias_hs = bias_hs; a.bias_qs = bias_qs; a.vt_pitch = vt_pitch;
@@ -113,15 +121,47 @@ extern "C" int b200pf_triatt_producer(const float* z, const float* ln_gamma, con
     return r512::launch_triatt(a, (cudaStream_t)stream);
 }
 
-extern "C" int b200pf_triatt_epilogue(float* z, const b200pf_bf16* o, const b200pf_bf16* g,
-                                      const b200pf_bf16* w_o, long long n_rows_flat, void* stream) {
-    B200PF_REQUIRE(z && o && g && w_o && n_rows_flat > 0, B200PF_ERR_INVALID, "triatt_epilogue: bad argument");
-    B200PF_REQUIRE(aligned16(z) && aligned16(o) && aligned16(g) && aligned16(w_o), B200PF_ERR_INVALID,
+extern "C" int b200pf_triatt_producer(const float* z, const float* ln_gamma, const float* ln_beta, const float* w_bias_f32,
+                                      const b200pf_bf16* w_qkgv,
+                                      b200pf_bf16* q, b200pf_bf16* k, b200pf_bf16* v, b200pf_bf16* g,
+                                      b200pf_bf16* tri_bias, long long bias_hs, long long bias_qs,
+                                      int vt_pitch, int rows, int n, int ending, void* stream) {
+    B200PF_REQUIRE(z, B200PF_ERR_INVALID, "triatt_producer: null pointer");
+    return triatt_producer(z, nullptr, ln_gamma, ln_beta, w_bias_f32, w_qkgv, q, k, v, g, tri_bias, bias_hs, bias_qs, vt_pitch,
+                           rows, n, ending, stream);
+}
+
+extern "C" int b200pf_triatt_producer_bf16z(const b200pf_bf16* z, const float* ln_gamma, const float* ln_beta, const float* w_bias_f32,
+                                            const b200pf_bf16* w_qkgv,
+                                            b200pf_bf16* q, b200pf_bf16* k, b200pf_bf16* v, b200pf_bf16* g,
+                                            b200pf_bf16* tri_bias, long long bias_hs, long long bias_qs,
+                                            int vt_pitch, int rows, int n, int ending, void* stream) {
+    B200PF_REQUIRE(z, B200PF_ERR_INVALID, "triatt_producer_bf16z: null pointer");
+    return triatt_producer(nullptr, z, ln_gamma, ln_beta, w_bias_f32, w_qkgv, q, k, v, g, tri_bias, bias_hs, bias_qs, vt_pitch,
+                           rows, n, ending, stream);
+}
+
+static int triatt_epilogue(float* z, b200pf_bf16* upd, const b200pf_bf16* o, const b200pf_bf16* g,
+                           const b200pf_bf16* w_o, long long n_rows_flat, void* stream) {
+    B200PF_REQUIRE((z || upd) && o && g && w_o && n_rows_flat > 0, B200PF_ERR_INVALID, "triatt_epilogue: bad argument");
+    B200PF_REQUIRE(aligned16(z) && aligned16(upd) && aligned16(o) && aligned16(g) && aligned16(w_o), B200PF_ERR_INVALID,
                    "triatt_epilogue: pointers must be 16-byte aligned");
-    AttEpilogueArgs p{z, (const __nv_bfloat16*)o, (const __nv_bfloat16*)g, (const __nv_bfloat16*)w_o, n_rows_flat};
+    AttEpilogueArgs p{z, (__nv_bfloat16*)upd, (const __nv_bfloat16*)o, (const __nv_bfloat16*)g, (const __nv_bfloat16*)w_o, n_rows_flat};
     B200PF_SMEM_ATTR_ONCE(triatt_epilogue_kernel, ATT_EPILOGUE_SMEM);
     long long units = (n_rows_flat + UNIT - 1) / UNIT;
     triatt_epilogue_kernel<<<grid_for_units(units, 2), WARPS * 32, ATT_EPILOGUE_SMEM, (cudaStream_t)stream>>>(p);
     B200PF_LAUNCH_CHECK();
     return B200PF_OK;
+}
+
+extern "C" int b200pf_triatt_epilogue(float* z, const b200pf_bf16* o, const b200pf_bf16* g,
+                                      const b200pf_bf16* w_o, long long n_rows_flat, void* stream) {
+    B200PF_REQUIRE(z, B200PF_ERR_INVALID, "triatt_epilogue: bad argument");
+    return triatt_epilogue(z, nullptr, o, g, w_o, n_rows_flat, stream);
+}
+
+extern "C" int b200pf_triatt_epilogue_update(b200pf_bf16* upd, const b200pf_bf16* o, const b200pf_bf16* g,
+                                             const b200pf_bf16* w_o, long long n_rows_flat, void* stream) {
+    B200PF_REQUIRE(upd, B200PF_ERR_INVALID, "triatt_epilogue_update: bad argument");
+    return triatt_epilogue(nullptr, upd, o, g, w_o, n_rows_flat, stream);
 }

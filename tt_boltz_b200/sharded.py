@@ -195,6 +195,26 @@ def rows_to_cols(z_loc: torch.Tensor, group=None) -> torch.Tensor:
     return all_to_all_blocks(send, group, "z_rows_to_cols").view(n, nr, c)   # [src s * nr + i_local][j_local][c]
 
 
+# Around the sharded ending-node attention z crosses the wire in bf16 and only the update comes back (half the bytes
+# of the fp32 round trip); "0" keeps the fp32 exchange, which reproduces the one-GPU result bit for bit.
+_BF16_EXCHANGE = {"enabled": os.environ.get("B200PF_BF16_EXCHANGE", "1") != "0"}
+
+
+def rows_to_cols_bf16(z_loc: torch.Tensor, group=None) -> Optional[torch.Tensor]:
+    """fp32 row shard [nr, N, C] -> bf16 column shard [N, nr, C], narrowed by the exchange kernel itself; None when
+    peer copies are off or unavailable (the caller then takes the fp32 path)."""
+    if not (z_loc.is_cuda and _PEER_COPY["enabled"] and z_loc.dtype == torch.float32):
+        return None
+    nr, n, c = z_loc.shape
+    peer = _peer_buffers("z_rows_to_cols_bf16", n * nr * c, torch.bfloat16, z_loc.device, group)
+    if peer is None:
+        return None
+    recv, _, ptrs = peer
+    call("b200pf_peer_scatter_strided_f32_bf16_sync", ptr(z_loc), ptrs, nr * c, nr, nr * c, n * c, nr * nr * c, nr * c,
+         dist.get_rank(group), dist.get_world_size(group), C.byref(_next_sync(z_loc.device, group, 0)), stream())
+    return recv.view(n, nr, c)
+
+
 def cols_to_rows(zc: torch.Tensor, group=None) -> torch.Tensor:
     """Inverse of rows_to_cols: column shard [N, nr, C] -> row shard [nr, N, C].  On CUDA every piece lands at its
     place in the receiver's row shard (no unpacking copy); the result is then the receive buffer (valid until the
@@ -318,15 +338,31 @@ def sharded_block(layer: B200PairformerLayer, s: Optional[torch.Tensor], z_loc: 
 
     # ---- triangle attention, ending node (lines = local columns of the column shard) ------------
     w = pk["tri_att_end"]
-    zc = rows_to_cols(z_loc, group)                                                  # [N][nr][128] fp32
-    call("b200pf_triatt_producer", ptr(zc), *ops.triatt_producer_weights(w), ptr(q), ptr(k), ptr(v), ptr(g),
-         ptr(bias_loc), pn, 4 * pn, pn, n, nr, 1, st)
-    bias_all = all_gather_cat(bias_loc, group, "tri_bias")
-    call("b200pf_triatt_core_tc4", ptr(q), ptr(k), ptr(v), pn, ptr(bias_all), pn, 4 * pn, ptr(masks.cols[r0:r0 + nr]),
-         masks.pitch, ptr(o), C_Z, nr * C_Z, nr, n, st)
-    call("b200pf_triatt_epilogue", ptr(zc), ptr(o), ptr(g), ptr(w["w_o"]), n * nr, st)
-    z_loc = cols_to_rows(zc, group)
-    del q, k, v, g, o, zc, bias_loc, bias_all
+    zc16 = rows_to_cols_bf16(z_loc, group) if _BF16_EXCHANGE["enabled"] else None
+    if zc16 is not None:
+        # bf16 on the wire both ways: z goes to the column owners narrowed (the producer rounds its LayerNorm output
+        # to bf16 anyway), and only the UPDATE comes back, to be added into the fp32 rows that never moved
+        call("b200pf_triatt_producer_bf16z", ptr(zc16), *ops.triatt_producer_weights(w), ptr(q), ptr(k), ptr(v), ptr(g),
+             ptr(bias_loc), pn, 4 * pn, pn, n, nr, 1, st)
+        bias_all = all_gather_cat(bias_loc, group, "tri_bias")
+        call("b200pf_triatt_core_tc4", ptr(q), ptr(k), ptr(v), pn, ptr(bias_all), pn, 4 * pn, ptr(masks.cols[r0:r0 + nr]),
+             masks.pitch, ptr(o), C_Z, nr * C_Z, nr, n, st)
+        upd = _bf16(n * nr * C_Z, dev).view(n, nr, C_Z)
+        call("b200pf_triatt_epilogue_update", ptr(upd), ptr(o), ptr(g), ptr(w["w_o"]), n * nr, st)
+        upd_rows = cols_to_rows(upd, group)                                           # [nr][N][128] bf16
+        call("b200pf_add_bf16", ptr(z_loc), ptr(upd_rows), nr * n * C_Z, st)
+        del upd, upd_rows
+    else:
+        zc = rows_to_cols(z_loc, group)                                              # [N][nr][128] fp32
+        call("b200pf_triatt_producer", ptr(zc), *ops.triatt_producer_weights(w), ptr(q), ptr(k), ptr(v), ptr(g),
+             ptr(bias_loc), pn, 4 * pn, pn, n, nr, 1, st)
+        bias_all = all_gather_cat(bias_loc, group, "tri_bias")
+        call("b200pf_triatt_core_tc4", ptr(q), ptr(k), ptr(v), pn, ptr(bias_all), pn, 4 * pn, ptr(masks.cols[r0:r0 + nr]),
+             masks.pitch, ptr(o), C_Z, nr * C_Z, nr, n, st)
+        call("b200pf_triatt_epilogue", ptr(zc), ptr(o), ptr(g), ptr(w["w_o"]), n * nr, st)
+        z_loc = cols_to_rows(zc, group)
+        del zc
+    del q, k, v, g, o, zc16, bias_loc, bias_all
 
     # ---- pair transition ---------------------------------------------------------------------------
     ops.transition_z_bf16(z_loc, pk["transition_z"])
