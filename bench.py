@@ -219,6 +219,71 @@ def parity_against_fixture(n: int, blocks: int, pad_frac: float, s_out, z_out, t
             "tolerance": tol, "ok": bool(rz < tol and rs < tol)}
 
 
+def outer_product_mean_leg(n: int, peaks, cpu: bool):
+    """The MSA stack's outer-product mean at the benchmark's token count and 1024 sequences (the reference's
+    --num_subsampled_msa default): ms per call with inputs resident, per entry point, the outer GEMM against the
+    sustained bf16 peak, parity of a small case against the CPU oracle, and the oracle timed on a bounded sample."""
+    import collections
+    import time as _time
+    from oracle import msa_oracle
+    from tt_boltz_b200 import B200OuterProductMean, _lib, synthetic
+    s_len = 1024
+    mod = B200OuterProductMean()
+    w = synthetic.make_opm_weights()
+    mod.load_state_dict(w)
+    mod.cuda()
+    ms_small, mask_small = synthetic.make_msa_inputs(96, 64, drop=0.3, seed=9)
+    got = mod(ms_small[None].cuda(), mask_small[None].cuda())[0].cpu()
+    with torch.no_grad():
+        want = msa_oracle.outer_product_mean(ms_small, mask_small, w)
+    rel = float((got.double() - want.double()).norm() / want.double().norm())
+    g = torch.Generator(device="cuda").manual_seed(0)
+    m = torch.randn(1, s_len, n, 64, device="cuda", generator=g)
+    mask = (torch.rand(1, s_len, n, device="cuda", generator=g) > 0.1).float()
+    z = torch.zeros(1, n, n, 128, device="cuda")
+    for _ in range(3):
+        mod.add_into(z, m, mask)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(5):
+        mod.add_into(z, m, mask)
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / 5
+    _lib.timer = _lib.KernelTimer()
+    mod.add_into(z, m, mask)
+    torch.cuda.synchronize()
+    events, _lib.timer = _lib.timer.events, None
+    per = collections.defaultdict(float)
+    for name, e0, e1 in events:
+        per[name] += e0.elapsed_time(e1)
+    flop_outer = 2.0 * s_len * (32.0 * n) ** 2
+    flop = flop_outer + 2.0 * n * n * 1024 * 128
+    out = {"config": {"workload": "outer-product mean of the MSA stack (reference.py:571-669)", "tokens": n, "msa_depth": s_len,
+                      "mask": "10 % of (sequence, token) entries masked", "inputs": "resident, 256 MB m > L2"},
+           "ms": ms, "tflops": flop / (ms * 1e-3) / 1e12, "kernels_ms": dict(per),
+           "roofline": {"kernel": "b200pf_opm_outer", "bound": "tensor", "achieved": flop_outer / (per["b200pf_opm_outer"] * 1e-3) / 1e12,
+                        "peak": peaks["tflops_sustained"], "unit": "TFLOP/s",
+                        "frac": flop_outer / (per["b200pf_opm_outer"] * 1e-3) / 1e12 / peaks["tflops_sustained"],
+                        "peak_source": peaks["source"]},
+           "parity": {"rel_l2": rel, "tolerance": 2e-2, "ok": rel < 2e-2, "case": "96 sequences x 64 tokens, 30 % masked, CPU oracle",
+                      "device_status": _lib.device_status()},
+           "cpu_baseline": None}
+    if cpu:
+        nc = min(n, 512)
+        mc, kc = synthetic.make_msa_inputs(s_len, nc, drop=0.1, seed=1)
+        t0 = _time.perf_counter()
+        with torch.no_grad():
+            msa_oracle.outer_product_mean(mc, kc, w)
+        sec = _time.perf_counter() - t0
+        out["cpu_baseline"] = {"value": sec * 1e3 * (n / nc) ** 2, "unit": "ms", "cores": os.cpu_count() or 1, "kind": "port",
+                               "sample": f"the oracle on {nc} of {n} tokens ({sec:.2f} s), scaled by the pair count"}
+    del m, mask, z, mod
+    torch.cuda.empty_cache()
+    return out
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -231,6 +296,7 @@ def main() -> None:
     ap.add_argument("--cpu-budget", type=float, default=150.0, help="seconds the CPU legs may spend")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-next", action="store_true", help="skip the outer-product-mean leg (one GPU only)")
     ap.add_argument("--pad-frac", type=float, default=0.0, help="fraction of tokens masked at random (seed 3); 0 = all-ones masks")
     ap.add_argument("--precision", default="bf16", choices=["bf16", "mxfp8"],
                     help="bf16 = the headline tier; mxfp8 = triangle-multiplication operands in MXFP8")
@@ -410,6 +476,9 @@ def main() -> None:
             roofline["algorithmic_per_launch"] = {"flop": fl, "bytes": by}
             roofline["launch_ms"] = kernels[top]["ms_per_launch"]
 
+    next_rows = None
+    if world == 1 and not args.no_next:
+        next_rows = {"outer_product_mean": outer_product_mean_leg(n, peaks, not args.no_cpu)}
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -428,7 +497,7 @@ def main() -> None:
             "tflops": block_flops(n) / (ms_block * 1e-3) / 1e12,
             "config": workload_config(args),
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "parity": parity, "roofline": roofline, "kernels": kernels,
-            "cpu_baseline": cpu}
+            "cpu_baseline": cpu, "next_rows": next_rows}
     print(json.dumps(line), flush=True)
 
 

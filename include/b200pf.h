@@ -300,6 +300,37 @@ int b200pf_tri_mul_noalloc(float* z, const uint8_t* mask, const float* ln_gamma,
                            const float* wsum, const float* wb,
                            int n, int incoming, void* stream);
 
+/* ----------------------------------------------------------------------------------------
+ * Outer-product mean: the MSA stack's write into the pair tensor, the step before the Pairformer
+ * in every recycle.  Replaces OuterProductMean at tt_bio/tenstorrent.py:1632-1718 (reference.py:571-669):
+ *   z[i][j][:] (+)= W_o vec(sum_s a[s][i][:] (x) b[s][j][:]) / max(1, sum_s mask[s][i] mask[s][j]) + bias,
+ *   a = mask * LN(m) W_a^T, b = mask * LN(m) W_b^T;   m fp32 [S][N][64], mask uint8 [S][N], 32 channels per side.
+ * Four stages: producer -> b200pf_opm_outer -> b200pf_trimul_contract (one channel, A = the outer products
+ * [pairs][1024], B = W_o bf16 [128][1024]) -> finalize.  A caller bounds the memory of the outer products by
+ * walking blocks of tokens i (n_i of them per call).
+ * ---------------------------------------------------------------------------------------- */
+
+/* LN + both projections + mask, written transposed as K-major GEMM operands:
+ * a_t[(tok*32 + c)][s], b_t[(tok*32 + d)][s], bf16, `pitch` elements per row (>= s_len, multiple of 8; elements at
+ * s >= s_len are not written and not read).  w_ab fp32 [64][64]: rows 0-31 proj_a.weight, rows 32-63 proj_b.weight. */
+int b200pf_opm_producer(const float* m, const uint8_t* mask, const float* ln_gamma, const float* ln_beta,
+                        const float* w_ab, b200pf_bf16* a_t, b200pf_bf16* b_t, int s_len, int n, int pitch, void* stream);
+
+/* x2[i][j][c][d] = sum_s a_t[(i, c)][s] * b_t[(j, d)][s] for n_i tokens i (a_t points at the first one's rows) and
+ * all n_j tokens j: bf16 [n_i][n_j][32][32], fp32 accumulation (the contraction kernel of the triangle
+ * multiplication with its output regrouped per token pair). */
+int b200pf_opm_outer(const b200pf_bf16* a_t, const b200pf_bf16* b_t, b200pf_bf16* x2, int s_len, int n_i, int n_j,
+                     int pitch, void* stream);
+
+/* bits[tok][w]: bit b of word w = mask[w*32 + b][tok] != 0; (s_len + 31) / 32 words per token. */
+int b200pf_opm_mask_bits(const uint8_t* mask, uint32_t* bits, int s_len, int n, void* stream);
+
+/* z[il][j][:] = (accumulate ? z[il][j][:] : 0) + y[il*n + j][:] / count(i0 + il, j) + bias for il < n_i, j < n;
+ * y bf16 [n_i*n][128] (the projected outer products), z fp32 rows of token i0 onwards, count from the mask bits
+ * (at least 1).  At most 16384 sequences. */
+int b200pf_opm_finalize(const b200pf_bf16* y, const uint32_t* bits, const float* bias, float* z, int s_len,
+                        int i0, int n_i, int n, int accumulate, void* stream);
+
 /* All-to-all of equal blocks over peer mappings (multi-GPU path, no counterpart in the reference, whose
  * cards do not exchange data: tt_bio/distributed.py fans whole jobs out).  Block t of `send` (world blocks
  * of block_bytes) is written to slot `rank` of rank t's receive buffer; recv_ptrs is a HOST array of the

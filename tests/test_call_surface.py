@@ -10,7 +10,7 @@ import inspect
 import pytest
 import torch
 
-from tt_boltz_b200 import (B200PairformerLayer, B200PairformerModule, B200PairformerNoSeqLayer,
+from tt_boltz_b200 import (B200OuterProductMean, B200PairformerLayer, B200PairformerModule, B200PairformerNoSeqLayer,
                            B200PairformerNoSeqModule, B200RecyclingTrunk, synthetic)
 
 
@@ -97,3 +97,16 @@ def test_recycling_trunk_carries_the_reference_key_names():
     assert _params(B200RecyclingTrunk.forward) == ["self", "s_init", "z_init", "mask", "pair_mask", "recycling_steps", "pair_update"]
     with pytest.raises(RuntimeError, match="CUDA"):
         trunk(torch.zeros(1, 8, 384), torch.zeros(1, 8, 8, 128))
+
+
+def test_outer_product_mean_surface():
+    """tt_bio/reference.py:574-597: constructor (c_in, c_hidden, c_out), forward(m, mask, chunk_size), six parameters."""
+    mod = B200OuterProductMean(64, 32, 128)
+    assert _params(B200OuterProductMean.forward) == ["self", "m", "mask", "chunk_size"]
+    assert set(mod.state_dict().keys()) == set(synthetic.make_opm_weights().keys())
+    mod.load_state_dict(synthetic.make_opm_weights(), strict=True)
+    with pytest.raises(ValueError):
+        B200OuterProductMean(64, 16, 128)
+    m, mask = synthetic.make_msa_inputs(4, 8)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        mod(m[None], mask[None])

@@ -10,12 +10,14 @@ import numpy as np
 import pytest
 import torch
 
+from oracle import msa_oracle
 from oracle import pairformer_oracle as orc
 from tests.golden.make_golden import weight_checksum
 from tt_boltz_b200 import synthetic
 from tests.conftest import rel_l2
 
 CASES = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.npz")))
+OPM_CASES = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(os.path.dirname(__file__), "golden", "msa", "opm_*.npz")))
 
 
 def load_case(golden_dir, name):
@@ -67,3 +69,18 @@ def test_oracle_padding_isolated(golden_dir):
     assert torch.equal(za[v][:, v], zb[v][:, v])
     assert torch.equal(sa[v], sb[v])
     assert torch.isfinite(zb).all() and torch.isfinite(sb).all()
+
+
+@pytest.mark.parametrize("name", OPM_CASES)
+def test_outer_product_mean_oracle_matches_reference_outputs(golden_dir, name):
+    """tests/golden/msa/make_opm.py stored what tt_bio.reference.OuterProductMean returns (both of its branches)."""
+    g = np.load(os.path.join(golden_dir, "msa", name + ".npz"))
+    w = synthetic.make_opm_weights(seed=int(g["weight_seed"]))
+    m, mask = synthetic.make_msa_inputs(int(g["s"]), int(g["n"]), drop=float(g["drop"]), seed=int(g["input_seed"]))
+    with torch.no_grad():
+        out = msa_oracle.outer_product_mean(m, mask, w)
+    assert rel_l2(out, torch.from_numpy(g["out"])) < 2e-6
+
+
+def test_outer_product_mean_fixtures_present():
+    assert len(OPM_CASES) >= 3

@@ -54,6 +54,10 @@ SIGNATURES = {
     "b200pf_trimul_producer": [_vp, _vp, _vp, _vp, _vp, C.POINTER(PlaneOut), C.POINTER(PlaneOut), _i, _i, _i, _i, _vp],
     "b200pf_trimul_contract": [C.POINTER(Planes), C.POINTER(Planes), _vp, _vp, _vp, _ll, _i, _i, _ll, _i, _i, _vp],
     "b200pf_mx_scale_bytes": [_i, _i, _i],
+    "b200pf_opm_producer": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "b200pf_opm_outer": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "b200pf_opm_mask_bits": [_vp, _vp, _i, _i, _vp],
+    "b200pf_opm_finalize": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "b200pf_trimul_producer_mx": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _vp],
     "b200pf_mx_dequant": [_vp, _vp, _vp, _ll, _i, _ll, _i, _i, _i, _i, _vp],
     "b200pf_trimul_epilogue_tc": [_vp, _vp, _ll, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],

@@ -28,6 +28,9 @@ struct GemmShape {
     long long x_plane_stride;
     int x_row_group;     // output rows per group (> m_rows when the output is plain planes)
     long long x_group_stride;
+    int x_cols;          // columns written (whole 8-column vectors below this bound)
+    int x_col_group;     // > 0: output columns in groups of this many (a multiple of 32), x_colgroup_stride elements apart
+    long long x_colgroup_stride;
 };
 // Output element (d, row, col) lives at (row / x_row_group) * x_group_stride + d * x_plane_stride + (row % x_row_group) * x_pitch + col.
 __device__ __forceinline__ long long x_row_offset(const GemmShape& s, int d, int row) {
@@ -148,20 +151,23 @@ trimul_contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 int col = n0 + c * 32;
-                if (col >= s.x_pitch) break;          // warp-uniform
+                if (col >= s.x_cols) break;           // warp-uniform
+                __nv_bfloat16* xdst = s.x_col_group > 0
+                                          ? xrow + (long long)(col / s.x_col_group) * s.x_colgroup_stride + (col % s.x_col_group)
+                                          : xrow + col;
                 uint32_t r[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + ab * BN + c * 32, r);
                 tmem_ld_wait();
                 if (row < s.m_rows) {
 #pragma unroll
                     for (int v = 0; v < 4; ++v) {
-                        if (col + v * 8 + 8 <= s.x_pitch) {
+                        if (col + v * 8 + 8 <= s.x_cols) {
                             uint4 o;
                             o.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
                             o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
                             o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
                             o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
-                            *reinterpret_cast<uint4*>(xrow + col + v * 8) = o;
+                            *reinterpret_cast<uint4*>(xdst + v * 8) = o;
                         }
                     }
                 }
@@ -229,6 +235,29 @@ static int check_planes(const b200pf_planes* p, const char* what) {
     return B200PF_OK;
 }
 
+static int launch_contract_tc(const b200pf_planes* a, const b200pf_planes* b, b200pf_bf16* x, const GemmShape& s, cudaStream_t st) {
+    unsigned int* status = device_status_word();
+    B200PF_REQUIRE(status, B200PF_ERR_CUDA, "trimul_contract: no device status word");
+    CUtensorMap map_a, map_b;
+    int rc;
+    if ((rc = make_plane_map(&map_a, a, s.channels, "A")) != B200PF_OK) return rc;
+    if ((rc = make_plane_map(&map_b, b, s.channels, "B")) != B200PF_OK) return rc;
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    B200PF_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        B200PF_CUDA(cudaFuncSetAttribute(trimul_contract_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM));
+        attr_set[dev] = true;
+    }
+    int sms = 0;
+    B200PF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    long long tiles = (long long)s.channels * ((s.m_rows + BM - 1) / BM) * ((s.n_rows + BN - 1) / BN);
+    unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+    trimul_contract_tc_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(map_a, map_b, (__nv_bfloat16*)x, s, status);
+    B200PF_LAUNCH_CHECK();
+    return B200PF_OK;
+}
+
 namespace gemm_mx {   // block-scaled fp8 kernel, trimul_gemm_mx.cu
 int launch_contract(const b200pf_planes* a, const b200pf_planes* b, const void* a_scales, const void* b_scales,
                     b200pf_bf16* x, long long x_plane_stride, int x_pitch, int x_row_group, long long x_group_stride,
@@ -269,30 +298,44 @@ extern "C" int b200pf_trimul_contract(const b200pf_planes* a, const b200pf_plane
     const bool grouped = x_row_group > 0 && x_row_group < s.m_rows;
     s.x_row_group = grouped ? x_row_group : s.m_rows + BM;
     s.x_group_stride = grouped ? x_group_stride : 0;
+    s.x_cols = x_pitch;
+    s.x_col_group = 0;
+    s.x_colgroup_stride = 0;
     B200PF_REQUIRE(x_pitch % 8 == 0 && x_pitch >= s.n_rows &&
                        x_plane_stride >= (long long)x_pitch * (grouped ? x_row_group : s.m_rows) && x_plane_stride % 8 == 0,
                    B200PF_ERR_INVALID, "trimul_contract: bad x pitch / plane stride");
     B200PF_REQUIRE(!grouped || (x_group_stride % 8 == 0 && x_group_stride >= x_plane_stride * channels), B200PF_ERR_INVALID,
                    "trimul_contract: bad x group stride");
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
     B200PF_REQUIRE(variant == 0, B200PF_ERR_UNSUPPORTED, "trimul_contract: variant %d is not built", variant);
-    unsigned int* status = device_status_word();
-    B200PF_REQUIRE(status, B200PF_ERR_CUDA, "trimul_contract: no device status word");
-    CUtensorMap map_a, map_b;
-    if ((rc = make_plane_map(&map_a, a, channels, "A")) != B200PF_OK) return rc;
-    if ((rc = make_plane_map(&map_b, b, channels, "B")) != B200PF_OK) return rc;
-    static bool attr_set[64] = {false};
-    int dev = 0;
-    B200PF_CUDA(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        B200PF_CUDA(cudaFuncSetAttribute(trimul_contract_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM));
-        attr_set[dev] = true;
-    }
-    int sms = 0;
-    B200PF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    long long tiles = (long long)channels * ((s.m_rows + BM - 1) / BM) * ((s.n_rows + BN - 1) / BN);
-    unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-    trimul_contract_tc_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(map_a, map_b, (__nv_bfloat16*)x, s, status);
-    B200PF_LAUNCH_CHECK();
-    return B200PF_OK;
+    return launch_contract_tc(a, b, x, s, static_cast<cudaStream_t>(stream));
+}
+
+/* Outer product of the outer-product-mean: x2[i][j][c][d] = sum_s a_t[(i, c)][s] * b_t[(j, d)][s], the same kernel with
+ * its output rows (i, c) and columns (j, d) regrouped so that the 32 x 32 block of a token pair is contiguous. */
+extern "C" int b200pf_opm_outer(const b200pf_bf16* a_t, const b200pf_bf16* b_t, b200pf_bf16* x2,
+                                int s_len, int n_i, int n_j, int pitch, void* stream) {
+    B200PF_REQUIRE(a_t && b_t && x2 && aligned16(a_t) && aligned16(b_t) && aligned16(x2), B200PF_ERR_INVALID,
+                   "opm_outer: null or misaligned pointer");
+    B200PF_REQUIRE(s_len > 0 && n_i > 0 && n_j > 0 && pitch >= s_len && pitch % 8 == 0, B200PF_ERR_INVALID, "opm_outer: bad sizes");
+    B200PF_REQUIRE((long long)n_j * 32 <= 0x7fffffffLL / 2 && (long long)n_i * 32 <= 0x7fffffffLL / 2, B200PF_ERR_UNSUPPORTED,
+                   "opm_outer: too many tokens");
+    b200pf_planes a{a_t, (long long)pitch * n_i * 32, 0, pitch, n_i * 32, s_len, 1, 0};
+    b200pf_planes b{b_t, (long long)pitch * n_j * 32, 0, pitch, n_j * 32, s_len, 1, 0};
+    GemmShape s;
+    s.m_rows = n_i * 32;
+    s.n_rows = n_j * 32;
+    s.k_total = s_len;
+    s.a_kseg_cols = s_len + BK;
+    s.b_kseg_cols = s_len + BK;
+    s.a_rowseg_rows = s.m_rows + BM;
+    s.b_rowseg_rows = s.n_rows + BN;
+    s.channels = 1;
+    s.x_pitch = 32;                                   // row (i, c): c * 32 inside the pair's block
+    s.x_plane_stride = 0;
+    s.x_row_group = 32;
+    s.x_group_stride = (long long)n_j * 1024;         // next i
+    s.x_cols = s.n_rows;
+    s.x_col_group = 32;
+    s.x_colgroup_stride = 1024;                       // next j
+    return launch_contract_tc(&a, &b, x2, s, static_cast<cudaStream_t>(stream));
 }

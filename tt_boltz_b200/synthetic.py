@@ -139,3 +139,28 @@ def sampled_fixture_errors(fixture, blocks: int, s_out: torch.Tensor, z_out: tor
     rz = float((z_got - z_ref).norm() / z_ref.norm())
     rs = float((s_got - s_ref).norm() / s_ref.norm())
     return rz, rs
+
+
+def make_opm_weights(seed: int = 11, c_in: int = 64, c_hidden: int = 32, c_out: int = 128, std: float = 0.05,
+                     affine_jitter: float = 0.2) -> Dict[str, torch.Tensor]:
+    """State dict of the outer-product mean with the reference's key names (tt_bio/reference.py:590-596); every
+    parameter random so that nothing the upstream zero-initialises (proj_o) hides an error."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return {
+        "norm.weight": 1 + affine_jitter * torch.randn(c_in, generator=g),
+        "norm.bias": affine_jitter * torch.randn(c_in, generator=g),
+        "proj_a.weight": torch.randn(c_hidden, c_in, generator=g) * std * 4,
+        "proj_b.weight": torch.randn(c_hidden, c_in, generator=g) * std * 4,
+        "proj_o.weight": torch.randn(c_out, c_hidden * c_hidden, generator=g) * std,
+        "proj_o.bias": torch.randn(c_out, generator=g) * std,
+    }
+
+
+def make_msa_inputs(s: int, n: int, c_in: int = 64, drop: float = 0.0, seed: int = 5) -> Tuple[torch.Tensor, torch.Tensor]:
+    """MSA activations m [s, n, c_in] ~ N(0.3, 1) and a mask [s, n] of ones with a share `drop` of zeros (the first
+    sequence, the query, is never masked)."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    m = torch.randn(s, n, c_in, generator=g) + 0.3
+    mask = (torch.rand(s, n, generator=g) >= drop).float()
+    mask[0] = 1.0
+    return m, mask
