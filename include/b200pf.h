@@ -331,6 +331,32 @@ int b200pf_opm_mask_bits(const uint8_t* mask, uint32_t* bits, int s_len, int n, 
 int b200pf_opm_finalize(const b200pf_bf16* y, const uint32_t* bits, const float* bias, float* z, int s_len,
                         int i0, int n_i, int n, int accumulate, void* stream);
 
+/* ----------------------------------------------------------------------------------------
+ * Row kernels of the MSA stack (m fp32 [S][N][64]) around GEMMs run by b200pf_trimul_contract.  The token axis
+ * of every bf16 operand is padded to np (a multiple of 8, >= n); padding rows are zero.
+ *   pair-weighted averaging (tt_bio/tenstorrent.py:1542-1629, reference.py:672-800):
+ *     ln = b200pf_msa_ln_bf16(m)                         [S*np][64]
+ *     vg = contract(A = [proj_m ; proj_g] bf16 [512][64], B = ln)     -> [512][S*np]: v rows 0-255, g rows 256-511
+ *     logits = b200pf_ln_proj_heads(z, norm_z, proj_z, 8 heads);  w = b200pf_pwa_softmax(logits, mask)
+ *     o = contract over 8 heads (A = v as [8][32*S][np], B = w [8][n][pitch])   -> [8][32*S][np]
+ *     b200pf_pwa_epilogue: m += W_o (sigmoid(g) * o)
+ *   MSA transition (Transition(64, 256), tt_bio/boltz2.py:1188-1258):
+ *     ln -> contract(A = ln, B = [fc1 ; fc2] bf16 [512][64]) -> b200pf_msa_swiglu -> contract(B = fc3 bf16 [64][256])
+ *     -> b200pf_msa_add_rows
+ * ---------------------------------------------------------------------------------------- */
+int b200pf_msa_ln_bf16(const float* m, const float* gamma, const float* beta, b200pf_bf16* out, int s_len, int n, int np,
+                       void* stream);
+/* w[h][i][j] = softmax over j of logits[h][i][j] - inf_value * (mask[i][j] == 0); bf16 rows of `pitch`, zero beyond n. */
+int b200pf_pwa_softmax(const float* logits, const uint8_t* mask, b200pf_bf16* w, int n, int pitch, int heads, float inf_value,
+                       void* stream);
+/* m[s][i][:] += W_o (sigmoid(g[:, s, i]) * o[:, s, i]);  o, g bf16 [256][S][np];  w_ot fp32 [256][64] = W_o transposed. */
+int b200pf_pwa_epilogue(const b200pf_bf16* o, const b200pf_bf16* g, const float* w_ot, float* m, int s_len, int n, int np,
+                        void* stream);
+/* out[r][c] = silu(h[r][c]) * h[r][256 + c]: bf16 rows of 512 -> bf16 rows of 256. */
+int b200pf_msa_swiglu(const b200pf_bf16* h, b200pf_bf16* out, long long rows, void* stream);
+/* m[s][i][:] += t[s*np + i][:]  (t bf16 rows of 64). */
+int b200pf_msa_add_rows(float* m, const b200pf_bf16* t, int s_len, int n, int np, void* stream);
+
 /* All-to-all of equal blocks over peer mappings (multi-GPU path, no counterpart in the reference, whose
  * cards do not exchange data: tt_bio/distributed.py fans whole jobs out).  Block t of `send` (world blocks
  * of block_bytes) is written to slot `rank` of rank t's receive buffer; recv_ptrs is a HOST array of the

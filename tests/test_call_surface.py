@@ -10,7 +10,7 @@ import inspect
 import pytest
 import torch
 
-from tt_boltz_b200 import (B200OuterProductMean, B200PairformerLayer, B200PairformerModule, B200PairformerNoSeqLayer,
+from tt_boltz_b200 import (B200MSALayer, B200MSATransition, B200OuterProductMean, B200PairWeightedAveraging, B200PairformerLayer, B200PairformerModule, B200PairformerNoSeqLayer,
                            B200PairformerNoSeqModule, B200RecyclingTrunk, synthetic)
 
 
@@ -110,3 +110,24 @@ def test_outer_product_mean_surface():
     m, mask = synthetic.make_msa_inputs(4, 8)
     with pytest.raises(RuntimeError, match="CUDA"):
         mod(m[None], mask[None])
+
+
+def test_msa_layer_surface():
+    """tt_bio/reference.py:1314-1376: constructor (msa_s, token_z, msa_dropout, z_dropout, head width, heads), the four
+    sub-modules by name, forward(z, m, token_mask, msa_mask, five chunk arguments, use_kernels) -> (z, m)."""
+    layer = B200MSALayer(64, 128, 0.0, 0.0)
+    assert set(layer.state_dict().keys()) == set(synthetic.make_msa_layer_weights().keys())
+    layer.load_state_dict(synthetic.make_msa_layer_weights(), strict=True)
+    assert _params(B200MSALayer.forward) == ["self", "z", "m", "token_mask", "msa_mask", "chunk_heads_pwa", "chunk_size_transition_z",
+                                             "chunk_size_transition_msa", "chunk_size_outer_product", "chunk_size_tri_attn", "use_kernels"]
+    # reference.py:727-729 and boltz2.py:1227
+    assert _params(B200PairWeightedAveraging.forward) == ["self", "m", "z", "mask", "chunk_heads"]
+    assert _params(B200MSATransition.forward) == ["self", "x", "chunk_size"]
+    z = torch.zeros(1, 8, 8, 128)
+    m, msa_mask = synthetic.make_msa_inputs(4, 8)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        layer(z, m[None], torch.ones(1, 8, 8), msa_mask[None])
+    with pytest.raises(RuntimeError, match="CUDA"):
+        layer.pair_weighted_averaging(m[None], z, torch.ones(1, 8, 8))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        layer.msa_transition(m[None])

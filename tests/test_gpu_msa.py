@@ -14,7 +14,7 @@ import torch
 
 from oracle import msa_oracle
 from tests.conftest import rel_l2
-from tt_boltz_b200 import B200OuterProductMean, _lib, synthetic
+from tt_boltz_b200 import B200MSALayer, B200OuterProductMean, _lib, synthetic
 
 pytestmark = pytest.mark.gpu
 TOL = 2e-2
@@ -89,3 +89,49 @@ def test_add_into_accumulates_in_place():
     ret = mod.add_into(z, m[None].cuda(), mask[None].cuda())
     assert ret is z
     assert torch.allclose(z, z0 + upd, rtol=0, atol=1e-5 * float(upd.abs().max()) + 1e-6)
+
+
+# ---- the whole MSA layer: pair-weighted averaging, transition, outer-product mean, pair block ----
+MSA_LAYER_CASES = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(os.path.dirname(__file__), "golden", "msa", "msa_layer_*.npz")))
+
+
+def _layer(seed=21):
+    layer = B200MSALayer(64, 128, 0.0, 0.0)
+    layer.load_state_dict(synthetic.make_msa_layer_weights(seed=seed), strict=True)
+    return layer.cuda()
+
+
+@pytest.mark.parametrize("name", MSA_LAYER_CASES)
+def test_msa_layer_against_reference_fixture(golden_dir, name):
+    from tests.test_oracle_golden import load_msa_layer_case
+    g, _, (z, m, token_mask, msa_mask) = load_msa_layer_case(golden_dir, name)
+    layer = _layer(int(g["weight_seed"]))
+    zc, mc, tm, mm = z[None].cuda(), m[None].cuda(), token_mask[None].cuda(), msa_mask[None].cuda()
+    pwa = layer.pair_weighted_averaging(mc, zc, tm)
+    trans = layer.msa_transition(mc)
+    z_o, m_o = layer(zc, mc, tm, mm)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    assert rel_l2(pwa[0].cpu(), torch.from_numpy(g["pwa"])) < TOL
+    assert rel_l2(trans[0].cpu(), torch.from_numpy(g["transition"])) < TOL
+    assert rel_l2(m_o[0].cpu(), torch.from_numpy(g["m_out"])) < TOL
+    assert rel_l2(z_o[0].cpu(), torch.from_numpy(g["z_out"])) < TOL
+
+
+def test_msa_layer_against_oracle_with_chunks(monkeypatch):
+    """Sizes at which the sequence chunking, ragged GEMM tiles and the padded token axis all come into play."""
+    from tt_boltz_b200 import msa as msa_mod
+    monkeypatch.setattr(msa_mod, "ROWS_PER_CHUNK", 4096)          # 28 sequences of 144 padded tokens per chunk
+    s_len, n = 75, 139
+    _, z = synthetic.make_inputs(n, seed=6, with_s=False)
+    m, msa_mask = synthetic.make_msa_inputs(s_len, n, drop=0.3, seed=7)
+    _, pm = synthetic.random_padding_mask(n, 0.1, seed=3)
+    w = synthetic.make_msa_layer_weights(seed=5)
+    with torch.no_grad():
+        z_want, m_want = msa_oracle.msa_layer(z[0], m, pm[0], msa_mask, w)
+    z_o, m_o = _layer(5)(z.cuda(), m[None].cuda(), pm.cuda(), msa_mask[None].cuda())
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    assert torch.isfinite(z_o).all() and torch.isfinite(m_o).all()
+    assert rel_l2(m_o[0].cpu(), m_want) < TOL
+    assert rel_l2(z_o[0].cpu(), z_want) < TOL

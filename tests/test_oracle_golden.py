@@ -84,3 +84,31 @@ def test_outer_product_mean_oracle_matches_reference_outputs(golden_dir, name):
 
 def test_outer_product_mean_fixtures_present():
     assert len(OPM_CASES) >= 3
+
+
+MSA_LAYER_CASES = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(os.path.dirname(__file__), "golden", "msa", "msa_layer_*.npz")))
+
+
+def load_msa_layer_case(golden_dir, name):
+    from tests.golden.msa.make_msa_layer import make_case_inputs
+    g = np.load(os.path.join(golden_dir, "msa", name + ".npz"))
+    c = dict(s=int(g["s"]), n=int(g["n"]), drop=float(g["drop"]), pad=int(g["pad"]))
+    return g, synthetic.make_msa_layer_weights(seed=int(g["weight_seed"])), make_case_inputs(c)
+
+
+@pytest.mark.parametrize("name", MSA_LAYER_CASES)
+def test_msa_layer_oracle_matches_reference_outputs(golden_dir, name):
+    """tests/golden/msa/make_msa_layer.py stored what tt_bio.reference.MSALayer and its sub-modules return."""
+    g, w, (z, m, token_mask, msa_mask) = load_msa_layer_case(golden_dir, name)
+    with torch.no_grad():
+        pwa = msa_oracle.pair_weighted_averaging(m, z, token_mask, msa_oracle._sub(w, "pair_weighted_averaging."))
+        trans = msa_oracle.msa_transition(m, msa_oracle._sub(w, "msa_transition."))
+        z_o, m_o = msa_oracle.msa_layer(z, m, token_mask, msa_mask, w)
+    assert rel_l2(pwa, torch.from_numpy(g["pwa"])) < 2e-6
+    assert rel_l2(trans, torch.from_numpy(g["transition"])) < 2e-6
+    assert rel_l2(m_o, torch.from_numpy(g["m_out"])) < 2e-6
+    assert rel_l2(z_o, torch.from_numpy(g["z_out"])) < 2e-6
+
+
+def test_msa_layer_fixtures_present():
+    assert len(MSA_LAYER_CASES) >= 2

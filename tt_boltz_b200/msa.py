@@ -122,3 +122,225 @@ class B200OuterProductMean(nn.Module):
         with torch.no_grad():
             self._run(out[0], m[0], mask[0], accumulate=False)
         return out
+
+
+# ------------------------------------------------------------------------------------------------
+# The MSA layer: pair-weighted averaging and transition on m, outer-product mean and a pair block on z
+# ------------------------------------------------------------------------------------------------
+ROWS_PER_CHUNK = 1 << 20           # (sequence, token) rows whose bf16 intermediates are held at a time
+
+
+def _gemm(a, a_rows, k, b, b_rows, x, channels=1, a_plane=None, b_plane=None, a_pitch=None, b_pitch=None,
+          x_plane=None, x_pitch=None, cols=None) -> None:
+    """x[d][i][j] = sum_k a[d][i][k] b[d][j][k] through the contraction kernel (bf16 operands, fp32 accumulation)."""
+    a_pitch, b_pitch = a_pitch or k, b_pitch or k
+    pa = Planes(ptr(a), a_plane if a_plane is not None else a_rows * a_pitch, 0, a_pitch, a_rows, cols or k, 1, 0)
+    pb = Planes(ptr(b), b_plane if b_plane is not None else b_rows * b_pitch, 0, b_pitch, b_rows, cols or k, 1, 0)
+    x_pitch = x_pitch or b_rows
+    call("b200pf_trimul_contract", C.byref(pa), C.byref(pb), None, None, ptr(x),
+         x_plane if x_plane is not None else a_rows * x_pitch, x_pitch, 0, 0, channels, 0, stream())
+
+
+def _check_m(m: torch.Tensor) -> None:
+    if not m.is_cuda:
+        raise RuntimeError("the MSA kernels need CUDA tensors: the b200pf kernels have no CPU path")
+    if m.dim() != 3 or m.shape[2] != C_M or m.dtype != torch.float32 or not m.is_contiguous():
+        raise ValueError("m must be a contiguous fp32 tensor [S, N, 64]")
+
+
+class B200PairWeightedAveraging(nn.Module):
+    """Drop-in for ``PairWeightedAveraging(c_m=64, c_z=128, c_h=32, num_heads=8)`` (tt_bio/reference.py:672-800; device
+    form tt_bio/tenstorrent.py:1542-1629): ``forward(m, z, mask, chunk_heads)`` returns the update of m, ``add_into``
+    accumulates it into a resident fp32 m."""
+
+    def __init__(self, c_m: int = C_M, c_z: int = 128, c_h: int = 32, num_heads: int = 8, inf: float = 1e6) -> None:
+        super().__init__()
+        if (c_m, c_z, c_h, num_heads) != (C_M, 128, 32, 8):
+            raise ValueError(f"B200PairWeightedAveraging is built for (c_m, c_z, c_h, heads) = (64, 128, 32, 8), got {(c_m, c_z, c_h, num_heads)}")
+        self.c_m, self.c_z, self.c_h, self.num_heads, self.inf = c_m, c_z, c_h, num_heads, inf
+        self.norm_m = nn.LayerNorm(c_m)
+        self.norm_z = nn.LayerNorm(c_z)
+        self.proj_m = nn.Linear(c_m, c_h * num_heads, bias=False)
+        self.proj_g = nn.Linear(c_m, c_h * num_heads, bias=False)
+        self.proj_z = nn.Linear(c_z, num_heads, bias=False)
+        self.proj_o = nn.Linear(c_h * num_heads, c_m, bias=False)
+        self._packed = None
+
+    def _load_from_state_dict(self, *args, **kwargs):
+        self._packed = None
+        return super()._load_from_state_dict(*args, **kwargs)
+
+    def _apply(self, fn, *args, **kwargs):
+        self._packed = None
+        return super()._apply(fn, *args, **kwargs)
+
+    def _pack(self, device):
+        if self._packed is None or self._packed["w_mg"].device != device:
+            with torch.no_grad():
+                f32 = dict(device=device, dtype=torch.float32)
+                self._packed = {
+                    "gm": self.norm_m.weight.detach().to(**f32).contiguous(), "bm": self.norm_m.bias.detach().to(**f32).contiguous(),
+                    "gz": self.norm_z.weight.detach().to(**f32).contiguous(), "bz": self.norm_z.bias.detach().to(**f32).contiguous(),
+                    "w_mg": torch.cat([self.proj_m.weight, self.proj_g.weight], 0).detach().to(device=device, dtype=torch.bfloat16).contiguous(),
+                    # the LayerNorm + head projection kernel is built for 16 heads: 8 real rows, 8 zero rows
+                    "w_z": torch.cat([self.proj_z.weight.detach().to(**f32), torch.zeros(8, self.c_z, **f32)], 0).contiguous(),
+                    "w_ot": self.proj_o.weight.detach().t().to(**f32).contiguous(),
+                }
+        return self._packed
+
+    def _run(self, m: torch.Tensor, z: torch.Tensor, mask_u8: torch.Tensor) -> None:
+        """m [S, N, 64] fp32 updated in place from z [N, N, 128] fp32 and the pair mask [N, N] (uint8)."""
+        _check_m(m)
+        s_len, n = m.shape[0], m.shape[1]
+        if tuple(z.shape) != (n, n, 128) or z.dtype != torch.float32 or not z.is_contiguous():
+            raise ValueError("z must be a contiguous fp32 tensor [N, N, 128]")
+        w = self._pack(m.device)
+        dev, st, heads = m.device, stream(), self.num_heads
+        np_, pw = _round_up(n, 8), _round_up(n, 8)
+        logits = torch.empty(16 * n * n, dtype=torch.float32, device=dev)
+        call("b200pf_ln_proj_heads", ptr(z), ptr(w["gz"]), ptr(w["bz"]), ptr(w["w_z"]), ptr(logits), n * n, n * n, 128, 16, st)
+        wt = torch.empty(heads * n * pw, dtype=torch.bfloat16, device=dev)
+        call("b200pf_pwa_softmax", ptr(logits), ptr(mask_u8), ptr(wt), n, pw, heads, float(self.inf), st)
+        sc = max(1, min(s_len, ROWS_PER_CHUNK // np_))
+        ln = torch.empty(sc * np_ * C_M, dtype=torch.bfloat16, device=dev)
+        vg = torch.empty(512 * sc * np_, dtype=torch.bfloat16, device=dev)
+        o = torch.empty(256 * sc * np_, dtype=torch.bfloat16, device=dev)
+        for s0 in range(0, s_len, sc):
+            ns = min(sc, s_len - s0)
+            p = ns * np_
+            call("b200pf_msa_ln_bf16", ptr(m[s0:]), ptr(w["gm"]), ptr(w["bm"]), ptr(ln), ns, n, np_, st)
+            _gemm(w["w_mg"], 512, C_M, ln, p, vg)                                        # [v ; g][(h, d)][s][token]
+            _gemm(vg, self.c_h * ns, n, wt, n, o, channels=heads, a_plane=self.c_h * p, a_pitch=np_,
+                  b_plane=n * pw, b_pitch=pw, x_plane=self.c_h * p, x_pitch=np_, cols=n)
+            call("b200pf_pwa_epilogue", ptr(o), ptr(vg[256 * p:]), ptr(w["w_ot"]), ptr(m[s0:]), ns, n, np_, st)
+
+    def add_into(self, m: torch.Tensor, z: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+        """m += pair_weighted_averaging(m, z, mask) in place; m [S, N, 64] fp32, z [N, N, 128] fp32, mask [N, N]."""
+        with torch.no_grad():
+            self._run(m, z, (mask != 0).to(torch.uint8).contiguous())
+        return m
+
+    def forward(self, m: torch.Tensor, z: torch.Tensor, mask: torch.Tensor, chunk_heads: bool = False) -> torch.Tensor:
+        """m [1, S, N, 64], z [1, N, N, 128], mask [1, N, N] -> the update [1, S, N, 64] (reference.py:727-800)."""
+        if m.dim() != 4 or m.shape[0] != 1:
+            raise ValueError("B200PairWeightedAveraging.forward takes m of shape [1, S, N, 64]")
+        if not m.is_cuda:
+            raise RuntimeError("the MSA kernels need CUDA tensors: the b200pf kernels have no CPU path")
+        with torch.no_grad():
+            m0 = m[0].to(torch.float32).contiguous()
+            work = m0.clone()
+            self._run(work, z[0].to(torch.float32).contiguous(), (mask[0] != 0).to(torch.uint8).contiguous())
+            return (work - m0)[None]
+
+
+class B200MSATransition(nn.Module):
+    """Drop-in for ``Transition(dim=64, hidden=256)`` on the MSA activations (tt_bio/boltz2.py:1188-1258):
+    ``forward(x, chunk_size)`` returns the update, ``add_into`` accumulates it into a resident fp32 m."""
+
+    def __init__(self, dim: int = C_M, hidden: int = 256, out_dim: Optional[int] = None) -> None:
+        super().__init__()
+        if (dim, hidden, out_dim or dim) != (C_M, 256, C_M):
+            raise ValueError(f"B200MSATransition is built for (dim, hidden) = (64, 256), got {(dim, hidden, out_dim)}")
+        self.norm = nn.LayerNorm(dim, eps=1e-5)
+        self.fc1 = nn.Linear(dim, hidden, bias=False)
+        self.fc2 = nn.Linear(dim, hidden, bias=False)
+        self.fc3 = nn.Linear(hidden, dim, bias=False)
+        self.hidden = hidden
+        self._packed = None
+
+    def _load_from_state_dict(self, *args, **kwargs):
+        self._packed = None
+        return super()._load_from_state_dict(*args, **kwargs)
+
+    def _apply(self, fn, *args, **kwargs):
+        self._packed = None
+        return super()._apply(fn, *args, **kwargs)
+
+    def _pack(self, device):
+        if self._packed is None or self._packed["w12"].device != device:
+            with torch.no_grad():
+                bf = dict(device=device, dtype=torch.bfloat16)
+                self._packed = {
+                    "g": self.norm.weight.detach().to(device=device, dtype=torch.float32).contiguous(),
+                    "b": self.norm.bias.detach().to(device=device, dtype=torch.float32).contiguous(),
+                    "w12": torch.cat([self.fc1.weight, self.fc2.weight], 0).detach().to(**bf).contiguous(),
+                    "w3": self.fc3.weight.detach().to(**bf).contiguous(),
+                }
+        return self._packed
+
+    def _run(self, m: torch.Tensor) -> None:
+        _check_m(m)
+        s_len, n = m.shape[0], m.shape[1]
+        w = self._pack(m.device)
+        dev, st = m.device, stream()
+        np_ = _round_up(n, 8)
+        sc = max(1, min(s_len, ROWS_PER_CHUNK // np_))
+        ln = torch.empty(sc * np_ * C_M, dtype=torch.bfloat16, device=dev)
+        h12 = torch.empty(sc * np_ * 512, dtype=torch.bfloat16, device=dev)
+        hsw = torch.empty(sc * np_ * 256, dtype=torch.bfloat16, device=dev)
+        t = torch.empty(sc * np_ * C_M, dtype=torch.bfloat16, device=dev)
+        for s0 in range(0, s_len, sc):
+            ns = min(sc, s_len - s0)
+            p = ns * np_
+            call("b200pf_msa_ln_bf16", ptr(m[s0:]), ptr(w["g"]), ptr(w["b"]), ptr(ln), ns, n, np_, st)
+            _gemm(ln, p, C_M, w["w12"], 512, h12)
+            call("b200pf_msa_swiglu", ptr(h12), ptr(hsw), p, st)
+            _gemm(hsw, p, 256, w["w3"], C_M, t)
+            call("b200pf_msa_add_rows", ptr(m[s0:]), ptr(t), ns, n, np_, st)
+
+    def add_into(self, m: torch.Tensor) -> torch.Tensor:
+        with torch.no_grad():
+            self._run(m)
+        return m
+
+    def forward(self, x: torch.Tensor, chunk_size: Optional[int] = None) -> torch.Tensor:
+        """x [1, S, N, 64] -> the update [1, S, N, 64]; ``chunk_size`` only bounds the reference's memory."""
+        if x.dim() != 4 or x.shape[0] != 1:
+            raise ValueError("B200MSATransition.forward takes x of shape [1, S, N, 64]")
+        if not x.is_cuda:
+            raise RuntimeError("the MSA kernels need CUDA tensors: the b200pf kernels have no CPU path")
+        with torch.no_grad():
+            x0 = x[0].to(torch.float32).contiguous()
+            work = x0.clone()
+            self._run(work)
+            return (work - x0)[None]
+
+
+class B200MSALayer(nn.Module):
+    """One block of the MSA module with the reference's constructor, sub-module names and
+    ``forward(z, m, token_mask, msa_mask, ...) -> (z, m)`` (tt_bio/reference.py:1311-1397; device form
+    tt_bio/tenstorrent.py:1721-1790): pair-weighted averaging and transition on m, then the outer-product mean and a
+    pair-only Pairformer block on z.  Inference only: the dropout masks of the reference are the identity in eval mode."""
+
+    def __init__(self, msa_s: int = C_M, token_z: int = 128, msa_dropout: float = 0.0, z_dropout: float = 0.0,
+                 pairwise_head_width: int = 32, pairwise_num_heads: int = 4, precision: str = "bf16") -> None:
+        super().__init__()
+        from .pairformer import B200PairformerNoSeqLayer
+        self.msa_dropout = msa_dropout
+        self.msa_transition = B200MSATransition(dim=msa_s, hidden=msa_s * 4)
+        self.pair_weighted_averaging = B200PairWeightedAveraging(c_m=msa_s, c_z=token_z, c_h=32, num_heads=8)
+        self.pairformer_layer = B200PairformerNoSeqLayer(token_z, z_dropout, pairwise_head_width, pairwise_num_heads,
+                                                         precision=precision)
+        self.outer_product_mean = B200OuterProductMean(c_in=msa_s, c_hidden=32, c_out=token_z)
+
+    def forward_inplace(self, z: torch.Tensor, m: torch.Tensor, token_mask: torch.Tensor, msa_mask: torch.Tensor) -> None:
+        """z [N, N, 128] and m [S, N, 64], contiguous fp32, updated where they are; token_mask [N, N], msa_mask [S, N]."""
+        from .pairformer import _run_layers
+        self.pair_weighted_averaging.add_into(m, z, token_mask)
+        self.msa_transition.add_into(m)
+        self.outer_product_mean.add_into(z, m, msa_mask)
+        _run_layers([self.pairformer_layer], None, z, None, token_mask[None], inplace=True)
+
+    def forward(self, z: torch.Tensor, m: torch.Tensor, token_mask: torch.Tensor, msa_mask: torch.Tensor,
+                chunk_heads_pwa: bool = False, chunk_size_transition_z: Optional[int] = None,
+                chunk_size_transition_msa: Optional[int] = None, chunk_size_outer_product: Optional[int] = None,
+                chunk_size_tri_attn: Optional[int] = None, use_kernels: bool = False):
+        """z [1, N, N, 128], m [1, S, N, 64], token_mask [1, N, N], msa_mask [1, S, N] -> (z, m); the chunk sizes only
+        bound the reference's memory and are ignored."""
+        if not (z.is_cuda and m.is_cuda):
+            raise RuntimeError("the MSA kernels need CUDA tensors: the b200pf kernels have no CPU path")
+        with torch.no_grad():
+            zw = z[0].to(torch.float32).clone(memory_format=torch.contiguous_format)
+            mw = m[0].to(torch.float32).clone(memory_format=torch.contiguous_format)
+            self.forward_inplace(zw, mw, token_mask[0], msa_mask[0])
+        return zw[None], mw[None]

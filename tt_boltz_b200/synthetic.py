@@ -164,3 +164,33 @@ def make_msa_inputs(s: int, n: int, c_in: int = 64, drop: float = 0.0, seed: int
     mask = (torch.rand(s, n, generator=g) >= drop).float()
     mask[0] = 1.0
     return m, mask
+
+
+def make_msa_layer_weights(seed: int = 21, std: float = 0.05, affine_jitter: float = 0.2) -> Dict[str, torch.Tensor]:
+    """State dict of one MSA layer with the reference's key names (tt_bio/reference.py:1336-1358): transition and
+    pair-weighted averaging on the 64-channel MSA activations, outer-product mean, and a pair-only Pairformer block."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+
+    def mat(*shape, scale=1.0):
+        return torch.randn(*shape, generator=g) * std * scale
+
+    def gain(c):
+        return 1 + affine_jitter * torch.randn(c, generator=g)
+
+    def offset(c):
+        return affine_jitter * torch.randn(c, generator=g)
+
+    sd = {
+        "msa_transition.norm.weight": gain(64), "msa_transition.norm.bias": offset(64),
+        "msa_transition.fc1.weight": mat(256, 64, scale=2), "msa_transition.fc2.weight": mat(256, 64, scale=2),
+        "msa_transition.fc3.weight": mat(64, 256, scale=2),
+        "pair_weighted_averaging.norm_m.weight": gain(64), "pair_weighted_averaging.norm_m.bias": offset(64),
+        "pair_weighted_averaging.norm_z.weight": gain(128), "pair_weighted_averaging.norm_z.bias": offset(128),
+        "pair_weighted_averaging.proj_m.weight": mat(256, 64, scale=2), "pair_weighted_averaging.proj_g.weight": mat(256, 64, scale=2),
+        "pair_weighted_averaging.proj_z.weight": mat(8, 128, scale=4), "pair_weighted_averaging.proj_o.weight": mat(64, 256, scale=2),
+    }
+    for k, v in make_opm_weights(seed=seed + 1).items():
+        sd["outer_product_mean." + k] = v
+    for k, v in make_weights(1, seed=seed + 2, std=std, affine_jitter=affine_jitter, with_s=False).items():
+        sd["pairformer_layer." + k[len("layers.0."):]] = v
+    return sd
