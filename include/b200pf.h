@@ -179,6 +179,15 @@ int b200pf_trimul_contract(const b200pf_planes* a, const b200pf_planes* b,
                            int x_row_group, long long x_group_stride,
                            int channels, int variant, void* stream);
 
+/* The bf16 contraction with both output indices regrouped: element (d, row, col) is written to
+ *   (row / x_row_group) * x_group_stride + d * x_plane_stride + (row % x_row_group) * x_pitch
+ *   + (col / x_col_group) * x_colgroup_stride + col % x_col_group
+ * (x_row_group <= 0: rows not grouped; x_col_group a multiple of 32; unsegmented operands).  Used where the consumer
+ * of a GEMM wants its output in another index order than [row][col] (MSA stack). */
+int b200pf_gemm_grouped(const b200pf_planes* a, const b200pf_planes* b, b200pf_bf16* x, long long x_plane_stride,
+                        int x_pitch, int x_row_group, long long x_group_stride, int x_col_group,
+                        long long x_colgroup_stride, int channels, void* stream);
+
 /* MXFP8 form of the producer (the counterpart of the reference's block-fp8 "fast" mode,
  * tt_bio/tenstorrent.py:178-181, 432-452): same computation as b200pf_trimul_producer, but
  * a / b are quantised straight from fp32 to e4m3 with one e8m0 scale per 32 elements along the
@@ -336,10 +345,12 @@ int b200pf_opm_finalize(const b200pf_bf16* y, const uint32_t* bits, const float*
  * of every bf16 operand is padded to np (a multiple of 8, >= n); padding rows are zero.
  *   pair-weighted averaging (tt_bio/tenstorrent.py:1542-1629, reference.py:672-800):
  *     ln = b200pf_msa_ln_bf16(m)                         [S*np][64]
- *     vg = contract(A = [proj_m ; proj_g] bf16 [512][64], B = ln)     -> [512][S*np]: v rows 0-255, g rows 256-511
+ *     vg = b200pf_gemm_grouped(A = [proj_m ; proj_g] bf16 [512][64], B = ln) -> [16][S][32][np]: v groups 0-7 (heads),
+ *          g groups 8-15; np a multiple of 32 here
  *     logits = b200pf_ln_proj_heads(z, norm_z, proj_z, 8 heads);  w = b200pf_pwa_softmax(logits, mask)
- *     o = contract over 8 heads (A = v as [8][32*S][np], B = w [8][n][pitch])   -> [8][32*S][np]
- *     b200pf_pwa_epilogue: m += W_o (sigmoid(g) * o)
+ *     o = contract over 8 heads (A = v as [8][S*32][np], B = w [8][n][pitch])   -> [8][S][32][np]
+ *     val = b200pf_pwa_gate_transpose(o, g);  t = contract(A = val [S*np][256], B = proj_o bf16 [64][256]);
+ *     b200pf_msa_add_rows(m, t)
  *   MSA transition (Transition(64, 256), tt_bio/boltz2.py:1188-1258):
  *     ln -> contract(A = ln, B = [fc1 ; fc2] bf16 [512][64]) -> b200pf_msa_swiglu -> contract(B = fc3 bf16 [64][256])
  *     -> b200pf_msa_add_rows
@@ -349,9 +360,9 @@ int b200pf_msa_ln_bf16(const float* m, const float* gamma, const float* beta, b2
 /* w[h][i][j] = softmax over j of logits[h][i][j] - inf_value * (mask[i][j] == 0); bf16 rows of `pitch`, zero beyond n. */
 int b200pf_pwa_softmax(const float* logits, const uint8_t* mask, b200pf_bf16* w, int n, int pitch, int heads, float inf_value,
                        void* stream);
-/* m[s][i][:] += W_o (sigmoid(g[:, s, i]) * o[:, s, i]);  o, g bf16 [256][S][np];  w_ot fp32 [256][64] = W_o transposed. */
-int b200pf_pwa_epilogue(const b200pf_bf16* o, const b200pf_bf16* g, const float* w_ot, float* m, int s_len, int n, int np,
-                        void* stream);
+/* val[s*np + tok][head*32 + d] = o * sigmoid(g) at (head, s, d, tok): o, g bf16 [8][S][32][np] -> bf16 [S*np][256], the
+ * K-major operand of the output projection. */
+int b200pf_pwa_gate_transpose(const b200pf_bf16* o, const b200pf_bf16* g, b200pf_bf16* val, int s_len, int np, void* stream);
 /* out[r][c] = silu(h[r][c]) * h[r][256 + c]: bf16 rows of 512 -> bf16 rows of 256. */
 int b200pf_msa_swiglu(const b200pf_bf16* h, b200pf_bf16* out, long long rows, void* stream);
 /* m[s][i][:] += t[s*np + i][:]  (t bf16 rows of 64). */

@@ -56,7 +56,8 @@ SIGNATURES = {
     "b200pf_mx_scale_bytes": [_i, _i, _i],
     "b200pf_msa_ln_bf16": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "b200pf_pwa_softmax": [_vp, _vp, _vp, _i, _i, _i, C.c_float, _vp],
-    "b200pf_pwa_epilogue": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "b200pf_pwa_gate_transpose": [_vp, _vp, _vp, _i, _i, _vp],
+    "b200pf_gemm_grouped": [C.POINTER(Planes), C.POINTER(Planes), _vp, _ll, _i, _i, _ll, _i, _ll, _i, _vp],
     "b200pf_msa_swiglu": [_vp, _vp, _ll, _vp],
     "b200pf_msa_add_rows": [_vp, _vp, _i, _i, _i, _vp],
     "b200pf_opm_producer": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],

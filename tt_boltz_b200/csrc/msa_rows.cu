@@ -3,7 +3,8 @@
 //   pair-weighted averaging  m += W_o (sigmoid(W_g LN(m)) * sum_j softmax_j(W_z LN(z) + mask)[i][j] (W_m LN(m))[j])
 //   MSA transition           m += W_3 (silu(W_1 LN(m)) * W_2 LN(m))
 // Every GEMM operand is bf16 and K-major; the token axis is padded to a multiple of 8 (`np`) so that rows of
-// every operand start 16-byte aligned, with zero rows for the padding tokens.
+// every operand start 16-byte aligned, with zero rows for the padding tokens (the pair-weighted averaging pads to
+// 32: its projected rows are written in groups of np columns).
 #include "common.cuh"
 
 namespace b200pf {
@@ -69,45 +70,40 @@ pwa_softmax_kernel(const float* __restrict__ logits, const uint8_t* __restrict__
         dst[j] = __float2bfloat16(j < n ? __expf(src[j] - (mk[j] ? 0.f : inf_value) - mx) * inv : 0.f);
 }
 
-// m[s][i][:] += W_o (sigmoid(g[:, s, i]) * o[:, s, i]); o and g are [256][S][np] bf16 (channel (head, d) major, token
-// contiguous), w_ot fp32 [256][64] = W_o transposed.  One thread per (s, i); the weights are broadcast from shared memory.
-constexpr int PWA_THREADS = 128;
-__global__ void __launch_bounds__(PWA_THREADS)
-pwa_epilogue_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ g, const float* __restrict__ w_ot,
-                    float* __restrict__ m, int s_len, int n, int np) {
-    extern __shared__ __align__(16) float w_s[];                 // [256][64]
-    for (int i = threadIdx.x; i < 256 * CM / 4; i += PWA_THREADS)
-        reinterpret_cast<float4*>(w_s)[i] = __ldg(reinterpret_cast<const float4*>(w_ot) + i);
-    __syncthreads();
-    const int s = blockIdx.y, tok = blockIdx.x * PWA_THREADS + threadIdx.x;
-    if (tok >= n) return;
-    const long long cs = (long long)s_len * np;                   // elements between channels
-    const __nv_bfloat16* op = o + (long long)s * np + tok;
-    const __nv_bfloat16* gp = g + (long long)s * np + tok;
-    float acc[CM];
+// val[(s, tok)][c] = o * sigmoid(g) for the 256 channels c = (head, d): the gated average turned K-major for the
+// output projection's GEMM.  o and g are [8 heads][S][32][np] (token contiguous), which is how the GEMMs before
+// leave them.  A CTA takes 64 tokens of one sequence.  Eight lanes read the 128 bytes of one channel (four channels
+// per warp and step, every load a full line); the tile is transposed through shared memory, whose 16-byte chunks
+// are XOR-swizzled with the token group so that neither side has bank conflicts, and leaves as full 512-byte rows.
+constexpr int GT_POS = 64;
+__global__ void __launch_bounds__(256)
+pwa_gate_transpose_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ g,
+                          __nv_bfloat16* __restrict__ val, int s_len, int np) {
+    __shared__ __align__(16) __nv_bfloat16 tile[GT_POS][256];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, q = lane & 7, csub = lane >> 3;
+    const int s = blockIdx.y, t0 = blockIdx.x * GT_POS;
+    const bool in_range = t0 + q * 8 < np;                                  // np is a multiple of 8
 #pragma unroll
-    for (int e = 0; e < CM; ++e) acc[e] = 0.f;
-#pragma unroll 2
-    for (int c = 0; c < 256; ++c) {
-        const float ov = __bfloat162float(op[c * cs]);
-        const float gv = __bfloat162float(gp[c * cs]);
-        const float val = ov * (1.f / (1.f + __expf(-gv)));
-        const float4* wr = reinterpret_cast<const float4*>(w_s + c * CM);
+    for (int it = 0; it < 8; ++it) {
+        const int c = warp * 32 + it * 4 + csub, head = c >> 5, d = c & 31;
+        if (!in_range) continue;
+        const long long row = (((long long)head * s_len + s) * 32 + d) * np + t0;
+        const uint4 ov = __ldg(reinterpret_cast<const uint4*>(o + row) + q);
+        const uint4 gv = __ldg(reinterpret_cast<const uint4*>(g + row) + q);
+        const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w}, gw[4] = {gv.x, gv.y, gv.z, gv.w};
+        const int cs = c ^ (q << 3);                                        // chunk (c >> 3) ^ token group
 #pragma unroll
-        for (int e4 = 0; e4 < CM / 4; ++e4) {
-            const float4 w4 = wr[e4];
-            acc[4 * e4] = fmaf(w4.x, val, acc[4 * e4]);
-            acc[4 * e4 + 1] = fmaf(w4.y, val, acc[4 * e4 + 1]);
-            acc[4 * e4 + 2] = fmaf(w4.z, val, acc[4 * e4 + 2]);
-            acc[4 * e4 + 3] = fmaf(w4.w, val, acc[4 * e4 + 3]);
+        for (int k = 0; k < 4; ++k) {
+            tile[q * 8 + 2 * k][cs] = __float2bfloat16(bf16_lo(ow[k]) / (1.f + __expf(-bf16_lo(gw[k]))));
+            tile[q * 8 + 2 * k + 1][cs] = __float2bfloat16(bf16_hi(ow[k]) / (1.f + __expf(-bf16_hi(gw[k]))));
         }
     }
-    float4* mp = reinterpret_cast<float4*>(m + ((long long)s * n + tok) * CM);
-#pragma unroll
-    for (int e4 = 0; e4 < CM / 4; ++e4) {
-        float4 v = mp[e4];
-        v.x += acc[4 * e4]; v.y += acc[4 * e4 + 1]; v.z += acc[4 * e4 + 2]; v.w += acc[4 * e4 + 3];
-        mp[e4] = v;
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < GT_POS * 32; idx += 256) {          // 32 chunks of 8 channels per token row
+        const int pl = idx >> 5, c8 = idx & 31;
+        if (t0 + pl >= np) break;
+        reinterpret_cast<uint4*>(val + ((long long)s * np + t0 + pl) * 256)[c8] =
+            *reinterpret_cast<const uint4*>(&tile[pl][(c8 ^ (pl >> 3)) * 8]);
     }
 }
 
@@ -179,16 +175,16 @@ extern "C" int b200pf_pwa_softmax(const float* logits, const uint8_t* mask, b200
     return B200PF_OK;
 }
 
-extern "C" int b200pf_pwa_epilogue(const b200pf_bf16* o, const b200pf_bf16* g, const float* w_ot, float* m, int s_len, int n,
-                                   int np, void* stream) {
+extern "C" int b200pf_pwa_gate_transpose(const b200pf_bf16* o, const b200pf_bf16* g, b200pf_bf16* val, int s_len, int np,
+                                         void* stream) {
     using namespace msa;
-    B200PF_REQUIRE(o && g && w_ot && m && aligned16(w_ot) && aligned16(m), B200PF_ERR_INVALID, "pwa_epilogue: null or misaligned pointer");
-    B200PF_REQUIRE(s_len > 0 && s_len <= 65535 && n > 0 && np >= n, B200PF_ERR_INVALID, "pwa_epilogue: bad sizes");
-    constexpr int SMEM = 256 * CM * 4;
-    B200PF_SMEM_ATTR_ONCE(pwa_epilogue_kernel, SMEM);
-    dim3 grid((unsigned)((n + PWA_THREADS - 1) / PWA_THREADS), (unsigned)s_len);
-    pwa_epilogue_kernel<<<grid, PWA_THREADS, SMEM, (cudaStream_t)stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)g, w_ot, m,
-                                                                           s_len, n, np);
+    B200PF_REQUIRE(o && g && val && aligned16(o) && aligned16(g) && aligned16(val), B200PF_ERR_INVALID,
+                   "pwa_gate_transpose: null or misaligned pointer");
+    B200PF_REQUIRE(s_len > 0 && s_len <= 65535 && np > 0 && np % 8 == 0, B200PF_ERR_INVALID,
+                   "pwa_gate_transpose: np must be a positive multiple of 8, at most 65535 sequences per call");
+    dim3 grid((unsigned)((np + GT_POS - 1) / GT_POS), (unsigned)s_len);
+    pwa_gate_transpose_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)g,
+                                                                      (__nv_bfloat16*)val, s_len, np);
     B200PF_LAUNCH_CHECK();
     return B200PF_OK;
 }

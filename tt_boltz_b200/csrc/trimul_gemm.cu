@@ -310,6 +310,42 @@ extern "C" int b200pf_trimul_contract(const b200pf_planes* a, const b200pf_plane
     return launch_contract_tc(a, b, x, s, static_cast<cudaStream_t>(stream));
 }
 
+/* The same GEMM with both output indices regrouped: element (d, row, col) is written to
+ *   (row / x_row_group) * x_group_stride + d * x_plane_stride + (row % x_row_group) * x_pitch
+ *   + (col / x_col_group) * x_colgroup_stride + col % x_col_group
+ * (x_row_group <= 0: rows not grouped; x_col_group a multiple of 32).  Operands as for b200pf_trimul_contract, bf16 only. */
+extern "C" int b200pf_gemm_grouped(const b200pf_planes* a, const b200pf_planes* b, b200pf_bf16* x, long long x_plane_stride,
+                                   int x_pitch, int x_row_group, long long x_group_stride, int x_col_group,
+                                   long long x_colgroup_stride, int channels, void* stream) {
+    int rc;
+    if ((rc = check_planes(a, "A")) != B200PF_OK) return rc;
+    if ((rc = check_planes(b, "B")) != B200PF_OK) return rc;
+    B200PF_REQUIRE(x && aligned16(x) && channels > 0, B200PF_ERR_INVALID, "gemm_grouped: bad output");
+    B200PF_REQUIRE(a->nseg == 1 && b->nseg == 1 && a->cols == b->cols, B200PF_ERR_INVALID,
+                   "gemm_grouped: unsegmented operands of equal contraction length only");
+    B200PF_REQUIRE(x_col_group > 0 && x_col_group % 32 == 0 && x_colgroup_stride % 8 == 0 && x_pitch % 8 == 0 &&
+                       x_pitch >= x_col_group && x_plane_stride % 8 == 0 && x_group_stride % 8 == 0,
+                   B200PF_ERR_INVALID, "gemm_grouped: column groups must be multiples of 32 and every stride a multiple of 8");
+    GemmShape s;
+    s.m_rows = a->rows;
+    s.n_rows = b->rows;
+    s.k_total = a->cols;
+    s.a_kseg_cols = a->cols + BK;
+    s.b_kseg_cols = b->cols + BK;
+    s.a_rowseg_rows = s.m_rows + BM;
+    s.b_rowseg_rows = s.n_rows + BN;
+    s.channels = channels;
+    s.x_pitch = x_pitch;
+    s.x_plane_stride = x_plane_stride;
+    const bool grouped = x_row_group > 0 && x_row_group < s.m_rows;
+    s.x_row_group = grouped ? x_row_group : s.m_rows + BM;
+    s.x_group_stride = grouped ? x_group_stride : 0;
+    s.x_cols = (s.n_rows + 7) / 8 * 8;
+    s.x_col_group = x_col_group;
+    s.x_colgroup_stride = x_colgroup_stride;
+    return launch_contract_tc(a, b, x, s, static_cast<cudaStream_t>(stream));
+}
+
 /* Outer product of the outer-product-mean: x2[i][j][c][d] = sum_s a_t[(i, c)][s] * b_t[(j, d)][s], the same kernel with
  * its output rows (i, c) and columns (j, d) regrouped so that the 32 x 32 block of a token pair is contiguous. */
 extern "C" int b200pf_opm_outer(const b200pf_bf16* a_t, const b200pf_bf16* b_t, b200pf_bf16* x2,

@@ -184,7 +184,7 @@ class B200PairWeightedAveraging(nn.Module):
                     "w_mg": torch.cat([self.proj_m.weight, self.proj_g.weight], 0).detach().to(device=device, dtype=torch.bfloat16).contiguous(),
                     # the LayerNorm + head projection kernel is built for 16 heads: 8 real rows, 8 zero rows
                     "w_z": torch.cat([self.proj_z.weight.detach().to(**f32), torch.zeros(8, self.c_z, **f32)], 0).contiguous(),
-                    "w_ot": self.proj_o.weight.detach().t().to(**f32).contiguous(),
+                    "w_o": self.proj_o.weight.detach().to(device=device, dtype=torch.bfloat16).contiguous(),
                 }
         return self._packed
 
@@ -196,7 +196,7 @@ class B200PairWeightedAveraging(nn.Module):
             raise ValueError("z must be a contiguous fp32 tensor [N, N, 128]")
         w = self._pack(m.device)
         dev, st, heads = m.device, stream(), self.num_heads
-        np_, pw = _round_up(n, 8), _round_up(n, 8)
+        np_, pw = _round_up(n, 32), _round_up(n, 8)          # the projected rows are written in column groups of np
         logits = torch.empty(16 * n * n, dtype=torch.float32, device=dev)
         call("b200pf_ln_proj_heads", ptr(z), ptr(w["gz"]), ptr(w["bz"]), ptr(w["w_z"]), ptr(logits), n * n, n * n, 128, 16, st)
         wt = torch.empty(heads * n * pw, dtype=torch.bfloat16, device=dev)
@@ -205,14 +205,21 @@ class B200PairWeightedAveraging(nn.Module):
         ln = torch.empty(sc * np_ * C_M, dtype=torch.bfloat16, device=dev)
         vg = torch.empty(512 * sc * np_, dtype=torch.bfloat16, device=dev)
         o = torch.empty(256 * sc * np_, dtype=torch.bfloat16, device=dev)
+        val = torch.empty(sc * np_ * 256, dtype=torch.bfloat16, device=dev)
+        t = torch.empty(sc * np_ * C_M, dtype=torch.bfloat16, device=dev)
         for s0 in range(0, s_len, sc):
             ns = min(sc, s_len - s0)
             p = ns * np_
             call("b200pf_msa_ln_bf16", ptr(m[s0:]), ptr(w["gm"]), ptr(w["bm"]), ptr(ln), ns, n, np_, st)
-            _gemm(w["w_mg"], 512, C_M, ln, p, vg)                                        # [v ; g][(h, d)][s][token]
+            # [v heads 0-7 ; g heads 0-7][s][d][token]: rows (head, d) in groups of 32, columns (s, token) in groups of np
+            pa = Planes(ptr(w["w_mg"]), 512 * C_M, 0, C_M, 512, C_M, 1, 0)
+            pb = Planes(ptr(ln), p * C_M, 0, C_M, p, C_M, 1, 0)
+            call("b200pf_gemm_grouped", C.byref(pa), C.byref(pb), ptr(vg), 0, np_, 32, ns * 32 * np_, np_, 32 * np_, 1, st)
             _gemm(vg, self.c_h * ns, n, wt, n, o, channels=heads, a_plane=self.c_h * p, a_pitch=np_,
                   b_plane=n * pw, b_pitch=pw, x_plane=self.c_h * p, x_pitch=np_, cols=n)
-            call("b200pf_pwa_epilogue", ptr(o), ptr(vg[256 * p:]), ptr(w["w_ot"]), ptr(m[s0:]), ns, n, np_, st)
+            call("b200pf_pwa_gate_transpose", ptr(o), ptr(vg[256 * p:]), ptr(val), ns, np_, st)        # sigmoid(g) * o, K-major
+            _gemm(val, p, 256, w["w_o"], C_M, t)
+            call("b200pf_msa_add_rows", ptr(m[s0:]), ptr(t), ns, n, np_, st)
 
     def add_into(self, m: torch.Tensor, z: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
         """m += pair_weighted_averaging(m, z, mask) in place; m [S, N, 64] fp32, z [N, N, 128] fp32, mask [N, N]."""
