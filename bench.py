@@ -38,6 +38,13 @@ def block_flops(n: int) -> float:
     return 2 * tri_mul + 2 * tri_att + trans_z + s_track
 
 
+def pair_block_flops(n: int) -> float:
+    """The same without the single track (the pair-only block of the MSA module and the template stack)."""
+    tri_mul = 2 * n ** 3 * C + n * n * (8 * C * C + 2 * C * C + 2 * C * C)
+    tri_att = 4 * n ** 3 * C + n * n * (8 * C * C + 2 * C * 4 + 2 * C * C)
+    return 2 * tri_mul + 2 * tri_att + 6 * n * n * C * 4 * C
+
+
 def kernel_work(n: int):
     """Per-launch algorithmic FLOPs and HBM bytes of each fused kernel (E = n*n*128 elements)."""
     e = n * n * C
@@ -284,6 +291,76 @@ def outer_product_mean_leg(n: int, peaks, cpu: bool):
     return out
 
 
+def msa_layer_leg(n: int, cpu: bool):
+    """One block of the MSA module (pair-weighted averaging, MSA transition, outer-product mean, pair-only Pairformer
+    block) at the benchmark's token count and 1024 sequences, z and m resident: ms per block and per entry point,
+    parity of a small case against the CPU oracle, the oracle timed on a bounded sample."""
+    import collections
+    import time as _time
+    from oracle import msa_oracle
+    from tt_boltz_b200 import B200MSALayer, _lib, synthetic
+    s_len = 1024
+    w = synthetic.make_msa_layer_weights()
+    layer = B200MSALayer()
+    layer.load_state_dict(w)
+    layer.cuda()
+    sn, nn_ = 40, 56
+    _, zs = synthetic.make_inputs(nn_, seed=6, with_s=False)
+    ms_, mk = synthetic.make_msa_inputs(sn, nn_, drop=0.2, seed=7)
+    _, pm = synthetic.tail_padding_mask(nn_, 5)
+    z_o, m_o = layer(zs.cuda(), ms_[None].cuda(), pm.cuda(), mk[None].cuda())
+    with torch.no_grad():
+        z_w, m_w = msa_oracle.msa_layer(zs[0], ms_, pm[0], mk, w)
+    rel_z = float((z_o[0].cpu().double() - z_w.double()).norm() / z_w.double().norm())
+    rel_m = float((m_o[0].cpu().double() - m_w.double()).norm() / m_w.double().norm())
+    g = torch.Generator(device="cuda").manual_seed(0)
+    m = torch.randn(s_len, n, 64, device="cuda", generator=g)
+    z = torch.randn(n, n, 128, device="cuda", generator=g)
+    msa_mask = (torch.rand(s_len, n, device="cuda", generator=g) > 0.1).float()
+    tm = torch.ones(n, n, device="cuda")
+    for _ in range(3):
+        layer.forward_inplace(z, m, tm, msa_mask)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(5):
+        layer.forward_inplace(z, m, tm, msa_mask)
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / 5
+    _lib.timer = _lib.KernelTimer()
+    layer.forward_inplace(z, m, tm, msa_mask)
+    torch.cuda.synchronize()
+    events, _lib.timer = _lib.timer.events, None
+    per = collections.defaultdict(float)
+    for name, e0, e1 in events:
+        per[name] += e0.elapsed_time(e1)
+    flop = (2.0 * s_len * (32.0 * n) ** 2 + 2.0 * n * n * 1024 * 128            # outer-product mean
+            + 2.0 * s_len * n * 64 * 512 + 2.0 * 8 * 32 * s_len * n * n + 2.0 * s_len * n * 256 * 64   # pair-weighted averaging
+            + 2.0 * s_len * n * (64 * 512 + 256 * 64)                              # MSA transition
+            + pair_block_flops(n))                                                 # pair-only Pairformer block
+    out = {"config": {"workload": "one block of the MSA module (reference.py:1311-1397)", "tokens": n, "msa_depth": s_len,
+                      "msa_mask": "10 % of (sequence, token) entries masked", "inputs": "z and m resident"},
+           "ms": ms, "tflops": flop / (ms * 1e-3) / 1e12, "kernels_ms": dict(sorted(per.items(), key=lambda kv: -kv[1])),
+           "parity": {"rel_l2_z": rel_z, "rel_l2_m": rel_m, "tolerance": 2e-2, "ok": rel_z < 2e-2 and rel_m < 2e-2,
+                      "case": f"{sn} sequences x {nn_} tokens, 5 padded tokens, 20 % of the MSA masked, CPU oracle",
+                      "device_status": _lib.device_status()},
+           "cpu_baseline": None}
+    if cpu:
+        nc, sc = min(n, 256), 256
+        _, zc = synthetic.make_inputs(nc, seed=1, with_s=False)
+        mc, kc = synthetic.make_msa_inputs(sc, nc, drop=0.1, seed=1)
+        t0 = _time.perf_counter()
+        with torch.no_grad():
+            msa_oracle.msa_layer(zc[0], mc, torch.ones(nc, nc), kc, w)
+        sec = _time.perf_counter() - t0
+        out["cpu_baseline"] = {"value": sec * 1e3, "unit": "ms", "cores": os.cpu_count() or 1, "kind": "port",
+                               "sample": f"the oracle on {sc} sequences x {nc} tokens (not scaled: the parts scale differently)"}
+    del m, z, layer
+    torch.cuda.empty_cache()
+    return out
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -296,7 +373,7 @@ def main() -> None:
     ap.add_argument("--cpu-budget", type=float, default=150.0, help="seconds the CPU legs may spend")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--no-next", action="store_true", help="skip the outer-product-mean leg (one GPU only)")
+    ap.add_argument("--no-next", action="store_true", help="skip the MSA-stack legs (one GPU only)")
     ap.add_argument("--pad-frac", type=float, default=0.0, help="fraction of tokens masked at random (seed 3); 0 = all-ones masks")
     ap.add_argument("--precision", default="bf16", choices=["bf16", "mxfp8"],
                     help="bf16 = the headline tier; mxfp8 = triangle-multiplication operands in MXFP8")
@@ -478,7 +555,8 @@ def main() -> None:
 
     next_rows = None
     if world == 1 and not args.no_next:
-        next_rows = {"outer_product_mean": outer_product_mean_leg(n, peaks, not args.no_cpu)}
+        next_rows = {"outer_product_mean": outer_product_mean_leg(n, peaks, not args.no_cpu),
+                     "msa_layer": msa_layer_leg(n, not args.no_cpu)}
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

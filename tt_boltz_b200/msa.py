@@ -351,3 +351,31 @@ class B200MSALayer(nn.Module):
             mw = m[0].to(torch.float32).clone(memory_format=torch.contiguous_format)
             self.forward_inplace(zw, mw, token_mask[0], msa_mask[0])
         return zw[None], mw[None]
+
+
+class B200MSAStack(nn.Module):
+    """The ``layers`` of the reference's MSA module (tt_bio/reference.py:1187-1201, loop at :1279-1307) on resident
+    tensors: ``forward(z, m, token_mask, msa_mask) -> z`` runs every block on copies, ``run_inplace`` on the caller's
+    fp32 z [N, N, 128] and m [S, N, 64].  The feature embedding in front of it (one-hot MSA features, ``msa_proj``,
+    ``s_proj``, reference.py:1250-1276) is a handful of small linear maps and stays with the caller."""
+
+    def __init__(self, msa_blocks: int = 4, msa_s: int = C_M, token_z: int = 128, msa_dropout: float = 0.0, z_dropout: float = 0.0,
+                 pairwise_head_width: int = 32, pairwise_num_heads: int = 4, precision: str = "bf16") -> None:
+        super().__init__()
+        self.msa_blocks = msa_blocks
+        self.layers = nn.ModuleList(B200MSALayer(msa_s, token_z, msa_dropout, z_dropout, pairwise_head_width,
+                                                 pairwise_num_heads, precision) for _ in range(msa_blocks))
+
+    def run_inplace(self, z: torch.Tensor, m: torch.Tensor, token_mask: torch.Tensor, msa_mask: torch.Tensor) -> None:
+        for layer in self.layers:
+            layer.forward_inplace(z, m, token_mask, msa_mask)
+
+    def forward(self, z: torch.Tensor, m: torch.Tensor, token_mask: torch.Tensor, msa_mask: torch.Tensor) -> torch.Tensor:
+        """z [1, N, N, 128], m [1, S, N, 64], token_mask [1, N, N], msa_mask [1, S, N] -> z (what MSAModule.forward returns)."""
+        if not (z.is_cuda and m.is_cuda):
+            raise RuntimeError("the MSA kernels need CUDA tensors: the b200pf kernels have no CPU path")
+        with torch.no_grad():
+            zw = z[0].to(torch.float32).clone(memory_format=torch.contiguous_format)
+            mw = m[0].to(torch.float32).clone(memory_format=torch.contiguous_format)
+            self.run_inplace(zw, mw, token_mask[0], msa_mask[0])
+        return zw[None]
