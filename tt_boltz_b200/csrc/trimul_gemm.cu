@@ -6,6 +6,8 @@
 //   warps 2-5: epilogue - tcgen05.ld the finished 128x256 accumulator, round to bf16, store
 // Two accumulators (2 x 256 TMEM columns) let the epilogue of tile t overlap the MMAs of t+1.
 // Ragged sizes need no padding: TMA zero-fills out-of-range rows / columns, stores are guarded.
+#include <cstdlib>
+
 #include "sm100.cuh"
 
 namespace b200pf {
@@ -183,6 +185,169 @@ trimul_contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
+// ---- the same GEMM on CTA pairs ------------------------------------------------------------------
+// Two CTAs of a cluster (the two SMs of a TPC) share one 256 x 256 output tile: each stages its 128 rows of A and
+// its 128 rows of B (32 KB per k-block instead of the 48 KB a lone CTA needs for 128 x 256: the lone kernel is bound
+// by the 96 bytes per clock it has to pull from L2), the even CTA issues tcgen05.mma.cta_group::2 over both halves,
+// and each CTA drains its own 128 accumulator rows.  Loads land in the loading CTA's own shared memory (never a
+// multicast); their bytes are counted on the even CTA's barrier.  Every role of both CTAs always reaches the two
+// cluster barriers, also after a wait ran out.
+constexpr int P_STAGES = 6, P_STAGE_BYTES = 2 * (128 * BK * 2);
+constexpr int PAIR_SMEM = P_STAGES * P_STAGE_BYTES + 1024 + 256;
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+trimul_contract_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                            __nv_bfloat16* __restrict__ x, GemmShape s, unsigned int* status) {
+    using namespace sm100;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P_STAGES * P_STAGE_BYTES);
+    uint64_t* full = bars;                      // [P_STAGES]  used in the even CTA: both CTAs' loads
+    uint64_t* empty = bars + P_STAGES;          // [P_STAGES]  one per CTA
+    uint64_t* acc_full = bars + 2 * P_STAGES;   // [2]         one per CTA
+    uint64_t* acc_empty = acc_full + 2;         // [2]         used in the even CTA: both CTAs' epilogue warps
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();                     // 0: issues the MMAs
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    const int mt = (s.m_rows + 255) / 256, nt = (s.n_rows + BN - 1) / BN;
+    const int kb_total = (s.k_total + BK - 1) / BK;
+    const long long tiles = (long long)s.channels * mt * nt;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < P_STAGES; ++i) { mbar_init(&full[i], 2); mbar_init(&empty[i], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 8); }
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) { tmem_alloc_pair(tmem_slot, 512); tmem_relinquish_pair(); }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();                                              // the other CTA's barriers and tensor memory are ready
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- TMA producer: this CTA's half of A and of B ----------------
+        tma_prefetch_desc(&map_a);
+        tma_prefetch_desc(&map_b);
+        const uint32_t full0 = map_to_cta(&full[0], 0);            // the even CTA's barriers, 8 bytes apart
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        for (long long t = pair; t < tiles && ok; t += pairs) {
+            const int d = (int)(t / (mt * nt));
+            const int rem = (int)(t % (mt * nt));
+            const int m0 = (rem / nt) * 256 + (int)rank * 128, n0 = (rem % nt) * BN + (int)rank * 128;
+            // row coordinates once per tile; the k coordinates advance by BK (a k segment is a multiple of BK long)
+            const int a_row = m0 % s.a_rowseg_rows, a_seg0 = m0 / s.a_rowseg_rows;
+            const int b_row = n0 % s.b_rowseg_rows, b_seg0 = n0 / s.b_rowseg_rows;
+            int a_k = 0, a_ks = 0, b_k = 0, b_ks = 0;
+            for (int kb = 0; kb < kb_total; ++kb) {
+                ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag);
+                if (!ok) break;
+                uint8_t* sa = smem + stage * P_STAGE_BYTES;
+                const uint32_t fb = full0 + stage * 8;
+                if (rank == 0) mbar_arrive_expect_tx(&full[stage], P_STAGE_BYTES);
+                else mbar_arrive_expect_tx_cluster(fb, P_STAGE_BYTES);
+                tma_load_4d_pair(sa, &map_a, fb, a_k, a_row, d, a_seg0 + a_ks);
+                tma_load_4d_pair(sa + 128 * BK * 2, &map_b, fb, b_k, b_row, d, b_seg0 + b_ks);
+                a_k += BK; if (a_k >= s.a_kseg_cols) { a_k = 0; ++a_ks; }
+                b_k += BK; if (b_k >= s.b_kseg_cols) { b_k = 0; ++b_ks; }
+                if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+        if (!ok) {   // give copies in flight time to land before the CTA's shared memory goes away
+            atomicOr(status, DEV_STATUS_MBAR_TIMEOUT);
+            uint64_t t0 = global_timer_ns();
+            while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+        }
+    } else if (warp == 1 && rank == 0) {
+        // ---------------- MMA issuer (even CTA only) ----------------
+        constexpr uint32_t idesc = make_idesc_bf16(256, BN);
+        const uint64_t d_a0 = make_desc_k_sw128(smem_u32(smem)), d_b0 = make_desc_k_sw128(smem_u32(smem + 128 * BK * 2));
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        long long it = 0;
+        for (long long t = pair; t < tiles && ok; t += pairs, ++it) {
+            uint32_t ab = (uint32_t)(it & 1), aphase = (uint32_t)((it >> 1) & 1);
+            ok = mbar_wait_warp(&acc_empty[ab], aphase ^ 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t tmem_d = tmem_base + ab * BN;
+            for (int kb = 0; kb < kb_total; ++kb) {
+                ok = mbar_wait_warp(&full[stage], phase, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                if (elect_one()) {
+                    const uint64_t so = stage * (uint64_t)(P_STAGE_BYTES >> 4);
+#pragma unroll
+                    for (int kk = 0; kk < BK / 16; ++kk) umma_bf16_pair(tmem_d, d_a0 + so + kk * 2, d_b0 + so + kk * 2, idesc, (kb | kk) ? 1u : 0u);
+                    umma_commit_pair(smem_u32(&empty[stage]));
+                    umma_commit_pair(map_to_cta(&empty[stage], 1));
+                    if (kb + 1 == kb_total) {
+                        umma_commit_pair(smem_u32(&acc_full[ab]));
+                        umma_commit_pair(map_to_cta(&acc_full[ab], 1));
+                    }
+                }
+                __syncwarp();
+                if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+        if (!ok && lane == 0) atomicOr(status, DEV_STATUS_MBAR_TIMEOUT);
+    } else if (warp >= 2) {
+        // ---------------- epilogue: this CTA's 128 rows of the tile ----------------
+        const int quarter = warp & 3;
+        bool ok = true;
+        long long it = 0;
+        for (long long t = pair; t < tiles && ok; t += pairs, ++it) {
+            uint32_t ab = (uint32_t)(it & 1), aphase = (uint32_t)((it >> 1) & 1);
+            int d = (int)(t / (mt * nt));
+            int rem = (int)(t % (mt * nt));
+            int m0 = (rem / nt) * 256 + (int)rank * 128, n0 = (rem % nt) * BN;
+            ok = mbar_wait(&acc_full[ab], aphase, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            int row = m0 + quarter * 32 + lane;
+            __nv_bfloat16* xrow = x + x_row_offset(s, d, row < s.m_rows ? row : 0);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                int col = n0 + c * 32;
+                if (col >= s.x_cols) break;           // warp-uniform
+                __nv_bfloat16* xdst = s.x_col_group > 0
+                                          ? xrow + (long long)(col / s.x_col_group) * s.x_colgroup_stride + (col % s.x_col_group)
+                                          : xrow + col;
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + ab * BN + c * 32, r);
+                tmem_ld_wait();
+                if (row < s.m_rows) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        if (col + v * 8 + 8 <= s.x_cols) {
+                            uint4 o;
+                            o.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+                            o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+                            o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+                            o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+                            *reinterpret_cast<uint4*>(xdst + v * 8) = o;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(&acc_empty[ab], 0));
+        }
+        if (!ok && lane == 0) atomicOr(status, DEV_STATUS_MBAR_TIMEOUT);
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();                                              // nobody signals or reads the other CTA after this
+    if (warp == 1) { tc_fence_after(); tmem_dealloc_pair(tmem_base, 512); }
+}
+
 // ---- host: tensor maps -----------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -235,6 +400,17 @@ static int check_planes(const b200pf_planes* p, const char* what) {
     return B200PF_OK;
 }
 
+// B200PF_CONTRACT_PAIR=0 keeps every GEMM on the one-CTA kernel (read once).
+static bool use_pair_kernel() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("B200PF_CONTRACT_PAIR");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+static bool pair_attr_set[64] = {false};
+
 static int launch_contract_tc(const b200pf_planes* a, const b200pf_planes* b, b200pf_bf16* x, const GemmShape& s, cudaStream_t st) {
     unsigned int* status = device_status_word();
     B200PF_REQUIRE(status, B200PF_ERR_CUDA, "trimul_contract: no device status word");
@@ -251,6 +427,38 @@ static int launch_contract_tc(const b200pf_planes* a, const b200pf_planes* b, b2
     }
     int sms = 0;
     B200PF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    if (use_pair_kernel() && s.m_rows > BM) {
+        if (dev >= 0 && dev < 64 && !pair_attr_set[dev]) {
+            B200PF_CUDA(cudaFuncSetAttribute(trimul_contract_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM));
+            pair_attr_set[dev] = true;
+        }
+        long long tiles = (long long)s.channels * ((s.m_rows + 255) / 256) * ((s.n_rows + BN - 1) / BN);
+        // A persistent grid must be resident at once: a pair that only starts when another has finished would
+        // double the time.  Not every SM can be half of a pair, so ask how many pairs fit.
+        static int resident_pairs[64] = {0};
+        if (dev >= 0 && dev < 64 && resident_pairs[dev] == 0) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned)(sms / 2 * 2));
+            cfg.blockDim = dim3(GEMM_THREADS);
+            cfg.dynamicSmemBytes = PAIR_SMEM;
+            cudaLaunchAttribute attr;
+            attr.id = cudaLaunchAttributeClusterDimension;
+            attr.val.clusterDim.x = 2;
+            attr.val.clusterDim.y = 1;
+            attr.val.clusterDim.z = 1;
+            cfg.attrs = &attr;
+            cfg.numAttrs = 1;
+            int n = 0;
+            B200PF_CUDA(cudaOccupancyMaxActiveClusters(&n, trimul_contract_pair_kernel, &cfg));
+            B200PF_REQUIRE(n > 0, B200PF_ERR_CUDA, "trimul_contract: no CTA pair fits on this device");
+            resident_pairs[dev] = n < sms / 2 ? n : sms / 2;
+        }
+        long long pairs = (dev >= 0 && dev < 64) ? resident_pairs[dev] : sms / 2;
+        unsigned grid = 2u * (unsigned)(tiles < pairs ? tiles : pairs);
+        trimul_contract_pair_kernel<<<grid, GEMM_THREADS, PAIR_SMEM, st>>>(map_a, map_b, (__nv_bfloat16*)x, s, status);
+        B200PF_LAUNCH_CHECK();
+        return B200PF_OK;
+    }
     long long tiles = (long long)s.channels * ((s.m_rows + BM - 1) / BM) * ((s.n_rows + BN - 1) / BN);
     unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
     trimul_contract_tc_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(map_a, map_b, (__nv_bfloat16*)x, s, status);
