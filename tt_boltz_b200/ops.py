@@ -205,11 +205,11 @@ def _attention_f32(q, k, v, bias, bias_strides, mask_u8, mask_strides, batch, n_
 
 
 def tri_att_f32(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Tensor], ending: bool) -> None:
-    n = z.shape[0]
+    n, c = z.shape[0], z.shape[-1]
     st = stream()
     if ending:      # the reference transposes z and the mask, runs the starting-node path, transposes back
         src = torch.empty_like(z)
-        call("b200pf_f32_transpose01", ptr(z), ptr(src), n, C_Z, 0, st)
+        call("b200pf_f32_transpose01", ptr(z), ptr(src), n, c, 0, st)
         mask_ls, mask_ks = 1, n
     else:
         src = z
@@ -218,8 +218,11 @@ def tri_att_f32(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Tenso
     hd = w["mha.linear_q.weight"].shape[0] // heads
     x = f32_layernorm(src, w["layer_norm.weight"], w["layer_norm.bias"])
     bias = torch.empty(heads, n * n, dtype=torch.float32, device=z.device)
-    call("b200pf_ln_proj_heads", ptr(src), ptr(w["layer_norm.weight"]), ptr(w["layer_norm.bias"]),
-         ptr(w["linear.weight"]), ptr(bias), n * n, n * n, C_Z, heads, st)
+    if c == C_Z and heads in (4, 16):       # one fused pass over z
+        call("b200pf_ln_proj_heads", ptr(src), ptr(w["layer_norm.weight"]), ptr(w["layer_norm.bias"]),
+             ptr(w["linear.weight"]), ptr(bias), n * n, n * n, c, heads, st)
+    else:                                   # other widths / head counts: the normalised rows through the transposing linear
+        call("b200pf_f32_linear_t", ptr(x), ptr(w["linear.weight"]), None, ptr(bias), n * n, n * n, c, heads, st)
     q = f32_linear(x, w["mha.linear_q.weight"])
     k = f32_linear(x, w["mha.linear_k.weight"])
     v = f32_linear(x, w["mha.linear_v.weight"])
@@ -229,7 +232,7 @@ def tri_att_f32(z: torch.Tensor, mask_u8: torch.Tensor, w: Dict[str, torch.Tenso
     og = f32_gate(o, g, 0)
     if ending:
         upd = f32_linear(og, w["mha.linear_o.weight"])
-        call("b200pf_f32_transpose01", ptr(upd), ptr(z), n, C_Z, 1, st)
+        call("b200pf_f32_transpose01", ptr(upd), ptr(z), n, c, 1, st)
     else:
         f32_linear(og, w["mha.linear_o.weight"], out=z, accumulate=True)
 
@@ -242,11 +245,15 @@ def transition_f32(x_res: torch.Tensor, w: Dict[str, torch.Tensor]) -> None:
 
 def pair_bias_heads(z: torch.Tensor, w: Dict[str, torch.Tensor]) -> torch.Tensor:
     """bias[h][i_local*N + j] of the single-track attention: one fp32 pass over the (local rows of) z."""
-    rows = z.shape[0] * z.shape[1]          # z may be a row shard [nr, N, 128]
+    rows, c = z.shape[0] * z.shape[1], z.shape[-1]          # z may be a row shard [nr, N, c_z]
     heads = w["proj_z.1.weight"].shape[0]
     bias = torch.empty(heads, rows, dtype=torch.float32, device=z.device)
-    call("b200pf_ln_proj_heads", ptr(z), ptr(w["proj_z.0.weight"]), ptr(w["proj_z.0.bias"]),
-         ptr(w["proj_z.1.weight"]), ptr(bias), rows, rows, C_Z, heads, stream())
+    if c == C_Z and heads in (4, 16):
+        call("b200pf_ln_proj_heads", ptr(z), ptr(w["proj_z.0.weight"]), ptr(w["proj_z.0.bias"]),
+             ptr(w["proj_z.1.weight"]), ptr(bias), rows, rows, c, heads, stream())
+    else:
+        x = f32_layernorm(z, w["proj_z.0.weight"], w["proj_z.0.bias"])
+        call("b200pf_f32_linear_t", ptr(x), ptr(w["proj_z.1.weight"]), None, ptr(bias), rows, rows, c, heads, stream())
     return bias
 
 

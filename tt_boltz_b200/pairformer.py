@@ -20,7 +20,10 @@ Parameters carry the reference's state-dict key names, so ``load_state_dict`` of
 checkpoint slice works unchanged (tt_bio/tenstorrent.py:2179-2180 does the same for its backend).
 
 Inference only (eval-mode semantics: dropout masks are 1).  Inputs must be CUDA tensors; there
-is no CPU path.  ``precision``: "bf16" (fused tensor-core kernels, fp32 residual stream),
+is no CPU path.  The fused kernels are built for c_z = 128 with 4 x 32 triangle-attention heads (Boltz-2's trunk, MSA
+and confidence stacks); other widths (the template stack's c_z = 64, the c_z = 256 / 8-head trunks of sibling models)
+run on the un-fused fp32 kernels, which take any width: pass ``precision="fp32"`` or ``"auto"``.
+``precision``: "bf16" (fused tensor-core kernels, fp32 residual stream),
 "mxfp8" (as bf16, but the triangle-multiplication operands a / b are MXFP8: e4m3 values with one
 e8m0 scale per 32 elements along the contraction index, contracted by the block-scaled tensor-core
 instruction - the counterpart of the reference's block-fp8 fast mode, tt_bio/tenstorrent.py:178-181)
@@ -91,8 +94,10 @@ class B200PairformerLayer(nn.Module):
         super().__init__()
         if post_layer_norm:
             raise NotImplementedError("post_layer_norm=True is not used by Boltz-2 and is not built")
+        if precision == "auto":     # the fused kernels where their widths fit, the un-fused fp32 kernels elsewhere
+            precision = "bf16" if (token_z, pairwise_num_heads, pairwise_head_width) == (128, 4, 32) else "fp32"
         if precision not in ("bf16", "mxfp8", "fp32"):
-            raise ValueError("precision must be 'bf16', 'mxfp8' or 'fp32'")
+            raise ValueError("precision must be 'bf16', 'mxfp8', 'fp32' or 'auto'")
         self.token_s, self.token_z, self.num_heads = token_s, token_z, num_heads
         self.dropout, self.with_s, self.precision = dropout, with_s, precision
         self.fused = precision != "fp32"
@@ -185,6 +190,54 @@ class B200PairformerNoSeqLayer(B200PairformerLayer):
                 chunk_size_tri_attn: Optional[int] = None, use_kernels: bool = False,
                 use_cuequiv_mul: bool = False, use_cuequiv_attn: bool = False) -> torch.Tensor:
         return _run_layers([self], None, z, None, pair_mask)[1]
+
+
+class B200PairUpdateBlock(nn.Module):
+    """The block of the ESMFold2 folding trunk (tt_bio/esmfold2.py:129-154): ``z += tri_mul_out(z); z += tri_mul_in(z);
+    z += transition(z)``, no triangle attention, any pair width and transition width.  Keys as in the Pairformer layer
+    (``tri_mul_out.*``, ``tri_mul_in.*``, ``transition_z.*``); ``remaps.esmfold2_pair_update_block`` produces them from
+    an ESMFold2 checkpoint.  Runs on the un-fused fp32 kernels."""
+
+    def __init__(self, token_z: int = 256, hidden: Optional[int] = None) -> None:
+        super().__init__()
+        hidden = hidden or 4 * token_z
+        self.token_z, self.hidden = token_z, hidden
+        for name in ("tri_mul_out", "tri_mul_in"):
+            for leaf, shape in (("norm_in.weight", (token_z,)), ("norm_in.bias", (token_z,)),
+                                ("p_in.weight", (2 * token_z, token_z)), ("g_in.weight", (2 * token_z, token_z)),
+                                ("norm_out.weight", (token_z,)), ("norm_out.bias", (token_z,)),
+                                ("p_out.weight", (token_z, token_z)), ("g_out.weight", (token_z, token_z))):
+                _register_tree(self, f"{name}.{leaf}", shape)
+        for leaf, shape in (("norm.weight", (token_z,)), ("norm.bias", (token_z,)), ("fc1.weight", (hidden, token_z)),
+                            ("fc2.weight", (hidden, token_z)), ("fc3.weight", (token_z, hidden))):
+            _register_tree(self, f"transition_z.{leaf}", shape)
+        self._packed = None
+        self.register_load_state_dict_post_hook(lambda module, incompatible: setattr(module, "_packed", None))
+
+    def _pack(self, device):
+        if self._packed is None or self._packed["_device"] != device:
+            sd = dict(self.state_dict().items())
+            self._packed = {"_device": device}
+            for name in ("tri_mul_out", "tri_mul_in", "transition_z"):
+                self._packed[name] = weights.to_device_f32(sd, name + ".", device)
+        return self._packed
+
+    def forward_inplace(self, z: torch.Tensor, pair_mask_u8: torch.Tensor) -> None:
+        """z [N, N, c_z] contiguous fp32, updated where it is; pair_mask_u8 [N, N]."""
+        pk = self._pack(z.device)
+        ops.tri_mul_f32(z, pair_mask_u8, pk["tri_mul_out"], False)
+        ops.tri_mul_f32(z, pair_mask_u8, pk["tri_mul_in"], True)
+        ops.transition_f32(z, pk["transition_z"])
+
+    def forward(self, z: torch.Tensor, mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """z [1, N, N, c_z], mask [1, N, N] or None -> z."""
+        if not z.is_cuda:
+            raise RuntimeError("B200 Pairformer: inputs must be CUDA tensors (there is no CPU path)")
+        n = z.shape[1]
+        with torch.cuda.device(z.device), torch.no_grad():
+            zw = z[0].to(torch.float32).clone(memory_format=torch.contiguous_format)
+            self.forward_inplace(zw, _mask_u8(mask, (n, n), z.device))
+        return zw[None]
 
 
 _TRI_ATT_KEY = re.compile(r"((?:^|\.)tri_att_(?:start|end)\.)linear_[qkvog]\.")
