@@ -367,6 +367,9 @@ int b200pf_pwa_gate_transpose(const b200pf_bf16* o, const b200pf_bf16* g, b200pf
 int b200pf_msa_swiglu(const b200pf_bf16* h, b200pf_bf16* out, long long rows, void* stream);
 /* m[s][i][:] += t[s*np + i][:]  (t bf16 rows of 64). */
 int b200pf_msa_add_rows(float* m, const b200pf_bf16* t, int s_len, int n, int np, void* stream);
+/* m[s][i][:] += e[i][:] (fp32 rows of 64): the projected single representation added to every sequence's embedding
+ * (MSAModule.forward, tt_bio/reference.py:1275-1276). */
+int b200pf_msa_add_token_rows(float* m, const float* e, int s_len, int n, void* stream);
 
 /* All-to-all of equal blocks over peer mappings (multi-GPU path, no counterpart in the reference, whose
  * cards do not exchange data: tt_bio/distributed.py fans whole jobs out).  Block t of `send` (world blocks

@@ -10,7 +10,7 @@ import inspect
 import pytest
 import torch
 
-from tt_boltz_b200 import (B200MSALayer, B200MSATransition, B200OuterProductMean, B200PairWeightedAveraging, B200PairformerLayer, B200PairformerModule, B200PairformerNoSeqLayer,
+from tt_boltz_b200 import (B200MSALayer, B200MSAModule, B200MSATransition, B200OuterProductMean, B200PairWeightedAveraging, B200PairformerLayer, B200PairformerModule, B200PairformerNoSeqLayer,
                            B200PairformerNoSeqModule, B200RecyclingTrunk, synthetic)
 
 
@@ -131,3 +131,15 @@ def test_msa_layer_surface():
         layer.pair_weighted_averaging(m[None], z, torch.ones(1, 8, 8))
     with pytest.raises(RuntimeError, match="CUDA"):
         layer.msa_transition(m[None])
+
+
+def test_msa_module_surface():
+    """tt_bio/reference.py:1153-1201, 1203-1209: constructor keywords, parameters, forward(z, emb, feats, use_kernels)."""
+    mod = B200MSAModule(msa_s=64, token_z=128, token_s=384, msa_blocks=4, msa_dropout=0.15, z_dropout=0.25,
+                        pairwise_head_width=32, pairwise_num_heads=4, activation_checkpointing=False,
+                        use_paired_feature=True, subsample_msa=False, num_subsampled_msa=1024)
+    assert set(mod.state_dict().keys()) == set(synthetic.make_msa_module_weights(4).keys())
+    assert _params(B200MSAModule.forward) == ["self", "z", "emb", "feats", "use_kernels"]
+    feats = synthetic.make_msa_features(4, 8)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        mod(torch.zeros(1, 8, 8, 128), torch.zeros(1, 8, 384), feats)

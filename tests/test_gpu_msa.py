@@ -14,7 +14,7 @@ import torch
 
 from oracle import msa_oracle
 from tests.conftest import rel_l2
-from tt_boltz_b200 import B200MSALayer, B200OuterProductMean, _lib, synthetic
+from tt_boltz_b200 import B200MSALayer, B200MSAModule, B200OuterProductMean, _lib, synthetic
 
 pytestmark = pytest.mark.gpu
 TOL = 2e-2
@@ -135,3 +135,17 @@ def test_msa_layer_against_oracle_with_chunks(monkeypatch):
     assert torch.isfinite(z_o).all() and torch.isfinite(m_o).all()
     assert rel_l2(m_o[0].cpu(), m_want) < TOL
     assert rel_l2(z_o[0].cpu(), z_want) < TOL
+
+
+def test_msa_module_against_reference_fixture(golden_dir):
+    """The whole MSA module (feature embedding + two blocks) against what tt_bio.reference.MSAModule returned."""
+    from tests.golden.msa.make_msa_module import make_case_inputs
+    g = np.load(os.path.join(golden_dir, "msa", "msa_module_s9_n21.npz"))
+    c = dict(s=int(g["s"]), n=int(g["n"]), blocks=int(g["blocks"]), pad=int(g["pad"]))
+    z, emb, feats = make_case_inputs(c)
+    mod = B200MSAModule(64, 128, 384, c["blocks"], 0.0, 0.0)
+    mod.load_state_dict(synthetic.make_msa_module_weights(c["blocks"]), strict=True)
+    out = mod.cuda()(z.cuda(), emb.cuda(), {k: v.cuda() for k, v in feats.items()})
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    assert rel_l2(out[0].cpu(), torch.from_numpy(g["z_out"])) < TOL

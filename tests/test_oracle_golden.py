@@ -112,3 +112,14 @@ def test_msa_layer_oracle_matches_reference_outputs(golden_dir, name):
 
 def test_msa_layer_fixtures_present():
     assert len(MSA_LAYER_CASES) >= 2
+
+
+def test_msa_module_oracle_matches_reference_output(golden_dir):
+    """tests/golden/msa/make_msa_module.py stored what tt_bio.reference.MSAModule.forward returns."""
+    from tests.golden.msa.make_msa_module import make_case_inputs
+    g = np.load(os.path.join(golden_dir, "msa", "msa_module_s9_n21.npz"))
+    c = dict(s=int(g["s"]), n=int(g["n"]), blocks=int(g["blocks"]), pad=int(g["pad"]))
+    z, emb, feats = make_case_inputs(c)
+    with torch.no_grad():
+        out = msa_oracle.msa_module(z[0], emb[0], feats, synthetic.make_msa_module_weights(c["blocks"]), c["blocks"])
+    assert rel_l2(out, torch.from_numpy(g["z_out"])) < 2e-6

@@ -3,7 +3,7 @@ reference's PairformerModule / PairformerLayer call surface.  See include/b200pf
 from .pairformer import (B200PairformerLayer, B200PairformerModule, B200PairformerNoSeqLayer,
                          B200PairformerNoSeqModule, B200PairUpdateBlock)
 
-from .msa import B200MSALayer, B200MSAStack, B200MSATransition, B200OuterProductMean, B200PairWeightedAveraging
+from .msa import B200MSALayer, B200MSAModule, B200MSAStack, B200MSATransition, B200OuterProductMean, B200PairWeightedAveraging
 from .recycling import B200RecyclingTrunk
 
-__all__ = ["B200MSALayer", "B200MSAStack", "B200MSATransition", "B200OuterProductMean", "B200PairWeightedAveraging", "B200RecyclingTrunk", "B200PairformerLayer", "B200PairformerModule", "B200PairformerNoSeqLayer", "B200PairformerNoSeqModule", "B200PairUpdateBlock"]
+__all__ = ["B200MSALayer", "B200MSAModule", "B200MSAStack", "B200MSATransition", "B200OuterProductMean", "B200PairWeightedAveraging", "B200RecyclingTrunk", "B200PairformerLayer", "B200PairformerModule", "B200PairformerNoSeqLayer", "B200PairformerNoSeqModule", "B200PairUpdateBlock"]

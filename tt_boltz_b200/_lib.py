@@ -60,6 +60,7 @@ SIGNATURES = {
     "b200pf_gemm_grouped": [C.POINTER(Planes), C.POINTER(Planes), _vp, _ll, _i, _i, _ll, _i, _ll, _i, _vp],
     "b200pf_msa_swiglu": [_vp, _vp, _ll, _vp],
     "b200pf_msa_add_rows": [_vp, _vp, _i, _i, _i, _vp],
+    "b200pf_msa_add_token_rows": [_vp, _vp, _i, _i, _vp],
     "b200pf_opm_producer": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "b200pf_opm_outer": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "b200pf_opm_mask_bits": [_vp, _vp, _i, _i, _vp],

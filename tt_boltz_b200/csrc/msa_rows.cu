@@ -143,6 +143,19 @@ add_rows_kernel(float* __restrict__ m, const __nv_bfloat16* __restrict__ t, int 
     }
 }
 
+// m[s][i][:] += e[i][:] (fp32 rows of 64): the single representation's projection added to every sequence's embedding.
+__global__ void __launch_bounds__(256)
+add_token_rows_kernel(float* __restrict__ m, const float* __restrict__ e, int s_len, int n) {
+    const long long per_seq = (long long)n * 16, total = per_seq * s_len;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+        const float4 ev = __ldg(reinterpret_cast<const float4*>(e) + idx % per_seq);
+        float4* mp = reinterpret_cast<float4*>(m) + idx;
+        float4 v = *mp;
+        v.x += ev.x; v.y += ev.y; v.z += ev.z; v.w += ev.w;
+        *mp = v;
+    }
+}
+
 static unsigned grid_for(long long items, int per_block) {
     long long b = (items + per_block - 1) / per_block;
     const long long cap = 148LL * 32;
@@ -202,6 +215,13 @@ extern "C" int b200pf_msa_add_rows(float* m, const b200pf_bf16* t, int s_len, in
                    "msa_add_rows: bad arguments");
     msa::add_rows_kernel<<<msa::grid_for((long long)s_len * n * 16, 256), 256, 0, (cudaStream_t)stream>>>(
         m, (const __nv_bfloat16*)t, s_len, n, np);
+    B200PF_LAUNCH_CHECK();
+    return B200PF_OK;
+}
+
+extern "C" int b200pf_msa_add_token_rows(float* m, const float* e, int s_len, int n, void* stream) {
+    B200PF_REQUIRE(m && e && aligned16(m) && aligned16(e) && s_len > 0 && n > 0, B200PF_ERR_INVALID, "msa_add_token_rows: bad arguments");
+    msa::add_token_rows_kernel<<<msa::grid_for((long long)s_len * n * 16, 256), 256, 0, (cudaStream_t)stream>>>(m, e, s_len, n);
     B200PF_LAUNCH_CHECK();
     return B200PF_OK;
 }

@@ -379,3 +379,66 @@ class B200MSAStack(nn.Module):
             mw = m[0].to(torch.float32).clone(memory_format=torch.contiguous_format)
             self.run_inplace(zw, mw, token_mask[0], msa_mask[0])
         return zw[None]
+
+
+NUM_TOKENS = 33                    # residue / nucleotide / gap classes of the MSA one-hot (tt_bio/data/const.py:157)
+
+
+class B200MSAModule(nn.Module):
+    """Drop-in for the reference's ``MSAModule`` (tt_bio/reference.py:1150-1308; device form
+    tt_bio/tenstorrent.py:2524-2621): the MSA features are embedded (``msa_proj`` of the one-hot residues, deletion and
+    pairing features, plus ``s_proj`` of the single representation for every sequence) and ``msa_blocks`` MSA layers
+    run on resident tensors; ``forward(z, emb, feats, use_kernels=False)`` returns the pair tensor after the last
+    block, which the trunk adds to z (tt_bio/boltz2.py:5230).  The one-hot and the concatenation of the raw features
+    are torch indexing at the boundary; both projections and everything after run on the b200pf kernels."""
+
+    def __init__(self, msa_s: int = C_M, token_z: int = 128, token_s: int = 384, msa_blocks: int = 4, msa_dropout: float = 0.0,
+                 z_dropout: float = 0.0, pairwise_head_width: int = 32, pairwise_num_heads: int = 4,
+                 activation_checkpointing: bool = False, use_paired_feature: bool = True, subsample_msa: bool = False,
+                 num_subsampled_msa: int = 1024, precision: str = "bf16", **kwargs) -> None:
+        super().__init__()
+        self.msa_blocks, self.use_paired_feature = msa_blocks, use_paired_feature
+        self.subsample_msa, self.num_subsampled_msa = subsample_msa, num_subsampled_msa
+        self.s_proj = nn.Linear(token_s, msa_s, bias=False)
+        self.msa_proj = nn.Linear(NUM_TOKENS + 2 + int(use_paired_feature), msa_s, bias=False)
+        self.layers = nn.ModuleList(B200MSALayer(msa_s, token_z, msa_dropout, z_dropout, pairwise_head_width,
+                                                 pairwise_num_heads, precision) for _ in range(msa_blocks))
+
+    def embed(self, emb: torch.Tensor, feats) -> torch.Tensor:
+        """m [S, N, 64] fp32 from the single representation emb [1, N, token_s] and the MSA features (reference.py:1252-1276)."""
+        from . import ops
+        msa = torch.nn.functional.one_hot(feats["msa"][0], num_classes=NUM_TOKENS).to(torch.float32)
+        parts = [msa, feats["has_deletion"][0].unsqueeze(-1).float(), feats["deletion_value"][0].unsqueeze(-1).float()]
+        if self.use_paired_feature:
+            parts.append(feats["msa_paired"][0].unsqueeze(-1).float())
+        raw = torch.cat(parts, dim=-1)                                      # [S, N, 35 or 36]
+        if raw.shape[-1] % 4:                                               # the linear kernel wants 16-byte rows
+            raw = torch.nn.functional.pad(raw, (0, 4 - raw.shape[-1] % 4))
+        w = self.msa_proj.weight.detach().to(device=raw.device, dtype=torch.float32)
+        if w.shape[1] != raw.shape[-1]:
+            w = torch.nn.functional.pad(w, (0, raw.shape[-1] - w.shape[1]))
+        s_len, n = raw.shape[0], raw.shape[1]
+        m = ops.f32_linear(raw.contiguous(), w.contiguous()).view(s_len, n, C_M)
+        e = ops.f32_linear(emb[0].to(torch.float32).contiguous(),
+                           self.s_proj.weight.detach().to(device=raw.device, dtype=torch.float32).contiguous())
+        call("b200pf_msa_add_token_rows", ptr(m), ptr(e), s_len, n, stream())
+        return m
+
+    def forward(self, z: torch.Tensor, emb: torch.Tensor, feats, use_kernels: bool = False) -> torch.Tensor:
+        """z [1, N, N, 128], emb [1, N, token_s], feats with ``msa`` [1, S, N] (int64), ``has_deletion``,
+        ``deletion_value``, ``msa_paired``, ``msa_mask`` [1, S, N] and ``token_pad_mask`` [1, N] -> z [1, N, N, 128]."""
+        if not (z.is_cuda and emb.is_cuda and feats["msa"].is_cuda):
+            raise RuntimeError("the MSA kernels need CUDA tensors: the b200pf kernels have no CPU path")
+        with torch.no_grad():
+            msa_mask = feats["msa_mask"][0]
+            if self.subsample_msa:                                          # reference.py:1269-1272
+                idx = torch.randperm(feats["msa"].shape[1], device=z.device)[: self.num_subsampled_msa]
+                feats = {k: (v[:, idx] if k in ("msa", "has_deletion", "deletion_value", "msa_paired") else v) for k, v in feats.items()}
+                msa_mask = msa_mask[idx]
+            tok = feats["token_pad_mask"][0].float()
+            token_mask = tok[:, None] * tok[None, :]
+            m = self.embed(emb, feats)
+            zw = z[0].to(torch.float32).clone(memory_format=torch.contiguous_format)
+            for layer in self.layers:
+                layer.forward_inplace(zw, m, token_mask, msa_mask)
+        return zw[None]

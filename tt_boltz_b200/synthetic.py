@@ -194,3 +194,32 @@ def make_msa_layer_weights(seed: int = 21, std: float = 0.05, affine_jitter: flo
     for k, v in make_weights(1, seed=seed + 2, std=std, affine_jitter=affine_jitter, with_s=False).items():
         sd["pairformer_layer." + k[len("layers.0."):]] = v
     return sd
+
+
+def make_msa_module_weights(blocks: int = 2, seed: int = 31) -> Dict[str, torch.Tensor]:
+    """State dict of the MSA module with the reference's key names (tt_bio/reference.py:1187-1201): the two input
+    projections and ``layers.{i}.*`` of ``make_msa_layer_weights``."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    sd = {"s_proj.weight": torch.randn(64, 384, generator=g) * 0.05, "msa_proj.weight": torch.randn(64, 36, generator=g) * 0.3}
+    for i in range(blocks):
+        for k, v in make_msa_layer_weights(seed=seed + 10 * (i + 1)).items():
+            sd[f"layers.{i}.{k}"] = v
+    return sd
+
+
+def make_msa_features(s: int, n: int, n_pad: int = 0, drop: float = 0.2, seed: int = 13) -> Dict[str, torch.Tensor]:
+    """The MSA entries of the feature dict the MSA module reads (tt_bio/reference.py:1252-1259), batch 1."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    mask = (torch.rand(1, s, n, generator=g) >= drop).float()
+    mask[:, 0] = 1.0
+    pad = torch.ones(1, n)
+    if n_pad:
+        pad[:, n - n_pad:] = 0
+    return {
+        "msa": torch.randint(0, 33, (1, s, n), generator=g),
+        "has_deletion": (torch.rand(1, s, n, generator=g) < 0.1).float(),
+        "deletion_value": torch.rand(1, s, n, generator=g),
+        "msa_paired": (torch.rand(1, s, n, generator=g) < 0.5).float(),
+        "msa_mask": mask,
+        "token_pad_mask": pad,
+    }
