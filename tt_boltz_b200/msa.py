@@ -356,8 +356,8 @@ class B200MSALayer(nn.Module):
 class B200MSAStack(nn.Module):
     """The ``layers`` of the reference's MSA module (tt_bio/reference.py:1187-1201, loop at :1279-1307) on resident
     tensors: ``forward(z, m, token_mask, msa_mask) -> z`` runs every block on copies, ``run_inplace`` on the caller's
-    fp32 z [N, N, 128] and m [S, N, 64].  The feature embedding in front of it (one-hot MSA features, ``msa_proj``,
-    ``s_proj``, reference.py:1250-1276) is a handful of small linear maps and stays with the caller."""
+    fp32 z [N, N, 128] and m [S, N, 64], for callers that keep the embedded MSA on the GPU across recycles
+    (``B200MSAModule`` embeds the features and runs the same blocks)."""
 
     def __init__(self, msa_blocks: int = 4, msa_s: int = C_M, token_z: int = 128, msa_dropout: float = 0.0, z_dropout: float = 0.0,
                  pairwise_head_width: int = 32, pairwise_num_heads: int = 4, precision: str = "bf16") -> None:
