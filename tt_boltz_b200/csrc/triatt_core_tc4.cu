@@ -4,10 +4,12 @@
 //   warps 0-15  softmax group g = warp / 4 -> line l + g   (thread = query row = TMEM lane); four groups, i.e.
 //               four warps per scheduler, so that one group's exponentials run in the latency gaps of the others
 //   warp  16    TMA producer   (bias tile shared by the four lines; K and V^T tiles per line)
-//   warps 17,18 MMA issuers    (one per pair of groups; a polling state machine, so a group that is not ready
-//                               never holds up the other.  The whole warp runs it and one elected lane issues.)
-// Per key tile of 64 and pair of groups: S_pair (128 x 128 fp32, TMEM) = bias_tile x [I | I]^T (the bf16 bias
-// lands in both lines' score columns exactly), then S_g += Q_g K_g^T per group.  The softmax thread reads its row
+//   warps 17,18 MMA issuers    (one per pair of groups; a polling state machine over both groups' next scores and
+//                               P V products, so a group that is not ready never holds up the other.  The whole warp
+//                               runs it and one elected lane issues.)
+// Per key tile of 64 and group: S_g (128 x 64 fp32, TMEM) = bias_tile x I^T (the bf16 bias lands in the score columns
+// exactly), then S_g += Q_g K_g^T.  (Producing the scores of a pair's two groups together, one bias product for
+// both, made each group wait for the other to release its columns: 2 % slower.)  The softmax thread reads its row
 // in two halves, applies the key mask and computes p = exp2(s - m) in ONE pass with the reference m of the tiles
 // before (scaling by a stale reference is exact in floating point; a check keeps it far from overflow and hands the
 // rare tile that fails it, like the first tile of a line, to a two-pass path).  p goes back to TENSOR memory as
@@ -17,7 +19,8 @@
 // second half is in registers, so the next tile's products run under this tile's exponentials.
 // What bounds it (measured by leaving parts out): with no softmax arithmetic at all the MMA / barrier skeleton takes
 // 1.08 ms at N = 1024 (every tcgen05.mma costs its issuing thread ~40 clocks and every tcgen05.commit ~75, and the
-// bias product alone 0.22 ms); with the softmax arithmetic and only the Q K^T products 1.36 ms; together 1.45 ms.
+// bias product alone 0.22 ms); with the softmax arithmetic and only the Q K^T products 1.36 ms; together 1.45 ms
+// (1.43 ms since the groups of a pair get their scores independently).
 // Scores are in the log2 domain (host folds log2(e)/sqrt(32) into W_q and log2(e) into the bias).
 // Every wait is bounded; a wait that runs out raises the status word and the CTA unwinds.
 #include "sm100.cuh"
@@ -200,9 +203,9 @@ triatt_core_tc4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         B->abort_flag = 0;
         fence_barrier_init();
     }
-    // identity stacked twice: row r has its one at column r % 64, so bias_tile x B^T adds bias[q][k]
-    // to score column k of BOTH lines of a pair (bf16 x 1 with fp32 accumulation: exact)
-    for (int i = tid; i < 2 * AK * 8; i += THREADS) {
+    // 64 x 64 identity as the B operand: bias_tile x I^T puts bias[q][k] into score column k (bf16 x 1 with fp32
+    // accumulation: exact)
+    for (int i = tid; i < AK * 8; i += THREADS) {
         const int row = i >> 3, chunk = i & 7, k = row & (AK - 1);
         uint32_t w4[4] = {0u, 0u, 0u, 0u};
         if ((k >> 3) == chunk) w4[(k & 7) >> 1] = (k & 1) ? 0x3F800000u : 0x00003F80u;
@@ -264,8 +267,7 @@ triatt_core_tc4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         // the non-blocking test_wait what is ready instead of blocking on one barrier: the next S of the
         // pair, and the P V product of either group.  Tiles are counted over all items of this CTA.
         const int pr = __shfl_sync(0xffffffffu, warp - MMA_WARP0, 0), g0 = 2 * pr;
-        constexpr uint32_t idesc_bias = make_idesc_bf16(AQ, 2 * AK);
-        constexpr uint32_t idesc_s = make_idesc_bf16(AQ, AK);
+        constexpr uint32_t idesc_s = make_idesc_bf16(AQ, AK), idesc_bias = idesc_s;
         constexpr uint32_t idesc_pv = make_idesc_bf16(AQ, HD);
         // every descriptor is a precomputed base plus a small constant (the address field counts 16-byte
         // units; a K step of 16 bf16 is 32 bytes = 2)
@@ -280,43 +282,45 @@ triatt_core_tc4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const uint32_t t_s = tmem_base + COL_S + (uint32_t)(g0 * AK);
         const uint32_t t_p = tmem_base + COL_P + (uint32_t)(g0 * (AK / 2));
         const uint32_t t_o = tmem_base + COL_O + (uint32_t)(g0 * HD);
-        uint32_t Gs = 0, Gp[2] = {0u, 0u};
-        uint32_t js = 0, ks = 0, stage_s = 0, phase_s = 0;          // tile-in-item, item, stage and its phase of the next S
+        uint32_t Gs[2] = {0u, 0u}, Gp[2] = {0u, 0u};
+        uint32_t js[2] = {0u, 0u}, ks[2] = {0u, 0u}, stage_s[2] = {0u, 0u}, phase_s[2] = {0u, 0u};   // per group: the next S
         uint32_t jp[2] = {0u, 0u}, stage_p[2] = {0u, 0u};
         IdleGuard guard;
         bool ok = true;
         while (ok && (Gp[0] < total_tiles || Gp[1] < total_tiles)) {
             bool progress = false;
-            if (Gs < total_tiles) {
-                const uint32_t qb = ks & 1;
-                if (mbar_test_wait(&B->kv_full[stage_s], phase_s) && mbar_test_wait(&B->s_empty[g0], (Gs & 1) ^ 1) &&
-                    mbar_test_wait(&B->s_empty[g0 + 1], (Gs & 1) ^ 1) && (js != 0 || mbar_test_wait(&B->q_full[qb], (ks >> 1) & 1))) {
-                    tc_fence_after();
-                    if (elect_one()) {
-                        const uint64_t so = stage_s * STAGE_STEP;
 #pragma unroll
-                        for (int kk = 0; kk < AK / 16; ++kk)
-                            umma_bf16(t_s, d_bias0 + so + 2 * kk, d_ident + 2 * kk, idesc_bias, kk ? 1u : 0u);
+            for (int i = 0; i < 2; ++i) {
+                if (Gs[i] < total_tiles) {
+                    const uint32_t qb = ks[i] & 1;
+                    if (mbar_test_wait(&B->kv_full[stage_s[i]], phase_s[i]) && mbar_test_wait(&B->s_empty[g0 + i], (Gs[i] & 1) ^ 1) &&
+                        (js[i] != 0 || mbar_test_wait(&B->q_full[qb], (ks[i] >> 1) & 1))) {
+                        tc_fence_after();
+                        if (elect_one()) {
+                            const uint64_t so = stage_s[i] * STAGE_STEP;
+                            const uint32_t ts = t_s + (uint32_t)(i * AK);
 #pragma unroll
-                        for (int i = 0; i < 2; ++i) {
+                            for (int kk = 0; kk < AK / 16; ++kk)
+                                umma_bf16(ts, d_bias0 + so + 2 * kk, d_ident + 2 * kk, idesc_bias, kk ? 1u : 0u);
 #pragma unroll
                             for (int kk = 0; kk < HD / 16; ++kk)
-                                umma_bf16(t_s + (uint32_t)(i * AK), d_q0[i] + qb * Q_STEP + 2 * kk, d_k0[i] + so + 2 * kk, idesc_s, 1u);
+                                umma_bf16(ts, d_q0[i] + qb * Q_STEP + 2 * kk, d_k0[i] + so + 2 * kk, idesc_s, 1u);
                             umma_commit(&B->s_full[g0 + i]);
+                            // the later of the pair's two groups to issue the item's last scores frees the Q tiles
+                            if (js[i] == (uint32_t)T - 1 && Gs[1 - i] > Gs[i]) umma_commit(&B->q_empty[qb]);
                         }
-                        if (js == (uint32_t)T - 1) umma_commit(&B->q_empty[qb]);
+                        __syncwarp();
+                        ++Gs[i];
+                        if (++js[i] == (uint32_t)T) { js[i] = 0; ++ks[i]; }
+                        if (++stage_s[i] == ST) { stage_s[i] = 0; phase_s[i] ^= 1; }
+                        progress = true;
                     }
-                    __syncwarp();
-                    ++Gs;
-                    if (++js == (uint32_t)T) { js = 0; ++ks; }
-                    if (++stage_s == ST) { stage_s = 0; phase_s ^= 1; }
-                    progress = true;
                 }
             }
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 const uint32_t G = Gp[i];
-                if (G < Gs && mbar_test_wait(&B->p_full[g0 + i], G & 1)) {
+                if (G < Gs[i] && mbar_test_wait(&B->p_full[g0 + i], G & 1)) {
                     tc_fence_after();
                     if (elect_one()) {
                         const uint64_t dv = d_vt0[i] + stage_p[i] * STAGE_STEP;
