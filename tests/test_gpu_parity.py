@@ -441,3 +441,46 @@ def test_staged_single_track_attention_equals_direct_kernel(dev, nq, nk):
     assert bias_al.data_ptr() % 16 == 0 and bias_un[1:].data_ptr() % 16 == 4
     assert torch.isfinite(outs[0]).all()
     assert torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("n, amp", [(200, 40.0), (320, 30.0)])
+def test_attention_core_with_scores_that_jump_far_above_the_running_reference(dev, n, amp):
+    """The core alone, on synthetic q / k / v / bias whose scores (log2 domain) span hundreds of units, so that within a
+    line a later key tile lies far more than 2^64 above everything seen before: the one-pass softmax has to notice
+    before it releases the scores and redo such a tile with a fresh reference.  Against a float64 softmax of the same
+    bf16 inputs; tolerance = the rounding of p to bf16 (2^-9 relative per term)."""
+    from tt_boltz_b200 import _lib
+    from tt_boltz_b200._lib import call, ptr, stream
+    g = torch.Generator().manual_seed(21)
+    heads, hd, lines = 4, 32, 9
+    pitch = (n + 7) // 8 * 8
+    mpitch = (n + 63) // 64 * 64
+    q = torch.randn(lines, n, heads, hd, generator=g).bfloat16()
+    k = (torch.randn(lines, n, heads, hd, generator=g) * amp / (hd ** 0.5)).bfloat16()
+    # keys later in the line are systematically larger: the running maximum keeps growing in big steps
+    k = (k.float() * torch.linspace(0.05, 1.0, n)[None, :, None, None] ** 2).bfloat16()
+    v = torch.randn(lines, n, heads, hd, generator=g).bfloat16()
+    bias = (torch.randn(n, heads, n, generator=g) * 3).bfloat16()           # [query][head][key]
+    mask = (torch.rand(lines, n, generator=g) > 0.1)
+    mask[:, 0] = True
+    vt = torch.zeros(lines, heads, hd, pitch, dtype=torch.bfloat16)
+    vt[..., :n] = v.permute(0, 2, 3, 1)
+    bias_p = torch.zeros(n, heads, pitch, dtype=torch.bfloat16)
+    bias_p[..., :n] = bias
+    mask_p = torch.zeros(lines, mpitch, dtype=torch.uint8)
+    mask_p[:, :n] = mask.to(torch.uint8)
+    o = torch.zeros(lines, n, heads * hd, dtype=torch.bfloat16, device=dev)
+    qd, kd, vtd, bd, md = q.to(dev).contiguous(), k.to(dev).contiguous(), vt.to(dev), bias_p.to(dev), mask_p.to(dev)
+    call("b200pf_triatt_core_tc4", ptr(qd), ptr(kd), ptr(vtd), pitch, ptr(bd), pitch, heads * pitch, ptr(md), mpitch,
+         ptr(o), n * heads * hd, heads * hd, lines, n, stream())
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    s = torch.einsum("lqhd,lkhd->lhqk", q.double(), k.double()) + bias.double().permute(1, 0, 2)[None]
+    s = s + torch.where(mask, 0.0, -1.0e9 * 1.4426950408889634)[:, None, None, :].double()
+    span = float((s.amax(-1) - s[..., : 64].amax(-1)).max())
+    assert span > 100, span                                                  # the premise: far beyond the 2^64 headroom
+    p = torch.exp2(s - s.amax(-1, keepdim=True))
+    want = torch.einsum("lhqk,lkhd->lqhd", p / p.sum(-1, keepdim=True), v.double()).reshape(lines, n, heads * hd)
+    got = o.cpu().double()
+    assert torch.isfinite(got).all()
+    assert rel_l2(got, want) < 6e-3
