@@ -97,8 +97,9 @@ int b200pf_f32_gate_strided(const float* a, long long a_pitch, const float* b, l
  *   o[q][h] = sigmoid(g[q][h]) * softmax_k( scale * <q[q][h], k[k][h]> + bias[h][q][k] - inf * (1 - mask[k]) ) v[k][h]
  * q, g, o are row-major with their own pitches (head h at columns h*24 ..); k and v come transposed,
  * kt[(h*24 + e)][key] with kt_pitch floats per row (as b200pf_f32_linear_t writes them); g may be NULL.
- * With kt, vt and bias 16-byte aligned and kt_pitch, bias_hs, bias_qs multiples of 4 the keys are staged through
- * shared memory in tiles of 128; otherwise they are loaded directly (slower, bit-identical result). */
+ * With kt, vt and bias 16-byte aligned and kt_pitch, bias_hs, bias_qs multiples of 4 the tensor-core kernel runs
+ * (3xTF32 products, key tiles of 64 staged through shared memory, one-pass softmax); otherwise a SIMT kernel that
+ * loads its operands directly (slower; the two agree to fp32 rounding). */
 int b200pf_f32_sattention(const float* q, long long q_pitch, const float* g, long long g_pitch,
                           const float* kt, const float* vt, long long kt_pitch, float* o, long long o_pitch,
                           const float* bias, long long bias_hs, long long bias_qs, const uint8_t* mask,

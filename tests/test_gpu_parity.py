@@ -415,9 +415,10 @@ def test_layer_forward_signature(dev):
 
 
 @pytest.mark.parametrize("nq,nk", [(1024, 1024), (128, 1024), (37, 300), (5, 132)])
-def test_staged_single_track_attention_equals_direct_kernel(dev, nq, nk):
-    """b200pf_f32_sattention picks a shared-memory staged kernel when its operands are 16-byte aligned and the
-    direct-load kernel otherwise; both use the same work split and arithmetic, so they must agree bit for bit."""
+def test_tensor_core_single_track_attention_agrees_with_direct_kernel(dev, nq, nk):
+    """b200pf_f32_sattention picks the tensor-core kernel (3xTF32 products, one-pass softmax over staged key tiles)
+    when its operands are 16-byte aligned and the direct-load SIMT kernel (two passes, fp32 FMAs) otherwise; both
+    compute the same fp32 attention, so they agree to fp32 rounding: 2e-5 absolute on outputs of order 1."""
     import math
     from tt_boltz_b200._lib import call, ptr, stream
     heads, hd = 16, 24
@@ -440,7 +441,7 @@ def test_staged_single_track_attention_equals_direct_kernel(dev, nq, nk):
     torch.cuda.synchronize()
     assert bias_al.data_ptr() % 16 == 0 and bias_un[1:].data_ptr() % 16 == 4
     assert torch.isfinite(outs[0]).all()
-    assert torch.equal(outs[0], outs[1])
+    assert (outs[0] - outs[1]).abs().max().item() < 2e-5
 
 
 @pytest.mark.parametrize("n, amp", [(200, 40.0), (320, 30.0)])

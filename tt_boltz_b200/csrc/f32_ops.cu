@@ -307,144 +307,6 @@ __global__ void __launch_bounds__(256) f32_sattention_kernel(SAttnArgs p) {
 }
 
 // ------------------------------------------------------------------------------------------
-// The same attention with K^T, V^T and the bias rows staged through shared memory in tiles of 128 keys
-// (cp.async, two stages): the direct kernel above is bound by the latency of its global loads (one
-// dependent L2 round trip per key step), here the inner loop only reads shared memory.  Work split, key
-// order and arithmetic per (query, lane) are those of the direct kernel, so the results are bit-identical.
-// Needs 16-byte aligned kt / vt / bias and pitches that are multiples of 4 floats.
-// ------------------------------------------------------------------------------------------
-namespace sat {
-constexpr int KT = 128, QB = 4, QBLK = 32, STAGES = 2;
-template <int HD> __host__ __device__ constexpr int stage_floats() { return (2 * HD + QBLK) * KT; }
-template <int HD> __host__ __device__ constexpr int smem_bytes() { return (STAGES * stage_floats<HD>() + 8 * HD * QB) * 4; }
-
-__device__ __forceinline__ void cp_async16(float* dst, const float* src, int src_bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(src_bytes)
-                 : "memory");
-}
-}  // namespace sat
-
-template <int HD>
-__global__ void __launch_bounds__(256) f32_sattention_staged_kernel(SAttnArgs p) {
-    using namespace sat;
-    extern __shared__ __align__(16) float sat_smem[];
-    float* qs = sat_smem + STAGES * stage_floats<HD>();                 // [8 warps][HD][QB]
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
-    const int qblocks = (p.n_q + QBLK - 1) / QBLK;
-    const int h = blockIdx.x / qblocks, qblk0 = (blockIdx.x % qblocks) * QBLK, q0 = qblk0 + warp * QB;
-    const bool active = q0 < p.n_q;                                     // idle warps still help to load
-    for (int i = lane; i < HD * QB; i += 32) {
-        int e = i / QB, qb = i % QB;
-        int qi = min(q0 + qb, p.n_q - 1);
-        qs[(warp * HD + e) * QB + qb] = p.q[(long long)qi * p.q_pitch + h * HD + e] * p.scale;
-    }
-    __syncwarp();
-    const float* kt = p.kt + (long long)h * HD * p.kt_pitch;
-    const float* vt = p.vt + (long long)h * HD * p.kt_pitch;
-    const int ntiles = (p.n_k + KT - 1) / KT;
-
-    auto load_tile = [&](int t, bool with_v) {
-        float* st = sat_smem + (t & 1) * stage_floats<HD>();
-        const int k0 = t * KT;
-        constexpr int CH = KT / 4;                                      // 16-byte chunks per row
-        for (int i = tid; i < HD * CH; i += 256) {
-            const int e = i / CH, kk = k0 + (i % CH) * 4;
-            const int bytes = max(0, min(16, (p.n_k - kk) * 4));
-            const long long off = (long long)e * p.kt_pitch + (bytes ? kk : 0);
-            cp_async16(st + e * KT + (i % CH) * 4, kt + off, bytes);
-            if (with_v) cp_async16(st + (HD + e) * KT + (i % CH) * 4, vt + off, bytes);
-        }
-        for (int i = tid; i < QBLK * CH; i += 256) {
-            const int r = i / CH, kk = k0 + (i % CH) * 4;
-            const int qi = min(qblk0 + r, p.n_q - 1);
-            const int bytes = max(0, min(16, (p.n_k - kk) * 4));
-            cp_async16(st + (2 * HD + r) * KT + (i % CH) * 4, p.bias + h * p.bias_hs + qi * p.bias_qs + (bytes ? kk : 0), bytes);
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    };
-    auto logits = [&](const float* st, int kl, int kk, float (&l)[QB]) {
-#pragma unroll
-        for (int qb = 0; qb < QB; ++qb) l[qb] = 0.f;
-#pragma unroll
-        for (int e = 0; e < HD; ++e) {
-            const float kv = st[e * KT + kl];
-            const float4 qv = *reinterpret_cast<const float4*>(&qs[(warp * HD + e) * QB]);
-            l[0] = fmaf(qv.x, kv, l[0]); l[1] = fmaf(qv.y, kv, l[1]); l[2] = fmaf(qv.z, kv, l[2]); l[3] = fmaf(qv.w, kv, l[3]);
-        }
-        const float mterm = p.mask ? -p.inf_value * (1.f - (float)p.mask[kk]) : 0.f;
-#pragma unroll
-        for (int qb = 0; qb < QB; ++qb) l[qb] = (l[qb] + st[(2 * HD + warp * QB + qb) * KT + kl]) + mterm;
-    };
-
-    float mx[QB], sum[QB], acc[QB][HD];
-#pragma unroll
-    for (int qb = 0; qb < QB; ++qb) {
-        mx[qb] = -INFINITY; sum[qb] = 0.f;
-#pragma unroll
-        for (int e = 0; e < HD; ++e) acc[qb][e] = 0.f;
-    }
-#pragma unroll 1
-    for (int pass = 0; pass < 2; ++pass) {
-        load_tile(0, pass == 1);
-#pragma unroll 1
-        for (int t = 0; t < ntiles; ++t) {
-            if (t + 1 < ntiles) {
-                load_tile(t + 1, pass == 1);
-                asm volatile("cp.async.wait_group 1;" ::: "memory");
-            } else {
-                asm volatile("cp.async.wait_group 0;" ::: "memory");
-            }
-            __syncthreads();
-            const float* st = sat_smem + (t & 1) * stage_floats<HD>();
-            if (active) {
-#pragma unroll 1
-                for (int j = 0; j < KT / 32; ++j) {
-                    const int kl = j * 32 + lane, kk = t * KT + kl;
-                    if (kk < p.n_k) {
-                        float l[QB];
-                        logits(st, kl, kk, l);
-                        if (pass == 0) {
-#pragma unroll
-                            for (int qb = 0; qb < QB; ++qb) mx[qb] = fmaxf(mx[qb], l[qb]);
-                        } else {
-#pragma unroll
-                            for (int qb = 0; qb < QB; ++qb) { l[qb] = expf(l[qb] - mx[qb]); sum[qb] += l[qb]; }
-#pragma unroll
-                            for (int e = 0; e < HD; ++e) {
-                                const float vv = st[(HD + e) * KT + kl];
-#pragma unroll
-                                for (int qb = 0; qb < QB; ++qb) acc[qb][e] = fmaf(l[qb], vv, acc[qb][e]);
-                            }
-                        }
-                    }
-                }
-            }
-            __syncthreads();                                            // the stage is refilled two tiles later
-        }
-        if (pass == 0) {
-#pragma unroll
-            for (int qb = 0; qb < QB; ++qb) mx[qb] = warp_max(mx[qb]);
-        }
-    }
-    if (!active) return;
-#pragma unroll
-    for (int qb = 0; qb < QB; ++qb) {
-        const float inv = 1.f / warp_sum(sum[qb]);
-        float mine = 0.f;
-#pragma unroll
-        for (int e = 0; e < HD; ++e) {
-            float tot = warp_sum(acc[qb][e]);
-            if (lane == e) mine = tot;
-        }
-        const int qi = q0 + qb;
-        if (qi < p.n_q && lane < HD) {
-            float gate = p.g ? sigmoid_precise(p.g[(long long)qi * p.g_pitch + h * HD + lane]) : 1.f;
-            p.o[(long long)qi * p.o_pitch + h * HD + lane] = mine * inv * gate;
-        }
-    }
-}
-
-// ------------------------------------------------------------------------------------------
 // dst[j][i][:] (+)= src[i][j][:]
 // ------------------------------------------------------------------------------------------
 __global__ void f32_transpose01_kernel(const float* __restrict__ src, float* __restrict__ dst, int n, int c,
@@ -657,6 +519,178 @@ ln_proj_heads16_mma_kernel(const float* __restrict__ z, const float* __restrict_
                 const int h = nt * 8 + 2 * t + (e & 1);
                 if (row < rows) out[h * out_hs + row] = acc[nt][e] + cs[h];
             }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// The single track's attention on the tensor cores at fp32 accuracy (3xTF32, see above).  One CTA = one head x 64
+// queries, 4 warps of 16 queries; keys walked in tiles of 64 with K^T, V^T, the 64 bias rows and the mask terms of a
+// tile staged in shared memory (cp.async, two stages).  Per tile and warp: S = Q K^T as m16n8k8 products (Q
+// pre-scaled and split once), + bias + mask term in the accumulator layout, one-pass softmax with a running row
+// maximum (rows g and g + 8 of a thread, reduced over the four lanes of a quad), then O += P V with P taken straight
+// from the accumulators: an accumulator holds columns 2t, 2t + 1 of an 8-key block where the A operand wants k slots
+// t, t + 4, so slot t stands for key 2t and slot t + 4 for key 2t + 1, and the V fragment is read in that order (a
+// sum over keys does not care).  Row pitch 72 floats: every fragment read is bank-conflict free.
+// Needs 16-byte aligned kt / vt / bias and pitches that are multiples of 4 floats.
+// ------------------------------------------------------------------------------------------
+namespace satc {
+constexpr int KT = 64, QT = 64, LD = KT + 8, STAGES = 2;
+template <int HD> __host__ __device__ constexpr int stage_floats() { return (2 * HD + QT) * LD + KT; }
+template <int HD> __host__ __device__ constexpr int smem_bytes() { return STAGES * stage_floats<HD>() * 4; }
+
+__device__ __forceinline__ void cp_async16(float* dst, const float* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(src_bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void split_tf32(float v, uint32_t& hi, uint32_t& lo) {
+    hi = to_tf32(v);
+    lo = to_tf32(v - __uint_as_float(hi));
+}
+}  // namespace satc
+
+template <int HD>
+__global__ void __launch_bounds__(128) f32_sattention_mma_kernel(SAttnArgs p) {
+    using namespace satc;
+    static_assert(HD % 8 == 0, "head dim in k steps of 8");
+    constexpr int KS = HD / 8, NB = KT / 8;
+    extern __shared__ __align__(16) float satc_smem[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int qblocks = (p.n_q + QT - 1) / QT;
+    const int h = blockIdx.x / qblocks, q0 = (blockIdx.x % qblocks) * QT, qw = q0 + warp * 16;
+    const bool active = qw < p.n_q;                                     // idle warps still help to load
+    const float* kt = p.kt + (long long)h * HD * p.kt_pitch;
+    const float* vt = p.vt + (long long)h * HD * p.kt_pitch;
+    const int ntiles = (p.n_k + KT - 1) / KT;
+    const int qr0 = min(qw + g, p.n_q - 1), qr1 = min(qw + g + 8, p.n_q - 1);
+
+    auto load_tile = [&](int tile) {
+        float* st = satc_smem + (tile & 1) * stage_floats<HD>();
+        const int k0 = tile * KT;
+        constexpr int CH = KT / 4;                                      // 16-byte chunks per row
+        for (int i = tid; i < HD * CH; i += 128) {
+            const int e = i / CH, c4 = (i % CH) * 4, kk = k0 + c4;
+            const int bytes = max(0, min(16, (p.n_k - kk) * 4));
+            const long long off = (long long)e * p.kt_pitch + (bytes ? kk : 0);
+            cp_async16(st + e * LD + c4, kt + off, bytes);
+            cp_async16(st + (HD + e) * LD + c4, vt + off, bytes);
+        }
+        for (int i = tid; i < QT * CH; i += 128) {
+            const int r = i / CH, c4 = (i % CH) * 4, kk = k0 + c4;
+            const int qi = min(q0 + r, p.n_q - 1);
+            const int bytes = max(0, min(16, (p.n_k - kk) * 4));
+            cp_async16(st + (2 * HD + r) * LD + c4, p.bias + h * p.bias_hs + qi * p.bias_qs + (bytes ? kk : 0), bytes);
+        }
+        if (tid < KT) {                                                 // keys past the end never count
+            const int kk = k0 + tid;
+            st[(2 * HD + QT) * LD + tid] = kk < p.n_k ? (p.mask ? -p.inf_value * (1.f - (float)p.mask[kk]) : 0.f) : -INFINITY;
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    // this warp's queries as A fragments, scaled, split once
+    uint32_t qh[KS][4], ql[KS][4];
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+        const float* r0 = p.q + (long long)qr0 * p.q_pitch + h * HD + 8 * ks;
+        const float* r1 = p.q + (long long)qr1 * p.q_pitch + h * HD + 8 * ks;
+        split_tf32(r0[t] * p.scale, qh[ks][0], ql[ks][0]);
+        split_tf32(r1[t] * p.scale, qh[ks][1], ql[ks][1]);
+        split_tf32(r0[t + 4] * p.scale, qh[ks][2], ql[ks][2]);
+        split_tf32(r1[t + 4] * p.scale, qh[ks][3], ql[ks][3]);
+    }
+    float o[KS][4];
+#pragma unroll
+    for (int ei = 0; ei < KS; ++ei) { o[ei][0] = o[ei][1] = o[ei][2] = o[ei][3] = 0.f; }
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+    load_tile(0);
+#pragma unroll 1
+    for (int tile = 0; tile < ntiles; ++tile) {
+        if (tile + 1 < ntiles) {
+            load_tile(tile + 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const float* st = satc_smem + (tile & 1) * stage_floats<HD>();
+        if (active) {
+            float s[NB][4];
+#pragma unroll
+            for (int ni = 0; ni < NB; ++ni) { s[ni][0] = s[ni][1] = s[ni][2] = s[ni][3] = 0.f; }
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+                for (int ni = 0; ni < NB; ++ni) {
+                    uint32_t bh0, bl0, bh1, bl1;                        // B[k = e][n = key]: K^T[e][key]
+                    split_tf32(st[(8 * ks + t) * LD + 8 * ni + g], bh0, bl0);
+                    split_tf32(st[(8 * ks + t + 4) * LD + 8 * ni + g], bh1, bl1);
+                    mma_tf32(s[ni], ql[ks][0], ql[ks][1], ql[ks][2], ql[ks][3], bh0, bh1);
+                    mma_tf32(s[ni], qh[ks][0], qh[ks][1], qh[ks][2], qh[ks][3], bl0, bl1);
+                    mma_tf32(s[ni], qh[ks][0], qh[ks][1], qh[ks][2], qh[ks][3], bh0, bh1);
+                }
+            }
+            // + bias + mask term (in that order), row maxima
+            const float* brow0 = st + (2 * HD + warp * 16 + g) * LD + 2 * t;
+            const float* brow1 = brow0 + 8 * LD;
+            const float* mrow = st + (2 * HD + QT) * LD + 2 * t;
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+            for (int ni = 0; ni < NB; ++ni) {
+                const float2 b0 = *reinterpret_cast<const float2*>(brow0 + 8 * ni);
+                const float2 b1 = *reinterpret_cast<const float2*>(brow1 + 8 * ni);
+                const float2 mt = *reinterpret_cast<const float2*>(mrow + 8 * ni);
+                s[ni][0] = (s[ni][0] + b0.x) + mt.x; s[ni][1] = (s[ni][1] + b0.y) + mt.y;
+                s[ni][2] = (s[ni][2] + b1.x) + mt.x; s[ni][3] = (s[ni][3] + b1.y) + mt.y;
+                mx0 = fmaxf(mx0, fmaxf(s[ni][0], s[ni][1]));
+                mx1 = fmaxf(mx1, fmaxf(s[ni][2], s[ni][3]));
+            }
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            // every tile holds at least one key inside n_k, whose logit is finite: the new maxima are finite
+            const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+            const float a0 = expf(m0 - n0), a1 = expf(m1 - n1);        // 0 on the first tile
+            m0 = n0; m1 = n1;
+            l0 *= a0; l1 *= a1;
+#pragma unroll
+            for (int ei = 0; ei < KS; ++ei) { o[ei][0] *= a0; o[ei][1] *= a0; o[ei][2] *= a1; o[ei][3] *= a1; }
+#pragma unroll
+            for (int ni = 0; ni < NB; ++ni) {
+                // ex2.approx of the scaled difference: relative error ~1e-6 for the differences that still count
+                const float p0 = __expf(s[ni][0] - n0), p1 = __expf(s[ni][1] - n0);
+                const float p2 = __expf(s[ni][2] - n1), p3 = __expf(s[ni][3] - n1);
+                l0 += p0 + p1; l1 += p2 + p3;
+                // A fragment of P: a0 (row g, slot t) = key 2t, a1 (row g + 8, slot t), a2 / a3 (slot t + 4) = key 2t + 1
+                uint32_t ph[4], pl[4];
+                split_tf32(p0, ph[0], pl[0]); split_tf32(p2, ph[1], pl[1]);
+                split_tf32(p1, ph[2], pl[2]); split_tf32(p3, ph[3], pl[3]);
+#pragma unroll
+                for (int ei = 0; ei < KS; ++ei) {
+                    // B[k slot][n = e]: V^T[e = 8 ei + g][keys 8 ni + 2t, 8 ni + 2t + 1]
+                    const float2 v = *reinterpret_cast<const float2*>(st + (HD + 8 * ei + g) * LD + 8 * ni + 2 * t);
+                    uint32_t vh0, vl0, vh1, vl1;
+                    split_tf32(v.x, vh0, vl0); split_tf32(v.y, vh1, vl1);
+                    mma_tf32(o[ei], pl[0], pl[1], pl[2], pl[3], vh0, vh1);
+                    mma_tf32(o[ei], ph[0], ph[1], ph[2], ph[3], vl0, vl1);
+                    mma_tf32(o[ei], ph[0], ph[1], ph[2], ph[3], vh0, vh1);
+                }
+            }
+        }
+        __syncthreads();                                                // the stage is refilled two tiles later
+    }
+    if (!active) return;
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float inv0 = 1.f / l0, inv1 = 1.f / l1;
+#pragma unroll
+    for (int ei = 0; ei < KS; ++ei) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int qi = qw + g + 8 * (c >> 1), e = 8 * ei + 2 * t + (c & 1);
+            if (qi >= p.n_q) continue;
+            const float gate = p.g ? sigmoid_precise(p.g[(long long)qi * p.g_pitch + h * HD + e]) : 1.f;
+            p.o[(long long)qi * p.o_pitch + h * HD + e] = o[ei][c] * ((c >> 1) ? inv1 : inv0) * gate;
+        }
     }
 }
 
@@ -874,13 +908,12 @@ int b200pf_f32_sattention(const float* q, long long q_pitch, const float* g, lon
     B200PF_REQUIRE(hd == 24, B200PF_ERR_UNSUPPORTED, "f32_sattention: built for head dim 24 (got %d)", hd);
     B200PF_REQUIRE(kt_pitch >= n_k, B200PF_ERR_INVALID, "f32_sattention: kt_pitch must cover the keys");
     SAttnArgs p{q, g, kt, vt, bias, o, mask, q_pitch, g_pitch, o_pitch, kt_pitch, bias_hs, bias_qs, n_q, n_k, heads, scale, inf_value};
-    unsigned blocks = (unsigned)(heads * ((n_q + 31) / 32));
     const bool staged = aligned16(kt) && aligned16(vt) && aligned16(bias) && kt_pitch % 4 == 0 && bias_hs % 4 == 0 && bias_qs % 4 == 0;
     if (staged) {
-        B200PF_SMEM_ATTR_ONCE(f32_sattention_staged_kernel<24>, sat::smem_bytes<24>());
-        f32_sattention_staged_kernel<24><<<blocks, 256, sat::smem_bytes<24>(), (cudaStream_t)stream>>>(p);
+        B200PF_SMEM_ATTR_ONCE(f32_sattention_mma_kernel<24>, satc::smem_bytes<24>());
+        f32_sattention_mma_kernel<24><<<(unsigned)(heads * ((n_q + satc::QT - 1) / satc::QT)), 128, satc::smem_bytes<24>(), (cudaStream_t)stream>>>(p);
     } else {
-        f32_sattention_kernel<24><<<blocks, 256, 0, (cudaStream_t)stream>>>(p);
+        f32_sattention_kernel<24><<<(unsigned)(heads * ((n_q + 31) / 32)), 256, 0, (cudaStream_t)stream>>>(p);
     }
     B200PF_LAUNCH_CHECK();
     return B200PF_OK;
