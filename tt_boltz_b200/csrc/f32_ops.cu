@@ -420,11 +420,11 @@ ln_proj_heads_kernel(const float* __restrict__ z, const float* __restrict__ gamm
 // 16 j + 4 t .. + 3 (j = 0 .. 7) of rows g and g + 8, so the four lanes of a row read 64 contiguous bytes
 // per load instruction.  K step ks uses the lane's values 2 ks and 2 ks + 1, i.e. channels
 // 16 (ks / 2) + 4 t + 2 (ks % 2) (+1): the k <-> channel map the weights are laid out with in shared memory.
-__device__ __forceinline__ uint32_t to_tf32(float x) {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-    return r;
-}
+// Round to tf32 (nearest, ties away from zero: what cvt.rna.tf32.f32 returns for every finite value that does not
+// overflow) with two integer instructions on the bit pattern.  The cvt instruction itself runs at a few lanes per
+// clock: with two of them per operand element the 3xTF32 kernels below were bound by the conversions, at a
+// quarter of the rate of the MMAs they feed.
+__device__ __forceinline__ uint32_t to_tf32(float x) { return (__float_as_uint(x) + 0x1000u) & 0xffffe000u; }
 __device__ __forceinline__ void mma_tf32(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -695,24 +695,34 @@ __global__ void __launch_bounds__(128) f32_sattention_mma_kernel(SAttnArgs p) {
 }
 
 // Linear on the tensor cores at fp32 accuracy (3xTF32, see above): y[M][N] (+)= x[M][K] w[N][K]^T (+ bias), or the
-// transposed result y^T[N][yt_pitch].  64 x 64 tile per CTA of 4 warps (each 32 x 32), K walked in steps of 32 with
-// the next step's global loads in flight while the current one is multiplied.  Needs K % 4 == 0 and 16-byte rows.
-__global__ void __launch_bounds__(128)
+// transposed result y^T[N][yt_pitch].  64 x 64 tile per CTA of KQ warp quartets: four warps cover the tile (32 x 32
+// each) and the quartets split every 64-wide K step between them (8 / KQ k steps of 8 each), so that an SM holds 16
+// warps whatever the launch: four quartets (one CTA per SM) when the launch has no more CTAs than SMs, two (two CTAs
+// per SM) otherwise.  With one quartet per CTA the single track's launches ran about one warp per scheduler and were
+// bound by instruction latency.  The quartets' partial sums meet in shared memory at the end, in a fixed order.  The
+// next K step's global loads are in flight while the current one is multiplied.  Needs K % 4 == 0 and 16-byte rows.
+template <int KQ>
+__global__ void __launch_bounds__(128 * KQ, KQ == 4 ? 1 : 2)
 f32_linear_mma_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
                       float* __restrict__ y, long long m, int k, int n, int accumulate, long long yt_pitch) {
-    constexpr int BM = 64, BN = 64, BK = 32, LD = BK + 4;
-    __shared__ float xs[BM][LD], ws[BN][LD];
+    static_assert(KQ == 2 || KQ == 4, "two or four warp quartets");
+    constexpr int BM = 64, BN = 64, BK = 64, LD = BK + 4, RL = 8 * KQ, LE = 64 / RL, KS = 8 / KQ;
+    __shared__ __align__(16) float lin_smem[(BM + BN) * LD];            // x tile | w tile; the partial sums afterwards
+    static_assert((BM + BN) * LD >= 8 * 32 * 32, "the tile buffer also holds eight warps' partial sums");
+    float (*xs)[LD] = reinterpret_cast<float (*)[LD]>(lin_smem);
+    float (*ws)[LD] = reinterpret_cast<float (*)[LD]>(lin_smem + BM * LD);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
-    const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+    const int kq = warp >> 2, wq = warp & 3;                    // K quarter of every step; position in the tile
+    const int wm = (wq >> 1) * 32, wn = (wq & 1) * 32;
     const long long m0 = (long long)blockIdx.x * BM;
     const int n0 = blockIdx.y * BN;
-    const int lr = tid >> 3, lk = (tid & 7) * 4;              // this thread's load slot: rows lr + 16 e, k offset lk
-    float4 px[4], pw[4];
+    const int lr = tid >> 4, lk = (tid & 15) * 4;               // this thread's load slot: rows lr + RL e, k offset lk
+    float4 px[LE], pw[LE];
     auto fetch = [&](int k0) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const long long r = m0 + lr + 16 * e;
-            const int c = n0 + lr + 16 * e;
+        for (int e = 0; e < LE; ++e) {
+            const long long r = m0 + lr + RL * e;
+            const int c = n0 + lr + RL * e;
             const bool kin = k0 + lk < k;
             px[e] = (r < m && kin) ? __ldg(reinterpret_cast<const float4*>(x + r * k + k0 + lk)) : make_float4(0.f, 0.f, 0.f, 0.f);
             pw[e] = (c < n && kin) ? __ldg(reinterpret_cast<const float4*>(w + (long long)c * k + k0 + lk)) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -722,14 +732,15 @@ f32_linear_mma_kernel(const float* __restrict__ x, const float* __restrict__ w, 
     fetch(0);
     for (int k0 = 0; k0 < k; k0 += BK) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            *reinterpret_cast<float4*>(&xs[lr + 16 * e][lk]) = px[e];
-            *reinterpret_cast<float4*>(&ws[lr + 16 * e][lk]) = pw[e];
+        for (int e = 0; e < LE; ++e) {
+            *reinterpret_cast<float4*>(&xs[lr + RL * e][lk]) = px[e];
+            *reinterpret_cast<float4*>(&ws[lr + RL * e][lk]) = pw[e];
         }
         __syncthreads();
         if (k0 + BK < k) fetch(k0 + BK);
 #pragma unroll
-        for (int k8 = 0; k8 < BK; k8 += 8) {
+        for (int kk = 0; kk < KS; ++kk) {
+            const int k8 = (kq * KS + kk) * 8;
             uint32_t ah[2][4], al[2][4], bh[4][2], bl[4][2];
 #pragma unroll
             for (int mi = 0; mi < 2; ++mi) {
@@ -755,6 +766,26 @@ f32_linear_mma_kernel(const float* __restrict__ x, const float* __restrict__ w, 
         }
         __syncthreads();
     }
+    // (quartet 0 + quartet 2) + (quartet 1 + quartet 3): partial sums laid out [warp slot][value][lane]
+    float* red = lin_smem;
+    auto put = [&](int slot) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) red[(slot * 32 + i) * 32 + lane] = acc[i >> 4][(i >> 2) & 3][i & 3];
+    };
+    auto add = [&](int slot) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[i >> 4][(i >> 2) & 3][i & 3] += red[(slot * 32 + i) * 32 + lane];
+    };
+    if (KQ == 4) {
+        if (kq >= 2) put(warp - 8);
+        __syncthreads();
+        if (kq < 2) add(warp);
+        __syncthreads();
+    }
+    if (kq == 1) put(warp - 4);
+    __syncthreads();
+    if (kq != 0) return;
+    add(warp);
 #pragma unroll
     for (int mi = 0; mi < 2; ++mi)
 #pragma unroll
@@ -791,9 +822,10 @@ int b200pf_f32_linear(const float* x, const float* w, const float* bias, float* 
     B200PF_REQUIRE(x && w && y && rows >= 0 && k > 0 && n_out > 0, B200PF_ERR_INVALID, "f32_linear: bad argument");
     if (rows == 0) return B200PF_OK;
     dim3 grid((unsigned)((rows + 63) / 64), (unsigned)((n_out + 63) / 64));
-    if (k % 4 == 0 && aligned16(x) && aligned16(w))
-        f32_linear_mma_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(x, w, bias, y, rows, k, n_out, accumulate, 0);
-    else
+    if (k % 4 == 0 && aligned16(x) && aligned16(w)) {
+        if ((long long)grid.x * grid.y <= 148) f32_linear_mma_kernel<4><<<grid, 512, 0, (cudaStream_t)stream>>>(x, w, bias, y, rows, k, n_out, accumulate, 0);
+        else f32_linear_mma_kernel<2><<<grid, 256, 0, (cudaStream_t)stream>>>(x, w, bias, y, rows, k, n_out, accumulate, 0);
+    } else
         f32_linear_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(x, w, bias, y, rows, k, n_out, accumulate, 0);
     B200PF_LAUNCH_CHECK();
     return B200PF_OK;
@@ -805,9 +837,10 @@ int b200pf_f32_linear_t(const float* x, const float* w, const float* bias, float
                    "f32_linear_t: bad argument");
     if (rows == 0) return B200PF_OK;
     dim3 grid((unsigned)((rows + 63) / 64), (unsigned)((n_out + 63) / 64));
-    if (k % 4 == 0 && aligned16(x) && aligned16(w))
-        f32_linear_mma_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(x, w, bias, yt, rows, k, n_out, 0, yt_pitch);
-    else
+    if (k % 4 == 0 && aligned16(x) && aligned16(w)) {
+        if ((long long)grid.x * grid.y <= 148) f32_linear_mma_kernel<4><<<grid, 512, 0, (cudaStream_t)stream>>>(x, w, bias, yt, rows, k, n_out, 0, yt_pitch);
+        else f32_linear_mma_kernel<2><<<grid, 256, 0, (cudaStream_t)stream>>>(x, w, bias, yt, rows, k, n_out, 0, yt_pitch);
+    } else
         f32_linear_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(x, w, bias, yt, rows, k, n_out, 0, yt_pitch);
     B200PF_LAUNCH_CHECK();
     return B200PF_OK;
