@@ -69,3 +69,19 @@ def test_pair_update_block_width_256():
         zz = zz + orc.transition(zz, sd, "transition_z")
     assert _lib.device_status() == 0
     assert rel_l2(got[0].cpu(), zz) < TOL
+
+
+def test_esmfold2_block_from_the_reference_model_through_the_remap():
+    """tests/golden/remaps/esmfold2_block_c64_n14.npz holds what the reference's vendored PyTorch ESMFold2
+    PairUpdateBlock (tt_bio/_vendor/esmfold2_hf/modeling_esmfold2_common.py) returns for weights under ITS key names;
+    the same checkpoint through remaps.esmfold2_pair_update_block and the GPU block must reproduce it."""
+    from tests.test_remaps import load_esmfold2_case
+    from tt_boltz_b200 import remaps
+    theirs, z, mask, want = load_esmfold2_case("esmfold2_block_c64_n14")
+    ours = remaps.esmfold2_pair_update_block(theirs)
+    blk = B200PairUpdateBlock(z.shape[-1], ours["transition_z.fc1.weight"].shape[0])
+    blk.load_state_dict(ours, strict=True)
+    got = blk.cuda()(z.cuda(), mask.cuda())
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    assert rel_l2(got[0].cpu(), want[0]) < TOL

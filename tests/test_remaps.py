@@ -80,3 +80,68 @@ def test_esmfold2_pair_update_block():
     blk.load_state_dict(back, strict=True)
     for k in ours:
         assert torch.equal(back[k], ours[k]), k
+
+
+# ---- pinned against the reference's own code (fixtures written by tests/golden/remaps/make_remap_vectors.py) ----
+
+import glob
+import os
+
+import numpy as np
+import pytest
+
+REMAP_DIR = os.path.join(os.path.dirname(__file__), "golden", "remaps")
+ESMFOLD2_CASES = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(REMAP_DIR, "esmfold2_block_*.npz")))
+
+
+def _tagged(g, tag, side):
+    pre = f"{tag}::{side}::"
+    return {k[len(pre):]: torch.from_numpy(g[k]) for k in g.files if k.startswith(pre)}
+
+
+@pytest.mark.parametrize("tag, fn", [("block", remaps.protenix_pairformer_block), ("pair_stack", remaps.protenix_pair_stack),
+                                     ("opm", remaps.protenix_outer_product_mean), ("pwa", remaps.protenix_pair_weighted_averaging)])
+def test_protenix_remaps_reproduce_the_reference_functions(tag, fn):
+    """tt_bio/protenix_weights.py remap_pairformer_block / remap_msa_pair_stack / remap_outer_product_mean /
+    remap_pair_weighted_averaging were run on state dicts whose every element is distinct; ours must return the same
+    keys with the same tensors (source key, concatenation order and row order all show in the values)."""
+    g = np.load(os.path.join(REMAP_DIR, "protenix_remaps.npz"))
+    theirs, want = _tagged(g, tag, "in"), _tagged(g, tag, "out")
+    assert len(theirs) > 0 and len(want) > 0
+    got = fn(theirs)
+    assert set(got) == set(want)
+    for k in want:
+        assert got[k].shape == want[k].shape and torch.equal(got[k], want[k]), k
+
+
+def test_protenix_pair_bias_norm_without_offset_matches_the_reference():
+    g = np.load(os.path.join(REMAP_DIR, "protenix_remaps.npz"))
+    theirs = _tagged(g, "block", "in")
+    del theirs["attention_pair_bias.layernorm_z.bias"]
+    want = torch.from_numpy(g["block_no_z_bias::out::attention.proj_z.0.bias"])
+    assert torch.equal(remaps.protenix_pairformer_block(theirs)["attention.proj_z.0.bias"], want)
+
+
+def load_esmfold2_case(name):
+    g = np.load(os.path.join(REMAP_DIR, name + ".npz"))
+    theirs = {k[3:]: torch.from_numpy(g[k]) for k in g.files if k.startswith("w::")}
+    return theirs, torch.from_numpy(g["z"]), torch.from_numpy(g["mask"]), torch.from_numpy(g["out"])
+
+
+@pytest.mark.parametrize("name", ESMFOLD2_CASES)
+def test_esmfold2_block_through_our_remap_and_oracle_matches_the_reference_model(name):
+    """The reference's vendored PyTorch ESMFold2 PairUpdateBlock (tt_bio/_vendor/esmfold2_hf/
+    modeling_esmfold2_common.py) computed the stored output from weights under ITS names; the same weights through our
+    remap and the CPU oracle's triangle multiplication and transition must give it back (fp32: 1e-5)."""
+    from oracle import pairformer_oracle as orc
+    theirs, z, mask, want = load_esmfold2_case(name)
+    ours = remaps.esmfold2_pair_update_block(theirs)
+    c = z.shape[-1]
+    B200PairUpdateBlock(c, ours["transition_z.fc1.weight"].shape[0]).load_state_dict(ours, strict=True)
+    with torch.no_grad():
+        zz = z[0]
+        zz = zz + orc.tri_mul(zz, ours, "tri_mul_out", mask[0], False)
+        zz = zz + orc.tri_mul(zz, ours, "tri_mul_in", mask[0], True)
+        zz = zz + orc.transition(zz, ours, "transition_z")
+    err = ((zz - want[0]).norm() / want[0].norm()).item()
+    assert err < 1e-5, err
