@@ -85,3 +85,25 @@ def test_esmfold2_block_from_the_reference_model_through_the_remap():
     torch.cuda.synchronize()
     assert _lib.device_status() == 0
     assert rel_l2(got[0].cpu(), want[0]) < TOL
+
+
+@pytest.mark.parametrize("name", ["template_noseq2_c64_n20_chain", "layer_c256_h8_n12_general"])
+def test_other_widths_against_the_reference_modules(golden_dir, name):
+    """tests/golden/widths/*.npz: what the reference's own PairformerNoSeqModule(64, 2) (the template stack) and
+    PairformerModule(384, 256, 1, pairwise_num_heads=8) return in fp32; the GPU modules must reproduce them."""
+    from tests.test_oracle_golden import load_width_case
+    g, sd, s, z, m, pm = load_width_case(golden_dir, name)
+    c_z, heads, blocks = int(g["c_z"]), int(g["tri_heads"]), int(g["blocks"])
+    if s is None:
+        mod = B200PairformerNoSeqModule(c_z, blocks, pairwise_num_heads=heads, precision="auto")
+        mod.load_state_dict(sd, strict=True)
+        z_o = mod.cuda()(z.cuda(), pm.cuda())
+    else:
+        mod = B200PairformerModule(384, c_z, blocks, pairwise_num_heads=heads, precision="auto")
+        mod.load_state_dict(sd, strict=True)
+        s_o, z_o = mod.cuda()(s.cuda(), z.cuda(), m.cuda(), pm.cuda())
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    assert rel_l2(z_o[0].cpu(), torch.from_numpy(g["z_out"])[0]) < TOL
+    if s is not None:
+        assert rel_l2(s_o[0].cpu(), torch.from_numpy(g["s_out"])[0]) < TOL

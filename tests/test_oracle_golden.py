@@ -123,3 +123,30 @@ def test_msa_module_oracle_matches_reference_output(golden_dir):
     with torch.no_grad():
         out = msa_oracle.msa_module(z[0], emb[0], feats, synthetic.make_msa_module_weights(c["blocks"]), c["blocks"])
     assert rel_l2(out, torch.from_numpy(g["z_out"])) < 2e-6
+
+
+WIDTH_CASES = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(os.path.dirname(__file__), "golden", "widths", "*.npz")))
+
+
+def load_width_case(golden_dir, name):
+    """Fixtures of tests/golden/widths/make_widths.py: the reference's modules at pair widths 64 and 256."""
+    g = np.load(os.path.join(golden_dir, "widths", name + ".npz"))
+    n, nb, with_s, c_z, heads = int(g["n"]), int(g["blocks"]), bool(g["with_s"]), int(g["c_z"]), int(g["tri_heads"])
+    sd = synthetic.make_weights(nb, seed=1, std=float(g["std"]), affine_jitter=float(g["jitter"]), with_s=with_s, c_z=c_z, tri_heads=heads)
+    assert abs(weight_checksum(sd) - float(g["weight_checksum"])) <= 1e-6 * float(g["weight_checksum"]), \
+        "regenerated weights differ from the ones the fixture was made with"
+    s, z = synthetic.make_inputs(n, c_z=c_z, seed=0, with_s=with_s)
+    return g, sd, s, z, torch.from_numpy(g["mask"]), torch.from_numpy(g["pair_mask"])
+
+
+@pytest.mark.parametrize("name", WIDTH_CASES)
+def test_oracle_matches_reference_outputs_at_other_widths(golden_dir, name):
+    """The template stack (c_z = 64) and a c_z = 256 / eight-head block: the oracle is generic in the widths and is
+    pinned to the reference's own modules there too."""
+    g, sd, s, z, m, pm = load_width_case(golden_dir, name)
+    assert len(WIDTH_CASES) >= 2
+    with torch.no_grad():
+        s_o, z_o = orc.pairformer_stack(None if s is None else s[0], z[0], m[0], pm[0], sd, int(g["blocks"]))
+    assert rel_l2(z_o, torch.from_numpy(g["z_out"])[0]) < 2e-6
+    if s is not None:
+        assert rel_l2(s_o, torch.from_numpy(g["s_out"])[0]) < 2e-6
