@@ -696,11 +696,12 @@ __global__ void __launch_bounds__(128) f32_sattention_mma_kernel(SAttnArgs p) {
 
 // Linear on the tensor cores at fp32 accuracy (3xTF32, see above): y[M][N] (+)= x[M][K] w[N][K]^T (+ bias), or the
 // transposed result y^T[N][yt_pitch].  64 x 64 tile per CTA of KQ warp quartets: four warps cover the tile (32 x 32
-// each) and the quartets split every 64-wide K step between them (8 / KQ k steps of 8 each), so that an SM holds 16
-// warps whatever the launch: four quartets (one CTA per SM) when the launch has no more CTAs than SMs, two (two CTAs
-// per SM) otherwise.  With one quartet per CTA the single track's launches ran about one warp per scheduler and were
-// bound by instruction latency.  The quartets' partial sums meet in shared memory at the end, in a fixed order.  The
-// next K step's global loads are in flight while the current one is multiplied.  Needs K % 4 == 0 and 16-byte rows.
+// each) and the quartets split every 64-wide K step between them (8 / KQ k steps of 8 each); their partial sums meet in
+// shared memory at the end, in a fixed order.  With one quartet per CTA the single track's launches (72 to 192 CTAs)
+// ran about one warp per scheduler and were bound by instruction latency.  The launches use KQ = 2 (256 threads, two
+// CTAs per SM): a CTA of four quartets holds an SM's whole register file, which on a side stream leaves it waiting
+// for an empty SM.  The next K step's global loads are in flight while the current one is multiplied.
+// Needs K % 4 == 0 and 16-byte rows.
 template <int KQ>
 __global__ void __launch_bounds__(128 * KQ, KQ == 4 ? 1 : 2)
 f32_linear_mma_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
@@ -823,8 +824,7 @@ int b200pf_f32_linear(const float* x, const float* w, const float* bias, float* 
     if (rows == 0) return B200PF_OK;
     dim3 grid((unsigned)((rows + 63) / 64), (unsigned)((n_out + 63) / 64));
     if (k % 4 == 0 && aligned16(x) && aligned16(w)) {
-        if ((long long)grid.x * grid.y <= 148) f32_linear_mma_kernel<4><<<grid, 512, 0, (cudaStream_t)stream>>>(x, w, bias, y, rows, k, n_out, accumulate, 0);
-        else f32_linear_mma_kernel<2><<<grid, 256, 0, (cudaStream_t)stream>>>(x, w, bias, y, rows, k, n_out, accumulate, 0);
+        f32_linear_mma_kernel<2><<<grid, 256, 0, (cudaStream_t)stream>>>(x, w, bias, y, rows, k, n_out, accumulate, 0);
     } else
         f32_linear_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(x, w, bias, y, rows, k, n_out, accumulate, 0);
     B200PF_LAUNCH_CHECK();
@@ -838,8 +838,7 @@ int b200pf_f32_linear_t(const float* x, const float* w, const float* bias, float
     if (rows == 0) return B200PF_OK;
     dim3 grid((unsigned)((rows + 63) / 64), (unsigned)((n_out + 63) / 64));
     if (k % 4 == 0 && aligned16(x) && aligned16(w)) {
-        if ((long long)grid.x * grid.y <= 148) f32_linear_mma_kernel<4><<<grid, 512, 0, (cudaStream_t)stream>>>(x, w, bias, yt, rows, k, n_out, 0, yt_pitch);
-        else f32_linear_mma_kernel<2><<<grid, 256, 0, (cudaStream_t)stream>>>(x, w, bias, yt, rows, k, n_out, 0, yt_pitch);
+        f32_linear_mma_kernel<2><<<grid, 256, 0, (cudaStream_t)stream>>>(x, w, bias, yt, rows, k, n_out, 0, yt_pitch);
     } else
         f32_linear_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(x, w, bias, yt, rows, k, n_out, 0, yt_pitch);
     B200PF_LAUNCH_CHECK();
