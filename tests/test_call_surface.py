@@ -12,6 +12,7 @@ import torch
 
 from tt_boltz_b200 import (B200MSALayer, B200MSAModule, B200MSATransition, B200OuterProductMean, B200PairWeightedAveraging, B200PairformerLayer, B200PairformerModule, B200PairformerNoSeqLayer,
                            B200PairformerNoSeqModule, B200RecyclingTrunk, synthetic)
+from tt_boltz_b200 import B200DistogramModule
 
 
 def _params(fn):
@@ -143,3 +144,21 @@ def test_msa_module_surface():
     feats = synthetic.make_msa_features(4, 8)
     with pytest.raises(RuntimeError, match="CUDA"):
         mod(torch.zeros(1, 8, 8, 128), torch.zeros(1, 8, 384), feats)
+
+
+def test_distogram_head_surface_and_fixture():
+    """tests/golden/heads/distogram_n12.npz holds the reference's DistogramModule (tt_bio/boltz2.py:2334-2368): its
+    state dict loads strictly into ours, the stored output is Linear(z + z^T) of the stored input, and there is no CPU
+    path."""
+    import os
+    import numpy as np
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "heads", "distogram_n12.npz"))
+    w = {k[3:]: torch.from_numpy(g[k]) for k in g.files if k.startswith("w::")}
+    head = B200DistogramModule(128, 64)
+    head.load_state_dict(w, strict=True)
+    assert _params(B200DistogramModule.forward) == ["self", "z"]
+    z, out = torch.from_numpy(g["z"]), torch.from_numpy(g["out"])
+    want = (z + z.transpose(1, 2)) @ w["distogram.weight"].T + w["distogram.bias"]
+    assert out.shape == (1, 12, 12, 1, 64) and torch.allclose(out[:, :, :, 0], want, atol=1e-5)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        head(z)

@@ -52,3 +52,19 @@ def test_recycling_loop_matches_cpu_restatement(precision, tol):
     with torch.no_grad():
         sr, zr = _cpu_loop(w, sd, blocks, s_init[0], z_init[0], m[0], pm[0], 0)
     assert rel_l2(zo[0].cpu()[:35, :35], zr[:35, :35]) < tol
+
+
+def test_distogram_head_against_the_reference_module():
+    """tests/golden/heads/distogram_n12.npz: the reference's DistogramModule on a non-symmetric z (fp32 tier: 1e-5)."""
+    import os
+    import numpy as np
+    from tt_boltz_b200 import B200DistogramModule
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "heads", "distogram_n12.npz"))
+    head = B200DistogramModule(128, 64)
+    head.load_state_dict({k[3:]: torch.from_numpy(g[k]) for k in g.files if k.startswith("w::")}, strict=True)
+    z = torch.from_numpy(g["z"])
+    got = head.cuda()(z.cuda())
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    assert got.shape == (1, 12, 12, 1, 64)
+    assert rel_l2(got.cpu(), torch.from_numpy(g["out"])) < 1e-5

@@ -4,6 +4,6 @@ from .pairformer import (B200PairformerLayer, B200PairformerModule, B200Pairform
                          B200PairformerNoSeqModule, B200PairUpdateBlock)
 
 from .msa import B200MSALayer, B200MSAModule, B200MSAStack, B200MSATransition, B200OuterProductMean, B200PairWeightedAveraging
-from .recycling import B200RecyclingTrunk
+from .recycling import B200DistogramModule, B200RecyclingTrunk
 
-__all__ = ["B200MSALayer", "B200MSAModule", "B200MSAStack", "B200MSATransition", "B200OuterProductMean", "B200PairWeightedAveraging", "B200RecyclingTrunk", "B200PairformerLayer", "B200PairformerModule", "B200PairformerNoSeqLayer", "B200PairformerNoSeqModule", "B200PairUpdateBlock"]
+__all__ = ["B200DistogramModule", "B200MSALayer", "B200MSAModule", "B200MSAStack", "B200MSATransition", "B200OuterProductMean", "B200PairWeightedAveraging", "B200RecyclingTrunk", "B200PairformerLayer", "B200PairformerModule", "B200PairformerNoSeqLayer", "B200PairformerNoSeqModule", "B200PairUpdateBlock"]

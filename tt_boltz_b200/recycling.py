@@ -12,6 +12,9 @@ N = 1024) on the device from the first recycle to the last instead of crossing P
 gain the reference takes from its resident-z loop on its own backend (tt_bio/esmfold2_runtime.py:227-289).
 Parameters carry the reference's key names (``s_norm``, ``z_norm``, ``s_recycle``, ``z_recycle``,
 ``pairformer_module``), so the matching slice of a Boltz-2 checkpoint loads unchanged.
+
+After the last recycle the reference reads the distogram off the resident z (tt_bio/boltz2.py:5250,
+``DistogramModule`` :2334-2368): ``B200DistogramModule`` does that on the device too.
 """
 from __future__ import annotations
 
@@ -21,6 +24,7 @@ import torch
 from torch import nn
 
 from . import ops
+from ._lib import call, ptr, stream
 from .pairformer import B200PairformerModule, _mask_u8
 
 
@@ -78,3 +82,30 @@ class B200RecyclingTrunk(nn.Module):
                 else:
                     pf.run_inplace(s, z, mask, pair_mask)
         return s.unsqueeze(0).to(s_init.dtype), z.unsqueeze(0).to(z_init.dtype)
+
+
+class B200DistogramModule(nn.Module):
+    """``forward(z) -> [1, N, N, num_distograms, num_bins]``: ``Linear(z + z^T)`` with the reference's parameter names
+    (``distogram.weight``, ``distogram.bias``; tt_bio/boltz2.py:2334-2368), in fp32 on the library's kernels: the
+    symmetrisation is one transpose-accumulate pass over a copy of z, the projection one 3xTF32 GEMM with its bias."""
+
+    def __init__(self, token_z: int = 128, num_bins: int = 64, num_distograms: int = 1) -> None:
+        super().__init__()
+        self.token_z, self.num_bins, self.num_distograms = token_z, num_bins, num_distograms
+        self.distogram = nn.Linear(token_z, num_distograms * num_bins)
+        for p in self.parameters():
+            p.requires_grad_(False)
+
+    def forward(self, z: torch.Tensor) -> torch.Tensor:
+        if not z.is_cuda:
+            raise RuntimeError("B200DistogramModule: inputs must be CUDA tensors (there is no CPU path)")
+        if z.dim() != 4 or z.shape[0] != 1 or z.shape[1] != z.shape[2] or z.shape[3] != self.token_z:
+            raise ValueError(f"B200DistogramModule: z must be [1, N, N, {self.token_z}], got {tuple(z.shape)}")
+        dev, n = z.device, z.shape[1]
+        with torch.cuda.device(dev), torch.no_grad():
+            f32 = lambda t: t.detach().to(device=dev, dtype=torch.float32).contiguous()
+            z0 = f32(z[0])
+            sym = z0.clone()
+            call("b200pf_f32_transpose01", ptr(z0), ptr(sym), n, self.token_z, 1, stream())      # sym += z^T
+            out = ops.f32_linear(sym, f32(self.distogram.weight), f32(self.distogram.bias))
+        return out.view(1, n, n, self.num_distograms, self.num_bins).to(z.dtype)
